@@ -1,0 +1,72 @@
+import torch
+from hypothesis import given, settings, strategies as st
+
+from zen_repro_b200.sparse import formats, hashing
+from zen_repro_b200.sparse.hashing import BlockPermutation
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(1, 200000), st.integers(1, 8), st.sampled_from([1, 64, 128]))
+def test_block_permutation_is_bijection(n, p, g):
+    perm = BlockPermutation.make(n, p, g)
+    idx = torch.arange(n)
+    owner, slot = perm.owner_slot(idx)
+    assert owner.min() >= 0 and owner.max() < p
+    assert slot.min() >= 0 and slot.max() < perm.slots_per_part
+    flat = owner * perm.slots_per_part + slot
+    assert flat.unique().numel() == n
+    back = torch.empty_like(idx)
+    for o in range(p):
+        m = owner == o
+        back[m] = perm.index_of(o, slot[m])
+    assert torch.equal(back, idx)
+
+
+def _zipf_positions(n, count, s, seed):
+    g = torch.Generator().manual_seed(seed)
+    w = 1.0 / torch.arange(1, n + 1, dtype=torch.float64) ** s
+    return torch.multinomial(w, count, replacement=False, generator=g)
+
+
+def test_partition_balance_on_zipf_positions():
+    n = 1 << 20
+    for p in (2, 4, 8):
+        perm = BlockPermutation.make(n, p, 64)
+        idx = _zipf_positions(n, n // 100, 1.1, seed=p)
+        owner, _ = perm.owner_slot(idx)
+        imb = hashing.partition_imbalance(owner, p)
+        contiguous = hashing.partition_imbalance(idx // (n // p), p)
+        assert imb < 1.10, (p, imb)
+        assert contiguous > 1.5
+
+
+def test_zen_poly3_matches_wrapping_arithmetic():
+    idx = torch.tensor([0, 1, 2, 12345, 2 ** 20 + 7])
+    h = hashing.zen_poly3(idx, 10001861)
+    for i, k in enumerate(idx.tolist()):
+        want = (573729859 * k ** 3 + 0xCC9E2D51 * k ** 2 + 0x1B873593 * k + 10001861) % (1 << 32)
+        assert int(h[i]) == want
+    own = hashing.zen_poly3_owner(torch.arange(100000), 100000 // 8 * 8, 8)
+    assert own.min() >= 0 and own.max() < 8
+    assert hashing.partition_imbalance(own, 8) < 1.1
+
+
+@settings(max_examples=50, deadline=None)
+@given(st.lists(st.booleans(), min_size=1, max_size=300))
+def test_bitmap_roundtrip_lsb_first(bits):
+    m = torch.tensor(bits)
+    packed = formats.pack_bitmap(m)
+    assert packed.numel() == (len(bits) + 7) // 8
+    assert torch.equal(formats.unpack_bitmap(packed, len(bits)), m)
+    if bits[0]:
+        assert int(packed[0]) & 1        # slot 0 is the least significant bit of byte 0
+
+
+def test_coo_and_format_choice():
+    d = torch.tensor([0.0, 1.5, 0.0, -2.0])
+    i, v = formats.coo_encode(d)
+    assert i.tolist() == [1, 3]
+    assert torch.equal(formats.coo_decode(i, v, 4), d)
+    assert formats.choose_index_format(10, 100000) == "coo"
+    assert formats.choose_index_format(5000, 100000) == "bitmap"
+    assert formats.choose_index_format(60000, 100000) == "dense"

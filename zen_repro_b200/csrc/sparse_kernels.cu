@@ -1,0 +1,742 @@
+// Sparse all-reduce kernels (element granule) for sm_100a.
+//
+// Pipeline per bucket, one launch each, all on one stream, no host sync:
+//   zen_partition_push  : scan the flat bucket once, hash 64-element blocks to
+//                         owners, stage (slot, value) records per owner in shared
+//                         memory and push them in large contiguous runs straight
+//                         into the owner's receive region over NVLink (P2P stores).
+//   zen_owner_reduce    : bounded wait on each source's mailbox, red.add the
+//                         records into this owner's fp32 slots, red.or the
+//                         occupancy bitmap.
+//   zen_gather_push     : count / scan the bitmap, compact the touched slots in
+//                         slot order and push bitmap|COO + values to every peer.
+//   zen_densify         : bounded wait on each owner's mailbox, one pass over
+//                         the output that writes zeros and values together.
+//
+// Replaces, in the reference: the three sparse_balance kernels and the
+// boolean-mask compaction after them (functions_cuda_kernel.cu:97-167,
+// tensor_load_balance.py:24-51), both all_to_all calls and the scatter_add /
+// nonzero between them (comm.py:117-127), encode_bitmap / decode_bitmap and the
+// padded all_gathers (comm.py:59-99, 128-145).
+#include "zen_common.cuh"
+
+struct ZenSparseCtx {
+  int32_t rank;
+  int32_t nranks;
+  uint32_t epoch;
+  uint32_t fmt_mode;        // 0 auto, ZEN_FMT_COO, ZEN_FMT_BITMAP
+  uint64_t wait_ns;
+  char* sym[ZEN_MAX_RANKS]; // base of every rank's symmetric region
+  uint64_t off_rec_mail;    // ZenMail[P], indexed by source
+  uint64_t off_g_mail;      // ZenMail[P], indexed by owner
+  uint64_t off_rec;         // uint2[P][cap_rec], indexed by source
+  uint64_t off_g_idx;       // uint32[P][g_idx_words]: bitmap words or COO slots
+  uint64_t off_g_off;       // uint32[P][nchunks + 1]: value offset of every 1024-slot chunk
+  uint64_t off_g_val;       // T[P][cap_g] (stride in bytes: cap_g * 4)
+  uint32_t cap_rec;
+  uint32_t cap_g;
+  uint32_t g_idx_words;
+  uint32_t nchunks;
+  float* acc;               // [S] local
+  uint32_t* bitmap;         // [nwords] local
+  uint32_t* chunk_off;      // [nchunks + 1] local: counts, then exclusive offsets
+  uint32_t* cursors;        // [P] record cursors, [P] = done counter K1, [P+1] = done counter K3
+  uint32_t* status;         // status word
+  uint64_t numel;           // N
+  uint32_t nslots;          // S = sb * G
+  uint32_t nwords;          // ceil(S / 32)
+  ZenPerm perm;
+};
+
+#define K1_THREADS 512
+#define K1_WARPS 16
+#define K1_U 4
+#define K1_QCAP 1024
+#define K1_FLUSH_MIN 256
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* g, uint64_t e0, uint64_t n, bool aligned, float (&v)[8]);
+
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* g, uint64_t e0, uint64_t n, bool aligned,
+                                                     float (&v)[8]) {
+  if (aligned && e0 + 8 <= n) {
+    uint4 r = __ldg(reinterpret_cast<const uint4*>(g + e0));
+    uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (e0 + i < n) ? __bfloat162float(g[e0 + i]) : 0.f;
+  }
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* g, uint64_t e0, uint64_t n, bool aligned, float (&v)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = (e0 + i < n) ? __half2float(g[e0 + i]) : 0.f;
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* g, uint64_t e0, uint64_t n, bool aligned, float (&v)[8]) {
+  if (aligned && e0 + 8 <= n) {
+    float4 a = __ldg(reinterpret_cast<const float4*>(g + e0));
+    float4 b = __ldg(reinterpret_cast<const float4*>(g + e0 + 4));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = (e0 + i < n) ? g[e0 + i] : 0.f;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// K1: partition + compact + push.  kBroadcast = true is the method-1 variant: one queue of
+// (global index, value) records pushed to every peer.
+template <typename T, bool kBroadcast>
+__global__ void __launch_bounds__(K1_THREADS, 1)
+zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const float* __restrict__ thr_ptr,
+                          int aligned) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int nq = kBroadcast ? 1 : c.nranks;
+  uint2* q = reinterpret_cast<uint2*>(smem_raw);                    // [nq][K1_QCAP]
+  __shared__ uint32_t qn[ZEN_MAX_RANKS];
+  __shared__ uint32_t qvalid[ZEN_MAX_RANKS];
+  __shared__ uint32_t s_last;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int sub = lane & 7;                                           // lane within its 64-element group
+  const float thr = thr_ptr ? *thr_ptr : 0.f;
+  const uint64_t N = c.numel;
+  const uint64_t nwi = (N + 255) / 256;                               // warp-iterations of 256 elements
+  const uint64_t ncta_it = (nwi + K1_WARPS * K1_U - 1) / (K1_WARPS * K1_U);
+  uint32_t local_status = 0;
+
+  if (tid < ZEN_MAX_RANKS) { qn[tid] = 0; qvalid[tid] = 0; }
+  __syncthreads();
+
+  for (uint64_t it = blockIdx.x; it < ncta_it; it += gridDim.x) {
+    float v[K1_U][8];
+#pragma unroll
+    for (int u = 0; u < K1_U; ++u) {
+      const uint64_t wi = it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp;
+      const uint64_t e0 = wi * 256 + (uint64_t)lane * 8;
+      if (e0 < N) load8<T>(g, e0, N, aligned != 0, v[u]);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < K1_U; ++u) {
+      const uint64_t wi = it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp;
+      const uint64_t e0 = wi * 256 + (uint64_t)lane * 8;
+      uint32_t m = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float a = fabsf(v[u][i]);
+        if (a != 0.f && a >= thr) m |= 1u << i;                      // NaN fails both tests: dropped
+      }
+      const uint32_t cnt = __popc(m);
+      uint32_t incl = cnt;                                            // inclusive prefix over the 8-lane group
+#pragma unroll
+      for (int d = 1; d < 8; d <<= 1) {
+        uint32_t t = __shfl_up_sync(0xffffffffu, incl, d, 8);
+        if (sub >= d) incl += t;
+      }
+      const uint32_t total = __shfl_sync(0xffffffffu, incl, 7, 8);
+      uint32_t owner = 0, slotbase = 0, pos = 0, direct = 0;
+      if (sub == 0 && total > 0) {
+        const uint64_t eg = e0;                                       // first element of this group
+        if (kBroadcast) {
+          owner = 0;
+          slotbase = (uint32_t)eg;
+        } else {
+          const uint32_t blk = (uint32_t)(eg / c.perm.block);
+          const uint32_t pb = zen_perm_fwd(c.perm, blk);
+          owner = pb / c.perm.sb;
+          slotbase = (pb % c.perm.sb) * c.perm.block + (uint32_t)(eg % c.perm.block);
+        }
+        pos = atomicAdd(&qn[owner], total);
+        if (pos + total > K1_QCAP) {
+          if (pos <= K1_QCAP) qvalid[owner] = pos;                    // exactly one group per overflow sees this
+          direct = 1;
+          pos = atomicAdd(&c.cursors[owner], total);                  // reserve directly in the destination
+        }
+      }
+      owner = __shfl_sync(0xffffffffu, owner, 0, 8);
+      slotbase = __shfl_sync(0xffffffffu, slotbase, 0, 8);
+      pos = __shfl_sync(0xffffffffu, pos, 0, 8);
+      direct = __shfl_sync(0xffffffffu, direct, 0, 8);
+      if (cnt) {
+        uint32_t k = pos + incl - cnt;
+        const uint32_t s0 = slotbase + sub * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (m & (1u << i)) {
+            const uint2 rec = make_uint2(s0 + i, ZenVal<T>::bits(ZenVal<T>::from_f(v[u][i])));
+            if (!direct) {
+              q[owner * K1_QCAP + k] = rec;
+            } else if (k < c.cap_rec) {
+              if (kBroadcast) {
+                for (int p = 0; p < c.nranks; ++p)
+                  reinterpret_cast<uint2*>(c.sym[p] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
+              } else {
+                reinterpret_cast<uint2*>(c.sym[owner] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
+              }
+            } else {
+              local_status |= ZEN_REC_OVERFLOW;
+            }
+            ++k;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    // flush phase: warp w drains queue w when it holds a worthwhile run (or on the last iteration)
+    const bool last_it = (it + gridDim.x >= ncta_it);
+    if (warp < nq) {
+      uint32_t n = qn[warp];
+      if (n > K1_QCAP) n = qvalid[warp];
+      const bool overflowed = qn[warp] > K1_QCAP;
+      if (n > 0 && (n >= K1_FLUSH_MIN || last_it || overflowed)) {
+        uint32_t gbase = 0;
+        if (lane == 0) gbase = atomicAdd(&c.cursors[warp], n);
+        gbase = __shfl_sync(0xffffffffu, gbase, 0);
+        uint32_t fit = (gbase >= c.cap_rec) ? 0u : min(n, c.cap_rec - gbase);
+        if (fit < n) local_status |= ZEN_REC_OVERFLOW;
+        const uint2* src = q + warp * K1_QCAP;
+        if (kBroadcast) {
+          for (int p = 0; p < c.nranks; ++p) {
+            uint2* dst = reinterpret_cast<uint2*>(c.sym[p] + c.off_rec) + (uint64_t)c.rank * c.cap_rec + gbase;
+            for (uint32_t i = lane; i < fit; i += 32) dst[i] = src[i];
+          }
+        } else {
+          uint2* dst = reinterpret_cast<uint2*>(c.sym[warp] + c.off_rec) + (uint64_t)c.rank * c.cap_rec + gbase;
+          for (uint32_t i = lane; i < fit; i += 32) dst[i] = src[i];
+        }
+        __syncwarp();
+        if (lane == 0) { qn[warp] = 0; qvalid[warp] = 0; }
+      } else if (overflowed && lane == 0) {
+        qn[warp] = 0; qvalid[warp] = 0;
+      }
+    }
+    __syncthreads();
+  }
+
+  if (local_status) atomicOr(c.status, local_status);
+  // completion: the last CTA to arrive publishes counts and epochs to the consumers
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const uint32_t prev = atomicAdd(&c.cursors[ZEN_MAX_RANKS], 1u);
+    s_last = (prev == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (tid < c.nranks) {
+      const int p = tid;
+      const uint32_t raw = atomicAdd(&c.cursors[kBroadcast ? 0 : p], 0u);
+      const uint32_t st = atomicOr(c.status, 0u);
+      ZenMail* mail = reinterpret_cast<ZenMail*>(c.sym[p] + c.off_rec_mail) + c.rank;
+      mail->count = min(raw, c.cap_rec);
+      mail->info = ((raw > c.cap_rec) || (st & ZEN_REC_OVERFLOW)) ? 1u : 0u;
+      mail->aux = 0;
+      __threadfence_system();
+      zen_st_release_sys(&mail->epoch, c.epoch);
+    }
+    __syncthreads();
+    if (tid < ZEN_MAX_RANKS + 1) c.cursors[tid] = 0;                  // ready for the next call
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// K2: owner-side reduce of sources [src_begin, src_end).  One launch over all sources is the fast
+// mode; one launch per source gives a fixed accumulation order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+zen_owner_reduce_kernel(const ZenSparseCtx c, int src_begin, int src_end) {
+  __shared__ uint32_t s_ok;
+  uint32_t local_status = 0;
+  for (int s = src_begin; s < src_end; ++s) {
+    const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_rec_mail) + s;
+    if (threadIdx.x == 0) s_ok = zen_wait_epoch(&mail->epoch, c.epoch, c.wait_ns) ? 1u : 0u;
+    __syncthreads();
+    const bool ok = s_ok != 0;
+    __syncthreads();
+    if (!ok) { local_status |= ZEN_TIMEOUT; continue; }
+    const uint32_t n = min(zen_ld_acquire_sys(&mail->count), c.cap_rec);
+    if (zen_ld_acquire_sys(&mail->info) & 1u) local_status |= ZEN_PEER_OVERFLOW;
+    const uint2* rec = reinterpret_cast<const uint2*>(c.sym[c.rank] + c.off_rec) + (uint64_t)s * c.cap_rec;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+      const uint2 r = rec[i];
+      if (r.x < c.nslots) {
+        atomicAdd(&c.acc[r.x], ZenVal<T>::unbits(r.y));
+        atomicOr(&c.bitmap[r.x >> 5], 1u << (r.x & 31));
+      } else {
+        local_status |= ZEN_BAD_ARG;
+      }
+    }
+  }
+  if (local_status) atomicOr(c.status, local_status);
+}
+
+// ---------------------------------------------------------------------------------------------
+// K3a: touched slots per 1024-slot chunk.
+__global__ void __launch_bounds__(256) zen_chunk_count_kernel(const ZenSparseCtx c) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t nw = (gridDim.x * blockDim.x) >> 5;
+  for (uint32_t ch = gw; ch < c.nchunks; ch += nw) {
+    const uint32_t wi = ch * 32 + lane;
+    uint32_t n = (wi < c.nwords) ? __popc(c.bitmap[wi]) : 0u;
+#pragma unroll
+    for (int d = 16; d; d >>= 1) n += __shfl_xor_sync(0xffffffffu, n, d);
+    if (lane == 0) c.chunk_off[ch] = n;
+  }
+}
+
+// K3b: exclusive scan of the chunk counts in place; total at [nchunks].  One CTA.
+__global__ void __launch_bounds__(1024) zen_chunk_scan_kernel(const ZenSparseCtx c) {
+  __shared__ uint32_t part[1024];
+  const uint32_t n = c.nchunks;
+  const uint32_t per = (n + 1023) / 1024;
+  const uint32_t b = threadIdx.x * per, e = min(n, b + per);
+  uint32_t s = 0;
+  for (uint32_t i = b; i < e; ++i) s += c.chunk_off[i];
+  part[threadIdx.x] = s;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {
+    uint32_t t = (threadIdx.x >= (unsigned)d) ? part[threadIdx.x - d] : 0u;
+    __syncthreads();
+    part[threadIdx.x] += t;
+    __syncthreads();
+  }
+  uint32_t run = part[threadIdx.x] - s;
+  for (uint32_t i = b; i < e; ++i) {
+    const uint32_t t = c.chunk_off[i];
+    c.chunk_off[i] = run;
+    run += t;
+  }
+  if (threadIdx.x == 1023) c.chunk_off[n] = part[1023];
+}
+
+// K3c: compact the touched slots of 8 consecutive chunks per CTA into shared memory, then push the
+// contiguous run (values, and COO slots or bitmap words + chunk offsets) to every peer.
+#define K3_WARPS 8
+template <typename T>
+__global__ void __launch_bounds__(K3_WARPS * 32)
+zen_gather_push_kernel(const ZenSparseCtx c) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem_raw);                       // [K3_WARPS * 1024 + 16]
+  T* s_val = reinterpret_cast<T*>(smem_raw + (K3_WARPS * 1024 + 16) * 4);        // [K3_WARPS * 1024 + 16]
+  __shared__ uint32_t s_last;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t total = c.chunk_off[c.nchunks];
+  const bool overflow = total > c.cap_g;
+  uint32_t fmt = c.fmt_mode;
+  if (fmt == 0) fmt = ((uint64_t)total * 32ull > (uint64_t)c.nslots) ? ZEN_FMT_BITMAP : ZEN_FMT_COO;
+  if (fmt == ZEN_FMT_COO && total > c.g_idx_words) fmt = ZEN_FMT_BITMAP;   // COO list would not fit
+  const uint32_t ngroups = (c.nchunks + K3_WARPS - 1) / K3_WARPS;
+  constexpr uint32_t VPV = 16 / sizeof(T);                               // values per 16-byte vector
+
+  for (uint32_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
+    const uint32_t ch0 = grp * K3_WARPS;
+    const uint32_t ch = ch0 + warp;
+    const uint32_t gbase = c.chunk_off[ch0];                             // first value of this CTA's run
+    const uint32_t gend = c.chunk_off[min(ch0 + K3_WARPS, c.nchunks)];
+    const uint32_t mis_v = gbase % VPV, mis_i = gbase % 4;
+    uint32_t word = 0, coff = 0;
+    if (ch < c.nchunks) {
+      const uint32_t wi = ch * 32 + lane;
+      word = (wi < c.nwords) ? c.bitmap[wi] : 0u;
+      coff = c.chunk_off[ch];
+      if (wi < c.nwords && word) c.bitmap[wi] = 0;                       // leave the bitmap clean for the next call
+    }
+    uint32_t incl = __popc(word);
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    const uint32_t woff = incl - __popc(word);
+    if (!overflow) {
+      for (int j = 0; j < 32; ++j) {
+        const uint32_t wj = __shfl_sync(0xffffffffu, word, j);
+        if (wj == 0) continue;
+        const uint32_t oj = __shfl_sync(0xffffffffu, woff, j);
+        if ((wj >> lane) & 1u) {
+          const uint32_t slot = ch * 1024 + j * 32 + lane;
+          const uint32_t r = (coff - gbase) + oj + __popc(wj & ((1u << lane) - 1u));
+          const float a = c.acc[slot];
+          c.acc[slot] = 0.f;
+          s_val[mis_v + r] = ZenVal<T>::from_f(a);
+          s_idx[mis_i + r] = slot;
+        }
+      }
+    } else {
+      for (int j = 0; j < 32; ++j) {                                     // still clear the accumulator
+        const uint32_t wj = __shfl_sync(0xffffffffu, word, j);
+        if ((wj >> lane) & 1u) c.acc[ch * 1024 + j * 32 + lane] = 0.f;
+      }
+    }
+    __syncthreads();
+    if (!overflow) {
+      const uint32_t n = gend - gbase;
+      for (int p = 0; p < c.nranks; ++p) {
+        char* base = c.sym[p];
+        // values: scalar head up to a 16-byte boundary, vector body, scalar tail
+        T* dv = reinterpret_cast<T*>(base + c.off_g_val + (uint64_t)c.rank * c.cap_g * 4ull) + gbase;
+        const uint32_t head = min(n, (VPV - mis_v) % VPV);
+        for (uint32_t i = tid; i < head; i += blockDim.x) dv[i] = s_val[mis_v + i];
+        const uint32_t nvec = (n - head) / VPV;
+        {
+          uint4* d4 = reinterpret_cast<uint4*>(dv + head);
+          const uint4* s4 = reinterpret_cast<const uint4*>(s_val + mis_v + head);
+          for (uint32_t i = tid; i < nvec; i += blockDim.x) d4[i] = s4[i];
+        }
+        for (uint32_t i = head + nvec * VPV + tid; i < n; i += blockDim.x) dv[i] = s_val[mis_v + i];
+        if (fmt == ZEN_FMT_COO) {
+          uint32_t* di = reinterpret_cast<uint32_t*>(base + c.off_g_idx) + (uint64_t)c.rank * c.g_idx_words + gbase;
+          const uint32_t hi = min(n, (4u - mis_i) % 4u);
+          for (uint32_t i = tid; i < hi; i += blockDim.x) di[i] = s_idx[mis_i + i];
+          const uint32_t nv = (n - hi) / 4;
+          uint4* d4 = reinterpret_cast<uint4*>(di + hi);
+          const uint4* s4 = reinterpret_cast<const uint4*>(s_idx + mis_i + hi);
+          for (uint32_t i = tid; i < nv; i += blockDim.x) d4[i] = s4[i];
+          for (uint32_t i = hi + nv * 4 + tid; i < n; i += blockDim.x) di[i] = s_idx[mis_i + i];
+        } else if (ch < c.nchunks) {
+          uint32_t* db = reinterpret_cast<uint32_t*>(base + c.off_g_idx) + (uint64_t)c.rank * c.g_idx_words;
+          const uint32_t wi = ch * 32 + lane;
+          if (wi < c.nwords) db[wi] = word;
+          if (lane == 0)
+            reinterpret_cast<uint32_t*>(base + c.off_g_off)[(uint64_t)c.rank * (c.nchunks + 1) + ch] = coff;
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const uint32_t prev = atomicAdd(&c.cursors[ZEN_MAX_RANKS + 1], 1u);
+    s_last = (prev == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (overflow && tid == 0) atomicOr(c.status, ZEN_GATHER_OVERFLOW);
+    if (tid < c.nranks) {
+      const uint32_t st = atomicOr(c.status, 0u);
+      ZenMail* mail = reinterpret_cast<ZenMail*>(c.sym[tid] + c.off_g_mail) + c.rank;
+      mail->count = overflow ? 0u : total;
+      mail->info = ((overflow || (st & (ZEN_REC_OVERFLOW | ZEN_PEER_OVERFLOW | ZEN_TIMEOUT))) ? 1u : 0u) | (fmt << 8);
+      mail->aux = 0;
+      __threadfence_system();
+      zen_st_release_sys(&mail->epoch, c.epoch);
+    }
+    if (tid == 0) c.cursors[ZEN_MAX_RANKS + 1] = 0;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// K4: densify.  Walks every owner's slot space chunk by chunk; every output element is written once
+// (zeros included), so the output needs no memset.  Owners that chose COO get their blocks
+// zero-filled here and their values scattered by zen_densify_coo_kernel afterwards.
+template <typename T>
+__global__ void __launch_bounds__(256)
+zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
+  __shared__ uint32_t s_fmt[ZEN_MAX_RANKS];
+  const int tid = threadIdx.x, lane = tid & 31;
+  uint32_t local_status = 0;
+  if (tid < c.nranks) {
+    const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_g_mail) + tid;
+    uint32_t f = 0;
+    if (zen_wait_epoch(&mail->epoch, c.epoch, c.wait_ns)) {
+      f = (mail->info >> 8) & 0xffu;
+      if (mail->info & 1u) { local_status |= ZEN_PEER_OVERFLOW; f = 0; }
+    } else {
+      local_status |= ZEN_TIMEOUT;
+    }
+    s_fmt[tid] = f;
+  }
+  __syncthreads();
+  const uint32_t G = c.perm.block;
+  const uint64_t N = c.numel;
+  const uint32_t gw = (blockIdx.x * blockDim.x + tid) >> 5;
+  const uint32_t nw = (gridDim.x * blockDim.x) >> 5;
+  const uint64_t nunits = (uint64_t)c.nranks * c.nchunks;
+  for (uint64_t unit = gw; unit < nunits; unit += nw) {
+    const uint32_t o = (uint32_t)(unit / c.nchunks), ch = (uint32_t)(unit % c.nchunks);
+    const bool bm = s_fmt[o] == ZEN_FMT_BITMAP;
+    const char* base = c.sym[c.rank];
+    const uint32_t* gbm = reinterpret_cast<const uint32_t*>(base + c.off_g_idx) + (uint64_t)o * c.g_idx_words;
+    const T* gval = reinterpret_cast<const T*>(base + c.off_g_val + (uint64_t)o * c.cap_g * 4ull);
+    const uint32_t wi = ch * 32 + lane;
+    uint32_t word = (bm && wi < c.nwords) ? gbm[wi] : 0u;
+    uint32_t incl = __popc(word);
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    const uint32_t coff = bm ? reinterpret_cast<const uint32_t*>(base + c.off_g_off)[(uint64_t)o * (c.nchunks + 1) + ch] : 0u;
+    const uint32_t woff = coff + incl - __popc(word);
+    // lanes 0..15 each invert the permutation for one 64-slot group of this chunk
+    uint64_t my_out = ~0ull;
+    if (lane < 16) {
+      const uint32_t slot0 = ch * 1024 + lane * 64;
+      if (slot0 < c.nslots) {
+        const uint32_t pb = o * c.perm.sb + slot0 / G;
+        const uint32_t blk = zen_perm_inv(c.perm, pb);
+        my_out = (uint64_t)blk * G + (slot0 % G);
+      }
+    }
+#pragma unroll 4
+    for (int jb = 0; jb < 16; ++jb) {
+      const uint64_t obase = __shfl_sync(0xffffffffu, my_out, jb);
+      const int wsel = 2 * jb + (lane >> 4);
+      const uint32_t w = __shfl_sync(0xffffffffu, word, wsel);
+      const uint32_t wo = __shfl_sync(0xffffffffu, woff, wsel);
+      if (obase == ~0ull) continue;
+      const int b0 = (2 * lane) & 31;
+      const uint64_t e = obase + 2 * lane;
+      T v0 = ZenVal<T>::from_f(0.f), v1 = v0;
+      if ((w >> b0) & 1u) v0 = gval[wo + __popc(w & ((1u << b0) - 1u))];
+      if ((w >> (b0 + 1)) & 1u) v1 = gval[wo + __popc(w & ((2u << b0) - 1u))];
+      if (e + 1 < N) {
+        if (sizeof(T) == 2) {
+          uint32_t pk = (ZenVal<T>::bits(v1) << 16) | ZenVal<T>::bits(v0);
+          *reinterpret_cast<uint32_t*>(out + e) = pk;
+        } else {
+          out[e] = v0; out[e + 1] = v1;
+        }
+      } else if (e < N) {
+        out[e] = v0;
+      }
+    }
+  }
+  if (local_status) atomicOr(c.status, local_status);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+zen_densify_coo_kernel(const ZenSparseCtx c, T* __restrict__ out) {
+  const uint32_t G = c.perm.block;
+  for (int o = 0; o < c.nranks; ++o) {
+    const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_g_mail) + o;
+    // the bitmap pass of this call already waited for this epoch
+    if (zen_ld_acquire_sys(&mail->epoch) != c.epoch) continue;
+    if (((mail->info >> 8) & 0xffu) != ZEN_FMT_COO || (mail->info & 1u)) continue;
+    const uint32_t n = min(mail->count, min(c.cap_g, c.g_idx_words));
+    const char* base = c.sym[c.rank];
+    const uint32_t* gi = reinterpret_cast<const uint32_t*>(base + c.off_g_idx) + (uint64_t)o * c.g_idx_words;
+    const T* gv = reinterpret_cast<const T*>(base + c.off_g_val + (uint64_t)o * c.cap_g * 4ull);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+      const uint32_t slot = gi[i];
+      if (slot >= c.nslots) continue;
+      const uint32_t blk = zen_perm_inv(c.perm, o * c.perm.sb + slot / G);
+      const uint64_t e = (uint64_t)blk * G + slot % G;
+      if (e < c.numel) out[e] = gv[i];
+    }
+  }
+}
+
+// Method 1 consumer: out[idx] += val for one source, read-modify-write in T (indices are unique
+// within a source, and sources are applied by separate launches in rank order).
+template <typename T>
+__global__ void __launch_bounds__(256)
+zen_scatter_source_kernel(const ZenSparseCtx c, T* __restrict__ out, int src) {
+  __shared__ uint32_t s_ok;
+  const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_rec_mail) + src;
+  if (threadIdx.x == 0) s_ok = zen_wait_epoch(&mail->epoch, c.epoch, c.wait_ns) ? 1u : 0u;
+  __syncthreads();
+  if (!s_ok) { if (threadIdx.x == 0) atomicOr(c.status, ZEN_TIMEOUT); return; }
+  if ((mail->info & 1u) && threadIdx.x == 0) atomicOr(c.status, ZEN_PEER_OVERFLOW);
+  const uint32_t n = min(mail->count, c.cap_rec);
+  const uint2* rec = reinterpret_cast<const uint2*>(c.sym[c.rank] + c.off_rec) + (uint64_t)src * c.cap_rec;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint2 r = rec[i];
+    if (r.x < c.numel) out[r.x] = ZenVal<T>::from_f(ZenVal<T>::to_f(out[r.x]) + ZenVal<T>::unbits(r.y));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Owner map (API parity with hash_index, functions_cuda_kernel.cu:169-177): out[i] = owner(i).
+// mode 0: block permutation; mode 1: the reference's cubic polynomial, owner = (h % M) / (M / P).
+__device__ __forceinline__ uint32_t zen_poly3(uint32_t k, uint32_t seed) {
+  return 573729859u * k * k * k + 0xcc9e2d51u * k * k + 0x1b873593u * k + seed;
+}
+
+__global__ void __launch_bounds__(256)
+zen_owner_map_kernel(int32_t* __restrict__ out, uint64_t n, ZenPerm perm, int mode, uint32_t table, int parts) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    if (mode == 0) {
+      out[i] = (int32_t)(zen_perm_fwd(perm, (uint32_t)(i / perm.block)) / perm.sb);
+    } else {
+      const uint32_t per = table / parts;
+      out[i] = (int32_t)((zen_poly3((uint32_t)i, 10001861u) % table) / per);
+    }
+  }
+}
+
+// Reference-compatible balancer (sparse_balance, functions_cuda_kernel.cu:97-167): open-addressing
+// table of element indices with up to `rehash` probes inside the partition chosen by the first
+// probe, overflow appended per partition.  Differences: slots are claimed with atomicCAS (no lost
+// indices), indices are stored +1 so that element 0 is representable, the overflow cursor is bounded.
+template <typename T>
+__global__ void __launch_bounds__(256)
+zen_sparse_balance_kernel(const T* __restrict__ in, uint64_t n, int32_t* __restrict__ table, uint32_t table_size,
+                          int32_t* __restrict__ serial, uint32_t serial_per_part, uint32_t* __restrict__ cursors,
+                          int parts, int rehash, uint32_t* __restrict__ status) {
+  const uint32_t per = table_size / parts;
+  const uint32_t seeds[3] = {10001861u, 100703u, 5002639u};
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    if (ZenVal<T>::to_f(in[i]) == 0.f) continue;
+    const uint32_t first = zen_poly3((uint32_t)i, seeds[0]) % table_size;
+    const uint32_t part = first / per, start = part * per;
+    bool placed = atomicCAS(&table[first], 0, (int32_t)i + 1) == 0;
+    for (int r = 1; r < rehash && r < 3 && !placed; ++r) {
+      const uint32_t s = start + zen_poly3((uint32_t)i, seeds[r]) % per;
+      placed = atomicCAS(&table[s], 0, (int32_t)i + 1) == 0;
+    }
+    if (!placed) {
+      const uint32_t k = atomicAdd(&cursors[part], 1u);
+      if (k < serial_per_part) serial[(uint64_t)part * serial_per_part + k] = (int32_t)i + 1;
+      else atomicOr(status, ZEN_REC_OVERFLOW);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host launchers (C ABI, called through ctypes with raw pointers and the caller's stream).
+static inline int grid_for(uint64_t work_items, int per_cta, int max_ctas) {
+  uint64_t g = (work_items + per_cta - 1) / per_cta;
+  if (g < 1) g = 1;
+  if (g > (uint64_t)max_ctas) g = max_ctas;
+  return (int)g;
+}
+
+static int g_sm_count = 0;
+static int sm_count() {
+  if (!g_sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sm_count <= 0) g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+template <typename T>
+static int launch_partition(const ZenSparseCtx& c, const void* g, const float* thr, int broadcast, cudaStream_t st) {
+  const uint64_t nwi = (c.numel + 255) / 256;
+  const uint64_t nit = (nwi + K1_WARPS * K1_U - 1) / (K1_WARPS * K1_U);
+  const int grid = grid_for(nit, 1, sm_count() * 2);
+  const int nq = broadcast ? 1 : c.nranks;
+  const size_t smem = (size_t)nq * K1_QCAP * sizeof(uint2);
+  const int aligned = (reinterpret_cast<uintptr_t>(g) % 16 == 0) ? 1 : 0;
+  if (broadcast) {
+    ZEN_CUDA_CHECK_RET(cudaFuncSetAttribute(zen_partition_push_kernel<T, true>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    zen_partition_push_kernel<T, true><<<grid, K1_THREADS, smem, st>>>(c, (const T*)g, thr, aligned);
+  } else {
+    ZEN_CUDA_CHECK_RET(cudaFuncSetAttribute(zen_partition_push_kernel<T, false>,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    zen_partition_push_kernel<T, false><<<grid, K1_THREADS, smem, st>>>(c, (const T*)g, thr, aligned);
+  }
+  return (int)cudaGetLastError();
+}
+
+#define DISPATCH_DTYPE(dtype, ...)                                       \
+  switch (dtype) {                                                       \
+    case ZEN_DTYPE_F32: { using T = float; __VA_ARGS__; } break;         \
+    case ZEN_DTYPE_BF16: { using T = __nv_bfloat16; __VA_ARGS__; } break; \
+    case ZEN_DTYPE_F16: { using T = __half; __VA_ARGS__; } break;        \
+    default: return -1;                                                  \
+  }
+
+extern "C" {
+
+int zen_sparse_ctx_size() { return (int)sizeof(ZenSparseCtx); }
+
+// K1.  `thr` may be null (keep every nonzero) or point at a device float threshold on |g|.
+int zen_partition_push(const ZenSparseCtx* c, const void* g, const float* thr, int dtype, int broadcast, void* stream) {
+  int rc = 0;
+  DISPATCH_DTYPE(dtype, rc = launch_partition<T>(*c, g, thr, broadcast, (cudaStream_t)stream));
+  return rc;
+}
+
+// K2.  deterministic != 0: one launch per source, in rank order.
+int zen_owner_reduce(const ZenSparseCtx* c, int dtype, int deterministic, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = sm_count() * 4;
+  if (deterministic) {
+    for (int s = 0; s < c->nranks; ++s) {
+      DISPATCH_DTYPE(dtype, zen_owner_reduce_kernel<T><<<grid, 256, 0, st>>>(*c, s, s + 1));
+    }
+  } else {
+    DISPATCH_DTYPE(dtype, zen_owner_reduce_kernel<T><<<grid, 256, 0, st>>>(*c, 0, c->nranks));
+  }
+  return (int)cudaGetLastError();
+}
+
+// K3 (count, scan, compact + push).
+int zen_gather_push(const ZenSparseCtx* c, int dtype, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const int g1 = grid_for(c->nchunks, 8, sm_count() * 8);
+  zen_chunk_count_kernel<<<g1, 256, 0, st>>>(*c);
+  zen_chunk_scan_kernel<<<1, 1024, 0, st>>>(*c);
+  const int g3 = grid_for(c->nchunks, K3_WARPS, sm_count() * 3);
+  DISPATCH_DTYPE(dtype, {
+    const size_t smem = (K3_WARPS * 1024 + 16) * (4 + sizeof(T));
+    ZEN_CUDA_CHECK_RET(cudaFuncSetAttribute(zen_gather_push_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    zen_gather_push_kernel<T><<<g3, K3_WARPS * 32, smem, st>>>(*c);
+  });
+  return (int)cudaGetLastError();
+}
+
+// K4 (bitmap walk with zero fill, then COO scatter for owners that chose COO).
+int zen_densify(const ZenSparseCtx* c, void* out, int dtype, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const uint64_t units = (uint64_t)c->nranks * c->nchunks;
+  const int g1 = grid_for(units, 8, sm_count() * 8);
+  DISPATCH_DTYPE(dtype, zen_densify_kernel<T><<<g1, 256, 0, st>>>(*c, (T*)out));
+  if (c->fmt_mode != ZEN_FMT_BITMAP) {
+    DISPATCH_DTYPE(dtype, zen_densify_coo_kernel<T><<<sm_count() * 4, 256, 0, st>>>(*c, (T*)out));
+  }
+  return (int)cudaGetLastError();
+}
+
+// Method 1 consumer: zero `out`, then add every source in rank order.
+int zen_scatter_sources(const ZenSparseCtx* c, void* out, int dtype, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t es = (dtype == ZEN_DTYPE_F32) ? 4 : 2;
+  ZEN_CUDA_CHECK_RET(cudaMemsetAsync(out, 0, c->numel * es, st));
+  for (int s = 0; s < c->nranks; ++s) {
+    DISPATCH_DTYPE(dtype, zen_scatter_source_kernel<T><<<sm_count() * 4, 256, 0, st>>>(*c, (T*)out, s));
+  }
+  return (int)cudaGetLastError();
+}
+
+int zen_owner_map(int32_t* out, uint64_t n, const ZenPerm* perm, int mode, uint32_t table, int parts, void* stream) {
+  ZenPerm p = *perm;
+  zen_owner_map_kernel<<<grid_for(n, 256 * 8, sm_count() * 8), 256, 0, (cudaStream_t)stream>>>(out, n, p, mode, table, parts);
+  return (int)cudaGetLastError();
+}
+
+int zen_sparse_balance(const void* in, uint64_t n, int dtype, int32_t* table, uint32_t table_size, int32_t* serial,
+                       uint32_t serial_per_part, uint32_t* cursors, int parts, int rehash, uint32_t* status,
+                       void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = grid_for(n, 256 * 4, sm_count() * 8);
+  DISPATCH_DTYPE(dtype, zen_sparse_balance_kernel<T><<<grid, 256, 0, st>>>((const T*)in, n, table, table_size, serial,
+                                                                           serial_per_part, cursors, parts, rehash,
+                                                                           status));
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,136 @@
+"""Partition functions for the sparse all-reduce.
+
+Two partitioners are provided.
+
+``BlockPermutation`` (default).  An invertible affine permutation of *blocks*
+of ``G`` consecutive elements.  With ``nb' = P * Sb`` padded blocks,
+
+    pi(b)    = (a * b + c) mod nb'          (gcd(a, nb') == 1)
+    owner(i) = pi(i // G) // Sb
+    slot(i)  = (pi(i // G) % Sb) * G + i % G
+    i        = pi^-1(owner * Sb + slot // G) * G + slot % G
+
+``a`` is chosen close to ``nb' / golden_ratio`` (Fibonacci hashing), which
+spreads any contiguous run of hot positions (the Zipf head of an embedding
+table) evenly over the ``P`` owners.  Because the map is a bijection the owner
+can reduce into ``S = Sb * G`` dense slots and the occupancy bitmap of those
+slots *is* the index encoding of the gather phase; no per-position ownership
+list has to be stored, and sizes that are not multiples of ``P`` need no
+special case.  The reference builds its ownership lists by hashing every
+position and comparing against each rank (comm.py:52-56) and its two hash
+users disagree when ``numel % P != 0`` (functions_cuda_kernel.cu:172-174 vs
+tensor_load_balance.py:15-16).
+
+``zen_poly3``.  The reference's cubic polynomial in wrapping uint32
+arithmetic (functions_cuda_kernel.cu:80-93), kept for A/B checks of the
+partition assignment: ``owner(i) = (h(i, seed0) % M) // (M // P)``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+GOLDEN = 0.6180339887498949
+
+ZEN_POLY3_D = 573729859
+ZEN_POLY3_A = 0xCC9E2D51
+ZEN_POLY3_B = 0x1B873593
+ZEN_SEEDS = (10001861, 100703, 5002639)
+
+
+def _coprime_near(target: int, modulus: int) -> int:
+    """Smallest ``a >= target`` (wrapping into [1, modulus)) coprime with ``modulus``."""
+    if modulus == 1:
+        return 0
+    a = max(1, target % modulus)
+    for _ in range(modulus):
+        if math.gcd(a, modulus) == 1:
+            return a
+        a += 1
+        if a >= modulus:
+            a = 1
+    raise ValueError("no coprime multiplier")
+
+
+@dataclass(frozen=True)
+class BlockPermutation:
+    """Invertible block permutation; see the module docstring for the maths."""
+
+    numel: int          # N: logical elements (or rows in row mode)
+    parts: int          # P
+    block: int          # G
+    nblocks: int        # nb' (padded, multiple of P)
+    blocks_per_part: int  # Sb
+    mult: int           # a
+    mult_inv: int       # a^-1 mod nb'
+    add: int            # c
+
+    @staticmethod
+    def make(numel: int, parts: int, block: int = 64) -> "BlockPermutation":
+        if numel <= 0 or parts <= 0 or block <= 0:
+            raise ValueError("numel, parts and block must be positive")
+        nb = -(-numel // block)
+        sb = -(-nb // parts)
+        nbp = sb * parts
+        if nbp >= 2 ** 31:
+            raise ValueError("too many blocks for 32-bit block ids")
+        a = _coprime_near(int(round(nbp * GOLDEN)), nbp)
+        ainv = pow(a, -1, nbp) if nbp > 1 else 0
+        c = int(round(nbp * (1.0 - GOLDEN) * 0.5)) % nbp
+        return BlockPermutation(numel, parts, block, nbp, sb, a, ainv, c)
+
+    @property
+    def slots_per_part(self) -> int:
+        return self.blocks_per_part * self.block
+
+    @property
+    def padded_numel(self) -> int:
+        return self.nblocks * self.block
+
+    # -- tensor forms (int64 in, int64 out); exact for nb' < 2**31 ----------
+    def permute_block(self, blk: torch.Tensor) -> torch.Tensor:
+        return (blk.to(torch.int64) * self.mult + self.add) % self.nblocks
+
+    def unpermute_block(self, pb: torch.Tensor) -> torch.Tensor:
+        return ((pb.to(torch.int64) - self.add) % self.nblocks * self.mult_inv) % self.nblocks
+
+    def owner_slot(self, idx: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        idx = idx.to(torch.int64)
+        pb = self.permute_block(idx // self.block)
+        owner = pb // self.blocks_per_part
+        slot = (pb % self.blocks_per_part) * self.block + idx % self.block
+        return owner, slot
+
+    def index_of(self, owner: int | torch.Tensor, slot: torch.Tensor) -> torch.Tensor:
+        slot = slot.to(torch.int64)
+        pb = owner * self.blocks_per_part + slot // self.block
+        return self.unpermute_block(pb) * self.block + slot % self.block
+
+    def as_kernel_args(self) -> tuple[int, int, int, int, int, int]:
+        """(block, nblocks, blocks_per_part, mult, mult_inv, add) for the CUDA side."""
+        return (self.block, self.nblocks, self.blocks_per_part, self.mult, self.mult_inv, self.add)
+
+
+def zen_poly3(idx: torch.Tensor, seed: int) -> torch.Tensor:
+    """h(k, c) = d k^3 + a k^2 + b k + c in wrapping uint32 arithmetic (int64 tensor out)."""
+    m = 0xFFFFFFFF
+    k = idx.to(torch.int64) & m
+    k2 = (k * k) & m
+    k3 = (k2 * k) & m
+    h = ((ZEN_POLY3_D * k3) & m) + ((ZEN_POLY3_A * k2) & m) + ((ZEN_POLY3_B * k) & m) + seed
+    return h & m
+
+
+def zen_poly3_owner(idx: torch.Tensor, table_size: int, parts: int) -> torch.Tensor:
+    """Owner of ``idx`` under the reference balancer: first probe decides the partition."""
+    per = table_size // parts
+    return (zen_poly3(idx, ZEN_SEEDS[0]) % table_size) // per
+
+
+def partition_imbalance(owner: torch.Tensor, parts: int) -> float:
+    """max / mean load over partitions (1.0 is perfect)."""
+    counts = torch.bincount(owner.to(torch.int64), minlength=parts).to(torch.float64)
+    mean = counts.mean().item()
+    return float(counts.max().item() / mean) if mean > 0 else 1.0
