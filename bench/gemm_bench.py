@@ -1,0 +1,63 @@
+"""GEMM microbenchmark: tcgen05 kernel vs torch.matmul (cuBLAS) on the shapes of the benchmark models.
+
+    python bench/gemm_bench.py [--shapes gpt2|llama|square] [--iters 20]
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from zen_repro_b200.ops import gemm as G  # noqa: E402
+
+SHAPES = {
+    "gpt2": [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072), (8192, 50304, 768)],
+    "gemma": [(8192, 2560, 2048), (8192, 2048, 2048), (8192, 32768, 2048), (8192, 2048, 16384)],
+    "llama": [(4096, 3072, 4096), (4096, 4096, 2048), (4096, 14336, 4096), (4096, 4096, 7168)],
+    "square": [(4096, 4096, 4096), (8192, 8192, 8192)],
+}
+
+
+def bench(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); fn(); e.record(); torch.cuda.synchronize()
+        ts.append(s.elapsed_time(e))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default="gpt2")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--modes", nargs="+", default=["nt", "nn", "tn"])
+    args = ap.parse_args()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for (M, N, K) in SHAPES[args.shapes]:
+        for mode in args.modes:
+            if mode == "nt":
+                a = torch.randn(M, K, device="cuda").bfloat16(); b = torch.randn(N, K, device="cuda").bfloat16()
+                mine, ref = (lambda: G.gemm_nt(a, b)), (lambda: a @ b.t())
+            elif mode == "nn":
+                a = torch.randn(M, K, device="cuda").bfloat16(); b = torch.randn(K, N, device="cuda").bfloat16()
+                mine, ref = (lambda: G.gemm_nn(a, b)), (lambda: a @ b)
+            else:
+                a = torch.randn(K, M, device="cuda").bfloat16(); b = torch.randn(K, N, device="cuda").bfloat16()
+                mine, ref = (lambda: G.gemm_tn(a, b)), (lambda: a.t() @ b)
+            tm, tr = bench(mine, args.iters, flush), bench(ref, args.iters, flush)
+            fl = 2.0 * M * N * K
+            print(json.dumps(dict(mode=mode, M=M, N=N, K=K, zen_ms=round(tm, 4), cublas_ms=round(tr, 4),
+                                  zen_tflops=round(fl / tm / 1e9, 1), cublas_tflops=round(fl / tr / 1e9, 1),
+                                  err=G.gemm_error())), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -96,7 +96,8 @@ def main():
                 eng.epoch += 1; e = eng.epoch
                 stage("partition_push_all", lambda: [r.partition_push(x, e) for r, x in zip(r0, xs)])
                 stage("owner_reduce_all", lambda: [r.owner_reduce(e, dtype) for r in r0])
-                [r.gather_push(e, dtype) for r in r0]
+                stage("reduce_plus_gather_all", lambda: ([r.owner_reduce(e, dtype) for r in r0], [r.gather_push(e, dtype) for r in r0]))
+                [r.owner_reduce(e, dtype) for r in r0]; [r.gather_push(e, dtype) for r in r0]
                 out = torch.empty_like(xs[0])
                 stage("densify_one", lambda: r0[0].densify(out, e))
                 eng.status()

@@ -1,0 +1,65 @@
+"""tcgen05 GEMM against an fp32 matmul of the same bf16 operands."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from zen_repro_b200.ops import gemm as G  # noqa: E402
+
+
+def _check(got, want, K):
+    err = (got.float() - want).abs().max().item()
+    scale = want.abs().max().item() + 1e-6
+    assert err <= 0.01 * scale + 0.02, (err, scale)
+
+
+SHAPES = [(128, 128, 64), (128, 256, 128), (256, 512, 256), (1000, 768, 768), (8192, 2304, 768), (300, 50257, 768),
+          (77, 130, 72), (4096, 4096, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("bn", [0, 128, 256])
+def test_nt(M, N, K, bn):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    got = G.gemm_nt(a, b, bn=bn)
+    assert G.gemm_error() == 0
+    _check(got, a.float() @ b.float().t(), K)
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES[:6])
+def test_nn_and_tn(M, N, K):
+    torch.manual_seed(1)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(K, N, device="cuda").bfloat16()
+    _check(G.gemm_nn(a, b), a.float() @ b.float(), K)
+    at = torch.randn(K, M, device="cuda").bfloat16()
+    _check(G.gemm_tn(at, b), at.float().t() @ b.float(), K)
+    assert G.gemm_error() == 0
+
+
+def test_bias_accumulate_fp32_out():
+    torch.manual_seed(2)
+    M, N, K = 512, 384, 320
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    want = a.float() @ b.float().t() + bias.float()
+    _check(G.gemm_nt(a, b, bias=bias), want, K)
+    acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
+    G.gemm_nt(a, b, out=acc, accumulate=True)
+    _check(acc, a.float() @ b.float().t() + 1.0, K)
+    accb = torch.ones(M, N, device="cuda", dtype=torch.bfloat16)
+    G.gemm_nt(a, b, out=accb, accumulate=True)
+    _check(accb, a.float() @ b.float().t() + 1.0, K)
+    assert G.gemm_error() == 0
+
+
+def test_strided_operands_inside_a_wider_buffer():
+    torch.manual_seed(3)
+    buf = torch.randn(256, 3 * 128, device="cuda").bfloat16()
+    q, k = buf[:, :128], buf[:, 128:256]
+    w = torch.randn(64, 128, device="cuda").bfloat16()
+    _check(G.gemm_nt(q, w), q.float() @ w.float().t(), 128)
+    _check(G.gemm_nt(k, w), k.float() @ w.float().t(), 128)

@@ -1,0 +1,738 @@
+// Memory-bound model ops for sm_100a: norms (with the residual add fused in), gated activations,
+// RoPE, embedding forward / row-sparse backward, cross-entropy (loss and dlogits in one kernel),
+// column sums, and a multi-tensor AdamW.  All are bandwidth kernels: 16-byte accesses, one pass over
+// each operand, fp32 math, bf16 / fp32 / fp16 storage.
+//
+// The reference takes these from HuggingFace modules and ColossalAI's HybridAdam
+// (train.py:149-157); nothing of them is in its tree.
+#include "zen_common.cuh"
+
+namespace {
+
+template <typename T> struct Vec8;   // 8 elements of T <-> 8 floats
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    uint4 r = *reinterpret_cast<const uint4*>(p);
+    uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <> struct Vec8<__half> {
+  static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
+    uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ void store(__half* p, const float (&v)[8]) {
+    uint4 r;
+    __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int d = 16; d; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int d = 16; d; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+  return v;
+}
+// Sum over the CTA (blockDim.x a multiple of 32, at most 1024); every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? sh[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* sh) {
+  v = warp_max(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) sh[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? sh[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+#define NORM_THREADS 128
+#define NORM_MAXV 8   // up to 128 * 8 * 8 = 8192 columns held in registers
+
+// --------------------------------------------------------------------------------------------
+// Norm forward.  h = x (+ res); y = (h - mean) * rstd * wgt + bias   (LayerNorm, kLayer)
+//                                y = h * rstd * (wgt or 1 + wgt)     (RMSNorm)
+// `hout` (optional) receives h, the new residual stream.  stats: rstd[rows] (+ mean[rows]).
+template <typename T, bool kLayer>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ wgt,
+                const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ hout, float* __restrict__ rstd_out,
+                float* __restrict__ mean_out, int rows, int cols, float eps, int unit_offset) {
+  __shared__ float sh[32];
+  const int nv = cols / 8;                         // cols % 8 == 0 checked on the host
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = (size_t)row * cols;
+    float h[NORM_MAXV][8];
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nv) {
+        Vec8<T>::load(x + base + (size_t)v * 8, h[j]);
+        if (res) {
+          float r[8];
+          Vec8<T>::load(res + base + (size_t)v * 8, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) h[j][i] += r[i];
+        }
+        if (hout) {
+          Vec8<T>::store(hout + base + (size_t)v * 8, h[j]);
+          // keep exactly what was stored so that forward and backward see the same h
+          Vec8<T>::load(hout + base + (size_t)v * 8, h[j]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s += h[j][i]; ss += h[j][i] * h[j][i]; }
+      }
+    }
+    float mean = 0.f, var;
+    if (kLayer) {
+      mean = block_sum(s, sh) / cols;
+      float d2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NORM_MAXV; ++j) {
+        const int v = threadIdx.x + j * NORM_THREADS;
+        if (v < nv) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { const float d = h[j][i] - mean; d2 += d * d; }
+        }
+      }
+      var = block_sum(d2, sh) / cols;
+    } else {
+      var = block_sum(ss, sh) / cols;
+    }
+    const float rstd = rsqrtf(var + eps);
+    if (threadIdx.x == 0) { rstd_out[row] = rstd; if (kLayer) mean_out[row] = mean; }
+#pragma unroll
+    for (int j = 0; j < NORM_MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nv) {
+        float w[8], o[8];
+        Vec8<T>::load(wgt + (size_t)v * 8, w);
+        if (kLayer) {
+          float b[8];
+          if (bias) Vec8<T>::load(bias + (size_t)v * 8, b);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = (h[j][i] - mean) * rstd * w[i] + (bias ? b[i] : 0.f);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = h[j][i] * rstd * (unit_offset ? 1.f + w[i] : w[i]);
+        }
+        Vec8<T>::store(y + base + (size_t)v * 8, o);
+      }
+    }
+  }
+}
+
+// Norm backward.  dh = grad through the norm (+ dres, the gradient arriving on the residual stream).
+// Per-CTA partial sums of dw (and db) go to part_dw/part_db [gridDim.x][cols] (fp32 scratch) and are
+// folded by colreduce_kernel.
+template <typename T, bool kLayer>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __restrict__ wgt,
+                const float* __restrict__ rstd_in, const float* __restrict__ mean_in, const T* __restrict__ dres,
+                T* __restrict__ dh, float* __restrict__ part_dw, float* __restrict__ part_db, int rows, int cols,
+                int unit_offset) {
+  __shared__ float sh[32];
+  const int nv = cols / 8;
+  float aw[NORM_MAXV][8], ab[NORM_MAXV][8];
+#pragma unroll
+  for (int j = 0; j < NORM_MAXV; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { aw[j][i] = 0.f; ab[j][i] = 0.f; }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = (size_t)row * cols;
+    const float rstd = rstd_in[row];
+    const float mean = kLayer ? mean_in[row] : 0.f;
+    float g[NORM_MAXV][8], xh[NORM_MAXV][8];
+    float s1 = 0.f, s2 = 0.f;                       // sum(g), sum(g * xhat)
+#pragma unroll
+    for (int j = 0; j < NORM_MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nv) {
+        float d[8], w[8];
+        Vec8<T>::load(dy + base + (size_t)v * 8, d);
+        Vec8<T>::load(h + base + (size_t)v * 8, xh[j]);
+        Vec8<T>::load(wgt + (size_t)v * 8, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[j][i] = (xh[j][i] - mean) * rstd;
+          aw[j][i] += d[i] * xh[j][i];
+          ab[j][i] += d[i];
+          g[j][i] = d[i] * (kLayer ? w[i] : (unit_offset ? 1.f + w[i] : w[i]));
+          s1 += g[j][i];
+          s2 += g[j][i] * xh[j][i];
+        }
+      }
+    }
+    s2 = block_sum(s2, sh) / cols;
+    if (kLayer) s1 = block_sum(s1, sh) / cols; else s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_MAXV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nv) {
+        float o[8];
+        if (dres) Vec8<T>::load(dres + base + (size_t)v * 8, o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float t = rstd * (g[j][i] - s1 - xh[j][i] * s2);
+          o[i] = dres ? o[i] + t : t;
+        }
+        Vec8<T>::store(dh + base + (size_t)v * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NORM_MAXV; ++j) {
+    const int v = threadIdx.x + j * NORM_THREADS;
+    if (v < nv) {
+      Vec8<float>::store(part_dw + (size_t)blockIdx.x * cols + (size_t)v * 8, aw[j]);
+      if (kLayer && part_db) Vec8<float>::store(part_db + (size_t)blockIdx.x * cols + (size_t)v * 8, ab[j]);
+    }
+  }
+}
+
+// out[c] = sum_p part[p][c], cast to T.  One thread per column, coalesced over columns.
+template <typename T>
+__global__ void colreduce_kernel(const float* __restrict__ part, T* __restrict__ out, int nparts, int cols, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += part[(size_t)p * cols + c];
+  if (accumulate) s += ZenVal<T>::to_f(out[c]);
+  out[c] = ZenVal<T>::from_f(s);
+}
+
+// Column sums of a [rows, cols] matrix into part[gridDim.y][cols] (bias gradients).
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_partial_kernel(const T* __restrict__ a, float* __restrict__ part, int rows, int cols) {
+  const int c8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c8 >= cols) return;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+    float v[8];
+    Vec8<T>::load(a + (size_t)r * cols + c8, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += v[i];
+  }
+  Vec8<float>::store(part + (size_t)blockIdx.y * cols + c8, acc);
+}
+
+// --------------------------------------------------------------------------------------------
+// Activations.  mode: 0 gelu(tanh) 1 relu 2 silu(a)*b 3 gelu_tanh(a)*b
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float k = 0.7978845608028654f;
+  const float t = tanhf(k * (x + 0.044715f * x * x * x));
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x * x);
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// a and b may be the two halves of one [rows, 2 * inner] matrix (strided) or separate tensors.
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int rows, int inner, int lda,
+               int ldb, int mode) {
+  const size_t nvec = (size_t)rows * (inner / 8);
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(v / (inner / 8)), c = (int)(v % (inner / 8)) * 8;
+    float x[8], y[8], o[8];
+    Vec8<T>::load(a + (size_t)r * lda + c, x);
+    if (mode >= 2) Vec8<T>::load(b + (size_t)r * ldb + c, y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (mode == 0) o[i] = gelu_tanh(x[i]);
+      else if (mode == 1) o[i] = fmaxf(x[i], 0.f);
+      else if (mode == 2) o[i] = x[i] * sigmoidf_(x[i]) * y[i];
+      else o[i] = gelu_tanh(x[i]) * y[i];
+    }
+    Vec8<T>::store(out + (size_t)r * inner + c, o);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_bwd_kernel(const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ dout, T* __restrict__ da,
+               T* __restrict__ db, int rows, int inner, int lda, int ldb, int mode) {
+  const size_t nvec = (size_t)rows * (inner / 8);
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(v / (inner / 8)), c = (int)(v % (inner / 8)) * 8;
+    float x[8], y[8], g[8], ga[8], gb[8];
+    Vec8<T>::load(a + (size_t)r * lda + c, x);
+    Vec8<T>::load(dout + (size_t)r * inner + c, g);
+    if (mode >= 2) Vec8<T>::load(b + (size_t)r * ldb + c, y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (mode == 0) ga[i] = g[i] * gelu_tanh_grad(x[i]);
+      else if (mode == 1) ga[i] = x[i] > 0.f ? g[i] : 0.f;
+      else if (mode == 2) {
+        const float s = sigmoidf_(x[i]);
+        ga[i] = g[i] * y[i] * s * (1.f + x[i] * (1.f - s));
+        gb[i] = g[i] * x[i] * s;
+      } else {
+        ga[i] = g[i] * y[i] * gelu_tanh_grad(x[i]);
+        gb[i] = g[i] * gelu_tanh(x[i]);
+      }
+    }
+    Vec8<T>::store(da + (size_t)r * lda + c, ga);
+    if (mode >= 2) Vec8<T>::store(db + (size_t)r * ldb + c, gb);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// RoPE (rotate-half convention): x is [tokens, heads, hd] with row stride `ld` elements between
+// tokens; token t sits at position pos0 + t % seq.  sign = -1 applies the inverse rotation
+// (the backward pass).  In place.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kernel(T* __restrict__ x, int tokens, int heads, int hd, int ld, int seq, int pos0, float log2_theta, float sign) {
+  const int half = hd / 2;
+  const size_t n = (size_t)tokens * heads * half;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int j = (int)(i % half);
+    const int hh = (int)((i / half) % heads);
+    const int t = (int)(i / ((size_t)half * heads));
+    const float inv_freq = exp2f(-log2_theta * (2.f * j / hd));
+    float s, c;
+    sincosf((float)(pos0 + t % seq) * inv_freq, &s, &c);
+    s *= sign;
+    T* p = x + (size_t)t * ld + (size_t)hh * hd;
+    const float a = ZenVal<T>::to_f(p[j]), b = ZenVal<T>::to_f(p[j + half]);
+    p[j] = ZenVal<T>::from_f(a * c - b * s);
+    p[j + half] = ZenVal<T>::from_f(b * c + a * s);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Embedding forward: out[t] = wte[ids[t]] * scale (+ wpe[pos_offset + t % seq]).
+template <typename T>
+__global__ void __launch_bounds__(128)
+embedding_fwd_kernel(const int64_t* __restrict__ ids, const T* __restrict__ wte, const T* __restrict__ wpe,
+                     T* __restrict__ out, int tokens, int d, int seq, int pos_offset, float scale, int vocab) {
+  for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
+    int64_t id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+      float v[8];
+      Vec8<T>::load(wte + (size_t)id * d + c, v);
+      if (scale != 1.f) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = ZenVal<T>::to_f(ZenVal<T>::from_f(v[i] * scale));
+      }
+      if (wpe) {
+        float p[8];
+        Vec8<T>::load(wpe + (size_t)(pos_offset + t % seq) * d + c, p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += p[i];
+      }
+      Vec8<T>::store(out + (size_t)t * d + c, v);
+    }
+  }
+}
+
+// Row-sparse embedding backward, three kernels:
+//   mark    : flag[id] = 1 for every token id
+//   compact : single-CTA scan over flag[V]: cid[row] = rank among touched rows, rows[] ascending, *count
+//   accum   : acc[cid[id]][:] += dy[t][:] * scale   (fp32 atomics into a [U, d] scratch)
+__global__ void embed_mark_kernel(const int64_t* __restrict__ ids, int32_t* __restrict__ flag, int tokens, int vocab) {
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < tokens; t += gridDim.x * blockDim.x) {
+    const int64_t id = ids[t];
+    if (id >= 0 && id < vocab) flag[id] = 1;
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+embed_compact_kernel(int32_t* __restrict__ flag_cid, int32_t* __restrict__ rows, int32_t* __restrict__ count, int vocab) {
+  __shared__ uint32_t part[1024];
+  const int per = (vocab + 1023) / 1024;
+  const int b = threadIdx.x * per, e = min(vocab, b + per);
+  uint32_t s = 0;
+  for (int i = b; i < e; ++i) s += flag_cid[i] != 0;
+  part[threadIdx.x] = s;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {
+    uint32_t t = (threadIdx.x >= (unsigned)d) ? part[threadIdx.x - d] : 0u;
+    __syncthreads();
+    part[threadIdx.x] += t;
+    __syncthreads();
+  }
+  uint32_t run = part[threadIdx.x] - s;
+  for (int i = b; i < e; ++i) {
+    if (flag_cid[i] != 0) { flag_cid[i] = (int32_t)run; rows[run] = i; ++run; } else flag_cid[i] = -1;
+  }
+  if (threadIdx.x == 1023) *count = (int32_t)part[1023];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+embed_accum_kernel(const int64_t* __restrict__ ids, const int32_t* __restrict__ cid, const T* __restrict__ dy,
+                   float* __restrict__ acc, int tokens, int d, int vocab, float scale) {
+  for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
+    const int64_t id = ids[t];
+    if (id < 0 || id >= vocab) continue;
+    const int u = cid[id];
+    if (u < 0) continue;
+    for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+      float v[8];
+      Vec8<T>::load(dy + (size_t)t * d + c, v);
+      float* a = acc + (size_t)u * d + c;
+      atomicAdd(reinterpret_cast<float4*>(a), make_float4(v[0] * scale, v[1] * scale, v[2] * scale, v[3] * scale));
+      atomicAdd(reinterpret_cast<float4*>(a + 4), make_float4(v[4] * scale, v[5] * scale, v[6] * scale, v[7] * scale));
+    }
+  }
+}
+
+// vals[u][:] = T(acc[u][:]) for u < *count, and reset acc, cid (through rows) for the next call.
+template <typename T>
+__global__ void __launch_bounds__(128)
+embed_finish_kernel(float* __restrict__ acc, int32_t* __restrict__ flag_cid, const int32_t* __restrict__ rows,
+                    const int32_t* __restrict__ count, T* __restrict__ vals, int d) {
+  const int n = *count;
+  for (int u = blockIdx.x; u < n; u += gridDim.x) {
+    for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+      float v[8];
+      Vec8<float>::load(acc + (size_t)u * d + c, v);
+      Vec8<T>::store(vals + (size_t)u * d + c, v);
+      const float z[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      Vec8<float>::store(acc + (size_t)u * d + c, z);
+    }
+  }
+}
+__global__ void embed_clear_flags_kernel(int32_t* __restrict__ flag_cid, int vocab) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) flag_cid[i] = 0;
+}
+
+// grad[rows[u]][:] += vals[u][:] for u < *count (rows unique): applies a row-sparse gradient to a dense one.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rows_add_kernel(T* __restrict__ grad, const int32_t* __restrict__ rows, const int32_t* __restrict__ count,
+                const T* __restrict__ vals, int d, int vocab, int max_rows) {
+  const int n = min(*count, max_rows);
+  for (int u = blockIdx.x; u < n; u += gridDim.x) {
+    const int r = rows[u];
+    if (r < 0 || r >= vocab) continue;
+    for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+      float a[8], b[8];
+      Vec8<T>::load(grad + (size_t)r * d + c, a);
+      Vec8<T>::load(vals + (size_t)u * d + c, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[i] += b[i];
+      Vec8<T>::store(grad + (size_t)r * d + c, a);
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Cross-entropy over [rows, vocab] logits.  One CTA per row, two passes: online max / sum-exp, then
+// dlogits = (softmax - onehot) * gscale written in place (or to `dlogits`).  loss[row] = lse - logit[label];
+// rows with label == ignore give loss 0 and zero gradient.  `ld` = row stride in elements.
+template <typename T>
+__global__ void __launch_bounds__(512)
+xent_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels, float* __restrict__ loss,
+            T* __restrict__ dlogits, int rows, int vocab, int ld, float gscale, int64_t ignore_index) {
+  __shared__ float sh[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* lp = logits + (size_t)row * ld;
+    T* dp = dlogits ? dlogits + (size_t)row * ld : nullptr;
+    const int64_t label = labels[row];
+    const bool valid = label != ignore_index && label >= 0 && label < vocab;
+    float m = -INFINITY, s = 0.f;
+    const int nv = vocab / 8;                       // vector body; tail handled scalar
+    const bool vec_ok = (ld % 8 == 0);
+    if (vec_ok) {
+      for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+        float x[8];
+        Vec8<T>::load(lp + (size_t)v * 8, x);
+        float mx = x[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) mx = fmaxf(mx, x[i]);
+        const float nm = fmaxf(m, mx);
+        float add = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) add += __expf(x[i] - nm);
+        s = s * __expf(m - nm) + add;
+        m = nm;
+      }
+    }
+    for (int c = (vec_ok ? nv * 8 : 0) + threadIdx.x; c < vocab; c += blockDim.x) {
+      const float x = ZenVal<T>::to_f(lp[c]);
+      const float nm = fmaxf(m, x);
+      s = s * __expf(m - nm) + __expf(x - nm);
+      m = nm;
+    }
+    const float gm = block_max(m, sh);
+    s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+    const float gs = block_sum(s, sh);
+    const float lse = gm + logf(gs);
+    if (threadIdx.x == 0) loss[row] = valid ? lse - ZenVal<T>::to_f(lp[label]) : 0.f;
+    if (dp) {
+      const float sc = valid ? gscale : 0.f;
+      if (vec_ok) {
+        for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+          float x[8];
+          Vec8<T>::load(lp + (size_t)v * 8, x);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float p = __expf(x[i] - lse);
+            if (v * 8 + i == label) p -= 1.f;
+            x[i] = p * sc;
+          }
+          Vec8<T>::store(dp + (size_t)v * 8, x);
+        }
+      }
+      for (int c = (vec_ok ? nv * 8 : 0) + threadIdx.x; c < vocab; c += blockDim.x) {
+        float p = __expf(ZenVal<T>::to_f(lp[c]) - lse);
+        if (c == label) p -= 1.f;
+        dp[c] = ZenVal<T>::from_f(p * sc);
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Multi-tensor AdamW.  One table entry per tensor; CTAs walk a flat list of 64K-element chunks.
+struct AdamTensor {
+  void* param;       // T (bf16 / fp32) weights used by the model
+  float* master;     // optional fp32 master copy (null when param is fp32)
+  const void* grad;  // T gradient
+  float* m;
+  float* v;
+  uint64_t numel;
+  uint64_t chunk0;   // index of this tensor's first chunk
+  float wd;          // weight decay for this tensor
+  float pad;
+};
+#define ADAM_CHUNK 65536
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+adamw_kernel(const AdamTensor* __restrict__ tab, int ntensors, const int32_t* __restrict__ chunk_tensor,
+             uint64_t nchunks, float lr, float b1, float b2, float eps, float bc1, float bc2, float gscale) {
+  for (uint64_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
+    const AdamTensor t = tab[chunk_tensor[ch]];
+    const uint64_t start = (ch - t.chunk0) * ADAM_CHUNK;
+    const uint64_t end = min(t.numel, start + ADAM_CHUNK);
+    T* p = reinterpret_cast<T*>(t.param);
+    const T* g = reinterpret_cast<const T*>(t.grad);
+    const float decay = 1.f - lr * t.wd;
+    for (uint64_t i = start + (uint64_t)threadIdx.x * 8; i < end; i += 256 * 8) {
+      if (i + 8 <= end) {
+        float pv[8], gv[8], mv[8], vv[8];
+        if (t.master) Vec8<float>::load(t.master + i, pv); else Vec8<T>::load(p + i, pv);
+        Vec8<T>::load(g + i, gv);
+        Vec8<float>::load(t.m + i, mv);
+        Vec8<float>::load(t.v + i, vv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float gg = gv[k] * gscale;
+          mv[k] = b1 * mv[k] + (1.f - b1) * gg;
+          vv[k] = b2 * vv[k] + (1.f - b2) * gg * gg;
+          const float den = __fsqrt_rn(vv[k] / bc2) + eps;
+          pv[k] = pv[k] * decay - lr * __fdiv_rn(mv[k] / bc1, den);
+        }
+        Vec8<float>::store(t.m + i, mv);
+        Vec8<float>::store(t.v + i, vv);
+        if (t.master) Vec8<float>::store(t.master + i, pv);
+        Vec8<T>::store(p + i, pv);
+      } else {
+        for (uint64_t k = i; k < end; ++k) {
+          float pv = t.master ? t.master[k] : ZenVal<T>::to_f(p[k]);
+          const float gg = ZenVal<T>::to_f(g[k]) * gscale;
+          const float mm = b1 * t.m[k] + (1.f - b1) * gg;
+          const float vv = b2 * t.v[k] + (1.f - b2) * gg * gg;
+          pv = pv * decay - lr * __fdiv_rn(mm / bc1, __fsqrt_rn(vv / bc2) + eps);
+          t.m[k] = mm; t.v[k] = vv;
+          if (t.master) t.master[k] = pv;
+          p[k] = ZenVal<T>::from_f(pv);
+        }
+      }
+    }
+  }
+}
+
+int sm_count_e() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+inline int cap_grid(size_t want, int mult) {
+  size_t mx = (size_t)sm_count_e() * mult;
+  return (int)(want < 1 ? 1 : (want > mx ? mx : want));
+}
+
+}  // namespace
+
+#define DISPATCH_T(dtype, ...)                                             \
+  switch (dtype) {                                                         \
+    case ZEN_DTYPE_F32: { using T = float; __VA_ARGS__; } break;           \
+    case ZEN_DTYPE_BF16: { using T = __nv_bfloat16; __VA_ARGS__; } break;  \
+    case ZEN_DTYPE_F16: { using T = __half; __VA_ARGS__; } break;          \
+    default: return -1;                                                    \
+  }
+
+extern "C" {
+
+// Number of per-CTA partial rows the norm backward writes (the caller sizes its scratch with this).
+int zen_norm_bwd_parts(int rows) { return cap_grid((size_t)rows, 4); }
+
+int zen_norm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* hout, float* rstd,
+                 float* mean, int rows, int cols, float eps, int layer, int unit_offset, int dtype, void* stream) {
+  if (cols % 8 || cols > NORM_THREADS * NORM_MAXV * 8) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = cap_grid((size_t)rows, 16);
+  DISPATCH_T(dtype, {
+    if (layer) norm_fwd_kernel<T, true><<<grid, NORM_THREADS, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b, (T*)y, (T*)hout, rstd, mean, rows, cols, eps, unit_offset);
+    else norm_fwd_kernel<T, false><<<grid, NORM_THREADS, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b, (T*)y, (T*)hout, rstd, mean, rows, cols, eps, unit_offset);
+  });
+  return (int)cudaGetLastError();
+}
+
+// part_dw / part_db: fp32 scratch of zen_norm_bwd_parts(rows) * cols each.  dw / db are written (or
+// accumulated into when accumulate != 0) in dtype.
+int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const float* mean, const void* dres,
+                 void* dh, float* part_dw, float* part_db, void* dw, void* db, int rows, int cols, int layer,
+                 int unit_offset, int accumulate, int dtype, void* stream) {
+  if (cols % 8 || cols > NORM_THREADS * NORM_MAXV * 8) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = zen_norm_bwd_parts(rows);
+  DISPATCH_T(dtype, {
+    if (layer) norm_bwd_kernel<T, true><<<grid, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+    else norm_bwd_kernel<T, false><<<grid, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+    colreduce_kernel<T><<<(cols + 127) / 128, 128, 0, st>>>(part_dw, (T*)dw, grid, cols, accumulate);
+    if (layer && db) colreduce_kernel<T><<<(cols + 127) / 128, 128, 0, st>>>(part_db, (T*)db, grid, cols, accumulate);
+  });
+  return (int)cudaGetLastError();
+}
+
+int zen_colsum_parts(int rows) { int p = rows / 64; return p < 1 ? 1 : (p > 64 ? 64 : p); }
+
+// out[c] (+)= sum_r a[r][c]; part: fp32 scratch zen_colsum_parts(rows) * cols.
+int zen_colsum(const void* a, float* part, void* out, int rows, int cols, int accumulate, int dtype, void* stream) {
+  if (cols % 8) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int parts = zen_colsum_parts(rows);
+  dim3 grid((cols / 8 + 255) / 256, parts);
+  DISPATCH_T(dtype, {
+    colsum_partial_kernel<T><<<grid, 256, 0, st>>>((const T*)a, part, rows, cols);
+    colreduce_kernel<T><<<(cols + 127) / 128, 128, 0, st>>>(part, (T*)out, parts, cols, accumulate);
+  });
+  return (int)cudaGetLastError();
+}
+
+int zen_act_fwd(const void* a, const void* b, void* out, int rows, int inner, int lda, int ldb, int mode, int dtype,
+                void* stream) {
+  if (inner % 8 || lda % 8 || ldb % 8) return -2;
+  const int grid = cap_grid(((size_t)rows * (inner / 8) + 255) / 256, 16);
+  DISPATCH_T(dtype, act_fwd_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)a, (const T*)b, (T*)out, rows, inner, lda, ldb, mode));
+  return (int)cudaGetLastError();
+}
+
+int zen_act_bwd(const void* a, const void* b, const void* dout, void* da, void* db, int rows, int inner, int lda,
+                int ldb, int mode, int dtype, void* stream) {
+  if (inner % 8 || lda % 8 || ldb % 8) return -2;
+  const int grid = cap_grid(((size_t)rows * (inner / 8) + 255) / 256, 16);
+  DISPATCH_T(dtype, act_bwd_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)a, (const T*)b, (const T*)dout, (T*)da, (T*)db, rows, inner, lda, ldb, mode));
+  return (int)cudaGetLastError();
+}
+
+int zen_rope(void* x, int tokens, int heads, int hd, int ld, int seq, int pos0, float theta, int inverse, int dtype,
+             void* stream) {
+  if (hd % 2) return -2;
+  const size_t n = (size_t)tokens * heads * (hd / 2);
+  const int grid = cap_grid((n + 255) / 256, 16);
+  DISPATCH_T(dtype, rope_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((T*)x, tokens, heads, hd, ld, seq, pos0, log2f(theta), inverse ? -1.f : 1.f));
+  return (int)cudaGetLastError();
+}
+
+int zen_embedding_fwd(const int64_t* ids, const void* wte, const void* wpe, void* out, int tokens, int d, int seq,
+                      int pos_offset, float scale, int vocab, int dtype, void* stream) {
+  if (d % 8) return -2;
+  DISPATCH_T(dtype, embedding_fwd_kernel<T><<<cap_grid((size_t)tokens, 32), 128, 0, (cudaStream_t)stream>>>(ids, (const T*)wte, (const T*)wpe, (T*)out, tokens, d, seq, pos_offset, scale, vocab));
+  return (int)cudaGetLastError();
+}
+
+// Row-sparse embedding backward.  Scratch owned by the caller and zero on entry (this call leaves it
+// zero again): flag_cid int32[vocab], acc fp32[max_rows][d].  Outputs: rows int32[max_rows] (ascending
+// unique ids), count int32[1], vals T[max_rows][d].  max_rows >= min(tokens, vocab).
+int zen_embedding_bwd_rows(const int64_t* ids, const void* dy, int32_t* flag_cid, float* acc, int32_t* rows,
+                           int32_t* count, void* vals, int tokens, int d, int vocab, float scale, int dtype,
+                           void* stream) {
+  if (d % 8) return -2;
+  cudaStream_t st = (cudaStream_t)stream;
+  embed_mark_kernel<<<cap_grid(((size_t)tokens + 255) / 256, 8), 256, 0, st>>>(ids, flag_cid, tokens, vocab);
+  embed_compact_kernel<<<1, 1024, 0, st>>>(flag_cid, rows, count, vocab);
+  DISPATCH_T(dtype, {
+    embed_accum_kernel<T><<<cap_grid((size_t)tokens, 32), 128, 0, st>>>(ids, flag_cid, (const T*)dy, acc, tokens, d, vocab, scale);
+    embed_finish_kernel<T><<<cap_grid((size_t)(tokens < vocab ? tokens : vocab), 32), 128, 0, st>>>(acc, flag_cid, rows, count, (T*)vals, d);
+  });
+  embed_clear_flags_kernel<<<cap_grid(((size_t)vocab + 255) / 256, 8), 256, 0, st>>>(flag_cid, vocab);
+  return (int)cudaGetLastError();
+}
+
+int zen_rows_add(void* grad, const int32_t* rows, const int32_t* count, const void* vals, int d, int vocab,
+                 int max_rows, int dtype, void* stream) {
+  if (d % 8) return -2;
+  DISPATCH_T(dtype, rows_add_kernel<T><<<cap_grid((size_t)max_rows, 32), 128, 0, (cudaStream_t)stream>>>((T*)grad, rows, count, (const T*)vals, d, vocab, max_rows));
+  return (int)cudaGetLastError();
+}
+
+int zen_xent(const void* logits, const int64_t* labels, float* loss, void* dlogits, int rows, int vocab, int ld,
+             float gscale, int64_t ignore_index, int dtype, void* stream) {
+  DISPATCH_T(dtype, xent_kernel<T><<<cap_grid((size_t)rows, 8), 512, 0, (cudaStream_t)stream>>>((const T*)logits, labels, loss, (T*)dlogits, rows, vocab, ld, gscale, ignore_index));
+  return (int)cudaGetLastError();
+}
+
+int zen_adam_tensor_size() { return (int)sizeof(AdamTensor); }
+
+int zen_adamw(const void* table, int ntensors, const int32_t* chunk_tensor, uint64_t nchunks, float lr, float b1,
+              float b2, float eps, float bc1, float bc2, float gscale, int dtype, void* stream) {
+  const int grid = cap_grid((size_t)nchunks, 8);
+  DISPATCH_T(dtype, adamw_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const AdamTensor*)table, ntensors, chunk_tensor, nchunks, lr, b1, b2, eps, bc1, bc2, gscale));
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -48,54 +48,77 @@ struct ZenSparseCtx {
   ZenPerm perm;
 };
 
-#define K1_THREADS 512
-#define K1_WARPS 16
+#define K1_THREADS 256
+#define K1_WARPS 8
 #define K1_U 4
 #define K1_QCAP 1024
 #define K1_FLUSH_MIN 256
 
-template <typename T>
-__device__ __forceinline__ void load8(const T* g, uint64_t e0, uint64_t n, bool aligned, float (&v)[8]);
-
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* g, uint64_t e0, uint64_t n, bool aligned,
-                                                     float (&v)[8]) {
-  if (aligned && e0 + 8 <= n) {
-    uint4 r = __ldg(reinterpret_cast<const uint4*>(g + e0));
-    uint32_t w[4] = {r.x, r.y, r.z, r.w};
+// Eight consecutive elements as raw bits: one 16-byte vector for 16-bit types, two for fp32.
+template <typename T> struct Raw8;
+template <> struct Raw8<float> {
+  uint32_t w[8];
+  __device__ __forceinline__ void load(const float* g, uint64_t e0, uint64_t n, bool aligned) {
+    if (aligned && e0 + 8 <= n) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(g + e0)), b = __ldg(reinterpret_cast<const uint4*>(g + e0 + 4));
+      w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      for (int i = 0; i < 8; ++i) w[i] = (e0 + i < n) ? __float_as_uint(g[e0 + i]) : 0u;
     }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = (e0 + i < n) ? __bfloat162float(g[e0 + i]) : 0.f;
   }
-}
-template <>
-__device__ __forceinline__ void load8<__half>(const __half* g, uint64_t e0, uint64_t n, bool aligned, float (&v)[8]) {
+  __device__ __forceinline__ void zero() {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = (e0 + i < n) ? __half2float(g[e0 + i]) : 0.f;
-}
-template <>
-__device__ __forceinline__ void load8<float>(const float* g, uint64_t e0, uint64_t n, bool aligned, float (&v)[8]) {
-  if (aligned && e0 + 8 <= n) {
-    float4 a = __ldg(reinterpret_cast<const float4*>(g + e0));
-    float4 b = __ldg(reinterpret_cast<const float4*>(g + e0 + 4));
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = (e0 + i < n) ? g[e0 + i] : 0.f;
+    for (int i = 0; i < 8; ++i) w[i] = 0u;
   }
-}
+  __device__ __forceinline__ bool any() const { return ((w[0] | w[1] | w[2] | w[3] | w[4] | w[5] | w[6] | w[7]) & 0x7fffffffu) != 0u; }
+  // select chains instead of dynamic indexing keep the vector in registers
+  __device__ __forceinline__ uint32_t bits(int i) const {
+    const uint32_t a = (i & 1) ? w[1] : w[0], b = (i & 1) ? w[3] : w[2], c = (i & 1) ? w[5] : w[4], d = (i & 1) ? w[7] : w[6];
+    const uint32_t ab = (i & 2) ? b : a, cd = (i & 2) ? d : c;
+    return (i & 4) ? cd : ab;
+  }
+  __device__ __forceinline__ float value(int i) const { return __uint_as_float(bits(i)); }
+  __device__ __forceinline__ bool nonzero(int i) const { return (bits(i) & 0x7fffffffu) != 0u; }
+};
+template <typename T16> struct Raw8Half {
+  uint32_t w[4];
+  __device__ __forceinline__ void load(const T16* g, uint64_t e0, uint64_t n, bool aligned) {
+    if (aligned && e0 + 8 <= n) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(g + e0));
+      w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    } else {
+      const unsigned short* gs = reinterpret_cast<const unsigned short*>(g);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = (e0 + 2 * i < n) ? gs[e0 + 2 * i] : 0u, hi = (e0 + 2 * i + 1 < n) ? gs[e0 + 2 * i + 1] : 0u;
+        w[i] = lo | (hi << 16);
+      }
+    }
+  }
+  __device__ __forceinline__ void zero() { w[0] = w[1] = w[2] = w[3] = 0u; }
+  __device__ __forceinline__ bool any() const { return ((w[0] | w[1] | w[2] | w[3]) & 0x7fff7fffu) != 0u; }
+  __device__ __forceinline__ uint32_t bits(int i) const {
+    const uint32_t a = (i & 2) ? w[1] : w[0], b = (i & 2) ? w[3] : w[2];
+    return (((i & 4) ? b : a) >> ((i & 1) * 16)) & 0xffffu;
+  }
+  __device__ __forceinline__ bool nonzero(int i) const { return (bits(i) & 0x7fffu) != 0u; }
+};
+template <> struct Raw8<__nv_bfloat16> : Raw8Half<__nv_bfloat16> {
+  __device__ __forceinline__ float value(int i) const { return __uint_as_float(bits(i) << 16); }
+};
+template <> struct Raw8<__half> : Raw8Half<__half> {
+  __device__ __forceinline__ float value(int i) const { return __half2float(__ushort_as_half((unsigned short)bits(i))); }
+};
 
 // ---------------------------------------------------------------------------------------------
-// K1: partition + compact + push.  kBroadcast = true is the method-1 variant: one queue of
-// (global index, value) records pushed to every peer.
+// K1: partition + compact + push.  Every lane owns 8 consecutive elements (all in one 64-element
+// block, hence one owner); a lane with nonzeros reserves room in its owner's shared-memory queue
+// with one atomic and writes its records there.  Warp w drains queue w to the owner's receive
+// region in runs of at least K1_FLUSH_MIN records.  kBroadcast = true is the method-1 variant: one
+// queue of (global index, value) records pushed to every peer.
 template <typename T, bool kBroadcast>
-__global__ void __launch_bounds__(K1_THREADS, 1)
+__global__ void __launch_bounds__(K1_THREADS, 2)
 zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const float* __restrict__ thr_ptr,
                           int aligned) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -106,8 +129,8 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
   __shared__ uint32_t s_last;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int sub = lane & 7;                                           // lane within its 64-element group
-  const float thr = thr_ptr ? *thr_ptr : 0.f;
+  const bool use_thr = thr_ptr != nullptr;
+  const float thr = use_thr ? *thr_ptr : 0.f;
   const uint64_t N = c.numel;
   const uint64_t nwi = (N + 255) / 256;                               // warp-iterations of 256 elements
   const uint64_t ncta_it = (nwi + K1_WARPS * K1_U - 1) / (K1_WARPS * K1_U);
@@ -117,80 +140,55 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
   __syncthreads();
 
   for (uint64_t it = blockIdx.x; it < ncta_it; it += gridDim.x) {
-    float v[K1_U][8];
+    Raw8<T> v[K1_U];
 #pragma unroll
     for (int u = 0; u < K1_U; ++u) {
-      const uint64_t wi = it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp;
-      const uint64_t e0 = wi * 256 + (uint64_t)lane * 8;
-      if (e0 < N) load8<T>(g, e0, N, aligned != 0, v[u]);
-      else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
-      }
+      const uint64_t e0 = (it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp) * 256 + (uint64_t)lane * 8;
+      if (e0 < N) v[u].load(g, e0, N, aligned != 0); else v[u].zero();
     }
 #pragma unroll
     for (int u = 0; u < K1_U; ++u) {
-      const uint64_t wi = it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp;
-      const uint64_t e0 = wi * 256 + (uint64_t)lane * 8;
+      if (!v[u].any()) continue;
       uint32_t m = 0;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float a = fabsf(v[u][i]);
-        if (a != 0.f && a >= thr) m |= 1u << i;                      // NaN fails both tests: dropped
+        bool keep = v[u].nonzero(i);
+        if (use_thr) keep = keep && (fabsf(v[u].value(i)) >= thr);
+        m |= keep ? (1u << i) : 0u;
+      }
+      if (!m) continue;
+      const uint32_t e32 = (uint32_t)((it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp) * 256) + lane * 8;
+      uint32_t owner = 0, slot0 = e32;
+      if (!kBroadcast) {
+        const uint32_t pb = zen_perm_fwd(c.perm, e32 >> c.perm.lg);
+        owner = zen_owner_of(c.perm, pb, c.nranks);
+        slot0 = ((pb - owner * c.perm.sb) << c.perm.lg) + (e32 & (c.perm.block - 1u));
       }
       const uint32_t cnt = __popc(m);
-      uint32_t incl = cnt;                                            // inclusive prefix over the 8-lane group
-#pragma unroll
-      for (int d = 1; d < 8; d <<= 1) {
-        uint32_t t = __shfl_up_sync(0xffffffffu, incl, d, 8);
-        if (sub >= d) incl += t;
+      uint32_t k = atomicAdd(&qn[owner], cnt);
+      bool direct = false;
+      if (k + cnt > K1_QCAP) {
+        if (k <= K1_QCAP) qvalid[owner] = k;                          // exactly one lane per overflow sees this
+        direct = true;
+        k = atomicAdd(&c.cursors[owner], cnt);                        // reserve directly in the destination
       }
-      const uint32_t total = __shfl_sync(0xffffffffu, incl, 7, 8);
-      uint32_t owner = 0, slotbase = 0, pos = 0, direct = 0;
-      if (sub == 0 && total > 0) {
-        const uint64_t eg = e0;                                       // first element of this group
-        if (kBroadcast) {
-          owner = 0;
-          slotbase = (uint32_t)eg;
-        } else {
-          const uint32_t blk = (uint32_t)(eg / c.perm.block);
-          const uint32_t pb = zen_perm_fwd(c.perm, blk);
-          owner = pb / c.perm.sb;
-          slotbase = (pb % c.perm.sb) * c.perm.block + (uint32_t)(eg % c.perm.block);
-        }
-        pos = atomicAdd(&qn[owner], total);
-        if (pos + total > K1_QCAP) {
-          if (pos <= K1_QCAP) qvalid[owner] = pos;                    // exactly one group per overflow sees this
-          direct = 1;
-          pos = atomicAdd(&c.cursors[owner], total);                  // reserve directly in the destination
-        }
-      }
-      owner = __shfl_sync(0xffffffffu, owner, 0, 8);
-      slotbase = __shfl_sync(0xffffffffu, slotbase, 0, 8);
-      pos = __shfl_sync(0xffffffffu, pos, 0, 8);
-      direct = __shfl_sync(0xffffffffu, direct, 0, 8);
-      if (cnt) {
-        uint32_t k = pos + incl - cnt;
-        const uint32_t s0 = slotbase + sub * 8;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if (m & (1u << i)) {
-            const uint2 rec = make_uint2(s0 + i, ZenVal<T>::bits(ZenVal<T>::from_f(v[u][i])));
-            if (!direct) {
-              q[owner * K1_QCAP + k] = rec;
-            } else if (k < c.cap_rec) {
-              if (kBroadcast) {
-                for (int p = 0; p < c.nranks; ++p)
-                  reinterpret_cast<uint2*>(c.sym[p] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
-              } else {
-                reinterpret_cast<uint2*>(c.sym[owner] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
-              }
-            } else {
-              local_status |= ZEN_REC_OVERFLOW;
-            }
-            ++k;
+      while (m) {
+        const int i = __ffs(m) - 1;
+        m &= m - 1;
+        const uint2 rec = make_uint2(slot0 + i, v[u].bits(i));
+        if (!direct) {
+          q[owner * K1_QCAP + k] = rec;
+        } else if (k < c.cap_rec) {
+          if (kBroadcast) {
+            for (int p = 0; p < c.nranks; ++p)
+              reinterpret_cast<uint2*>(c.sym[p] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
+          } else {
+            reinterpret_cast<uint2*>(c.sym[owner] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
           }
+        } else {
+          local_status |= ZEN_REC_OVERFLOW;
         }
+        ++k;
       }
     }
     __syncthreads();
@@ -198,13 +196,13 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
     const bool last_it = (it + gridDim.x >= ncta_it);
     if (warp < nq) {
       uint32_t n = qn[warp];
-      if (n > K1_QCAP) n = qvalid[warp];
-      const bool overflowed = qn[warp] > K1_QCAP;
+      const bool overflowed = n > K1_QCAP;
+      if (overflowed) n = qvalid[warp];
       if (n > 0 && (n >= K1_FLUSH_MIN || last_it || overflowed)) {
         uint32_t gbase = 0;
         if (lane == 0) gbase = atomicAdd(&c.cursors[warp], n);
         gbase = __shfl_sync(0xffffffffu, gbase, 0);
-        uint32_t fit = (gbase >= c.cap_rec) ? 0u : min(n, c.cap_rec - gbase);
+        const uint32_t fit = (gbase >= c.cap_rec) ? 0u : min(n, c.cap_rec - gbase);
         if (fit < n) local_status |= ZEN_REC_OVERFLOW;
         const uint2* src = q + warp * K1_QCAP;
         if (kBroadcast) {
@@ -362,24 +360,26 @@ zen_gather_push_kernel(const ZenSparseCtx c) {
       if (lane >= d) incl += t;
     }
     const uint32_t woff = incl - __popc(word);
-    if (!overflow) {
-      for (int j = 0; j < 32; ++j) {
-        const uint32_t wj = __shfl_sync(0xffffffffu, word, j);
-        if (wj == 0) continue;
-        const uint32_t oj = __shfl_sync(0xffffffffu, woff, j);
-        if ((wj >> lane) & 1u) {
-          const uint32_t slot = ch * 1024 + j * 32 + lane;
-          const uint32_t r = (coff - gbase) + oj + __popc(wj & ((1u << lane) - 1u));
-          const float a = c.acc[slot];
-          c.acc[slot] = 0.f;
-          s_val[mis_v + r] = ZenVal<T>::from_f(a);
-          s_idx[mis_i + r] = slot;
-        }
+    {
+      // phase A: every lane lists the set bits of its own word (shared memory only)
+      uint32_t w = word;
+      uint32_t r = (coff - gbase) + woff;
+      const uint32_t slot0 = ch * 1024 + lane * 32;
+      while (w) {
+        s_idx[mis_i + r] = slot0 + (uint32_t)(__ffs(w) - 1);
+        w &= w - 1;
+        ++r;
       }
-    } else {
-      for (int j = 0; j < 32; ++j) {                                     // still clear the accumulator
-        const uint32_t wj = __shfl_sync(0xffffffffu, word, j);
-        if ((wj >> lane) & 1u) c.acc[ch * 1024 + j * 32 + lane] = 0.f;
+    }
+    __syncthreads();
+    {
+      // phase B: the whole CTA fetches and clears the listed slots, independent loads in flight
+      const uint32_t n = gend - gbase;
+      for (uint32_t i = tid; i < n; i += blockDim.x) {
+        const uint32_t slot = s_idx[mis_i + i];
+        const float a = c.acc[slot];
+        c.acc[slot] = 0.f;
+        s_val[mis_v + i] = ZenVal<T>::from_f(a);
       }
     }
     __syncthreads();
@@ -490,12 +490,12 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
     if (lane < 16) {
       const uint32_t slot0 = ch * 1024 + lane * 64;
       if (slot0 < c.nslots) {
-        const uint32_t pb = o * c.perm.sb + slot0 / G;
+        const uint32_t pb = o * c.perm.sb + (slot0 >> c.perm.lg);
         const uint32_t blk = zen_perm_inv(c.perm, pb);
-        my_out = (uint64_t)blk * G + (slot0 % G);
+        my_out = ((uint64_t)blk << c.perm.lg) + (slot0 & (G - 1u));
       }
     }
-#pragma unroll 4
+#pragma unroll
     for (int jb = 0; jb < 16; ++jb) {
       const uint64_t obase = __shfl_sync(0xffffffffu, my_out, jb);
       const int wsel = 2 * jb + (lane >> 4);
@@ -525,21 +525,31 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 zen_densify_coo_kernel(const ZenSparseCtx c, T* __restrict__ out) {
+  __shared__ uint32_t s_n[ZEN_MAX_RANKS];
   const uint32_t G = c.perm.block;
-  for (int o = 0; o < c.nranks; ++o) {
-    const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_g_mail) + o;
+  if (threadIdx.x < c.nranks) {
+    const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_g_mail) + threadIdx.x;
+    uint32_t n = 0;
     // the bitmap pass of this call already waited for this epoch
-    if (zen_ld_acquire_sys(&mail->epoch) != c.epoch) continue;
-    if (((mail->info >> 8) & 0xffu) != ZEN_FMT_COO || (mail->info & 1u)) continue;
-    const uint32_t n = min(mail->count, min(c.cap_g, c.g_idx_words));
+    if (zen_ld_acquire_sys(&mail->epoch) == c.epoch) {
+      const uint32_t info = zen_ld_acquire_sys(&mail->info);
+      if (((info >> 8) & 0xffu) == ZEN_FMT_COO && !(info & 1u))
+        n = min(zen_ld_acquire_sys(&mail->count), min(c.cap_g, c.g_idx_words));
+    }
+    s_n[threadIdx.x] = n;
+  }
+  __syncthreads();
+  for (int o = 0; o < c.nranks; ++o) {
+    const uint32_t n = s_n[o];
+    if (n == 0) continue;
     const char* base = c.sym[c.rank];
     const uint32_t* gi = reinterpret_cast<const uint32_t*>(base + c.off_g_idx) + (uint64_t)o * c.g_idx_words;
     const T* gv = reinterpret_cast<const T*>(base + c.off_g_val + (uint64_t)o * c.cap_g * 4ull);
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
       const uint32_t slot = gi[i];
       if (slot >= c.nslots) continue;
-      const uint32_t blk = zen_perm_inv(c.perm, o * c.perm.sb + slot / G);
-      const uint64_t e = (uint64_t)blk * G + slot % G;
+      const uint32_t blk = zen_perm_inv(c.perm, o * c.perm.sb + (slot >> c.perm.lg));
+      const uint64_t e = ((uint64_t)blk << c.perm.lg) + (slot & (G - 1u));
       if (e < c.numel) out[e] = gv[i];
     }
   }
@@ -575,7 +585,7 @@ __global__ void __launch_bounds__(256)
 zen_owner_map_kernel(int32_t* __restrict__ out, uint64_t n, ZenPerm perm, int mode, uint32_t table, int parts) {
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
     if (mode == 0) {
-      out[i] = (int32_t)(zen_perm_fwd(perm, (uint32_t)(i / perm.block)) / perm.sb);
+      out[i] = (int32_t)zen_owner_of(perm, zen_perm_fwd(perm, (uint32_t)(i >> perm.lg)), parts);
     } else {
       const uint32_t per = table / parts;
       out[i] = (int32_t)((zen_poly3((uint32_t)i, 10001861u) % table) / per);
@@ -635,7 +645,7 @@ template <typename T>
 static int launch_partition(const ZenSparseCtx& c, const void* g, const float* thr, int broadcast, cudaStream_t st) {
   const uint64_t nwi = (c.numel + 255) / 256;
   const uint64_t nit = (nwi + K1_WARPS * K1_U - 1) / (K1_WARPS * K1_U);
-  const int grid = grid_for(nit, 1, sm_count() * 2);
+  const int grid = grid_for(nit, 1, sm_count() * 3);
   const int nq = broadcast ? 1 : c.nranks;
   const size_t smem = (size_t)nq * K1_QCAP * sizeof(uint2);
   const int aligned = (reinterpret_cast<uintptr_t>(g) % 16 == 0) ? 1 : 0;

@@ -38,18 +38,31 @@ struct ZenPerm {
   uint32_t block;      // G
   uint32_t nblocks;    // nb' = P * sb
   uint32_t sb;         // blocks per owner
-  uint32_t pad;
-  uint64_t mult;       // a
-  uint64_t mult_inv;   // a^-1 mod nb'
-  uint64_t add;        // c
+  uint32_t mask;       // 2^k - 1, 2^k >= nb'
+  uint32_t mult;       // a (odd)
+  uint32_t mult_inv;   // a^-1 mod 2^k
+  uint32_t add;        // c
+  uint32_t lg;         // log2(G); G is a power of two
 };
 
+// Affine bijection of [0, 2^k) restricted to [0, nb') by cycle walking.  The walk always ends (the
+// orbit of an in-range value returns in range); the cap only guards against bad parameters.
 __device__ __forceinline__ uint32_t zen_perm_fwd(const ZenPerm& p, uint32_t blk) {
-  return (uint32_t)((p.mult * (uint64_t)blk + p.add) % (uint64_t)p.nblocks);
+  uint32_t y = (p.mult * blk + p.add) & p.mask;
+  for (int i = 0; i < 64 && y >= p.nblocks; ++i) y = (p.mult * y + p.add) & p.mask;
+  return y;
 }
 __device__ __forceinline__ uint32_t zen_perm_inv(const ZenPerm& p, uint32_t pb) {
-  uint64_t t = ((uint64_t)pb + (uint64_t)p.nblocks - p.add % p.nblocks) % (uint64_t)p.nblocks;
-  return (uint32_t)((t * p.mult_inv) % (uint64_t)p.nblocks);
+  uint32_t y = (p.mult_inv * ((pb - p.add) & p.mask)) & p.mask;
+  for (int i = 0; i < 64 && y >= p.nblocks; ++i) y = (p.mult_inv * ((y - p.add) & p.mask)) & p.mask;
+  return y;
+}
+// owner = y / sb for y < P * sb with P <= 8, without a division.
+__device__ __forceinline__ uint32_t zen_owner_of(const ZenPerm& p, uint32_t y, int nranks) {
+  uint32_t o = 0, t = p.sb;
+#pragma unroll
+  for (int i = 1; i < ZEN_MAX_RANKS; ++i) { o += (i < nranks && y >= t) ? 1u : 0u; t += p.sb; }
+  return o;
 }
 
 __device__ __forceinline__ void zen_st_release_sys(uint32_t* p, uint32_t v) {

@@ -1,0 +1,213 @@
+"""Decoder-only language model on the framework's own ops.
+
+One implementation serves GPT-2, OPT, Llama and Gemma; ``ModelConfig`` selects norms, activations,
+positions, weight layout and biases.  Projections are stored fused (one qkv matrix, one gate|up
+matrix) because one wide GEMM beats three narrow ones; ``hf_state_dict`` / ``load_hf_state_dict``
+split and join them so that checkpoints carry HuggingFace parameter names and shapes.
+
+Pre-norm blocks; the residual add is fused into the following norm kernel, so a block passes on
+(branch output, residual stream) rather than their sum.  Tensor parallelism is Megatron-style 1-D:
+qkv / gate|up are column-parallel, attention-out / down are row-parallel, embeddings and the LM head
+are vocab-parallel.  The reference obtains models from ``AutoModelForCausalLM.from_config`` and
+tensor parallelism from ColossalAI's shardformer (train.py:117-123, 149-157).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from ..ops import autograd as O
+from .config import ModelConfig
+
+
+def _tp(group) -> tuple[int, int]:
+    if group is None:
+        return 0, 1
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: ModelConfig, tp_group=None, device=None, dtype=None):
+        super().__init__()
+        self.cfg, self.tp_group = cfg, tp_group
+        _, tp = _tp(tp_group)
+        d, hd = cfg.hidden_size, cfg.head_dim
+        assert cfg.num_heads % tp == 0 and (cfg.num_kv_heads % tp == 0 or cfg.num_kv_heads < tp)
+        self.hq = cfg.num_heads // tp
+        self.hkv = max(1, cfg.num_kv_heads // tp)         # MQA under TP replicates the single KV head
+        self.inner = cfg.intermediate_size // tp
+        kw = dict(device=device, dtype=dtype)
+        qkv_out = (self.hq + 2 * self.hkv) * hd
+        up_out = self.inner * (2 if cfg.gated else 1)
+
+        def w(i, o):
+            return nn.Parameter(torch.empty((i, o) if cfg.weight_layout == "in_out" else (o, i), **kw))
+
+        self.norm1_w = nn.Parameter(torch.empty(d, **kw))
+        self.norm2_w = nn.Parameter(torch.empty(d, **kw))
+        self.qkv_w, self.o_w = w(d, qkv_out), w(self.hq * hd, d)
+        self.up_w, self.down_w = w(d, up_out), w(self.inner, d)
+        if cfg.has_bias:
+            self.norm1_b = nn.Parameter(torch.empty(d, **kw))
+            self.norm2_b = nn.Parameter(torch.empty(d, **kw))
+            self.qkv_b = nn.Parameter(torch.empty(qkv_out, **kw))
+            self.o_b = nn.Parameter(torch.empty(d, **kw))
+            self.up_b = nn.Parameter(torch.empty(up_out, **kw))
+            self.down_b = nn.Parameter(torch.empty(d, **kw))
+        else:
+            self.norm1_b = self.norm2_b = self.qkv_b = self.o_b = self.up_b = self.down_b = None
+
+    def forward(self, x, res, bsz: int, seq: int):
+        cfg, g = self.cfg, self.tp_group
+        rank, tp = _tp(g)
+        y, h = O.fused_norm(x, res, self.norm1_w, self.norm1_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
+        y = O.copy_to_tp(y, g)
+        qkv = O.linear(y, self.qkv_w, self.qkv_b, cfg.weight_layout)
+        if not cfg.learned_positions:
+            qkv = O.rope_qkv(qkv, self.hq, self.hkv, cfg.head_dim, seq, cfg.rope_theta)
+        a = O.attention(qkv, bsz, seq, self.hq, self.hkv, cfg.head_dim)
+        # the bias of a row-parallel layer is added once, after the reduction
+        o = O.linear(a, self.o_w, self.o_b if tp == 1 else None, cfg.weight_layout)
+        o = O.reduce_from_tp(o, g)
+        if tp > 1 and self.o_b is not None:
+            o = o + self.o_b
+        y2, h2 = O.fused_norm(o, h, self.norm2_w, self.norm2_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
+        y2 = O.copy_to_tp(y2, g)
+        u = O.linear(y2, self.up_w, self.up_b, cfg.weight_layout)
+        m = O.activation(u, cfg.act)
+        dn = O.linear(m, self.down_w, self.down_b if tp == 1 else None, cfg.weight_layout)
+        dn = O.reduce_from_tp(dn, g)
+        if tp > 1 and self.down_b is not None:
+            dn = dn + self.down_b
+        return dn, h2
+
+
+class DecoderLM(nn.Module):
+    """Causal LM.  ``forward(input_ids, labels)`` returns the mean next-token loss."""
+
+    def __init__(self, cfg: ModelConfig, tp_group=None, device=None, dtype=torch.bfloat16, sparse_sink=None):
+        super().__init__()
+        self.cfg, self.tp_group = cfg, tp_group
+        rank, tp = _tp(tp_group)
+        kw = dict(device=device, dtype=dtype)
+        d = cfg.hidden_size
+        self.vocab_padded = (cfg.vocab_size + tp - 1) // tp * tp
+        self.vocab_local = self.vocab_padded // tp
+        self.vocab_start = rank * self.vocab_local
+        self.wte = nn.Parameter(torch.empty(self.vocab_local, d, **kw))
+        self.wpe = nn.Parameter(torch.empty(cfg.max_position + cfg.pos_offset, d, **kw)) if cfg.learned_positions else None
+        self.blocks = nn.ModuleList([Block(cfg, tp_group, device, dtype) for _ in range(cfg.num_layers)])
+        self.norm_f_w = nn.Parameter(torch.empty(d, **kw))
+        self.norm_f_b = nn.Parameter(torch.empty(d, **kw)) if cfg.has_bias else None
+        self.lm_head = None if cfg.tie_embeddings else nn.Parameter(torch.empty(self.vocab_local, d, **kw))
+        self.sparse_sink = sparse_sink          # receives the row-sparse lookup gradient of wte when set
+        self.reset_parameters()
+
+    @torch.no_grad()
+    def reset_parameters(self, seed: int | None = None):
+        cfg = self.cfg
+        gen = None
+        if seed is not None:
+            gen = torch.Generator(device=self.wte.device).manual_seed(seed)
+        for name, p in self.named_parameters():
+            if name.endswith("_b"):
+                p.zero_()
+            elif "norm" in name:
+                p.fill_(0.0 if cfg.norm_unit_offset else 1.0)
+            else:
+                p.normal_(0.0, cfg.init_std, generator=gen)
+
+    def head_weight(self):
+        return self.wte if self.lm_head is None else self.lm_head
+
+    def forward(self, input_ids: torch.Tensor, labels: torch.Tensor | None = None, shift_labels: bool = True):
+        cfg = self.cfg
+        bsz, seq = input_ids.shape
+        _, tp = _tp(self.tp_group)
+        ids = input_ids.reshape(-1)
+        if tp > 1:
+            x = self._vocab_parallel_embed(ids, seq)
+        else:
+            x = O.embedding(ids, self.wte, self.wpe, seq, cfg.pos_offset, cfg.embed_scale, self.sparse_sink)
+        res = None
+        for blk in self.blocks:
+            if cfg.grad_checkpoint and torch.is_grad_enabled():
+                x, res = checkpoint(blk, x, res, bsz, seq, use_reentrant=False)
+            else:
+                x, res = blk(x, res, bsz, seq)
+        y, _ = O.fused_norm(x, res, self.norm_f_w, self.norm_f_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
+        if labels is None:
+            return self._logits(y).view(bsz, seq, -1)
+        if shift_labels:
+            lab = torch.full_like(labels, -100)
+            lab[:, :-1] = labels[:, 1:]
+        else:
+            lab = labels
+        if tp > 1:
+            return self._vocab_parallel_loss(y, lab.reshape(-1))
+        return O.lm_head_loss(y, self.head_weight(), lab.reshape(-1))
+
+    # ---- vocab-parallel pieces (TP > 1) ------------------------------------------------------
+    def _vocab_parallel_embed(self, ids, seq):
+        cfg = self.cfg
+        lo, hi = self.vocab_start, self.vocab_start + self.vocab_local
+        mine = (ids >= lo) & (ids < hi)
+        local = torch.where(mine, ids - lo, torch.zeros_like(ids))
+        x = O.embedding(local, self.wte, None, seq, 0, cfg.embed_scale, None)
+        x = x * mine.unsqueeze(-1).to(x.dtype)
+        x = O.reduce_from_tp(x, self.tp_group)
+        if self.wpe is not None:
+            x = x + self.wpe[cfg.pos_offset:cfg.pos_offset + seq].repeat(ids.numel() // seq, 1)
+        return x
+
+    def _logits(self, y):
+        w = self.head_weight()
+        logits = O.linear(y, w, None, "out_in")
+        _, tp = _tp(self.tp_group)
+        if tp > 1:
+            parts = [torch.empty_like(logits) for _ in range(tp)]
+            dist.all_gather(parts, logits.contiguous(), group=self.tp_group)
+            logits = torch.cat(parts, dim=-1)
+        return logits[..., : self.cfg.vocab_size]
+
+    def _vocab_parallel_loss(self, y, labels):
+        """Cross-entropy over vocabulary shards: local max / sum-exp / target logit, three small all-reduces."""
+        g = self.tp_group
+        y = O.copy_to_tp(y, g)
+        logits = O.linear(y, self.head_weight(), None, "out_in").float()
+        col = torch.arange(self.vocab_local, device=logits.device) + self.vocab_start
+        logits = logits.masked_fill(col[None, :] >= self.cfg.vocab_size, float("-inf"))
+        m = logits.max(dim=-1).values.detach()
+        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=g)
+        e = (logits - m[:, None]).exp()
+        s = O.reduce_from_tp(e.sum(-1), g)
+        valid = labels != -100
+        lo = self.vocab_start
+        mine = valid & (labels >= lo) & (labels < lo + self.vocab_local)
+        idx = torch.where(mine, labels - lo, torch.zeros_like(labels))
+        tgt = logits.gather(1, idx[:, None]).squeeze(1) * mine
+        tgt = O.reduce_from_tp(tgt, g)
+        loss = (s.log() + m - tgt) * valid
+        return loss.sum() / valid.sum().clamp(min=1)
+
+    # ---- HuggingFace-format state dicts ---------------------------------------------------------
+    def hf_state_dict(self) -> dict:
+        from .hf_names import to_hf
+
+        return to_hf(self)
+
+    def load_hf_state_dict(self, sd: dict, strict: bool = True):
+        from .hf_names import from_hf
+
+        return from_hf(self, sd, strict)
+
+
+def build_model(name_or_cfg, tp_group=None, device=None, dtype=torch.bfloat16, sparse_sink=None, **overrides) -> DecoderLM:
+    from .config import get_config
+
+    cfg = get_config(name_or_cfg, **overrides) if isinstance(name_or_cfg, str) else name_or_cfg
+    return DecoderLM(cfg, tp_group, device, dtype, sparse_sink)

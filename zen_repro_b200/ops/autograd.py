@@ -1,0 +1,276 @@
+"""Autograd wrappers that models are built from.  Each forwards to the raw ops (CUDA kernels on GPU,
+PyTorch restatements on CPU), saves only what its hand-written backward needs, and never
+materialises a transposed operand.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import elementwise as E
+from . import gemm as G
+from . import attention as A
+
+
+class LinearFn(torch.autograd.Function):
+    """y = x @ W^T + b with W stored [out, in] ("out_in", nn.Linear) or [in, out] ("in_out", GPT-2 Conv1D)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, layout):
+        ctx.layout = layout
+        ctx.has_bias = bias is not None
+        x2 = x.reshape(-1, x.shape[-1])
+        if layout == "out_in":
+            y = G.gemm_nt(x2, weight, bias=bias)
+            n = weight.shape[0]
+        else:
+            y = G.gemm_nn(x2, weight, bias=bias)
+            n = weight.shape[1]
+        ctx.save_for_backward(x2, weight)
+        ctx.xshape = x.shape
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], n)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = (G.gemm_nn(dy2, weight) if ctx.layout == "out_in" else G.gemm_nt(dy2, weight)).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            dw = G.gemm_tn(dy2, x2) if ctx.layout == "out_in" else G.gemm_tn(x2, dy2)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = E.colsum(dy2)
+        return dx, dw, db, None
+
+
+def linear(x, weight, bias=None, layout="out_in"):
+    return LinearFn.apply(x, weight, bias, layout)
+
+
+class NormFn(torch.autograd.Function):
+    """(y, h) = norm(x + residual): y feeds the next sub-layer, h is the updated residual stream."""
+
+    @staticmethod
+    def forward(ctx, x, residual, weight, bias, eps, layer, unit_offset):
+        y, h, rstd, mean = E.norm_fwd(x, weight, bias, residual, eps=eps, layer=layer, unit_offset=unit_offset)
+        ctx.save_for_backward(h, weight, rstd, mean if mean is not None else rstd)
+        ctx.cfg = (layer, unit_offset, bias is not None, residual is not None)
+        return y, h
+
+    @staticmethod
+    def backward(ctx, dy, dh_in):
+        h, weight, rstd, mean = ctx.saved_tensors
+        layer, unit_offset, has_bias, has_res = ctx.cfg
+        dh, dw, db = E.norm_bwd(dy.contiguous(), h, weight, rstd, mean if layer else None, dh_in,
+                                layer=layer, unit_offset=unit_offset, has_bias=has_bias)
+        return dh, (dh if has_res else None), dw, db, None, None, None
+
+
+def fused_norm(x, residual, weight, bias=None, eps=1e-5, layer=False, unit_offset=False):
+    return NormFn.apply(x, residual, weight, bias, eps, layer, unit_offset)
+
+
+class ActFn(torch.autograd.Function):
+    """Activation on a [.., inner] tensor, or gated activation on the two halves of a [.., 2 * inner] tensor."""
+
+    @staticmethod
+    def forward(ctx, x, kind):
+        ctx.kind = kind
+        gated = kind in ("swiglu", "geglu")
+        x2 = x.reshape(-1, x.shape[-1])
+        if gated:
+            inner = x2.shape[1] // 2
+            out = E.act_fwd(x2[:, :inner], x2[:, inner:], kind)
+        else:
+            inner = x2.shape[1]
+            out = E.act_fwd(x2, None, kind)
+        ctx.save_for_backward(x2)
+        ctx.xshape = x.shape
+        return out.view(*x.shape[:-1], inner)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (x2,) = ctx.saved_tensors
+        kind = ctx.kind
+        d2 = dout.reshape(-1, dout.shape[-1])
+        if kind in ("swiglu", "geglu"):
+            inner = x2.shape[1] // 2
+            da, db = E.act_bwd(x2[:, :inner], x2[:, inner:], d2, kind)
+            dx = torch.cat([da.view(-1, inner), db.view(-1, inner)], dim=1)
+        else:
+            dx, _ = E.act_bwd(x2, None, d2, kind)
+        return dx.view(ctx.xshape), None
+
+
+def activation(x, kind):
+    return ActFn.apply(x, kind)
+
+
+class RopeFn(torch.autograd.Function):
+    """Rotary embedding on the q and k parts of a fused [tokens, (Hq + 2 Hkv) * hd] projection, in place."""
+
+    @staticmethod
+    def forward(ctx, qkv, hq, hkv, hd, seq, theta):
+        ctx.cfg = (hq, hkv, hd, seq, theta)
+        t = qkv.shape[0]
+        v3 = qkv.view(t, hq + 2 * hkv, hd)
+        E.rope_(v3[:, :hq], seq, theta)
+        E.rope_(v3[:, hq:hq + hkv], seq, theta)
+        ctx.mark_dirty(qkv)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, d):
+        hq, hkv, hd, seq, theta = ctx.cfg
+        d = d.contiguous().clone() if not d.is_contiguous() else d.clone()
+        v3 = d.view(d.shape[0], hq + 2 * hkv, hd)
+        E.rope_(v3[:, :hq], seq, theta, inverse=True)
+        E.rope_(v3[:, hq:hq + hkv], seq, theta, inverse=True)
+        return d, None, None, None, None, None
+
+
+def rope_qkv(qkv, hq, hkv, hd, seq, theta):
+    return RopeFn.apply(qkv, hq, hkv, hd, seq, theta)
+
+
+class EmbeddingFn(torch.autograd.Function):
+    """Token (+ learned position) embedding.  With ``sparse_sink`` the lookup gradient is produced as
+    (rows, count, values) and handed to the sink instead of being scattered into a dense [V, d] tensor."""
+
+    @staticmethod
+    def forward(ctx, ids, wte, wpe, seq, pos_offset, scale, sparse_sink, vocab_start):
+        local = ids - vocab_start if vocab_start else ids
+        out = E.embedding_fwd(local, wte, wpe, seq=seq, pos_offset=pos_offset, scale=scale)
+        ctx.save_for_backward(local)
+        ctx.cfg = (wte.shape, wte.dtype, wpe.shape if wpe is not None else None, seq, pos_offset, scale, sparse_sink)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        wshape, wdtype, pshape, seq, pos_offset, scale, sink = ctx.cfg
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dwpe = None
+        if pshape is not None:
+            bsz = dy2.shape[0] // seq
+            dwpe = torch.zeros(pshape, dtype=dy.dtype, device=dy.device)
+            dwpe[pos_offset:pos_offset + seq] = dy2.view(bsz, seq, -1).float().sum(0).to(dy.dtype)
+        scratch = sink.scratch_for(ids.numel(), dy2) if sink is not None else None
+        rows, count, vals = E.embedding_bwd_rows(ids, dy2, wshape[0], scale=scale, scratch=scratch)
+        if sink is not None:
+            sink.put(rows, count, vals)
+            return None, None, dwpe, None, None, None, None, None
+        dw = torch.zeros(wshape, dtype=wdtype, device=dy.device)
+        E.rows_add_(dw, rows, count, vals)
+        return None, dw, dwpe, None, None, None, None, None
+
+
+def embedding(ids, wte, wpe=None, seq=1, pos_offset=0, scale=1.0, sparse_sink=None, vocab_start=0):
+    return EmbeddingFn.apply(ids, wte, wpe, seq, pos_offset, scale, sparse_sink, vocab_start)
+
+
+class LMHeadLossFn(torch.autograd.Function):
+    """mean cross-entropy(h @ W^T, labels).  Logits are computed, turned into dlogits in place by one
+    kernel, and immediately consumed by the two gradient GEMMs; only dh and dW survive the forward."""
+
+    @staticmethod
+    def forward(ctx, h, weight, labels, ignore_index, chunk_tokens):
+        h2 = h.reshape(-1, h.shape[-1])
+        lab = labels.reshape(-1)
+        T = h2.shape[0]
+        nvalid = (lab != ignore_index).sum().clamp_(min=1).to(torch.float32)
+        V = weight.shape[0]
+        vpad = (V + 7) // 8 * 8
+        dh = torch.empty_like(h2)
+        dw = torch.zeros(weight.shape, dtype=torch.float32 if h2.is_cuda else weight.dtype, device=h2.device)
+        loss_sum = torch.zeros((), dtype=torch.float32, device=h2.device)
+        for s in range(0, T, chunk_tokens):
+            e = min(T, s + chunk_tokens)
+            buf = torch.empty(e - s, vpad, dtype=h2.dtype, device=h2.device)
+            logits = buf[:, :V]
+            G.gemm_nt(h2[s:e], weight, out=logits)
+            # gradient is scaled by 1 / T here and corrected to 1 / nvalid below without a host sync
+            loss, dl = E.cross_entropy(logits, lab[s:e], grad_scale=1.0, ignore_index=ignore_index)
+            loss_sum += loss.sum()
+            dh[s:e] = G.gemm_nn(dl, weight)
+            G.gemm_tn(dl, h2[s:e], out=dw, accumulate=True)
+        inv = 1.0 / nvalid
+        ctx.save_for_backward(dh, dw, inv)
+        ctx.hshape = h.shape
+        ctx.wdtype = weight.dtype
+        return loss_sum * inv
+
+    @staticmethod
+    def backward(ctx, g):
+        dh, dw, inv = ctx.saved_tensors
+        s = (g * inv)
+        return (dh.float() * s).to(dh.dtype).view(ctx.hshape), (dw.float() * s).to(ctx.wdtype), None, None, None
+
+
+def lm_head_loss(h, weight, labels, ignore_index=-100, chunk_tokens=8192):
+    return LMHeadLossFn.apply(h, weight, labels, ignore_index, chunk_tokens)
+
+
+class AttentionFn(torch.autograd.Function):
+    """Causal self-attention over a fused qkv projection [B*S, (Hq + 2 Hkv) * hd] -> [B*S, Hq * hd]."""
+
+    @staticmethod
+    def forward(ctx, qkv, bsz, seq, hq, hkv, hd, scale):
+        out, saved = A.attention_fwd(qkv, bsz, seq, hq, hkv, hd, scale)
+        ctx.save_for_backward(qkv, out, *saved)
+        ctx.cfg = (bsz, seq, hq, hkv, hd, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, *saved = ctx.saved_tensors
+        dqkv = A.attention_bwd(dout.contiguous(), qkv, out, saved, *ctx.cfg)
+        return dqkv, None, None, None, None, None, None
+
+
+def attention(qkv, bsz, seq, hq, hkv, hd, scale=None):
+    return AttentionFn.apply(qkv, bsz, seq, hq, hkv, hd, scale if scale is not None else 1.0 / math.sqrt(hd))
+
+
+# ------------------------------------------------------------------------------------------ tensor parallel
+class _CopyToTP(torch.autograd.Function):
+    """Identity forward, all-reduce backward (input of a column-parallel linear)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    """All-reduce forward, identity backward (output of a row-parallel linear)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def copy_to_tp(x, group):
+    return x if group is None or dist.get_world_size(group) == 1 else _CopyToTP.apply(x, group)
+
+
+def reduce_from_tp(x, group):
+    return x if group is None or dist.get_world_size(group) == 1 else _ReduceFromTP.apply(x, group)

@@ -1,0 +1,317 @@
+"""Raw (non-autograd) functional forms of the memory-bound model ops.
+
+Every function dispatches on the device of its inputs: CUDA tensors run the
+hand-written kernels in ``csrc/elementwise_kernels.cu``; CPU tensors run the
+PyTorch restatement in the same function, which is also the oracle of the GPU
+tests.  The autograd wrappers that models use live in ``ops/autograd.py``.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+import torch.nn.functional as F
+
+from .. import _native
+
+ACT_GELU_TANH, ACT_RELU, ACT_SILU_GATE, ACT_GELU_GATE = 0, 1, 2, 3
+_ACT = {"gelu_tanh": 0, "relu": 1, "swiglu": 2, "geglu": 3}
+
+_scratch: dict = {}
+
+
+def _scratch_buf(key, numel: int, dtype, device) -> torch.Tensor:
+    """Per-(purpose, device, stream) scratch that grows but is never freed."""
+    k = (key, device, dtype, torch.cuda.current_stream().cuda_stream)
+    buf = _scratch.get(k)
+    if buf is None or buf.numel() < numel:
+        buf = torch.empty(max(numel, 1), dtype=dtype, device=device)
+        _scratch[k] = buf
+    return buf
+
+
+def _code(t: torch.Tensor) -> int:
+    return _native.DTYPE_CODE[t.dtype]
+
+
+def _c(t: torch.Tensor) -> torch.Tensor:
+    return t if t.is_contiguous() else t.contiguous()
+
+
+# ----------------------------------------------------------------------------- norms
+def norm_fwd(x, weight, bias=None, residual=None, *, eps=1e-5, layer=False, unit_offset=False, want_h=True):
+    """h = x (+ residual); y = norm(h).  Returns (y, h, rstd, mean) -- h is x itself without a residual."""
+    cols = x.shape[-1]
+    x2 = _c(x).view(-1, cols)
+    rows = x2.shape[0]
+    if not x.is_cuda:
+        h = x2.float() + (residual.reshape(-1, cols).float() if residual is not None else 0)
+        h = h.to(x.dtype)                     # the residual stream is stored in the activation dtype
+        hf = h.float()
+        if layer:
+            mean = hf.mean(-1)
+            var = hf.var(-1, unbiased=False)
+            rstd = torch.rsqrt(var + eps)
+            y = (hf - mean[:, None]) * rstd[:, None] * weight.float() + (bias.float() if bias is not None else 0)
+        else:
+            mean = None
+            rstd = torch.rsqrt(hf.pow(2).mean(-1) + eps)
+            w = weight.float() + 1.0 if unit_offset else weight.float()
+            y = hf * rstd[:, None] * w
+        return y.to(x.dtype).view(x.shape), h.view(x.shape), rstd, mean
+    y = torch.empty_like(x2)
+    res2 = _c(residual).view(-1, cols) if residual is not None else None
+    h = torch.empty_like(x2) if residual is not None else x2
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device) if layer else None
+    rc = _native.lib().zen_norm_fwd(_native.ptr(x2), _native.ptr(res2), _native.ptr(weight), _native.ptr(bias),
+                                    _native.ptr(y), _native.ptr(h if residual is not None else None),
+                                    _native.ptr(rstd), _native.ptr(mean), rows, cols, ctypes.c_float(eps),
+                                    int(layer), int(unit_offset), _code(x2), _native.stream_ptr())
+    _native.check(rc, "zen_norm_fwd")
+    return y.view(x.shape), h.view(x.shape), rstd, mean
+
+
+def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_offset=False, has_bias=False):
+    """Returns (dh, dweight, dbias): dh includes ``dres`` (gradient on the residual stream) when given."""
+    cols = h.shape[-1]
+    dy2, h2 = _c(dy).view(-1, cols), _c(h).view(-1, cols)
+    rows = h2.shape[0]
+    if not h.is_cuda:
+        hf, g = h2.float(), dy2.float()
+        if layer:
+            xh = (hf - mean[:, None]) * rstd[:, None]
+            gw = g * weight.float()
+            dh = rstd[:, None] * (gw - gw.mean(-1, keepdim=True) - xh * (gw * xh).mean(-1, keepdim=True))
+        else:
+            xh = hf * rstd[:, None]
+            w = weight.float() + 1.0 if unit_offset else weight.float()
+            gw = g * w
+            dh = rstd[:, None] * (gw - xh * (gw * xh).mean(-1, keepdim=True))
+        dw = (g * xh).sum(0).to(weight.dtype)
+        db = g.sum(0).to(weight.dtype) if (layer and has_bias) else None
+        if dres is not None:
+            dh = dh + dres.reshape(-1, cols).float()
+        return dh.to(h.dtype).view(h.shape), dw, db
+    lib = _native.lib()
+    parts = lib.zen_norm_bwd_parts(rows)
+    part_dw = _scratch_buf("norm_dw", parts * cols, torch.float32, h.device)
+    part_db = _scratch_buf("norm_db", parts * cols, torch.float32, h.device) if layer else None
+    dh = torch.empty_like(h2)
+    dw = torch.empty_like(weight)
+    db = torch.empty_like(weight) if (layer and has_bias) else None
+    dres2 = _c(dres).view(-1, cols) if dres is not None else None
+    rc = lib.zen_norm_bwd(_native.ptr(dy2), _native.ptr(h2), _native.ptr(weight), _native.ptr(rstd), _native.ptr(mean),
+                          _native.ptr(dres2), _native.ptr(dh), _native.ptr(part_dw), _native.ptr(part_db),
+                          _native.ptr(dw), _native.ptr(db), rows, cols, int(layer), int(unit_offset), 0, _code(h2),
+                          _native.stream_ptr())
+    _native.check(rc, "zen_norm_bwd")
+    return dh.view(h.shape), dw, db
+
+
+def colsum(a: torch.Tensor) -> torch.Tensor:
+    """Column sums of a [rows, cols] matrix (bias gradients)."""
+    cols = a.shape[-1]
+    a2 = _c(a).view(-1, cols)
+    if not a.is_cuda:
+        return a2.float().sum(0).to(a.dtype)
+    lib = _native.lib()
+    rows = a2.shape[0]
+    part = _scratch_buf("colsum", lib.zen_colsum_parts(rows) * cols, torch.float32, a.device)
+    out = torch.empty(cols, dtype=a.dtype, device=a.device)
+    _native.check(lib.zen_colsum(_native.ptr(a2), _native.ptr(part), _native.ptr(out), rows, cols, 0, _code(a2),
+                                 _native.stream_ptr()), "zen_colsum")
+    return out
+
+
+# ----------------------------------------------------------------------------- activations
+def _gelu_tanh(x):
+    return F.gelu(x, approximate="tanh")
+
+
+def act_fwd(a: torch.Tensor, b: torch.Tensor | None, kind: str) -> torch.Tensor:
+    """gelu_tanh(a) | relu(a) | silu(a) * b | gelu_tanh(a) * b.  a, b: [rows, inner] (row-strided views allowed)."""
+    mode = _ACT[kind]
+    if not a.is_cuda:
+        af = a.float()
+        if mode == 0:
+            o = _gelu_tanh(af)
+        elif mode == 1:
+            o = F.relu(af)
+        elif mode == 2:
+            o = F.silu(af) * b.float()
+        else:
+            o = _gelu_tanh(af) * b.float()
+        return o.to(a.dtype)
+    inner = a.shape[-1]
+    a2 = a.reshape(-1, inner) if a.dim() != 2 else a
+    b2 = (b.reshape(-1, inner) if b.dim() != 2 else b) if b is not None else None
+    assert a2.stride(1) == 1 and (b2 is None or b2.stride(1) == 1)
+    rows = a2.shape[0]
+    out = torch.empty(rows, inner, dtype=a.dtype, device=a.device)
+    rc = _native.lib().zen_act_fwd(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), rows, inner, a2.stride(0),
+                                   b2.stride(0) if b2 is not None else inner, mode, _code(a2), _native.stream_ptr())
+    _native.check(rc, "zen_act_fwd")
+    return out.view(*a.shape[:-1], inner)
+
+
+def act_bwd(a, b, dout, kind: str):
+    """Gradients (da, db) of act_fwd; db is None for the ungated kinds."""
+    mode = _ACT[kind]
+    if not a.is_cuda:
+        af = a.float().detach().requires_grad_(True)
+        bf = b.float().detach().requires_grad_(True) if b is not None else None
+        with torch.enable_grad():
+            if mode == 0:
+                o = _gelu_tanh(af)
+            elif mode == 1:
+                o = F.relu(af)
+            elif mode == 2:
+                o = F.silu(af) * bf
+            else:
+                o = _gelu_tanh(af) * bf
+        gs = torch.autograd.grad(o, [af] + ([bf] if bf is not None else []), dout.float())
+        return gs[0].to(a.dtype), (gs[1].to(a.dtype) if bf is not None else None)
+    inner = a.shape[-1]
+    a2 = a.reshape(-1, inner) if a.dim() != 2 else a
+    b2 = (b.reshape(-1, inner) if b.dim() != 2 else b) if b is not None else None
+    d2 = _c(dout).view(-1, inner)
+    rows = a2.shape[0]
+    da = torch.empty(rows, inner, dtype=a.dtype, device=a.device)
+    db = torch.empty(rows, inner, dtype=a.dtype, device=a.device) if b is not None else None
+    # da / db are dense [rows, inner]; the kernel strides them like a / b, so pass dense strides for outputs
+    a_c = a2 if a2.stride(0) == inner else a2.contiguous()
+    b_c = (b2 if b2.stride(0) == inner else b2.contiguous()) if b2 is not None else None
+    rc = _native.lib().zen_act_bwd(_native.ptr(a_c), _native.ptr(b_c), _native.ptr(d2), _native.ptr(da), _native.ptr(db),
+                                   rows, inner, inner, inner, mode, _code(a2), _native.stream_ptr())
+    _native.check(rc, "zen_act_bwd")
+    return da.view(a.shape), (db.view(a.shape) if db is not None else None)
+
+
+# ----------------------------------------------------------------------------- RoPE
+def rope_(x: torch.Tensor, seq: int, theta: float = 10000.0, inverse: bool = False, pos0: int = 0) -> torch.Tensor:
+    """In-place rotary embedding (rotate-half) on x[tokens, heads, hd]; token t has position pos0 + t % seq."""
+    tokens, heads, hd = x.shape
+    if not x.is_cuda:
+        half = hd // 2
+        inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float32) * 2 / hd))
+        pos = (pos0 + torch.arange(tokens) % seq).float()
+        ang = pos[:, None] * inv[None, :]
+        s, c = ang.sin()[:, None, :], ang.cos()[:, None, :]
+        if inverse:
+            s = -s
+        a, b = x[..., :half].float().clone(), x[..., half:].float().clone()
+        x[..., :half] = (a * c - b * s).to(x.dtype)
+        x[..., half:] = (b * c + a * s).to(x.dtype)
+        return x
+    assert x.stride(2) == 1 and x.stride(1) == hd
+    rc = _native.lib().zen_rope(_native.ptr(x), tokens, heads, hd, x.stride(0), seq, pos0, ctypes.c_float(theta),
+                                int(inverse), _code(x), _native.stream_ptr())
+    _native.check(rc, "zen_rope")
+    return x
+
+
+# ----------------------------------------------------------------------------- embedding
+def embedding_fwd(ids, wte, wpe=None, *, seq: int, pos_offset: int = 0, scale: float = 1.0):
+    """out[t] = wte[ids[t]] * scale (+ wpe[pos_offset + t % seq]); ids int64 [tokens]."""
+    tokens, d = ids.numel(), wte.shape[1]
+    ids1 = _c(ids).view(-1)
+    if not wte.is_cuda:
+        out = wte[ids1]
+        if scale != 1.0:
+            out = (out.float() * scale).to(wte.dtype)
+        if wpe is not None:
+            out = (out.float() + wpe[pos_offset + torch.arange(tokens) % seq].float()).to(wte.dtype)
+        return out
+    out = torch.empty(tokens, d, dtype=wte.dtype, device=wte.device)
+    rc = _native.lib().zen_embedding_fwd(_native.ptr(ids1), _native.ptr(wte), _native.ptr(wpe), _native.ptr(out), tokens,
+                                         d, seq, pos_offset, ctypes.c_float(scale), wte.shape[0], _code(wte),
+                                         _native.stream_ptr())
+    _native.check(rc, "zen_embedding_fwd")
+    return out
+
+
+class RowSparseScratch:
+    """Reusable buffers of the row-sparse embedding backward for one (vocab, d, max_rows)."""
+
+    def __init__(self, vocab: int, d: int, max_rows: int, dtype, device):
+        self.vocab, self.d, self.max_rows = vocab, d, max_rows
+        self.flag = torch.zeros(vocab, dtype=torch.int32, device=device)
+        self.acc = torch.zeros(max_rows, d, dtype=torch.float32, device=device)
+        self.rows = torch.zeros(max_rows, dtype=torch.int32, device=device)
+        self.count = torch.zeros(1, dtype=torch.int32, device=device)
+        self.vals = torch.zeros(max_rows, d, dtype=dtype, device=device)
+
+
+def embedding_bwd_rows(ids, dy, vocab: int, scale: float = 1.0, scratch: RowSparseScratch | None = None):
+    """Row-sparse gradient of an embedding lookup: (rows int32 ascending unique, count int32[1], vals[max_rows, d]).
+
+    Only ``count`` leading rows are meaningful; nothing is synchronised with the host.
+    """
+    tokens, d = ids.numel(), dy.shape[-1]
+    ids1, dy2 = _c(ids).view(-1), _c(dy).view(-1, d)
+    if not dy.is_cuda:
+        uniq, inv = torch.unique(ids1, return_inverse=True)
+        vals = torch.zeros(uniq.numel(), d, dtype=torch.float32)
+        vals.index_add_(0, inv, dy2.float() * scale)
+        return uniq.to(torch.int32), torch.tensor([uniq.numel()], dtype=torch.int32), vals.to(dy.dtype)
+    max_rows = min(tokens, vocab)
+    if scratch is None:
+        scratch = RowSparseScratch(vocab, d, max_rows, dy.dtype, dy.device)
+    assert scratch.max_rows >= max_rows and scratch.vocab == vocab and scratch.d == d
+    rc = _native.lib().zen_embedding_bwd_rows(_native.ptr(ids1), _native.ptr(dy2), _native.ptr(scratch.flag),
+                                              _native.ptr(scratch.acc), _native.ptr(scratch.rows),
+                                              _native.ptr(scratch.count), _native.ptr(scratch.vals), tokens, d, vocab,
+                                              ctypes.c_float(scale), _code(dy2), _native.stream_ptr())
+    _native.check(rc, "zen_embedding_bwd_rows")
+    return scratch.rows, scratch.count, scratch.vals
+
+
+def rows_add_(grad, rows, count, vals) -> torch.Tensor:
+    """grad[rows[u]] += vals[u] for u < count (rows unique)."""
+    if not grad.is_cuda:
+        n = int(count.item())
+        grad.index_add_(0, rows[:n].long(), vals[:n].to(grad.dtype))
+        return grad
+    rc = _native.lib().zen_rows_add(_native.ptr(grad), _native.ptr(rows), _native.ptr(count), _native.ptr(vals),
+                                    grad.shape[1], grad.shape[0], rows.numel(), _code(grad), _native.stream_ptr())
+    _native.check(rc, "zen_rows_add")
+    return grad
+
+
+# ----------------------------------------------------------------------------- cross entropy
+def cross_entropy(logits, labels, *, grad_scale: float | None = None, ignore_index: int = -100, inplace_grad=True):
+    """Per-row loss (fp32) and, when ``grad_scale`` is given, dlogits = (softmax - onehot) * grad_scale.
+
+    With ``inplace_grad`` the gradient overwrites ``logits`` (they are not needed afterwards).
+    """
+    vocab = logits.shape[-1]
+    lg = logits.view(-1, vocab) if logits.dim() != 2 else logits
+    rows = lg.shape[0]
+    lb = _c(labels).view(-1)
+    if not logits.is_cuda:
+        lf = lg.float()
+        loss = F.cross_entropy(lf, lb, reduction="none", ignore_index=ignore_index)
+        d = None
+        if grad_scale is not None:
+            p = torch.softmax(lf, -1)
+            valid = lb != ignore_index
+            onehot = torch.zeros_like(p)
+            onehot[valid, lb[valid]] = 1.0
+            d = ((p - onehot) * grad_scale * valid[:, None]).to(logits.dtype)
+            if inplace_grad:
+                lg.copy_(d)
+                d = lg
+        return loss, d
+    assert lg.stride(1) == 1
+    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    d = None
+    if grad_scale is not None:
+        d = lg if inplace_grad else torch.empty_like(lg)
+        assert d.stride(0) == lg.stride(0)
+    rc = _native.lib().zen_xent(_native.ptr(lg), _native.ptr(lb), _native.ptr(loss), _native.ptr(d), rows, vocab,
+                                lg.stride(0), ctypes.c_float(grad_scale or 0.0), ctypes.c_int64(ignore_index),
+                                _code(lg), _native.stream_ptr())
+    _native.check(rc, "zen_xent")
+    return loss, d

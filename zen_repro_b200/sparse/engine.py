@@ -31,8 +31,8 @@ FMT_AUTO, FMT_COO, FMT_BITMAP = 0, 1, 2
 
 class _Perm(ctypes.Structure):
     _fields_ = [("block", ctypes.c_uint32), ("nblocks", ctypes.c_uint32), ("sb", ctypes.c_uint32),
-                ("pad", ctypes.c_uint32), ("mult", ctypes.c_uint64), ("mult_inv", ctypes.c_uint64),
-                ("add", ctypes.c_uint64)]
+                ("mask", ctypes.c_uint32), ("mult", ctypes.c_uint32), ("mult_inv", ctypes.c_uint32),
+                ("add", ctypes.c_uint32), ("lg", ctypes.c_uint32)]
 
 
 class _Ctx(ctypes.Structure):
@@ -52,7 +52,8 @@ class _Ctx(ctypes.Structure):
 
 
 def perm_struct(perm: BlockPermutation) -> _Perm:
-    return _Perm(perm.block, perm.nblocks, perm.blocks_per_part, 0, perm.mult, perm.mult_inv, perm.add)
+    return _Perm(perm.block, perm.nblocks, perm.blocks_per_part, perm.mask, perm.mult, perm.mult_inv, perm.add,
+                 perm.block.bit_length() - 1)
 
 
 def _up(x: int, a: int) -> int:
@@ -75,8 +76,8 @@ class SparsePlan:
     def __post_init__(self):
         if not (1 <= self.nranks <= MAX_RANKS):
             raise ValueError(f"nranks must be in [1, {MAX_RANKS}]")
-        if self.block % 64:
-            raise ValueError("element-granule block must be a multiple of 64")
+        if self.block < 64 or self.block & (self.block - 1):
+            raise ValueError("element-granule block must be a power of two >= 64")
         if self.numel >= 2 ** 32 - 4096:
             raise ValueError("numel must fit 32-bit indices")
         self.perm = BlockPermutation.make(self.numel, self.nranks, self.block)

@@ -2,23 +2,29 @@
 
 Two partitioners are provided.
 
-``BlockPermutation`` (default).  An invertible affine permutation of *blocks*
-of ``G`` consecutive elements.  With ``nb' = P * Sb`` padded blocks,
+``BlockPermutation`` (default).  An invertible permutation of *blocks* of ``G``
+consecutive elements, cheap enough to evaluate per block inside the scan kernel
+(32-bit multiply-add, no division by a runtime modulus).  With ``nb' = P * Sb``
+padded blocks and ``2**k`` the next power of two >= ``nb'``,
 
-    pi(b)    = (a * b + c) mod nb'          (gcd(a, nb') == 1)
+    f(y)     = (a * y + c) mod 2**k           (a odd, so f is a bijection of [0, 2**k))
+    pi(b)    = f applied to b until the value is < nb'       (cycle walking)
     owner(i) = pi(i // G) // Sb
     slot(i)  = (pi(i // G) % Sb) * G + i % G
     i        = pi^-1(owner * Sb + slot // G) * G + slot % G
 
-``a`` is chosen close to ``nb' / golden_ratio`` (Fibonacci hashing), which
-spreads any contiguous run of hot positions (the Zipf head of an embedding
-table) evenly over the ``P`` owners.  Because the map is a bijection the owner
-can reduce into ``S = Sb * G`` dense slots and the occupancy bitmap of those
-slots *is* the index encoding of the gather phase; no per-position ownership
-list has to be stored, and sizes that are not multiples of ``P`` need no
-special case.  The reference builds its ownership lists by hashing every
-position and comparing against each rank (comm.py:52-56) and its two hash
-users disagree when ``numel % P != 0`` (functions_cuda_kernel.cu:172-174 vs
+``a`` is the odd integer nearest ``2**k / golden_ratio`` and the owner is taken
+from the HIGH bits of ``pi`` (Fibonacci hashing), which spreads any contiguous
+run of hot positions (the Zipf head of an embedding table) evenly over the
+``P`` owners.  Cycle walking restricts the power-of-two bijection to
+``[0, nb')`` and keeps it a bijection; since ``nb' > 2**(k-1)`` it needs less
+than one extra step on average.  Because the map is invertible the owner can
+reduce into ``S = Sb * G`` dense slots and the occupancy bitmap of those slots
+*is* the index encoding of the gather phase; no per-position ownership list has
+to be stored, and sizes that are not multiples of ``P`` need no special case.
+The reference builds its ownership lists by hashing every position and
+comparing against each rank (comm.py:52-56) and its two hash users disagree
+when ``numel % P != 0`` (functions_cuda_kernel.cu:172-174 vs
 tensor_load_balance.py:15-16).
 
 ``zen_poly3``.  The reference's cubic polynomial in wrapping uint32
@@ -27,7 +33,6 @@ partition assignment: ``owner(i) = (h(i, seed0) % M) // (M // P)``.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import torch
@@ -39,33 +44,22 @@ ZEN_POLY3_A = 0xCC9E2D51
 ZEN_POLY3_B = 0x1B873593
 ZEN_SEEDS = (10001861, 100703, 5002639)
 
-
-def _coprime_near(target: int, modulus: int) -> int:
-    """Smallest ``a >= target`` (wrapping into [1, modulus)) coprime with ``modulus``."""
-    if modulus == 1:
-        return 0
-    a = max(1, target % modulus)
-    for _ in range(modulus):
-        if math.gcd(a, modulus) == 1:
-            return a
-        a += 1
-        if a >= modulus:
-            a = 1
-    raise ValueError("no coprime multiplier")
+_MAX_WALK = 64
 
 
 @dataclass(frozen=True)
 class BlockPermutation:
     """Invertible block permutation; see the module docstring for the maths."""
 
-    numel: int          # N: logical elements (or rows in row mode)
-    parts: int          # P
-    block: int          # G
-    nblocks: int        # nb' (padded, multiple of P)
+    numel: int            # N: logical elements (or rows in row mode)
+    parts: int            # P
+    block: int            # G
+    nblocks: int          # nb' (padded, multiple of P)
     blocks_per_part: int  # Sb
-    mult: int           # a
-    mult_inv: int       # a^-1 mod nb'
-    add: int            # c
+    mask: int             # 2**k - 1
+    mult: int             # a (odd)
+    mult_inv: int         # a^-1 mod 2**k
+    add: int              # c
 
     @staticmethod
     def make(numel: int, parts: int, block: int = 64) -> "BlockPermutation":
@@ -76,10 +70,12 @@ class BlockPermutation:
         nbp = sb * parts
         if nbp >= 2 ** 31:
             raise ValueError("too many blocks for 32-bit block ids")
-        a = _coprime_near(int(round(nbp * GOLDEN)), nbp)
-        ainv = pow(a, -1, nbp) if nbp > 1 else 0
-        c = int(round(nbp * (1.0 - GOLDEN) * 0.5)) % nbp
-        return BlockPermutation(numel, parts, block, nbp, sb, a, ainv, c)
+        k = max(1, (nbp - 1).bit_length())
+        size = 1 << k
+        a = int(round(size * GOLDEN)) | 1
+        ainv = pow(a, -1, size)
+        c = int(round(size * (1.0 - GOLDEN) * 0.5)) & (size - 1)
+        return BlockPermutation(numel, parts, block, nbp, sb, size - 1, a, ainv, c)
 
     @property
     def slots_per_part(self) -> int:
@@ -89,12 +85,21 @@ class BlockPermutation:
     def padded_numel(self) -> int:
         return self.nblocks * self.block
 
-    # -- tensor forms (int64 in, int64 out); exact for nb' < 2**31 ----------
+    # -- tensor forms (int64 in, int64 out) ---------------------------------
+    def _walk(self, y: torch.Tensor, step) -> torch.Tensor:
+        y = step(y)
+        for _ in range(_MAX_WALK):
+            out = y >= self.nblocks
+            if not bool(out.any()):
+                return y
+            y = torch.where(out, step(y), y)
+        raise RuntimeError("cycle walk did not terminate")
+
     def permute_block(self, blk: torch.Tensor) -> torch.Tensor:
-        return (blk.to(torch.int64) * self.mult + self.add) % self.nblocks
+        return self._walk(blk.to(torch.int64), lambda y: (y * self.mult + self.add) & self.mask)
 
     def unpermute_block(self, pb: torch.Tensor) -> torch.Tensor:
-        return ((pb.to(torch.int64) - self.add) % self.nblocks * self.mult_inv) % self.nblocks
+        return self._walk(pb.to(torch.int64), lambda y: ((y - self.add) & self.mask) * self.mult_inv & self.mask)
 
     def owner_slot(self, idx: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         idx = idx.to(torch.int64)
@@ -107,10 +112,6 @@ class BlockPermutation:
         slot = slot.to(torch.int64)
         pb = owner * self.blocks_per_part + slot // self.block
         return self.unpermute_block(pb) * self.block + slot % self.block
-
-    def as_kernel_args(self) -> tuple[int, int, int, int, int, int]:
-        """(block, nblocks, blocks_per_part, mult, mult_inv, add) for the CUDA side."""
-        return (self.block, self.nblocks, self.blocks_per_part, self.mult, self.mult_inv, self.add)
 
 
 def zen_poly3(idx: torch.Tensor, seed: int) -> torch.Tensor:
