@@ -12,6 +12,19 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
+def _plain(x):
+    """Tensors -> numpy (pickled by value; shared-memory handles die with the child process)."""
+    import torch
+
+    if torch.is_tensor(x):
+        return x.detach().cpu().numpy()
+    if isinstance(x, (list, tuple)):
+        return type(x)(_plain(v) for v in x)
+    if isinstance(x, dict):
+        return {k: _plain(v) for k, v in x.items()}
+    return x
+
+
 def _entry(rank, world, port, fn, args, q):
     import torch.distributed as dist
 
@@ -20,7 +33,7 @@ def _entry(rank, world, port, fn, args, q):
     try:
         dist.init_process_group("gloo", rank=rank, world_size=world)
         res = fn(rank, world, *args)
-        q.put((rank, "ok", res))
+        q.put((rank, "ok", _plain(res)))
     except Exception:
         q.put((rank, "err", traceback.format_exc()))
     finally:

@@ -1,0 +1,128 @@
+"""Worker run under torchrun by tests/test_multigpu.py (one process per GPU).  Prints ``OK <name>`` per check."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def make_sparse(n, density, seed, dtype, dev):
+    g = torch.Generator().manual_seed(seed)
+    k = max(1, int(n * density))
+    idx = torch.randperm(n, generator=g)[:k]
+    x = torch.zeros(n)
+    x[idx] = torch.randn(k, generator=g)
+    return x.to(dtype).to(dev)
+
+
+def check_sparse_allreduce(rank, world, dev):
+    from zen_repro_b200.sparse.engine import SparseAllReduce
+
+    for n, dtype in [(300007, torch.float32), (1 << 22, torch.bfloat16)]:
+        eng = SparseAllReduce(n, None, max_density=0.2, methods=(1, 2, 3), deterministic=True)
+        for rep in range(3):
+            x = make_sparse(n, 0.02 * (rep + 1), 100 * rep + rank, dtype, dev)
+            want = x.clone().float()
+            dist.all_reduce(want)
+            for method in (1, 2, 3, "auto"):
+                out = eng(x, method=method)
+                st = eng.check()
+                assert st == 0, (method, st)
+                tol = 1e-5 if dtype == torch.float32 else 0.05
+                err = (out.float() - want).abs().max().item()
+                assert err <= tol, (n, dtype, method, err)
+        eng.close()
+    print(f"OK sparse_allreduce rank{rank}", flush=True)
+
+
+def check_row_engine(rank, world, dev):
+    from zen_repro_b200.sparse.row_engine import RowSparseAllReduce
+
+    vocab, d, max_rows = 50257, 768, 4096
+    eng = RowSparseAllReduce(vocab, d, max_rows, None, dtype=torch.bfloat16)
+    for rep in range(2):
+        g = torch.Generator().manual_seed(10 * rep + rank)
+        n = 2000 + 100 * rank
+        ids = torch.randperm(vocab, generator=g)[:n].sort().values.to(torch.int32)
+        rows = torch.zeros(max_rows, dtype=torch.int32); rows[:n] = ids
+        vals = torch.zeros(max_rows, d); vals[:n] = torch.randn(n, d, generator=g)
+        rows, vals = rows.to(dev), vals.bfloat16().to(dev)
+        cnt = torch.tensor([n], dtype=torch.int32, device=dev)
+        dense = torch.zeros(vocab, d, device=dev)
+        dense.index_add_(0, rows[:n].long(), vals[:n].float())
+        dist.all_reduce(dense)
+        grad = torch.zeros(vocab, d, dtype=torch.bfloat16, device=dev)
+        eng(rows, cnt, vals, grad, scale=1.0)
+        assert eng.check() == 0
+        err = (grad.float() - dense).abs().max().item()
+        assert err < 0.1, err
+    eng.close()
+    print(f"OK row_engine rank{rank}", flush=True)
+
+
+def check_trainer_dp(rank, world, dev):
+    from zen_repro_b200.trainer import TrainConfig, Trainer
+
+    losses = {}
+    for sparse in (True, False):
+        torch.manual_seed(0)
+        t = Trainer(TrainConfig(model="gpt2", num_layers=2, micro_batch=2, seq_len=128, sparse_embedding=sparse, lr=1e-3,
+                                data_pool=0), init_dist=False)
+        losses[sparse] = [t.step(next(t.data)) for _ in range(6)]
+        if sparse:
+            assert t.model.module.embedding_sync.check() == 0
+    a, b = losses[True], losses[False]
+    assert all(abs(x - y) < 0.05 for x, y in zip(a, b)), (a, b)
+    assert a[-1] < a[0]
+    print(f"OK trainer_dp rank{rank} {a[0]:.3f}->{a[-1]:.3f}", flush=True)
+
+
+def check_zen_hook(rank, world, dev):
+    from zen_repro_b200.trainer import TrainConfig, Trainer
+
+    t = Trainer(TrainConfig(model="tiny-llama", micro_batch=2, seq_len=32, method=3, top_k=10, lr=1e-2, data_pool=0,
+                            bucket_cap_mb=0.1), init_dist=False)
+    ls = [t.step(next(t.data)) for _ in range(8)]
+    assert ls[-1] < ls[0], ls
+    print(f"OK zen_hook rank{rank} {ls[0]:.3f}->{ls[-1]:.3f}", flush=True)
+
+
+def check_departed_rank(rank, world, dev):
+    """A rank that stops taking part between steps: the others' next sparse all-reduce must return a TIMEOUT
+    status within its bound (no hang, context usable afterwards)."""
+    from zen_repro_b200.sparse import engine as E
+
+    n = 100000
+    eng = E.SparseAllReduce(n, None, max_density=0.2, wait_ms=300.0)
+    x = make_sparse(n, 0.01, rank, torch.float32, dev)
+    eng(x, method=3)
+    assert eng.check() == 0
+    dist.barrier()
+    torch.cuda.synchronize()
+    if rank == world - 1:
+        print(f"OK departed_rank rank{rank} (leaving)", flush=True)
+    else:
+        eng(x, method=3)                       # the last rank never launches this step
+        st = eng.check()
+        assert st & E.ST_TIMEOUT, st
+        assert float(torch.ones(8, device=dev).sum()) == 8.0
+        print(f"OK departed_rank rank{rank} status={st}", flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()                             # everybody is idle again before anyone frees peer-mapped memory
+    eng.close()
+
+
+CHECKS = {"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
+          "hook": check_zen_hook, "departed": check_departed_rank}
+
+if __name__ == "__main__":
+    from zen_repro_b200.parallel import launch_from_torch
+
+    rank, world, dev = launch_from_torch()
+    names = sys.argv[1:] or list(CHECKS)
+    for nme in names:
+        CHECKS[nme](rank, world, dev)
+        dist.barrier()
+    dist.destroy_process_group()

@@ -1,0 +1,101 @@
+"""Reducer, embedding row sync and tensor parallelism on CPU ranks (gloo)."""
+import pytest
+import torch
+
+from _dist_util import run_gloo
+from zen_repro_b200.models import build_model, get_config
+
+
+@pytest.mark.parametrize("name", ["tiny-gpt2", "tiny-llama", "tiny-gemma", "tiny-opt"])
+def test_reducer_grads_equal_plain_autograd(name):
+    from zen_repro_b200.parallel.embedding_sync import EmbeddingRowSync
+    from zen_repro_b200.parallel.reducer import ZenDDP
+
+    torch.manual_seed(0)
+    ids = torch.randint(0, 1000, (2, 16))
+    a = build_model(name, dtype=torch.float32)
+    b = build_model(name, dtype=torch.float32)
+    b.load_state_dict(a.state_dict())
+    a(ids, ids).backward()
+    sync = EmbeddingRowSync(b.wte.shape[0], b.wte.shape[1], 32, None, dtype=torch.float32)
+    sync.target_param = b.wte
+    b.sparse_sink = sync
+    if b.lm_head is not None:
+        b.wte.zen_sparse_only = True
+    ddp = ZenDDP(b, None, 0.05, sync)
+    for _ in range(2):                       # second pass checks zero_grad / re-arming
+        ddp.zero_grad()
+        ddp(ids, ids).backward()
+        ddp.finalize_grads()
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        torch.testing.assert_close(q.grad, p.grad, atol=1e-6, rtol=1e-5, msg=lambda m, n=n: f"{n}: {m}")
+
+
+def _dp_worker(rank, world, sparse, method):
+    from zen_repro_b200.trainer import TrainConfig, Trainer
+
+    t = Trainer(TrainConfig(model="tiny-gpt2", micro_batch=2, seq_len=16, precision="fp32", lr=1e-2, data_pool=0,
+                            sparse_embedding=sparse, method=method, top_k=20, bucket_cap_mb=0.05), init_dist=False)
+    losses = [t.step(next(t.data)) for _ in range(6)]
+    w = t.model.unwrap().wte.detach().clone()
+    return losses, w
+
+
+def test_sparse_embedding_rows_match_dense_sync_on_two_ranks():
+    s = run_gloo(_dp_worker, 2, True, 0)
+    d = run_gloo(_dp_worker, 2, False, 0)
+    for r in range(2):
+        assert s[r][0] == pytest.approx(d[r][0], rel=1e-4, abs=1e-4)
+        torch.testing.assert_close(torch.as_tensor(s[r][1]), torch.as_tensor(d[r][1]), atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(torch.as_tensor(s[0][1]), torch.as_tensor(s[1][1]), atol=0, rtol=0)         # replicas stay identical
+
+
+def test_zen_hook_trains_on_two_ranks():
+    out = run_gloo(_dp_worker, 2, False, 3)
+    losses = out[0][0]
+    assert losses[-1] < losses[0]
+    torch.testing.assert_close(torch.as_tensor(out[0][1]), torch.as_tensor(out[1][1]), atol=0, rtol=0)
+
+
+def _tp_worker(rank, world, name):
+    import torch.distributed as dist
+
+    from zen_repro_b200.models.sharding import shard_state_dict
+
+    torch.manual_seed(0)
+    cfg = get_config(name)
+    full = build_model(cfg, dtype=torch.float32)
+    ids = torch.randint(0, cfg.vocab_size, (2, 16))
+    want = full(ids, ids)
+    want.backward()
+    g = dist.group.WORLD
+    sh = build_model(cfg, tp_group=g, dtype=torch.float32)
+    sh.load_state_dict(shard_state_dict(full.state_dict(), cfg, rank, world))
+    got = sh(ids, ids)
+    got.backward()
+    sh.sync_replicated_grads()
+    gfull = shard_state_dict({k: p.grad for k, p in full.named_parameters()}, cfg, rank, world)
+    errs = {k: float((p.grad - gfull[k]).abs().max()) for k, p in sh.named_parameters()}
+    logits = sh(ids)
+    ref_logits = full(ids)
+    return float(want.detach()), float(got.detach()), max(errs.values()), float((logits - ref_logits).abs().max())
+
+
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-gpt2", "tiny-gemma"])
+def test_tensor_parallel_matches_single_rank(name):
+    for want, got, gerr, lerr in run_gloo(_tp_worker, 2, name):
+        assert got == pytest.approx(want, rel=1e-5, abs=1e-5)
+        assert gerr < 1e-4
+        assert lerr < 1e-4
+
+
+def test_mesh_groups():
+    def w(rank, world):
+        from zen_repro_b200.parallel.mesh import ProcessGroupMesh
+
+        m = ProcessGroupMesh(tp_size=2)
+        return m.dp_rank, m.tp_rank, m.get_ranks_in_group(m.dp_group), m.get_ranks_in_group(m.tp_group)
+
+    res = run_gloo(w, 4)
+    assert res[0] == (0, 0, [0, 2], [0, 1])
+    assert res[3] == (1, 1, [1, 3], [2, 3])

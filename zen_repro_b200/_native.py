@@ -15,14 +15,46 @@ import torch
 from . import build as _build
 
 _LOCK = threading.Lock()
-_LIB: ctypes.CDLL | None = None
+_LIB = None
 
 
 class NativeUnavailable(RuntimeError):
     pass
 
 
-def lib() -> ctypes.CDLL:
+# kernels launched by one call of each entry point (entries not listed launch one, helpers launch none)
+KERNELS_PER_CALL = {
+    "zen_gather_push": 3, "zen_densify": 2, "zen_norm_bwd": 2, "zen_colsum": 2, "zen_embedding_bwd_rows": 5,
+    "zen_row_gather_push": 2, "zen_sparse_ctx_size": 0, "zen_row_ctx_size": 0, "zen_adam_tensor_size": 0,
+    "zen_norm_bwd_parts": 0, "zen_colsum_parts": 0, "zen_gemm_error": 0, "zen_sym_alloc": 0, "zen_sym_free": 0,
+    "zen_ipc_get_handle": 0, "zen_ipc_open": 0, "zen_ipc_close": 0, "zen_enable_peer": 0, "zen_ipc_handle_size": 0,
+}
+
+
+class _CountingLib:
+    """Proxy over the CDLL that counts kernel launches issued through it (read by the benchmark)."""
+
+    def __init__(self, cdll: ctypes.CDLL):
+        self._cdll = cdll
+        self.launches = 0
+        self._cache: dict = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._cdll, name)
+            n = KERNELS_PER_CALL.get(name, 1)
+            if n == 0:
+                fn = raw
+            else:
+                def fn(*a, _raw=raw, _n=n, _self=self):
+                    _self.launches += _n
+                    return _raw(*a)
+            self._cache[name] = fn
+        return fn
+
+
+def lib() -> "_CountingLib":
     """The loaded native library; builds it first if the ``.so`` is missing and nvcc exists."""
     global _LIB
     if _LIB is not None:
@@ -35,8 +67,13 @@ def lib() -> ctypes.CDLL:
                     path = _build.build()
                 except Exception as e:  # pragma: no cover - depends on toolchain
                     raise NativeUnavailable(f"native library missing and build failed: {e}") from e
-            _LIB = ctypes.CDLL(str(path))
+            _LIB = _CountingLib(ctypes.CDLL(str(path)))
     return _LIB
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far in this process."""
+    return _LIB.launches if _LIB is not None else 0
 
 
 def available() -> bool:

@@ -84,13 +84,13 @@ __device__ __forceinline__ float block_max(float v, float* sh) {
 }
 
 #define NORM_THREADS 128
-#define NORM_MAXV 8   // up to 128 * 8 * 8 = 8192 columns held in registers
+#define NORM_MAXV 8   // up to 128 * 8 * 8 = 8192 columns held in registers; kernels are instantiated for 1, 2, 4, 8
 
 // --------------------------------------------------------------------------------------------
 // Norm forward.  h = x (+ res); y = (h - mean) * rstd * wgt + bias   (LayerNorm, kLayer)
 //                                y = h * rstd * (wgt or 1 + wgt)     (RMSNorm)
 // `hout` (optional) receives h, the new residual stream.  stats: rstd[rows] (+ mean[rows]).
-template <typename T, bool kLayer>
+template <typename T, bool kLayer, int NV>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ wgt,
                 const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ hout, float* __restrict__ rstd_out,
@@ -99,10 +99,10 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __r
   const int nv = cols / 8;                         // cols % 8 == 0 checked on the host
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const size_t base = (size_t)row * cols;
-    float h[NORM_MAXV][8];
+    float h[NV][8];
     float s = 0.f, ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < NORM_MAXV; ++j) {
+    for (int j = 0; j < NV; ++j) {
       const int v = threadIdx.x + j * NORM_THREADS;
       if (v < nv) {
         Vec8<T>::load(x + base + (size_t)v * 8, h[j]);
@@ -126,7 +126,7 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __r
       mean = block_sum(s, sh) / cols;
       float d2 = 0.f;
 #pragma unroll
-      for (int j = 0; j < NORM_MAXV; ++j) {
+      for (int j = 0; j < NV; ++j) {
         const int v = threadIdx.x + j * NORM_THREADS;
         if (v < nv) {
 #pragma unroll
@@ -140,7 +140,7 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __r
     const float rstd = rsqrtf(var + eps);
     if (threadIdx.x == 0) { rstd_out[row] = rstd; if (kLayer) mean_out[row] = mean; }
 #pragma unroll
-    for (int j = 0; j < NORM_MAXV; ++j) {
+    for (int j = 0; j < NV; ++j) {
       const int v = threadIdx.x + j * NORM_THREADS;
       if (v < nv) {
         float w[8], o[8];
@@ -163,7 +163,7 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __r
 // Norm backward.  dh = grad through the norm (+ dres, the gradient arriving on the residual stream).
 // Per-CTA partial sums of dw (and db) go to part_dw/part_db [gridDim.x][cols] (fp32 scratch) and are
 // folded by colreduce_kernel.
-template <typename T, bool kLayer>
+template <typename T, bool kLayer, int NV>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __restrict__ wgt,
                 const float* __restrict__ rstd_in, const float* __restrict__ mean_in, const T* __restrict__ dres,
@@ -171,19 +171,19 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __re
                 int unit_offset) {
   __shared__ float sh[32];
   const int nv = cols / 8;
-  float aw[NORM_MAXV][8], ab[NORM_MAXV][8];
+  float aw[NV][8], ab[NV][8];
 #pragma unroll
-  for (int j = 0; j < NORM_MAXV; ++j)
+  for (int j = 0; j < NV; ++j)
 #pragma unroll
     for (int i = 0; i < 8; ++i) { aw[j][i] = 0.f; ab[j][i] = 0.f; }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const size_t base = (size_t)row * cols;
     const float rstd = rstd_in[row];
     const float mean = kLayer ? mean_in[row] : 0.f;
-    float g[NORM_MAXV][8], xh[NORM_MAXV][8];
+    float g[NV][8], xh[NV][8];
     float s1 = 0.f, s2 = 0.f;                       // sum(g), sum(g * xhat)
 #pragma unroll
-    for (int j = 0; j < NORM_MAXV; ++j) {
+    for (int j = 0; j < NV; ++j) {
       const int v = threadIdx.x + j * NORM_THREADS;
       if (v < nv) {
         float d[8], w[8];
@@ -204,7 +204,7 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __re
     s2 = block_sum(s2, sh) / cols;
     if (kLayer) s1 = block_sum(s1, sh) / cols; else s1 = 0.f;
 #pragma unroll
-    for (int j = 0; j < NORM_MAXV; ++j) {
+    for (int j = 0; j < NV; ++j) {
       const int v = threadIdx.x + j * NORM_THREADS;
       if (v < nv) {
         float o[8];
@@ -219,7 +219,7 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __re
     }
   }
 #pragma unroll
-  for (int j = 0; j < NORM_MAXV; ++j) {
+  for (int j = 0; j < NV; ++j) {
     const int v = threadIdx.x + j * NORM_THREADS;
     if (v < nv) {
       Vec8<float>::store(part_dw + (size_t)blockIdx.x * cols + (size_t)v * 8, aw[j]);
@@ -228,41 +228,60 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __re
   }
 }
 
-// out[c] = sum_p part[p][c], cast to T.  One thread per column, coalesced over columns.
+// out[c] (+)= sum_p part[p][c], cast to T.  CTA = 32 columns x 32 part-lanes; fixed summation order.
 template <typename T>
-__global__ void colreduce_kernel(const float* __restrict__ part, T* __restrict__ out, int nparts, int cols, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+__global__ void __launch_bounds__(1024)
+colreduce_kernel(const float* __restrict__ part, T* __restrict__ out, int nparts, int cols, int accumulate) {
+  __shared__ float sh[32][33];
+  const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + x;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += part[(size_t)p * cols + c];
-  if (accumulate) s += ZenVal<T>::to_f(out[c]);
-  out[c] = ZenVal<T>::from_f(s);
+  if (c < cols)
+    for (int p = y; p < nparts; p += 32) s += part[(size_t)p * cols + c];
+  sh[y][x] = s;
+  __syncthreads();
+  if (y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t += sh[i][x];
+    if (accumulate) t += ZenVal<T>::to_f(out[c]);
+    out[c] = ZenVal<T>::from_f(t);
+  }
 }
 
-// Column sums of a [rows, cols] matrix into part[gridDim.y][cols] (bias gradients).
+// Column sums of a [rows, cols] matrix: CTA b sums rows [b * COLSUM_ROWS, ...) for every column (thread = one
+// 8-column vector, coalesced along the row) into part[b][cols] (bias gradients).
+#define COLSUM_ROWS 64
 template <typename T>
 __global__ void __launch_bounds__(256) colsum_partial_kernel(const T* __restrict__ a, float* __restrict__ part, int rows, int cols) {
-  const int c8 = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
-  if (c8 >= cols) return;
-  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int r = blockIdx.y; r < rows; r += gridDim.y) {
-    float v[8];
-    Vec8<T>::load(a + (size_t)r * cols + c8, v);
+  const int r0 = blockIdx.x * COLSUM_ROWS, r1 = min(rows, r0 + COLSUM_ROWS);
+  for (int c8 = threadIdx.x * 8; c8 < cols; c8 += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 8
+    for (int r = r0; r < r1; ++r) {
+      float v[8];
+      Vec8<T>::load(a + (size_t)r * cols + c8, v);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] += v[i];
+      for (int i = 0; i < 8; ++i) acc[i] += v[i];
+    }
+    Vec8<float>::store(part + (size_t)blockIdx.x * cols + c8, acc);
   }
-  Vec8<float>::store(part + (size_t)blockIdx.y * cols + c8, acc);
 }
 
 // --------------------------------------------------------------------------------------------
 // Activations.  mode: 0 gelu(tanh) 1 relu 2 silu(a)*b 3 gelu_tanh(a)*b
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));   // max relative error about 2^-11, below bf16 resolution
+  return y;
+}
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k = 0.7978845608028654f;
-  return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+  return 0.5f * x * (1.f + tanh_fast(k * (x + 0.044715f * x * x * x)));
 }
 __device__ __forceinline__ float gelu_tanh_grad(float x) {
   const float k = 0.7978845608028654f;
-  const float t = tanhf(k * (x + 0.044715f * x * x * x));
+  const float t = tanh_fast(k * (x + 0.044715f * x * x * x));
   return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x * x);
 }
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
@@ -468,8 +487,10 @@ rows_add_kernel(T* __restrict__ grad, const int32_t* __restrict__ rows, const in
 template <typename T>
 __global__ void __launch_bounds__(512)
 xent_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels, float* __restrict__ loss,
-            T* __restrict__ dlogits, int rows, int vocab, int ld, float gscale, int64_t ignore_index) {
+            T* __restrict__ dlogits, int rows, int vocab, int ld, float gscale_host, const float* __restrict__ gscale_dev,
+            int64_t ignore_index) {
   __shared__ float sh[32];
+  const float gscale = gscale_dev ? gscale_host * (*gscale_dev) : gscale_host;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const T* lp = logits + (size_t)row * ld;
     T* dp = dlogits ? dlogits + (size_t)row * ld : nullptr;
@@ -617,7 +638,13 @@ inline int cap_grid(size_t want, int mult) {
 extern "C" {
 
 // Number of per-CTA partial rows the norm backward writes (the caller sizes its scratch with this).
-int zen_norm_bwd_parts(int rows) { return cap_grid((size_t)rows, 4); }
+int zen_norm_bwd_parts(int rows) { return cap_grid((size_t)rows, 2); }
+
+#define NORM_NV_DISPATCH(cols, ...)                                   \
+  if (cols <= NORM_THREADS * 8) { constexpr int NV = 1; __VA_ARGS__; } \
+  else if (cols <= NORM_THREADS * 16) { constexpr int NV = 2; __VA_ARGS__; } \
+  else if (cols <= NORM_THREADS * 32) { constexpr int NV = 4; __VA_ARGS__; } \
+  else { constexpr int NV = 8; __VA_ARGS__; }
 
 int zen_norm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* hout, float* rstd,
                  float* mean, int rows, int cols, float eps, int layer, int unit_offset, int dtype, void* stream) {
@@ -625,8 +652,10 @@ int zen_norm_fwd(const void* x, const void* res, const void* w, const void* b, v
   cudaStream_t st = (cudaStream_t)stream;
   const int grid = cap_grid((size_t)rows, 16);
   DISPATCH_T(dtype, {
-    if (layer) norm_fwd_kernel<T, true><<<grid, NORM_THREADS, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b, (T*)y, (T*)hout, rstd, mean, rows, cols, eps, unit_offset);
-    else norm_fwd_kernel<T, false><<<grid, NORM_THREADS, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b, (T*)y, (T*)hout, rstd, mean, rows, cols, eps, unit_offset);
+    NORM_NV_DISPATCH(cols, {
+      if (layer) norm_fwd_kernel<T, true, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b, (T*)y, (T*)hout, rstd, mean, rows, cols, eps, unit_offset);
+      else norm_fwd_kernel<T, false, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b, (T*)y, (T*)hout, rstd, mean, rows, cols, eps, unit_offset);
+    });
   });
   return (int)cudaGetLastError();
 }
@@ -640,25 +669,26 @@ int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd
   cudaStream_t st = (cudaStream_t)stream;
   const int grid = zen_norm_bwd_parts(rows);
   DISPATCH_T(dtype, {
-    if (layer) norm_bwd_kernel<T, true><<<grid, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
-    else norm_bwd_kernel<T, false><<<grid, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
-    colreduce_kernel<T><<<(cols + 127) / 128, 128, 0, st>>>(part_dw, (T*)dw, grid, cols, accumulate);
-    if (layer && db) colreduce_kernel<T><<<(cols + 127) / 128, 128, 0, st>>>(part_db, (T*)db, grid, cols, accumulate);
+    NORM_NV_DISPATCH(cols, {
+      if (layer) norm_bwd_kernel<T, true, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+      else norm_bwd_kernel<T, false, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+    });
+    colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, grid, cols, accumulate);
+    if (layer && db) colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_db, (T*)db, grid, cols, accumulate);
   });
   return (int)cudaGetLastError();
 }
 
-int zen_colsum_parts(int rows) { int p = rows / 64; return p < 1 ? 1 : (p > 64 ? 64 : p); }
+int zen_colsum_parts(int rows) { return (rows + COLSUM_ROWS - 1) / COLSUM_ROWS; }
 
 // out[c] (+)= sum_r a[r][c]; part: fp32 scratch zen_colsum_parts(rows) * cols.
 int zen_colsum(const void* a, float* part, void* out, int rows, int cols, int accumulate, int dtype, void* stream) {
   if (cols % 8) return -2;
   cudaStream_t st = (cudaStream_t)stream;
   const int parts = zen_colsum_parts(rows);
-  dim3 grid((cols / 8 + 255) / 256, parts);
   DISPATCH_T(dtype, {
-    colsum_partial_kernel<T><<<grid, 256, 0, st>>>((const T*)a, part, rows, cols);
-    colreduce_kernel<T><<<(cols + 127) / 128, 128, 0, st>>>(part, (T*)out, parts, cols, accumulate);
+    colsum_partial_kernel<T><<<parts, 256, 0, st>>>((const T*)a, part, rows, cols);
+    colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part, (T*)out, parts, cols, accumulate);
   });
   return (int)cudaGetLastError();
 }
@@ -720,9 +750,10 @@ int zen_rows_add(void* grad, const int32_t* rows, const int32_t* count, const vo
   return (int)cudaGetLastError();
 }
 
+// gscale_dev (optional device float) multiplies gscale; lets the caller scale by 1 / (valid tokens) without a host sync.
 int zen_xent(const void* logits, const int64_t* labels, float* loss, void* dlogits, int rows, int vocab, int ld,
-             float gscale, int64_t ignore_index, int dtype, void* stream) {
-  DISPATCH_T(dtype, xent_kernel<T><<<cap_grid((size_t)rows, 8), 512, 0, (cudaStream_t)stream>>>((const T*)logits, labels, loss, (T*)dlogits, rows, vocab, ld, gscale, ignore_index));
+             float gscale, const float* gscale_dev, int64_t ignore_index, int dtype, void* stream) {
+  DISPATCH_T(dtype, xent_kernel<T><<<cap_grid((size_t)rows, 8), 512, 0, (cudaStream_t)stream>>>((const T*)logits, labels, loss, (T*)dlogits, rows, vocab, ld, gscale, gscale_dev, ignore_index));
   return (int)cudaGetLastError();
 }
 

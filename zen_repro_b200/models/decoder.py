@@ -39,6 +39,7 @@ class Block(nn.Module):
         assert cfg.num_heads % tp == 0 and (cfg.num_kv_heads % tp == 0 or cfg.num_kv_heads < tp)
         self.hq = cfg.num_heads // tp
         self.hkv = max(1, cfg.num_kv_heads // tp)         # MQA under TP replicates the single KV head
+        self.kv_replicated = cfg.num_kv_heads < tp
         self.inner = cfg.intermediate_size // tp
         kw = dict(device=device, dtype=dtype)
         qkv_out = (self.hq + 2 * self.hkv) * hd
@@ -193,6 +194,24 @@ class DecoderLM(nn.Module):
         tgt = O.reduce_from_tp(tgt, g)
         loss = (s.log() + m - tgt) * valid
         return loss.sum() / valid.sum().clamp(min=1)
+
+    def sync_replicated_grads(self):
+        """Sum over the TP group the gradients of weights that are replicated but see only part of the work: the
+        k / v projections when there are fewer KV heads than TP ranks (each rank back-propagates its own query
+        heads through the same KV head)."""
+        _, tp = _tp(self.tp_group)
+        if tp == 1:
+            return
+        for b in self.blocks:
+            if not b.kv_replicated or b.qkv_w.grad is None:
+                continue
+            lo = b.hq * self.cfg.head_dim
+            gw = b.qkv_w.grad[:, lo:] if self.cfg.weight_layout == "in_out" else b.qkv_w.grad[lo:]
+            buf = gw.contiguous()
+            dist.all_reduce(buf, group=self.tp_group)
+            gw.copy_(buf)
+            if b.qkv_b is not None and b.qkv_b.grad is not None:
+                dist.all_reduce(b.qkv_b.grad[lo:], group=self.tp_group)
 
     # ---- HuggingFace-format state dicts ---------------------------------------------------------
     def hf_state_dict(self) -> dict:

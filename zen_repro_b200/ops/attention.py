@@ -12,6 +12,11 @@ import torch
 import torch.nn.functional as F
 
 
+def have_kernel(seq, hq, hkv, hd, dtype) -> bool:
+    """True when the hand-written attention kernels cover this shape."""
+    return False
+
+
 def _split(qkv, bsz, seq, hq, hkv, hd):
     t = qkv.view(bsz, seq, hq + 2 * hkv, hd)
     q = t[:, :, :hq].transpose(1, 2)

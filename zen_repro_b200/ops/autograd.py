@@ -15,6 +15,25 @@ from . import gemm as G
 from . import attention as A
 
 
+def _claim(p) -> bool:
+    """Called in forward.  True when this op will ADD its gradient for ``p`` straight into ``p.grad`` (a bucket
+    view of the data-parallel reducer) and signal ``p.zen_ready``; the claim is counted so that the reducer knows
+    how many such signals to expect before the parameter's bucket may be sent."""
+    if p is None or not getattr(p, "zen_direct_grad", False) or p.grad is None:
+        return False
+    if not (torch.is_grad_enabled() and p.requires_grad):
+        return False
+    p.zen_expected = getattr(p, "zen_expected", 0) + 1
+    return True
+
+
+def _declare_autograd_use(p) -> None:
+    """Called in forward by an op whose gradient for ``p`` travels through autograd although other ops write
+    theirs directly: the reducer then also waits for the accumulate-grad hook of ``p``."""
+    if p is not None and getattr(p, "zen_direct_grad", False) and torch.is_grad_enabled() and p.requires_grad:
+        p.zen_autograd_use = True
+
+
 class LinearFn(torch.autograd.Function):
     """y = x @ W^T + b with W stored [out, in] ("out_in", nn.Linear) or [in, out] ("in_out", GPT-2 Conv1D)."""
 
@@ -30,6 +49,8 @@ class LinearFn(torch.autograd.Function):
             y = G.gemm_nn(x2, weight, bias=bias)
             n = weight.shape[1]
         ctx.save_for_backward(x2, weight)
+        ctx.params = (weight, bias)
+        ctx.direct = (_claim(weight), _claim(bias))
         ctx.xshape = x.shape
         return y if x.dim() == 2 else y.view(*x.shape[:-1], n)
 
@@ -42,10 +63,20 @@ class LinearFn(torch.autograd.Function):
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = (G.gemm_nn(dy2, weight) if ctx.layout == "out_in" else G.gemm_nt(dy2, weight)).view(ctx.xshape)
+        wp, bp = ctx.params
         if ctx.needs_input_grad[1]:
-            dw = G.gemm_tn(dy2, x2) if ctx.layout == "out_in" else G.gemm_tn(x2, dy2)
+            a, b = (dy2, x2) if ctx.layout == "out_in" else (x2, dy2)
+            if ctx.direct[0]:
+                G.gemm_tn(a, b, out=wp.grad, accumulate=True)
+                wp.zen_ready(wp)
+            else:
+                dw = G.gemm_tn(a, b)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = E.colsum(dy2)
+            if ctx.direct[1]:
+                E.colsum(dy2, out=bp.grad)
+                bp.zen_ready(bp)
+            else:
+                db = E.colsum(dy2)
         return dx, dw, db, None
 
 
@@ -61,14 +92,25 @@ class NormFn(torch.autograd.Function):
         y, h, rstd, mean = E.norm_fwd(x, weight, bias, residual, eps=eps, layer=layer, unit_offset=unit_offset)
         ctx.save_for_backward(h, weight, rstd, mean if mean is not None else rstd)
         ctx.cfg = (layer, unit_offset, bias is not None, residual is not None)
+        ctx.params = (weight, bias)
+        cw = _claim(weight)
+        ctx.direct = cw and (bias is None or _claim(bias))
         return y, h
 
     @staticmethod
     def backward(ctx, dy, dh_in):
         h, weight, rstd, mean = ctx.saved_tensors
         layer, unit_offset, has_bias, has_res = ctx.cfg
+        wp, bp = ctx.params
+        direct = ctx.direct
         dh, dw, db = E.norm_bwd(dy.contiguous(), h, weight, rstd, mean if layer else None, dh_in,
-                                layer=layer, unit_offset=unit_offset, has_bias=has_bias)
+                                layer=layer, unit_offset=unit_offset, has_bias=has_bias,
+                                dw_out=wp.grad if direct else None, db_out=bp.grad if (direct and bp is not None) else None)
+        if direct:
+            wp.zen_ready(wp)
+            if bp is not None:
+                bp.zen_ready(bp)
+            dw = db = None
         return dh, (dh if has_res else None), dw, db, None, None, None
 
 
@@ -146,6 +188,8 @@ class EmbeddingFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ids, wte, wpe, seq, pos_offset, scale, sparse_sink, vocab_start):
         local = ids - vocab_start if vocab_start else ids
+        if sparse_sink is None:
+            _declare_autograd_use(wte)
         out = E.embedding_fwd(local, wte, wpe, seq=seq, pos_offset=pos_offset, scale=scale)
         ctx.save_for_backward(local)
         ctx.cfg = (wte.shape, wte.dtype, wpe.shape if wpe is not None else None, seq, pos_offset, scale, sparse_sink)
@@ -177,44 +221,57 @@ def embedding(ids, wte, wpe=None, seq=1, pos_offset=0, scale=1.0, sparse_sink=No
 
 class LMHeadLossFn(torch.autograd.Function):
     """mean cross-entropy(h @ W^T, labels).  Logits are computed, turned into dlogits in place by one
-    kernel, and immediately consumed by the two gradient GEMMs; only dh and dW survive the forward."""
+    kernel (already scaled by 1 / valid-token-count, read from the device), and immediately consumed
+    by the two gradient GEMMs; only dh and dW survive the forward.  The incoming gradient of the loss
+    is assumed to be 1 (``unit_grad``); otherwise the saved gradients are rescaled in backward."""
 
     @staticmethod
-    def forward(ctx, h, weight, labels, ignore_index, chunk_tokens):
+    def forward(ctx, h, weight, labels, ignore_index, chunk_tokens, unit_grad):
         h2 = h.reshape(-1, h.shape[-1])
         lab = labels.reshape(-1)
         T = h2.shape[0]
-        nvalid = (lab != ignore_index).sum().clamp_(min=1).to(torch.float32)
+        inv = 1.0 / (lab != ignore_index).sum().clamp_(min=1).to(torch.float32).reshape(1)
         V = weight.shape[0]
         vpad = (V + 7) // 8 * 8
         dh = torch.empty_like(h2)
-        dw = torch.zeros(weight.shape, dtype=torch.float32 if h2.is_cuda else weight.dtype, device=h2.device)
+        direct = unit_grad and _claim(weight)
+        if not direct:
+            _declare_autograd_use(weight)
+        nchunks = (T + chunk_tokens - 1) // chunk_tokens
+        if direct:
+            dw = weight.grad
+        else:
+            dw = torch.zeros(weight.shape, dtype=torch.float32 if (h2.is_cuda and nchunks > 1) else weight.dtype,
+                             device=h2.device)
         loss_sum = torch.zeros((), dtype=torch.float32, device=h2.device)
         for s in range(0, T, chunk_tokens):
             e = min(T, s + chunk_tokens)
             buf = torch.empty(e - s, vpad, dtype=h2.dtype, device=h2.device)
             logits = buf[:, :V]
             G.gemm_nt(h2[s:e], weight, out=logits)
-            # gradient is scaled by 1 / T here and corrected to 1 / nvalid below without a host sync
-            loss, dl = E.cross_entropy(logits, lab[s:e], grad_scale=1.0, ignore_index=ignore_index)
+            loss, dl = E.cross_entropy(logits, lab[s:e], grad_scale=1.0, grad_scale_dev=inv, ignore_index=ignore_index)
             loss_sum += loss.sum()
-            dh[s:e] = G.gemm_nn(dl, weight)
+            G.gemm_nn(dl, weight, out=dh[s:e])
             G.gemm_tn(dl, h2[s:e], out=dw, accumulate=True)
-        inv = 1.0 / nvalid
-        ctx.save_for_backward(dh, dw, inv)
-        ctx.hshape = h.shape
-        ctx.wdtype = weight.dtype
-        return loss_sum * inv
+        ctx.save_for_backward(dh, dw if not direct else dh)
+        ctx.cfg = (h.shape, weight.dtype, direct, unit_grad)
+        ctx.wp = weight
+        return loss_sum * inv.squeeze(0)
 
     @staticmethod
     def backward(ctx, g):
-        dh, dw, inv = ctx.saved_tensors
-        s = (g * inv)
-        return (dh.float() * s).to(dh.dtype).view(ctx.hshape), (dw.float() * s).to(ctx.wdtype), None, None, None
+        dh, dw = ctx.saved_tensors
+        hshape, wdtype, direct, unit = ctx.cfg
+        if direct:
+            ctx.wp.zen_ready(ctx.wp)
+            return dh.view(hshape), None, None, None, None, None
+        if unit:
+            return dh.view(hshape), dw.to(wdtype), None, None, None, None
+        return (dh.float() * g).to(dh.dtype).view(hshape), (dw.float() * g).to(wdtype), None, None, None, None
 
 
-def lm_head_loss(h, weight, labels, ignore_index=-100, chunk_tokens=8192):
-    return LMHeadLossFn.apply(h, weight, labels, ignore_index, chunk_tokens)
+def lm_head_loss(h, weight, labels, ignore_index=-100, chunk_tokens=8192, unit_grad=True):
+    return LMHeadLossFn.apply(h, weight, labels, ignore_index, chunk_tokens, unit_grad)
 
 
 class AttentionFn(torch.autograd.Function):
@@ -235,7 +292,13 @@ class AttentionFn(torch.autograd.Function):
 
 
 def attention(qkv, bsz, seq, hq, hkv, hd, scale=None):
-    return AttentionFn.apply(qkv, bsz, seq, hq, hkv, hd, scale if scale is not None else 1.0 / math.sqrt(hd))
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    if qkv.is_cuda and not A.have_kernel(seq, hq, hkv, hd, qkv.dtype):
+        # library fallback under plain autograd (keeps the forward's softmax statistics, no recompute)
+        q, k, v = A._split(qkv, bsz, seq, hq, hkv, hd)
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale, enable_gqa=(hq != hkv))
+        return o.transpose(1, 2).reshape(bsz * seq, hq * hd)
+    return AttentionFn.apply(qkv, bsz, seq, hq, hkv, hd, scale)
 
 
 # ------------------------------------------------------------------------------------------ tensor parallel

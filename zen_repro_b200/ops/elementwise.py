@@ -73,8 +73,10 @@ def norm_fwd(x, weight, bias=None, residual=None, *, eps=1e-5, layer=False, unit
     return y.view(x.shape), h.view(x.shape), rstd, mean
 
 
-def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_offset=False, has_bias=False):
-    """Returns (dh, dweight, dbias): dh includes ``dres`` (gradient on the residual stream) when given."""
+def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_offset=False, has_bias=False,
+             dw_out=None, db_out=None):
+    """Returns (dh, dweight, dbias): dh includes ``dres`` (gradient on the residual stream) when given.
+    With ``dw_out`` / ``db_out`` the parameter gradients are ADDED into those tensors instead."""
     cols = h.shape[-1]
     dy2, h2 = _c(dy).view(-1, cols), _c(h).view(-1, cols)
     rows = h2.shape[0]
@@ -93,34 +95,44 @@ def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_off
         db = g.sum(0).to(weight.dtype) if (layer and has_bias) else None
         if dres is not None:
             dh = dh + dres.reshape(-1, cols).float()
+        if dw_out is not None:
+            dw_out.add_(dw)
+            dw = dw_out
+        if db_out is not None and db is not None:
+            db_out.add_(db)
+            db = db_out
         return dh.to(h.dtype).view(h.shape), dw, db
     lib = _native.lib()
     parts = lib.zen_norm_bwd_parts(rows)
     part_dw = _scratch_buf("norm_dw", parts * cols, torch.float32, h.device)
     part_db = _scratch_buf("norm_db", parts * cols, torch.float32, h.device) if layer else None
     dh = torch.empty_like(h2)
-    dw = torch.empty_like(weight)
-    db = torch.empty_like(weight) if (layer and has_bias) else None
+    acc = dw_out is not None
+    dw = dw_out if acc else torch.empty_like(weight)
+    db = (db_out if acc else torch.empty_like(weight)) if (layer and has_bias) else None
     dres2 = _c(dres).view(-1, cols) if dres is not None else None
     rc = lib.zen_norm_bwd(_native.ptr(dy2), _native.ptr(h2), _native.ptr(weight), _native.ptr(rstd), _native.ptr(mean),
                           _native.ptr(dres2), _native.ptr(dh), _native.ptr(part_dw), _native.ptr(part_db),
-                          _native.ptr(dw), _native.ptr(db), rows, cols, int(layer), int(unit_offset), 0, _code(h2),
+                          _native.ptr(dw), _native.ptr(db), rows, cols, int(layer), int(unit_offset), int(acc), _code(h2),
                           _native.stream_ptr())
     _native.check(rc, "zen_norm_bwd")
     return dh.view(h.shape), dw, db
 
 
-def colsum(a: torch.Tensor) -> torch.Tensor:
-    """Column sums of a [rows, cols] matrix (bias gradients)."""
+def colsum(a: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Column sums of a [rows, cols] matrix (bias gradients); added into ``out`` when given."""
     cols = a.shape[-1]
     a2 = _c(a).view(-1, cols)
     if not a.is_cuda:
-        return a2.float().sum(0).to(a.dtype)
+        r = a2.float().sum(0).to(a.dtype)
+        return r if out is None else out.add_(r)
     lib = _native.lib()
     rows = a2.shape[0]
     part = _scratch_buf("colsum", lib.zen_colsum_parts(rows) * cols, torch.float32, a.device)
-    out = torch.empty(cols, dtype=a.dtype, device=a.device)
-    _native.check(lib.zen_colsum(_native.ptr(a2), _native.ptr(part), _native.ptr(out), rows, cols, 0, _code(a2),
+    acc = out is not None
+    if out is None:
+        out = torch.empty(cols, dtype=a.dtype, device=a.device)
+    _native.check(lib.zen_colsum(_native.ptr(a2), _native.ptr(part), _native.ptr(out), rows, cols, int(acc), _code(a2),
                                  _native.stream_ptr()), "zen_colsum")
     return out
 
@@ -281,7 +293,8 @@ def rows_add_(grad, rows, count, vals) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- cross entropy
-def cross_entropy(logits, labels, *, grad_scale: float | None = None, ignore_index: int = -100, inplace_grad=True):
+def cross_entropy(logits, labels, *, grad_scale: float | None = None, ignore_index: int = -100, inplace_grad=True,
+                  grad_scale_dev: torch.Tensor | None = None):
     """Per-row loss (fp32) and, when ``grad_scale`` is given, dlogits = (softmax - onehot) * grad_scale.
 
     With ``inplace_grad`` the gradient overwrites ``logits`` (they are not needed afterwards).
@@ -299,7 +312,8 @@ def cross_entropy(logits, labels, *, grad_scale: float | None = None, ignore_ind
             valid = lb != ignore_index
             onehot = torch.zeros_like(p)
             onehot[valid, lb[valid]] = 1.0
-            d = ((p - onehot) * grad_scale * valid[:, None]).to(logits.dtype)
+            gs = grad_scale * (float(grad_scale_dev) if grad_scale_dev is not None else 1.0)
+            d = ((p - onehot) * gs * valid[:, None]).to(logits.dtype)
             if inplace_grad:
                 lg.copy_(d)
                 d = lg
@@ -311,7 +325,8 @@ def cross_entropy(logits, labels, *, grad_scale: float | None = None, ignore_ind
         d = lg if inplace_grad else torch.empty_like(lg)
         assert d.stride(0) == lg.stride(0)
     rc = _native.lib().zen_xent(_native.ptr(lg), _native.ptr(lb), _native.ptr(loss), _native.ptr(d), rows, vocab,
-                                lg.stride(0), ctypes.c_float(grad_scale or 0.0), ctypes.c_int64(ignore_index),
+                                lg.stride(0), ctypes.c_float(grad_scale or 0.0), _native.ptr(grad_scale_dev),
+                                ctypes.c_int64(ignore_index),
                                 _code(lg), _native.stream_ptr())
     _native.check(rc, "zen_xent")
     return loss, d

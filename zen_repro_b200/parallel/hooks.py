@@ -1,0 +1,124 @@
+"""Gradient sparsifier and the ZEN communication hook.
+
+``compress_with_allgather`` is the sampled top-k sparsifier of the reference (train.py:56-73): buckets
+of at most 4096 elements pass unchanged; otherwise 1 % of |g| is sampled at random positions (with
+replacement), the samples are all-gathered across the tensor-parallel group so that every TP shard of
+a replica uses one threshold, the top ``k`` % of the gathered samples are taken and their minimum is
+the threshold.  Here the threshold stays on the device and is handed to the partition kernel, which
+applies ``|g| >= thr`` while it scans, so the masked bucket is never written.
+
+``make_zen_comm_hook`` returns a DDP-style hook ``hook(state, bucket) -> Future`` (train.py:167-183)
+that works with ``ZenDDP`` and with ``torch.nn.parallel.DistributedDataParallel.register_comm_hook``.
+Methods 1-3 return the SUM over data-parallel ranks, as the reference does.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..sparse import torch_pipeline
+from ..utils.trace import trace_range
+
+SMALL_BUCKET = 4096
+
+
+def sampled_threshold(tensor: torch.Tensor, top_k: float, group=None, generator=None) -> torch.Tensor | None:
+    """Device scalar threshold on |tensor| (None for buckets of at most 4096 elements)."""
+    flat = tensor.reshape(-1)
+    numel = flat.numel()
+    if numel <= SMALL_BUCKET:
+        return None
+    ns = math.ceil(0.01 * numel)
+    pos = torch.randint(0, numel, (ns,), device=flat.device, generator=generator)
+    sample = flat[pos].abs()
+    if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+        gathered = torch.empty(dist.get_world_size(group) * ns, device=flat.device, dtype=sample.dtype)
+        dist.all_gather_into_tensor(gathered, sample, group=group)
+        sample = gathered
+    k = max(1, int(sample.numel() * top_k // 100))
+    with trace_range("topk"):
+        top = torch.topk(sample, k, 0, largest=True, sorted=False)[0]
+    with trace_range("min"):
+        return top.min().float().reshape(1)
+
+
+def compress_with_allgather(top_k: float, tensor: torch.Tensor, pg_group=None) -> torch.Tensor:
+    """Materialising form (API parity): where(|g| >= thr, g, 0)."""
+    thr = sampled_threshold(tensor, top_k, pg_group)
+    if thr is None:
+        return tensor
+    with trace_range("where"):
+        return torch.where(tensor.abs() >= thr.to(tensor.dtype), tensor, torch.zeros((), device=tensor.device, dtype=tensor.dtype))
+
+
+def compress(top_k: float, tensor: torch.Tensor) -> torch.Tensor:
+    """Local form without the cross-group sample exchange (train.py:75-84)."""
+    return compress_with_allgather(top_k, tensor, None)
+
+
+class _Ready:
+    """Minimal completed future for reducers that do not need ``torch.futures``."""
+
+    def __init__(self, value):
+        self._v = value
+
+    def wait(self):
+        return self._v
+
+    def value(self):
+        return self._v
+
+
+def _future(value, like_torch: bool):
+    if like_torch:
+        f = torch.futures.Future()
+        f.set_result(value)
+        return f
+    return _Ready(value)
+
+
+def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, engines: dict | None = None,
+                       skip_first: bool = False, torch_future: bool = True, max_density: float | None = None):
+    """Build the hook.  ``engines`` caches one CUDA ``SparseAllReduce`` per bucket size (create them with
+    ``prepare_engines`` before training so that buffer exchange does not happen inside backward)."""
+    state = {"skip": skip_first, "engines": engines if engines is not None else {}}
+    P = dist.get_world_size(dp_group) if dist.is_initialized() else 1
+    density = max_density if max_density is not None else min(1.0, top_k / 100.0 * 2.0 + 0.01)
+
+    def engine_for(numel: int, device):
+        eng = state["engines"].get(numel)
+        if eng is None and device.type == "cuda":
+            from ..sparse.engine import SparseAllReduce
+
+            eng = SparseAllReduce(numel, dp_group, max_density=density, methods=(1, 2, 3))
+            state["engines"][numel] = eng
+        return eng
+
+    def hook(_state, bucket):
+        buf = bucket.buffer()
+        if state["skip"]:
+            state["skip"] = False
+            return _future(buf, torch_future)
+        with trace_range("compress"):
+            thr = sampled_threshold(buf, top_k, tp_group)
+        if P <= 1:
+            if thr is not None:
+                buf.copy_(torch.where(buf.abs() >= thr.to(buf.dtype), buf, torch.zeros((), device=buf.device, dtype=buf.dtype)))
+            return _future(buf, torch_future)
+        if buf.device.type == "cuda" and buf.numel() > SMALL_BUCKET:
+            eng = engine_for(buf.numel(), buf.device)
+            out = eng(buf, method=method, threshold=thr)
+        else:
+            masked = buf if thr is None else torch.where(buf.abs() >= thr.to(buf.dtype), buf, torch.zeros_like(buf))
+            if buf.numel() <= SMALL_BUCKET:
+                out = masked.clone()
+                dist.all_reduce(out, group=dp_group)
+            else:
+                out = torch_pipeline.dist_sparse_allreduce(masked, dp_group, method=method if method in (1, 2, 3) else 3)
+        return _future(out, torch_future)
+
+    hook.engine_for = engine_for
+    hook.state = state
+    return hook

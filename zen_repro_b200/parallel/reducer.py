@@ -1,0 +1,220 @@
+"""Data-parallel gradient reducer with bucketed, overlapped communication and DDP-style comm hooks.
+
+``ZenDDP`` wraps a module the way ``torch.nn.parallel.DistributedDataParallel`` does for the
+reference (through ColossalAI's plugin, train.py:157,184-185): parameters are packed into flat
+buckets of ``bucket_cap_mb`` in reverse registration order, ``param.grad`` are views of those buffers,
+a bucket's communication starts as soon as its last gradient has been accumulated, on a side stream
+that waits for the producing stream, and ``finalize_grads()`` joins everything before the optimizer
+step.  ``register_comm_hook(state, hook)`` takes hooks with torch's signature
+``hook(state, bucket) -> Future[Tensor]``; the default is an averaged dense all-reduce.
+Parameters flagged ``zen_sparse_only`` (an untied embedding whose gradient exists only as sparse rows)
+stay out of the buckets and are filled by the embedding row synchroniser.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..utils.trace import trace_range
+
+
+class GradBucket:
+    """The part of ``torch.distributed.GradBucket`` that hooks use."""
+
+    def __init__(self, index: int, buffer: torch.Tensor, params: list, last: bool):
+        self._index, self._buffer, self._params, self._last = index, buffer, params, last
+
+    def index(self) -> int:
+        return self._index
+
+    def buffer(self) -> torch.Tensor:
+        return self._buffer
+
+    def set_buffer(self, t: torch.Tensor) -> None:
+        self._buffer.copy_(t)
+
+    def is_last(self) -> bool:
+        return self._last
+
+    def parameters(self) -> list:
+        return list(self._params)
+
+    def gradients(self) -> list:
+        return [p.grad for p in self._params]
+
+
+class _Bucket:
+    def __init__(self, index, params, dtype, device):
+        self.index, self.params = index, params
+        sizes = [(p.numel() + 7) // 8 * 8 for p in params]          # 16-byte aligned views for bf16
+        self.buffer = torch.zeros(sum(sizes), dtype=dtype, device=device)
+        self.views, off = [], 0
+        for p, s in zip(params, sizes):
+            self.views.append(self.buffer[off:off + p.numel()].view(p.shape))
+            off += s
+        self.pending = len(params)
+        self.future = None
+        self.launched = False
+
+
+class ZenDDP(nn.Module):
+    def __init__(self, module: nn.Module, process_group=None, bucket_cap_mb: float = 25.0, embedding_sync=None,
+                 overlap: bool = True):
+        super().__init__()
+        self.module = module
+        self.process_group = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.embedding_sync = embedding_sync
+        self._hook, self._hook_state = None, None
+        params = [p for p in module.parameters() if p.requires_grad]
+        self.device = params[0].device
+        self._sparse_only = [p for p in params if getattr(p, "zen_sparse_only", False)]
+        dense = [p for p in params if not getattr(p, "zen_sparse_only", False)]
+        cap = int(bucket_cap_mb * 1024 * 1024)
+        self.buckets: list[_Bucket] = []
+        cur, cur_bytes, cur_dtype = [], 0, None
+        for p in reversed(dense):
+            nbytes = p.numel() * p.element_size()
+            if cur and (cur_bytes + nbytes > cap or p.dtype != cur_dtype):
+                self.buckets.append(_Bucket(len(self.buckets), cur, cur_dtype, self.device))
+                cur, cur_bytes = [], 0
+            cur.append(p)
+            cur_bytes += nbytes
+            cur_dtype = p.dtype
+        if cur:
+            self.buckets.append(_Bucket(len(self.buckets), cur, cur_dtype, self.device))
+        self._bucket_of, self._view_of = {}, {}
+        for b in self.buckets:
+            for p, v in zip(b.params, b.views):
+                p.grad = v
+                self._bucket_of[id(p)] = b
+                self._view_of[id(p)] = v
+                p.register_post_accumulate_grad_hook(self._on_autograd_ready)
+                # ops that can add their result into the bucket view themselves do so and call zen_ready
+                p.zen_direct_grad = True
+                p.zen_ready = self._on_grad_ready
+        for p in self._sparse_only:
+            p.grad = torch.zeros_like(p)
+        self._cuda = self.device.type == "cuda"
+        self.comm_stream = torch.cuda.Stream() if (self._cuda and overlap) else None
+        self._launched = 0
+        self.require_sync = True
+
+    # ---- torch DDP surface --------------------------------------------------------------------
+    def forward(self, *a, **kw):
+        return self.module(*a, **kw)
+
+    def register_comm_hook(self, state, hook) -> None:
+        self._hook_state, self._hook = state, hook
+
+    def no_sync(self):
+        ddp = self
+
+        class _Ctx:
+            def __enter__(self_):
+                ddp.require_sync = False
+
+            def __exit__(self_, *exc):
+                ddp.require_sync = True
+
+        return _Ctx()
+
+    # ---- reduction --------------------------------------------------------------------------------
+    def _default_hook(self, _state, bucket: GradBucket):
+        buf = bucket.buffer()
+        if self.world > 1:
+            buf.div_(self.world)
+            dist.all_reduce(buf, group=self.process_group)
+        from .hooks import _Ready
+
+        return _Ready(buf)
+
+    def _on_autograd_ready(self, p):
+        p.zen_autograd_done = True
+        self._on_grad_ready(p, from_autograd=True)
+
+    def _on_grad_ready(self, p, from_autograd: bool = False):
+        """A gradient contribution for ``p`` has landed in its bucket view.  A parameter is complete when every
+        op that claimed a direct write has signalled and, if an autograd-path use was declared (or happened), the
+        accumulate-grad hook has fired; its bucket goes out when all its parameters are complete."""
+        b = self._bucket_of[id(p)]
+        v = self._view_of[id(p)]
+        if p.grad.data_ptr() != v.data_ptr():
+            # autograd replaced the view (first accumulation into an undefined grad): copy back in
+            v.copy_(p.grad)
+            p.grad = v
+        if not from_autograd:
+            p.zen_signals = getattr(p, "zen_signals", 0) + 1
+        done_direct = getattr(p, "zen_signals", 0) == getattr(p, "zen_expected", 0)
+        done_auto = getattr(p, "zen_autograd_done", False) or not getattr(p, "zen_autograd_use", False)
+        if done_direct and done_auto and not getattr(p, "zen_complete", False):
+            p.zen_complete = True
+            b.pending -= 1
+            if b.pending == 0 and self.require_sync and not b.launched:
+                self._launch(b)
+
+    def _launch(self, b: _Bucket):
+        hook = self._hook or self._default_hook
+        b.launched = True
+        if self._hook is None and self.world == 1:
+            b.future = None
+            return
+        gb = GradBucket(b.index, b.buffer, b.params, b.index == len(self.buckets) - 1)
+        with trace_range(f"bucket{b.index}"):
+            if self.comm_stream is not None:
+                self.comm_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.comm_stream):
+                    b.future = hook(self._hook_state, gb)
+            else:
+                b.future = hook(self._hook_state, gb)
+        self._launched += 1
+
+    def finalize_grads(self) -> None:
+        """Join all bucket communication, write hook results back, then apply the sparse embedding rows."""
+        if self.require_sync:
+            for b in self.buckets:
+                if not b.launched:           # parameters without a gradient this step, or undeclared uses
+                    self._launch(b)
+            ctx = torch.cuda.stream(self.comm_stream) if self.comm_stream is not None else _null()
+            with ctx:
+                for b in self.buckets:
+                    if b.future is not None:
+                        res = b.future.wait() if hasattr(b.future, "wait") else b.future
+                        if isinstance(res, (list, tuple)):
+                            res = res[0]
+                        if res is not b.buffer and res.data_ptr() != b.buffer.data_ptr():
+                            b.buffer.copy_(res.reshape(-1))
+                        b.future = None
+            if self.comm_stream is not None:
+                torch.cuda.current_stream().wait_stream(self.comm_stream)
+            if hasattr(self.module, "sync_replicated_grads"):
+                self.module.sync_replicated_grads()
+            if self.embedding_sync is not None:
+                emb = self.embedding_sync
+                target = emb.target_param
+                emb.sync_into(target.grad, zero_first=getattr(target, "zen_sparse_only", False))
+        for b in self.buckets:
+            b.pending = len(b.params)
+            b.launched = False
+            for p in b.params:
+                p.zen_signals = 0
+                p.zen_expected = 0
+                p.zen_autograd_use = False
+                p.zen_autograd_done = False
+                p.zen_complete = False
+
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        for b in self.buckets:
+            b.buffer.zero_()
+        for p in self._sparse_only:
+            if p.grad is not None:
+                p.grad.zero_()
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

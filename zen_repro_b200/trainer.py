@@ -1,0 +1,110 @@
+"""Training engine: the public entry point that scripts, the benchmark and the smoke test share.
+
+    trainer = Trainer(TrainConfig(model="gpt2", micro_batch=8, seq_len=1024))
+    loss = trainer.step(next(trainer.data))          # H2D copy, forward, backward, gradient sync, AdamW, loss read
+
+It wires together what the reference's ``train.py`` assembles by hand (plugin, booster, model,
+optimizer, hook registration: train.py:109-185) and runs the same loop body (train.py:198-211).
+"""
+from __future__ import annotations
+
+import dataclasses
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from .data import ZipfTokenStream
+from .models import build_model, get_config
+from .optim import FusedAdamW
+from .parallel import Booster, DistCoordinator, HybridParallelPlugin, launch_from_torch, make_zen_comm_hook
+from .utils.trace import trace_range
+
+
+@dataclass
+class TrainConfig:
+    model: str = "gpt2"
+    micro_batch: int = 8
+    seq_len: int = 1024
+    tp: int = 1
+    method: int = 0                   # 0 dense buckets (+ sparse embedding rows); 1/2/3 ZEN top-k hook on all buckets
+    top_k: float = 1.0
+    bucket_cap_mb: float = 128.0
+    sparse_embedding: bool = True
+    grad_checkpoint: bool = False
+    lr: float = 1e-3
+    weight_decay: float = 0.0
+    zipf_s: float = 1.1
+    seed: int = 0
+    num_layers: int | None = None
+    kv_heads: int | None = None
+    precision: str = "bf16"
+    data_pool: int = 8                # pre-generated pinned batches that the stream cycles through (0 = generate per step)
+    overlap: bool = True
+
+    def to_dict(self):
+        return dataclasses.asdict(self)
+
+
+class Trainer:
+    def __init__(self, cfg: TrainConfig, init_dist: bool = True):
+        self.cfg = cfg
+        if init_dist and not dist.is_initialized():
+            launch_from_torch()
+        self.coordinator = DistCoordinator()
+        self.plugin = HybridParallelPlugin(tp_size=cfg.tp, pp_size=1, precision=cfg.precision,
+                                           ddp_bucket_cap_mb=cfg.bucket_cap_mb,
+                                           sparse_embedding=cfg.sparse_embedding and cfg.method == 0, overlap=cfg.overlap)
+        self.booster = Booster(self.plugin)
+        self.device = self.plugin.device
+        mc = get_config(cfg.model, num_layers=cfg.num_layers, num_kv_heads=cfg.kv_heads,
+                        grad_checkpoint=cfg.grad_checkpoint or None)
+        self.model_cfg = mc
+        torch.manual_seed(cfg.seed)
+        model = build_model(mc, tp_group=self.plugin.tp_group if cfg.tp > 1 else None, device=self.device,
+                            dtype=self.plugin.dtype)
+        model.reset_parameters(seed=cfg.seed + 1000 * self.plugin.pg_mesh.tp_rank)
+        optimizer = FusedAdamW(model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay)
+        self.data = ZipfTokenStream(mc.vocab_size, cfg.seq_len, cfg.micro_batch, s=cfg.zipf_s, seed=cfg.seed,
+                                    dp_rank=self.plugin.dp_rank, pool=cfg.data_pool)
+        self.model, self.optimizer, _, _, _ = self.booster.boost(model, optimizer, dataloader=self.data,
+                                                                 max_tokens=cfg.micro_batch * cfg.seq_len)
+        if cfg.method != 0:
+            hook = make_zen_comm_hook(self.model.dp_group, self.model.tp_group, top_k=cfg.top_k, method=cfg.method,
+                                      torch_future=False)
+            if self.device.type == "cuda" and self.plugin.dp_size > 1:
+                for b in self.model.module.buckets:          # allocate peer buffers outside backward
+                    if b.buffer.numel() > 4096:
+                        hook.engine_for(b.buffer.numel(), self.device)
+            self.model.module.register_comm_hook(None, hook)
+        self.step_count = 0
+        self._ids_dev = None
+
+    @property
+    def tokens_per_step(self) -> int:
+        """Tokens consumed per optimizer step by the whole job."""
+        return self.cfg.micro_batch * self.cfg.seq_len * self.plugin.dp_size
+
+    def step(self, batch: dict, read_loss: bool = True):
+        """One optimizer step on a host batch.  Returns the loss as a float (read_loss) or a device tensor."""
+        with trace_range("h2d"):
+            ids = batch["input_ids"].to(self.device, non_blocking=True)
+            labels = batch["labels"].to(self.device, non_blocking=True) if batch["labels"] is not batch["input_ids"] else ids
+        return self.step_device(ids, labels, read_loss)
+
+    def step_device(self, ids: torch.Tensor, labels: torch.Tensor, read_loss: bool = False):
+        with trace_range("forward"):
+            loss = self.model(ids, labels)
+        with trace_range("backward"):
+            self.booster.backward(loss, self.optimizer)
+        with trace_range("optimizer_step"):
+            self.optimizer.step()
+            self.model.module.zero_grad()
+        self.step_count += 1
+        return float(loss.item()) if read_loss else loss.detach()
+
+    def bytes_per_step(self, batch: dict) -> tuple[int, int]:
+        h2d = batch["input_ids"].numel() * batch["input_ids"].element_size()
+        if batch["labels"] is not batch["input_ids"]:
+            h2d += batch["labels"].numel() * batch["labels"].element_size()
+        return h2d, 4
