@@ -54,12 +54,14 @@ def test_activations(dtype, kind):
     gud = gu.to(DEV)
     ad, bd = gud[:, :inner], (gud[:, inner:] if gated else None)
     o1 = E.act_fwd(ad, bd, kind)
-    torch.testing.assert_close(o1.cpu().float(), o0.float(), **tol(dtype))
+    # the kernels use tanh.approx (relative error about 2^-11), so fp32 is compared at 3e-3
+    t = tol(dtype) if dtype != torch.float32 else dict(atol=3e-3, rtol=3e-3)
+    torch.testing.assert_close(o1.cpu().float(), o0.float(), **t)
     da0, db0 = E.act_bwd(a, b, dout, kind)
     da1, db1 = E.act_bwd(ad, bd, dout.to(DEV), kind)
-    torch.testing.assert_close(da1.cpu().float(), da0.float(), **tol(dtype))
+    torch.testing.assert_close(da1.cpu().float(), da0.float(), **t)
     if gated:
-        torch.testing.assert_close(db1.cpu().float(), db0.float(), **tol(dtype))
+        torch.testing.assert_close(db1.cpu().float(), db0.float(), **t)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -228,6 +228,206 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __re
   }
 }
 
+// ---- warp-per-row variants for narrow rows (cols <= 256 * NV): no block barriers, many rows in flight per SM.
+// Rows are kept as raw 16-byte vectors (8 registers per vector for fp32, 4 for 16-bit types) and unpacked on use.
+template <typename T> struct Pack;
+template <> struct Pack<float> {
+  struct raw_t { float4 a, b; };
+  static __device__ __forceinline__ raw_t load(const float* p) { raw_t r; r.a = *reinterpret_cast<const float4*>(p); r.b = *reinterpret_cast<const float4*>(p + 4); return r; }
+  static __device__ __forceinline__ void unpack(const raw_t& r, float (&v)[8]) { v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w; }
+};
+template <> struct Pack<__nv_bfloat16> {
+  typedef uint4 raw_t;
+  static __device__ __forceinline__ raw_t load(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  static __device__ __forceinline__ void unpack(const raw_t& r, float (&v)[8]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  }
+};
+template <> struct Pack<__half> {
+  typedef uint4 raw_t;
+  static __device__ __forceinline__ raw_t load(const __half* p) { return *reinterpret_cast<const uint4*>(p); }
+  static __device__ __forceinline__ void unpack(const raw_t& r, float (&v)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+};
+
+#define NORMW_WARPS 8
+
+template <typename T, bool kLayer, int NV>
+__global__ void __launch_bounds__(NORMW_WARPS * 32)
+norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ wgt,
+                     const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ hout, float* __restrict__ rstd_out,
+                     float* __restrict__ mean_out, int rows, int cols, float eps, int unit_offset) {
+  const int lane = threadIdx.x & 31;
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
+  const int nv = cols / 8;
+  for (int row = gw; row < rows; row += nw) {
+    const size_t base = (size_t)row * cols;
+    float h[NV][8];
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = lane + 32 * j;
+      if (v < nv) {
+        Vec8<T>::load(x + base + (size_t)v * 8, h[j]);
+        if (res) {
+          float r[8];
+          Vec8<T>::load(res + base + (size_t)v * 8, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) h[j][i] += r[i];
+        }
+        if (hout) {
+          Vec8<T>::store(hout + base + (size_t)v * 8, h[j]);
+          if (sizeof(T) == 2) {   // continue with exactly what was stored
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h[j][i] = ZenVal<T>::to_f(ZenVal<T>::from_f(h[j][i]));
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s += h[j][i]; ss += h[j][i] * h[j][i]; }
+      }
+    }
+    float mean = 0.f, var;
+    if (kLayer) {
+      mean = warp_sum(s) / cols;
+      float d2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        if (lane + 32 * j < nv) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { const float d = h[j][i] - mean; d2 += d * d; }
+        }
+      }
+      var = warp_sum(d2) / cols;
+    } else {
+      var = warp_sum(ss) / cols;
+    }
+    const float rstd = rsqrtf(var + eps);
+    if (lane == 0) { rstd_out[row] = rstd; if (kLayer) mean_out[row] = mean; }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = lane + 32 * j;
+      if (v < nv) {
+        float w[8], o[8];
+        Vec8<T>::load(wgt + (size_t)v * 8, w);
+        if (kLayer) {
+          float b[8];
+          if (bias) Vec8<T>::load(bias + (size_t)v * 8, b);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = (h[j][i] - mean) * rstd * w[i] + (bias ? b[i] : 0.f);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = h[j][i] * rstd * (unit_offset ? 1.f + w[i] : w[i]);
+        }
+        Vec8<T>::store(y + base + (size_t)v * 8, o);
+      }
+    }
+  }
+}
+
+template <typename T, bool kLayer, int NV>
+__global__ void __launch_bounds__(NORMW_WARPS * 32)
+norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __restrict__ wgt,
+                     const float* __restrict__ rstd_in, const float* __restrict__ mean_in, const T* __restrict__ dres,
+                     T* __restrict__ dh, float* __restrict__ part_dw, float* __restrict__ part_db, int rows, int cols,
+                     int unit_offset) {
+  extern __shared__ float sm_acc[];                 // [2][cols]: dw and db sums of this CTA
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
+  const int nv = cols / 8;
+  float aw[NV][8], ab[kLayer ? NV : 1][8];
+  float wv[NV][8];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { aw[j][i] = 0.f; if (kLayer) ab[j][i] = 0.f; wv[j][i] = 0.f; }
+    if (lane + 32 * j < nv) {
+      Vec8<T>::load(wgt + (size_t)(lane + 32 * j) * 8, wv[j]);
+      if (!kLayer && unit_offset) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) wv[j][i] += 1.f;
+      }
+    }
+  }
+  for (int row = gw; row < rows; row += nw) {
+    const size_t base = (size_t)row * cols;
+    const float rstd = rstd_in[row];
+    const float mean = kLayer ? mean_in[row] : 0.f;
+    typename Pack<T>::raw_t rd[NV], rh[NV];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (lane + 32 * j < nv) {
+        rd[j] = Pack<T>::load(dy + base + (size_t)(lane + 32 * j) * 8);
+        rh[j] = Pack<T>::load(h + base + (size_t)(lane + 32 * j) * 8);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (lane + 32 * j < nv) {
+        float d[8], xh[8];
+        Pack<T>::unpack(rd[j], d);
+        Pack<T>::unpack(rh[j], xh);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[i] = (xh[i] - mean) * rstd;
+          aw[j][i] += d[i] * xh[i];
+          if (kLayer) ab[j][i] += d[i];
+          const float g = d[i] * wv[j][i];
+          s1 += g;
+          s2 += g * xh[i];
+        }
+      }
+    }
+    s2 = warp_sum(s2) / cols;
+    s1 = kLayer ? warp_sum(s1) / cols : 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = lane + 32 * j;
+      if (v < nv) {
+        float d[8], xh[8], o[8];
+        Pack<T>::unpack(rd[j], d);
+        Pack<T>::unpack(rh[j], xh);
+        if (dres) Vec8<T>::load(dres + base + (size_t)v * 8, o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xhat = (xh[i] - mean) * rstd;
+          const float t = rstd * (d[i] * wv[j][i] - s1 - xhat * s2);
+          o[i] = dres ? o[i] + t : t;
+        }
+        Vec8<T>::store(dh + base + (size_t)v * 8, o);
+      }
+    }
+  }
+  // fold the warps' partial dw / db through shared memory, one warp at a time (fixed order)
+  float* sdw = sm_acc;
+  float* sdb = sm_acc + cols;
+  for (int wsel = 0; wsel < NORMW_WARPS; ++wsel) {
+    if (warp == wsel) {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int v = lane + 32 * j;
+        if (v < nv) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            sdw[v * 8 + i] = (wsel == 0 ? 0.f : sdw[v * 8 + i]) + aw[j][i];
+            if (kLayer) sdb[v * 8 + i] = (wsel == 0 ? 0.f : sdb[v * 8 + i]) + ab[j][i];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    part_dw[(size_t)blockIdx.x * cols + c] = sdw[c];
+    if (kLayer && part_db) part_db[(size_t)blockIdx.x * cols + c] = sdb[c];
+  }
+}
+
 // out[c] (+)= sum_p part[p][c], cast to T.  CTA = 32 columns x 32 part-lanes; fixed summation order.
 template <typename T>
 __global__ void __launch_bounds__(1024)
@@ -251,7 +451,7 @@ colreduce_kernel(const float* __restrict__ part, T* __restrict__ out, int nparts
 
 // Column sums of a [rows, cols] matrix: CTA b sums rows [b * COLSUM_ROWS, ...) for every column (thread = one
 // 8-column vector, coalesced along the row) into part[b][cols] (bias gradients).
-#define COLSUM_ROWS 64
+#define COLSUM_ROWS 32
 template <typename T>
 __global__ void __launch_bounds__(256) colsum_partial_kernel(const T* __restrict__ a, float* __restrict__ part, int rows, int cols) {
   const int r0 = blockIdx.x * COLSUM_ROWS, r1 = min(rows, r0 + COLSUM_ROWS);
@@ -637,19 +837,37 @@ inline int cap_grid(size_t want, int mult) {
 
 extern "C" {
 
+// Rows of at most NORMW_MAXCOLS columns use the warp-per-row kernels, wider rows the CTA-per-row kernels.
+#define NORMW_MAXCOLS 1024
+static inline bool norm_warp_path(int cols, int dtype) { (void)dtype; return cols <= NORMW_MAXCOLS; }
+
 // Number of per-CTA partial rows the norm backward writes (the caller sizes its scratch with this).
-int zen_norm_bwd_parts(int rows) { return cap_grid((size_t)rows, 2); }
+int zen_norm_bwd_parts(int rows) { return cap_grid((size_t)(rows + NORMW_WARPS - 1) / NORMW_WARPS, 3); }
 
 #define NORM_NV_DISPATCH(cols, ...)                                   \
   if (cols <= NORM_THREADS * 8) { constexpr int NV = 1; __VA_ARGS__; } \
   else if (cols <= NORM_THREADS * 16) { constexpr int NV = 2; __VA_ARGS__; } \
   else if (cols <= NORM_THREADS * 32) { constexpr int NV = 4; __VA_ARGS__; } \
   else { constexpr int NV = 8; __VA_ARGS__; }
+#define NORMW_NV_DISPATCH(cols, ...)                        \
+  if (cols <= 256) { constexpr int NV = 1; __VA_ARGS__; }   \
+  else if (cols <= 512) { constexpr int NV = 2; __VA_ARGS__; } \
+  else { constexpr int NV = 4; __VA_ARGS__; }
 
 int zen_norm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* hout, float* rstd,
                  float* mean, int rows, int cols, float eps, int layer, int unit_offset, int dtype, void* stream) {
   if (cols % 8 || cols > NORM_THREADS * NORM_MAXV * 8) return -2;
   cudaStream_t st = (cudaStream_t)stream;
+  if (norm_warp_path(cols, dtype)) {
+    const int grid = cap_grid((size_t)(rows + NORMW_WARPS - 1) / NORMW_WARPS, 8);
+    DISPATCH_T(dtype, {
+      NORMW_NV_DISPATCH(cols, {
+        if (layer) norm_fwd_warp_kernel<T, true, NV><<<grid, NORMW_WARPS * 32, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b, (T*)y, (T*)hout, rstd, mean, rows, cols, eps, unit_offset);
+        else norm_fwd_warp_kernel<T, false, NV><<<grid, NORMW_WARPS * 32, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b, (T*)y, (T*)hout, rstd, mean, rows, cols, eps, unit_offset);
+      });
+    });
+    return (int)cudaGetLastError();
+  }
   const int grid = cap_grid((size_t)rows, 16);
   DISPATCH_T(dtype, {
     NORM_NV_DISPATCH(cols, {
@@ -668,6 +886,18 @@ int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd
   if (cols % 8 || cols > NORM_THREADS * NORM_MAXV * 8) return -2;
   cudaStream_t st = (cudaStream_t)stream;
   const int grid = zen_norm_bwd_parts(rows);
+  if (norm_warp_path(cols, dtype)) {
+    const size_t smem = (size_t)2 * cols * sizeof(float);
+    DISPATCH_T(dtype, {
+      NORMW_NV_DISPATCH(cols, {
+        if (layer) norm_bwd_warp_kernel<T, true, NV><<<grid, NORMW_WARPS * 32, smem, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+        else norm_bwd_warp_kernel<T, false, NV><<<grid, NORMW_WARPS * 32, smem, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+      });
+      colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, grid, cols, accumulate);
+      if (layer && db) colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_db, (T*)db, grid, cols, accumulate);
+    });
+    return (int)cudaGetLastError();
+  }
   DISPATCH_T(dtype, {
     NORM_NV_DISPATCH(cols, {
       if (layer) norm_bwd_kernel<T, true, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);

@@ -283,7 +283,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 *reinterpret_cast<float4*>(cp + i) = o;
               }
             } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) cp[i] = p.accumulate ? cp[i] + v[i] : v[i];
+#pragma unroll
+              for (int i = 0; i < 32; ++i)        // fully unrolled: v[] must stay in registers
+                if (col0 + i < p.N) cp[i] = p.accumulate ? cp[i] + v[i] : v[i];
             }
           } else {
             __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
@@ -305,9 +307,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 *reinterpret_cast<uint4*>(cp + i) = make_uint4(o[0], o[1], o[2], o[3]);
               }
             } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) {
-                const float o = p.accumulate ? __bfloat162float(cp[i]) + v[i] : v[i];
-                cp[i] = __float2bfloat16_rn(o);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (col0 + i < p.N) {
+                  const float o = p.accumulate ? __bfloat162float(cp[i]) + v[i] : v[i];
+                  cp[i] = __float2bfloat16_rn(o);
+                }
               }
             }
           }
