@@ -997,3 +997,74 @@ int zen_adamw(const void* table, int ntensors, const int32_t* chunk_tensor, uint
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free column sum (declared in zen_noalloc.h, which says who needs it and why).
+#include "zen_noalloc.h"
+
+#include <mutex>
+#include <stdio.h>
+
+// Scratch of the allocation-free entry point: per-CTA partial sums, [ceil(rows / 32)][cols] floats.
+// In host code this name is only a handle for cudaGetSymbolAddress, never a pointer to hand to a kernel.
+static __device__ __align__(256) float g_colsum_noalloc_scratch[ZEN_COLSUM_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address of the scratch, per device
+std::mutex g_noalloc_mu;
+thread_local char g_noalloc_err[256] = "";
+
+int noalloc_fail(int code, const char* what) {
+  snprintf(g_noalloc_err, sizeof(g_noalloc_err), "%s", what);
+  return code;
+}
+
+// Device address of the scratch array on the current device; looked up once per device.
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return noalloc_fail((int)e, cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return noalloc_fail(ZEN_NOALLOC_BAD_ARG, "device index out of range");
+  std::lock_guard<std::mutex> g(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_colsum_noalloc_scratch);
+    if (e != cudaSuccess) return noalloc_fail((int)e, cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" {
+
+const char* zen_noalloc_last_error(void) { return g_noalloc_err; }
+
+int zen_colsum_noalloc(const void* a, void* out, int rows, int cols, int accumulate, int dtype, void* stream) {
+  if (!a || !out || rows <= 0 || cols <= 0) return noalloc_fail(ZEN_NOALLOC_BAD_ARG, "null pointer or empty matrix");
+  if (cols % 8) return noalloc_fail(ZEN_NOALLOC_BAD_ARG, "cols must be a multiple of 8");
+  if (reinterpret_cast<uintptr_t>(a) % 16) return noalloc_fail(ZEN_NOALLOC_BAD_ARG, "input must be 16-byte aligned");
+  if (dtype < 0 || dtype > 2) return noalloc_fail(ZEN_NOALLOC_BAD_ARG, "dtype must be 0 (fp32), 1 (bf16) or 2 (fp16)");
+  const int parts = (rows + COLSUM_ROWS - 1) / COLSUM_ROWS;
+  if ((uint64_t)parts * (uint64_t)cols > (uint64_t)ZEN_COLSUM_NOALLOC_MAX_FLOATS) {
+    snprintf(g_noalloc_err, sizeof(g_noalloc_err),
+             "scratch of %llu floats needed for %d x %d, the built-in array holds %u: use zen_colsum with caller scratch",
+             (unsigned long long)parts * cols, rows, cols, (unsigned)ZEN_COLSUM_NOALLOC_MAX_FLOATS);
+    return ZEN_NOALLOC_TOO_LARGE;
+  }
+  float* part = nullptr;
+  int rc = noalloc_scratch(&part);
+  if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  DISPATCH_T(dtype, {
+    colsum_partial_kernel<T><<<parts, 256, 0, st>>>((const T*)a, part, rows, cols);
+    colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part, (T*)out, parts, cols, accumulate);
+  });
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return noalloc_fail((int)e, cudaGetErrorString(e));
+  return 0;
+}
+
+}  // extern "C"
