@@ -114,7 +114,50 @@ def check_departed_rank(rank, world, dev):
     eng.close()
 
 
-CHECKS = {"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
+def check_gemm_allreduce(rank, world, dev):
+    """GEMM with the all-reduce fused into its epilogue == GEMM followed by an NCCL all-reduce, on every rank."""
+    from zen_repro_b200.ops import gemm as G
+    from zen_repro_b200.parallel.tp_fused import FusedTPWorkspace
+
+    ws = FusedTPWorkspace(None, 4096, 4096, wait_ms=1000.0)
+    for (M, N, K) in [(256, 384, 320), (4096, 768, 1536), (1000, 4096, 512), (77, 130, 72)]:
+        for rep in range(3):
+            g = torch.Generator().manual_seed(1000 * rep + rank)
+            a = torch.randn(M, K, generator=g).bfloat16().to(dev)
+            w = torch.randn(N, K, generator=g).bfloat16().to(dev)
+            bias = torch.randn(N, generator=torch.Generator().manual_seed(7)).bfloat16().to(dev)
+            got = ws.gemm_ar_nt(a, w, bias)
+            want = (a.float() @ w.float().t())
+            dist.all_reduce(want)
+            want = want + bias.float()
+            assert ws.check() == 0 and G.gemm_error() == 0
+            err = (got.float() - want).abs().max().item()
+            assert err <= 0.02 * want.abs().max().item() + 0.05, (M, N, K, err)
+            # every rank holds the same bits
+            ref = got.clone()
+            dist.broadcast(ref, 0)
+            assert torch.equal(ref, got)
+            wt = w.t().contiguous()
+            got2 = ws.gemm_ar_nn(a, wt)
+            assert (got2.float() + bias.float() - want).abs().max().item() <= 0.02 * want.abs().max().item() + 0.1
+    ws.close()
+    print(f"OK gemm_allreduce rank{rank}", flush=True)
+
+
+def check_tp_trainer(rank, world, dev):
+    """TP = 2 training with fused GEMM + all-reduce tracks the NCCL-based TP path."""
+    from zen_repro_b200.trainer import TrainConfig, Trainer
+
+    out = {}
+    for fused in (True, False):
+        t = Trainer(TrainConfig(model="meta-llama/Llama-3.2-3B", num_layers=2, micro_batch=1, seq_len=256, tp=2, lr=1e-4,
+                                data_pool=0, fused_tp=fused), init_dist=False)
+        out[fused] = [t.step(next(t.data)) for _ in range(4)]
+    assert all(abs(a - b) < 0.05 for a, b in zip(out[True], out[False])), out
+    print(f"OK tp_trainer rank{rank} {out[True]}", flush=True)
+
+
+CHECKS = {"gemm_ar": check_gemm_allreduce, "tp_trainer": check_tp_trainer,"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
           "hook": check_zen_hook, "departed": check_departed_rank}
 
 if __name__ == "__main__":

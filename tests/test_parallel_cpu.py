@@ -89,13 +89,14 @@ def test_tensor_parallel_matches_single_rank(name):
         assert lerr < 1e-4
 
 
+def _mesh_worker(rank, world):
+    from zen_repro_b200.parallel.mesh import ProcessGroupMesh
+
+    m = ProcessGroupMesh(tp_size=2)
+    return m.dp_rank, m.tp_rank, m.get_ranks_in_group(m.dp_group), m.get_ranks_in_group(m.tp_group)
+
+
 def test_mesh_groups():
-    def w(rank, world):
-        from zen_repro_b200.parallel.mesh import ProcessGroupMesh
-
-        m = ProcessGroupMesh(tp_size=2)
-        return m.dp_rank, m.tp_rank, m.get_ranks_in_group(m.dp_group), m.get_ranks_in_group(m.tp_group)
-
-    res = run_gloo(w, 4)
+    res = run_gloo(_mesh_worker, 4)
     assert res[0] == (0, 0, [0, 2], [0, 1])
     assert res[3] == (1, 1, [1, 3], [2, 3])

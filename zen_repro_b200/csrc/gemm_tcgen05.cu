@@ -43,6 +43,21 @@ struct GemmParams {
   int out_fp32;         // C is float instead of bf16
   int accumulate;       // C += result
   int num_m_tiles, num_n_tiles;
+  // ---- fused all-reduce over tensor-parallel peers (npeers == 0: plain GEMM) ----
+  int npeers;                 // other ranks of the TP group
+  int rank;                   // this rank's index in the group
+  uint32_t epoch;             // call counter, same on every rank; parity selects the exchange buffer
+  uint32_t max_tiles;         // capacity of one flag row
+  uint64_t wait_ns;
+  __nv_bfloat16* my_recv;     // this rank's exchange region: [2 parities][npeers slots][M * recv_ld] bf16
+  uint32_t* my_flags;         // this rank's flags: [2 parities][npeers slots][max_tiles] epochs
+  __nv_bfloat16* peer_recv[7];// peers' exchange regions (same layout), indexed by peer slot
+  uint32_t* peer_flags[7];
+  int peer_slot_of_me[7];     // which slot this rank writes in peer i's region
+  int peer_rank[7];           // group rank of peer slot i (for the fixed summation order)
+  uint64_t slot_elems;        // elements per (parity, slot)
+  int recv_ld;                // row stride of exchanged partial tiles
+  uint32_t* status;           // device word: bit 2 set when a peer wait timed out
 };
 
 // ------------------------------------------------------------------------------------ PTX helpers
@@ -130,6 +145,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {   // L2-coherent load: peers write this memory
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (128-byte swizzle).  K-major: rows of 128 bytes, 8-row groups
 // 1024 bytes apart (SBO).  MN-major: 64-element groups along M/N `lbo_bytes` apart, 8-row groups
@@ -258,6 +288,53 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const int row = m0 + grp * 32 + lane;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(grp * 32) << 16) + acc * BN;
+      const uint32_t par = p.epoch & 1u;
+      if (p.npeers > 0) {
+        // ---- fused all-reduce, step 1: push this rank's partial tile (bf16) into every peer's exchange region
+#pragma unroll 1
+        for (int ch = 0; ch < BN / 32; ++ch) {
+          uint32_t r[32];
+          tmem_ld32(taddr0 + ch * 32, r);
+          const int col0 = n0 + ch * 32;
+          if (row < p.M && col0 < p.N) {
+            uint32_t o[16];
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
+              o[q] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            for (int pe = 0; pe < p.npeers; ++pe) {
+              __nv_bfloat16* dst = p.peer_recv[pe] + ((size_t)par * p.npeers + p.peer_slot_of_me[pe]) * p.slot_elems +
+                                   (size_t)row * p.recv_ld + col0;
+              if (col0 + 32 <= p.N) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) dst[i] = __ushort_as_bfloat16((unsigned short)((o[i >> 1] >> ((i & 1) * 16)) & 0xffffu));
+              }
+            }
+          }
+        }
+        __threadfence_system();
+        epilogue_barrier();
+        const int et = threadIdx.x - 64;                                   // 0..127 among the epilogue threads
+        if (et < p.npeers)
+          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + tile, p.epoch);
+        // ---- step 2: bounded wait for every peer's partial of this tile
+        if (et < p.npeers) {
+          const uint32_t* f = p.my_flags + ((size_t)par * p.npeers + et) * p.max_tiles + tile;
+          const uint64_t t0 = gtimer();
+          bool got = ld_acquire_sys_u32(f) == p.epoch;
+          while (!got) {
+            for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f) == p.epoch;
+            if (!got && (gtimer() - t0 > p.wait_ns || *abort_flag)) break;
+          }
+          if (!got) { atomicOr(p.status, 4u); *abort_flag = 5; atomicCAS(&g_gemm_error, 0, 5); }
+        }
+        epilogue_barrier();
+      }
 #pragma unroll 1
       for (int ch = 0; ch < BN / 32; ++ch) {
         uint32_t r[32];
@@ -267,6 +344,40 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (p.npeers > 0) {
+            // step 3: sum the bf16-rounded partials of all ranks in rank order, so every rank gets the same bits
+            float own[32];
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+              own[2 * q] = __bfloat162float(h.x); own[2 * q + 1] = __bfloat162float(h.y);
+            }
+            bool own_added = false;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            for (int pe = 0; pe <= p.npeers; ++pe) {
+              if (!own_added && (pe == p.npeers || p.peer_rank[pe] > p.rank)) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] += own[i];
+                own_added = true;
+              }
+              if (pe == p.npeers) break;
+              const __nv_bfloat16* src = p.my_recv + ((size_t)par * p.npeers + pe) * p.slot_elems + (size_t)row * p.recv_ld + col0;
+              if (col0 + 32 <= p.N) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 w4 = ld_cg_v4(src + 8 * q);
+                  const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                  for (int k2 = 0; k2 < 4; ++k2) { v[8 * q + 2 * k2] += __uint_as_float(w[k2] << 16); v[8 * q + 2 * k2 + 1] += __uint_as_float(w[k2] & 0xffff0000u); }
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) v[i] += __bfloat162float(*reinterpret_cast<const volatile __nv_bfloat16*>(src + i));
+              }
+            }
+          }
           const bool fullw = (col0 + 32 <= p.N);
           if (p.bias) {
             const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
@@ -425,6 +536,43 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStrea
 
 }  // namespace
 
+// Exchange set-up handed in by zen_gemm_bf16_ar for the launch that follows on the same thread.
+struct ZenGemmArCtx {
+  int32_t nranks;
+  int32_t rank;
+  uint32_t epoch;
+  uint32_t max_tiles;
+  uint64_t wait_ns;
+  uint64_t slot_elems;        // capacity (elements) of one (parity, slot) exchange buffer
+  void* recv[8];              // exchange region of every rank (this rank's own address included)
+  void* flags[8];             // flag region of every rank
+  uint32_t* status;
+};
+namespace {
+thread_local const ZenGemmArCtx* g_ar_next = nullptr;
+void fill_ar(GemmParams& p, const ZenGemmArCtx& c) {
+  p.npeers = c.nranks - 1;
+  p.rank = c.rank;
+  p.epoch = c.epoch;
+  p.max_tiles = c.max_tiles;
+  p.wait_ns = c.wait_ns;
+  p.slot_elems = c.slot_elems;
+  p.recv_ld = (p.N + 7) / 8 * 8;
+  p.status = c.status;
+  p.my_recv = reinterpret_cast<__nv_bfloat16*>(c.recv[c.rank]);
+  p.my_flags = reinterpret_cast<uint32_t*>(c.flags[c.rank]);
+  int s = 0;
+  for (int r = 0; r < c.nranks; ++r) {
+    if (r == c.rank) continue;
+    p.peer_recv[s] = reinterpret_cast<__nv_bfloat16*>(c.recv[r]);
+    p.peer_flags[s] = reinterpret_cast<uint32_t*>(c.flags[r]);
+    p.peer_rank[s] = r;
+    p.peer_slot_of_me[s] = c.rank < r ? c.rank : c.rank - 1;   // this rank's slot among r's peers (rank order)
+    ++s;
+  }
+}
+}  // namespace
+
 extern "C" {
 
 // C[M,N] (+)= A * B^T (+ bias).  a_mn / b_mn: operand stored MN-major ([K, M] resp. [K, N] row-major)
@@ -449,7 +597,9 @@ int zen_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
   if (!b_mn) rc = get_map(B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, (uint32_t)bn, &tb);
   else rc = get_map(B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64, &tb);
   if (rc) return rc;
-  GemmParams p{C, bias, M, N, K, ldc, out_fp32, accumulate, 0, 0};
+  GemmParams p{};
+  p.C = C; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
+  if (g_ar_next) { fill_ar(p, *g_ar_next); g_ar_next = nullptr; }
   cudaStream_t st = (cudaStream_t)stream;
 #define LAUNCH(BN_)                                                        \
   do {                                                                     \
@@ -461,6 +611,27 @@ int zen_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
   if (bn == 256) LAUNCH(256);
   LAUNCH(128);
 #undef LAUNCH
+}
+
+int zen_gemm_ar_ctx_size() { return (int)sizeof(ZenGemmArCtx); }
+
+// GEMM fused with an all-reduce (SUM) over a tensor-parallel group: every rank computes its partial product and
+// the epilogue exchanges bf16 partial tiles through peer memory (P2P stores into the peers' exchange regions, one
+// flag per tile, bounded waits), so the reduction overlaps the main loop of the following tiles.  All ranks end up
+// with identical results.  Requirements on top of zen_gemm_bf16: the same M, N, K on every rank,
+// M * round_up(N, 8) <= ctx->slot_elems, number of tiles <= ctx->max_tiles, out_fp32 == 0 or 1 as wanted.
+int zen_gemm_bf16_ar(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
+                     int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, int bn, const ZenGemmArCtx* ctx,
+                     void* stream) {
+  if (!ctx || ctx->nranks < 1 || ctx->nranks > 8) return -3;
+  if ((uint64_t)M * (uint64_t)((N + 7) / 8 * 8) > ctx->slot_elems) return -4;
+  if (bn == 0) bn = 128;
+  const uint64_t tiles = (uint64_t)((M + 127) / 128) * ((N + bn - 1) / bn);
+  if (tiles > ctx->max_tiles) return -5;
+  if (ctx->nranks > 1) g_ar_next = ctx;
+  const int rc = zen_gemm_bf16(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, bn, stream);
+  g_ar_next = nullptr;
+  return rc;
 }
 
 // Last error code recorded by a kernel that gave up a wait (0 = none); clears it.

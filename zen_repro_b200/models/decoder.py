@@ -62,9 +62,14 @@ class Block(nn.Module):
         else:
             self.norm1_b = self.norm2_b = self.qkv_b = self.o_b = self.up_b = self.down_b = None
 
+    tp_ws = None        # FusedTPWorkspace shared by all blocks of a model (set by DecoderLM.enable_fused_tp)
+
     def forward(self, x, res, bsz: int, seq: int):
         cfg, g = self.cfg, self.tp_group
         rank, tp = _tp(g)
+        ws = self.tp_ws if (tp > 1 and x.is_cuda and x.dtype == torch.bfloat16) else None
+        if ws is not None and ws.fits(x.shape[0], cfg.hidden_size):
+            return self._forward_fused_tp(x, res, bsz, seq, ws)
         y, h = O.fused_norm(x, res, self.norm1_w, self.norm1_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
         y = O.copy_to_tp(y, g)
         qkv = O.linear(y, self.qkv_w, self.qkv_b, cfg.weight_layout)
@@ -85,6 +90,26 @@ class Block(nn.Module):
         if tp > 1 and self.down_b is not None:
             dn = dn + self.down_b
         return dn, h2
+
+
+def _block_forward_fused_tp(self, x, res, bsz, seq, ws):
+    """Tensor-parallel block with both all-reduces of the forward (attention out, MLP down) and both of the backward
+    (qkv and up input gradients) fused into the GEMM epilogues."""
+    cfg = self.cfg
+    y, h = O.fused_norm(x, res, self.norm1_w, self.norm1_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
+    qkv = O.linear(y, self.qkv_w, self.qkv_b, cfg.weight_layout, "col", ws)
+    if not cfg.learned_positions:
+        qkv = O.rope_qkv(qkv, self.hq, self.hkv, cfg.head_dim, seq, cfg.rope_theta)
+    a = O.attention(qkv, bsz, seq, self.hq, self.hkv, cfg.head_dim)
+    o = O.linear(a, self.o_w, self.o_b, cfg.weight_layout, "row", ws)
+    y2, h2 = O.fused_norm(o, h, self.norm2_w, self.norm2_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
+    u = O.linear(y2, self.up_w, self.up_b, cfg.weight_layout, "col", ws)
+    m = O.activation(u, cfg.act)
+    dn = O.linear(m, self.down_w, self.down_b, cfg.weight_layout, "row", ws)
+    return dn, h2
+
+
+Block._forward_fused_tp = _block_forward_fused_tp
 
 
 class DecoderLM(nn.Module):
@@ -121,6 +146,19 @@ class DecoderLM(nn.Module):
                 p.fill_(0.0 if cfg.norm_unit_offset else 1.0)
             else:
                 p.normal_(0.0, cfg.init_std, generator=gen)
+
+    def enable_fused_tp(self, max_tokens: int, backend: str | None = None):
+        """Allocate the symmetric exchange workspace (collective over the TP group) and switch the blocks to the
+        GEMMs with the all-reduce fused into their epilogue."""
+        from ..parallel.tp_fused import FusedTPWorkspace
+
+        _, tp = _tp(self.tp_group)
+        if tp > 1 and self.wte.is_cuda:
+            ws = FusedTPWorkspace(self.tp_group, max_tokens, self.cfg.hidden_size, backend=backend)
+            for b in self.blocks:
+                b.tp_ws = ws
+            self.tp_ws = ws
+        return self
 
     def head_weight(self):
         return self.wte if self.lm_head is None else self.lm_head

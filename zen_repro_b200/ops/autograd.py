@@ -35,19 +35,25 @@ def _declare_autograd_use(p) -> None:
 
 
 class LinearFn(torch.autograd.Function):
-    """y = x @ W^T + b with W stored [out, in] ("out_in", nn.Linear) or [in, out] ("in_out", GPT-2 Conv1D)."""
+    """y = x @ W^T + b with W stored [out, in] ("out_in", nn.Linear) or [in, out] ("in_out", GPT-2 Conv1D).
+
+    ``tp_mode`` selects a tensor-parallel variant whose all-reduce is fused into the GEMM epilogue through the
+    workspace ``tp_ws``: "row" = the output is summed over the TP group (row-parallel layer; the bias is added once
+    after the sum), "col" = the input gradient is summed over the TP group (column-parallel layer)."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, layout):
+    def forward(ctx, x, weight, bias, layout, tp_mode=None, tp_ws=None):
         ctx.layout = layout
         ctx.has_bias = bias is not None
+        ctx.tp = (tp_mode, tp_ws)
         x2 = x.reshape(-1, x.shape[-1])
-        if layout == "out_in":
+        n = weight.shape[0] if layout == "out_in" else weight.shape[1]
+        if tp_mode == "row":
+            y = tp_ws.gemm_ar_nt(x2, weight, bias) if layout == "out_in" else tp_ws.gemm_ar_nn(x2, weight, bias)
+        elif layout == "out_in":
             y = G.gemm_nt(x2, weight, bias=bias)
-            n = weight.shape[0]
         else:
             y = G.gemm_nn(x2, weight, bias=bias)
-            n = weight.shape[1]
         ctx.save_for_backward(x2, weight)
         ctx.params = (weight, bias)
         ctx.direct = (_claim(weight), _claim(bias))
@@ -57,12 +63,17 @@ class LinearFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x2, weight = ctx.saved_tensors
+        tp_mode, tp_ws = ctx.tp
         dy2 = dy.reshape(-1, dy.shape[-1])
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
-            dx = (G.gemm_nn(dy2, weight) if ctx.layout == "out_in" else G.gemm_nt(dy2, weight)).view(ctx.xshape)
+            if tp_mode == "col":
+                dx = tp_ws.gemm_ar_nn(dy2, weight) if ctx.layout == "out_in" else tp_ws.gemm_ar_nt(dy2, weight)
+            else:
+                dx = G.gemm_nn(dy2, weight) if ctx.layout == "out_in" else G.gemm_nt(dy2, weight)
+            dx = dx.view(ctx.xshape)
         wp, bp = ctx.params
         if ctx.needs_input_grad[1]:
             a, b = (dy2, x2) if ctx.layout == "out_in" else (x2, dy2)
@@ -77,11 +88,11 @@ class LinearFn(torch.autograd.Function):
                 bp.zen_ready(bp)
             else:
                 db = E.colsum(dy2)
-        return dx, dw, db, None
+        return dx, dw, db, None, None, None
 
 
-def linear(x, weight, bias=None, layout="out_in"):
-    return LinearFn.apply(x, weight, bias, layout)
+def linear(x, weight, bias=None, layout="out_in", tp_mode=None, tp_ws=None):
+    return LinearFn.apply(x, weight, bias, layout, tp_mode, tp_ws)
 
 
 class NormFn(torch.autograd.Function):

@@ -1,0 +1,85 @@
+"""Workspace and entry points of the GEMM fused with a tensor-parallel all-reduce.
+
+``FusedTPWorkspace`` owns the symmetric exchange region of one TP group (two parities of partial-tile
+buffers and per-tile flags per peer) and the call counter that every rank advances in lockstep.
+``gemm_ar_*`` run the tcgen05 GEMM whose epilogue pushes bf16 partial tiles into the peers' regions with
+P2P stores and sums the partials tile by tile behind bounded waits; they replace "GEMM, then NCCL
+all-reduce" of a row-parallel forward and of a column-parallel input-gradient (the shardformer layers the
+reference gets from ColossalAI, train.py:117-123).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..runtime.symmetric import make_symmetric
+
+
+class _ArCtx(ctypes.Structure):
+    _fields_ = [("nranks", ctypes.c_int32), ("rank", ctypes.c_int32), ("epoch", ctypes.c_uint32),
+                ("max_tiles", ctypes.c_uint32), ("wait_ns", ctypes.c_uint64), ("slot_elems", ctypes.c_uint64),
+                ("recv", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8), ("status", ctypes.c_void_p)]
+
+
+class FusedTPWorkspace:
+    def __init__(self, group, max_rows: int, max_cols: int, wait_ms: float = 2000.0, backend: str | None = None):
+        self.group = group
+        self.P = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        lib = _native.lib()
+        assert lib.zen_gemm_ar_ctx_size() == ctypes.sizeof(_ArCtx), "AR ctx layout mismatch"
+        npeers = max(1, self.P - 1)
+        self.slot_elems = max_rows * ((max_cols + 7) // 8 * 8)
+        self.max_tiles = ((max_rows + 127) // 128) * ((max_cols + 127) // 128)
+        flag_bytes = (2 * npeers * self.max_tiles * 4 + 255) // 256 * 256
+        recv_bytes = 2 * npeers * self.slot_elems * 2
+        self.region = make_symmetric(flag_bytes + recv_bytes, group, backend)
+        self.status = torch.zeros(1, dtype=torch.int32, device=f"cuda:{torch.cuda.current_device()}")
+        c = _ArCtx()
+        c.nranks, c.rank, c.max_tiles, c.wait_ns, c.slot_elems = self.P, self.rank, self.max_tiles, int(wait_ms * 1e6), self.slot_elems
+        for r in range(self.P):
+            c.flags[r] = self.region.ptrs[r]
+            c.recv[r] = self.region.ptrs[r] + flag_bytes
+        c.status = self.status.data_ptr()
+        self.ctx = c
+        self.epoch = 0
+
+    def fits(self, M: int, N: int) -> bool:
+        return M * ((N + 7) // 8 * 8) <= self.slot_elems and ((M + 127) // 128) * ((N + 127) // 128) <= self.max_tiles
+
+    def _call(self, a, b, M, N, K, a_mn, b_mn, bias, out, out_dtype):
+        from ..ops.gemm import _rowmajor
+
+        a2, b2 = _rowmajor(a), _rowmajor(b)
+        if out is None:
+            out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
+        self.epoch += 1
+        self.ctx.epoch = self.epoch
+        rc = _native.lib().zen_gemm_bf16_ar(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
+                                            a2.stride(0), b2.stride(0), out.stride(0), int(a_mn), int(b_mn),
+                                            int(out.dtype == torch.float32), 0, 128, ctypes.byref(self.ctx),
+                                            _native.stream_ptr())
+        _native.check(rc, "zen_gemm_bf16_ar")
+        return out
+
+    def gemm_ar_nt(self, a, b, bias=None, out=None):
+        """all_reduce(a[M,K] @ b[N,K]^T) (+ bias, added once after the sum)."""
+        K = a.shape[-1]
+        return self._call(a, b, a.numel() // K, b.shape[0], K, False, False, bias, out, None)
+
+    def gemm_ar_nn(self, a, b, bias=None, out=None):
+        """all_reduce(a[M,K] @ b[K,N]) (+ bias)."""
+        K = a.shape[-1]
+        return self._call(a, b, a.numel() // K, b.shape[1], K, False, True, bias, out, None)
+
+    def check(self) -> int:
+        v = int(self.status.item())
+        if v:
+            self.status.zero_()
+        return v
+
+    def close(self):
+        self.region.close()

@@ -41,6 +41,7 @@ class TrainConfig:
     precision: str = "bf16"
     data_pool: int = 8                # pre-generated pinned batches that the stream cycles through (0 = generate per step)
     overlap: bool = True
+    fused_tp: bool = True             # TP all-reduces fused into the GEMM epilogues (peer memory) instead of NCCL
 
     def to_dict(self):
         return dataclasses.asdict(self)
@@ -64,6 +65,8 @@ class Trainer:
         model = build_model(mc, tp_group=self.plugin.tp_group if cfg.tp > 1 else None, device=self.device,
                             dtype=self.plugin.dtype)
         model.reset_parameters(seed=cfg.seed + 1000 * self.plugin.pg_mesh.tp_rank)
+        if cfg.tp > 1 and self.device.type == "cuda" and cfg.fused_tp:
+            model.enable_fused_tp(cfg.micro_batch * cfg.seq_len)
         optimizer = FusedAdamW(model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay)
         self.data = ZipfTokenStream(mc.vocab_size, cfg.seq_len, cfg.micro_batch, s=cfg.zipf_s, seed=cfg.seed,
                                     dp_rank=self.plugin.dp_rank, pool=cfg.data_pool)
