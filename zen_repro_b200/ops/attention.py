@@ -12,9 +12,44 @@ import torch
 import torch.nn.functional as F
 
 
+import ctypes
+import os
+
+from .. import _native
+
+_MODE = os.environ.get("ZEN_ATTN", "auto")        # auto | own | lib
+
+
+def kernel_covers(seq, hq, hkv, hd, dtype, backward: bool = False) -> bool:
+    """Shapes the tcgen05 attention kernels handle."""
+    if dtype != torch.bfloat16 or seq % 128 or hq % hkv:
+        return False
+    return hd in ((64, 128) if backward else (64, 128, 256))
+
+
 def have_kernel(seq, hq, hkv, hd, dtype) -> bool:
-    """True when the hand-written attention kernels cover this shape."""
-    return False
+    """True when forward AND backward run on the hand-written kernels for this shape."""
+    if _MODE == "lib":
+        return False
+    return kernel_covers(seq, hq, hkv, hd, dtype, backward=True) and HAVE_BWD
+
+
+HAVE_BWD = False
+
+
+def attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale):
+    """tcgen05 forward: returns (out[B*S, Hq*hd], lse2[B, Hq, S]) with lse2 in base 2 of the scaled scores."""
+    assert qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
+    out = torch.empty(bsz * seq, hq * hd, dtype=qkv.dtype, device=qkv.device)
+    lse2 = torch.empty(bsz, hq, seq, dtype=torch.float32, device=qkv.device)
+    rc = _native.lib().zen_attn_fwd(_native.ptr(qkv), _native.ptr(out), _native.ptr(lse2), bsz, seq, hq, hkv, hd,
+                                    qkv.stride(0), out.stride(0), ctypes.c_float(scale), _native.stream_ptr())
+    _native.check(rc, "zen_attn_fwd")
+    return out, lse2
+
+
+def attention_error() -> int:
+    return int(_native.lib().zen_attn_error())
 
 
 def _split(qkv, bsz, seq, hq, hkv, hd):
