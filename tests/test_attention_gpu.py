@@ -34,3 +34,41 @@ def test_forward(B, S, hq, hkv, hd):
     want, lse = _ref(qkv, B, S, hq, hkv, hd, scale)
     torch.testing.assert_close(out.float(), want, atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(lse2 * math.log(2.0), lse, atol=2e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("B,S,hq,hkv,hd", [(1, 128, 1, 1, 64), (2, 384, 4, 4, 64), (1, 1024, 12, 12, 64), (1, 256, 8, 2, 128),
+                                           (2, 512, 4, 1, 128)])
+def test_backward(B, S, hq, hkv, hd):
+    torch.manual_seed(1)
+    qkv = (torch.randn(B * S, (hq + 2 * hkv) * hd, device="cuda") * 0.7).bfloat16()
+    dout = (torch.randn(B * S, hq * hd, device="cuda") * 0.5).bfloat16()
+    scale = 1.0 / math.sqrt(hd)
+    out, lse2 = A.attention_fwd_kernel(qkv, B, S, hq, hkv, hd, scale)
+    dqkv = A.attention_bwd_kernel(dout, qkv, out, lse2, B, S, hq, hkv, hd, scale)
+    torch.cuda.synchronize()
+    assert A.attention_error() == 0
+    x = qkv.float().requires_grad_(True)
+    want, _ = _ref(x, B, S, hq, hkv, hd, scale)
+    (g,) = torch.autograd.grad(want, x, dout.float())
+    err = (dqkv.float() - g).abs().max().item()
+    assert err <= 0.02 * g.abs().max().item() + 0.02, (err, g.abs().max().item())
+    # per-part relative error
+    for name, sl in (("q", slice(0, hq * hd)), ("k", slice(hq * hd, (hq + hkv) * hd)), ("v", slice((hq + hkv) * hd, None))):
+        a, b_ = dqkv[:, sl].float(), g[:, sl]
+        rel = (a - b_).norm() / (b_.norm() + 1e-6)
+        assert rel < 0.02, (name, float(rel))
+
+
+def test_autograd_path_uses_the_kernels():
+    from zen_repro_b200.ops import autograd as O
+
+    torch.manual_seed(2)
+    B, S, hq, hkv, hd = 2, 256, 4, 2, 64
+    qkv = (torch.randn(B * S, (hq + 2 * hkv) * hd, device="cuda") * 0.7).bfloat16().requires_grad_(True)
+    out = O.attention(qkv, B, S, hq, hkv, hd)
+    out.float().square().mean().backward()
+    x = qkv.detach().float().requires_grad_(True)
+    want, _ = _ref(x, B, S, hq, hkv, hd, 1.0 / math.sqrt(hd))
+    want.square().mean().backward()
+    rel = (qkv.grad.float() - x.grad).norm() / x.grad.norm()
+    assert rel < 0.03, float(rel)

@@ -237,6 +237,447 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
   }
 }
 
+// ====================================================================================== backward
+// D[b, h, s] = sum_c dO[row, h*hd + c] * O[row, h*hd + c]   (one warp per (row, head))
+__global__ void __launch_bounds__(256)
+attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out, float* __restrict__ D,
+                     int B, int S, int Hq, int hd, int ld) {
+  const int lane = threadIdx.x & 31;
+  const long gw = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = ((long)gridDim.x * blockDim.x) >> 5;
+  const long total = (long)B * S * Hq;
+  for (long u = gw; u < total; u += nw) {
+    const int h = (int)(u % Hq);
+    const long row = u / Hq;
+    const __nv_bfloat16* a = dout + row * ld + h * hd;
+    const __nv_bfloat16* o = out + row * ld + h * hd;
+    float acc = 0.f;
+    for (int c = lane * 8; c < hd; c += 256) {
+      const uint4 x = *reinterpret_cast<const uint4*>(a + c), y = *reinterpret_cast<const uint4*>(o + c);
+      const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc += __uint_as_float(xw[i] << 16) * __uint_as_float(yw[i] << 16);
+        acc += __uint_as_float(xw[i] & 0xffff0000u) * __uint_as_float(yw[i] & 0xffff0000u);
+      }
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    if (lane == 0) {
+      const int b = (int)(row / S), sidx = (int)(row % S);
+      D[((size_t)b * Hq + h) * S + sidx] = acc;
+    }
+  }
+}
+
+struct AttnBwdParams {
+  __nv_bfloat16* dqkv;    // [B*S, (Hq + 2*Hkv) * hd]
+  const float* lse2;      // [B, Hq, S]
+  const float* D;         // [B, Hq, S]
+  int B, S, Hq, Hkv;
+  int ld_dqkv;
+  float scale_log2;
+  float scale;
+};
+
+// ---- dQ: one CTA per (query tile, head, batch).  Per key tile: S = Q K^T and dP = dO V^T into tensor memory,
+// dS = P * (dP - D) written to shared memory as an operand, dQ += dS K (K as MN-major operand).
+template <int HD>
+struct DqCfg {
+  static constexpr int ATOMS = HD / 64;
+  static constexpr int TILE_BYTES = 128 * HD * 2;
+  static constexpr int KV_STAGES = (HD <= 64) ? 2 : 1;
+  static constexpr int DS_BYTES = 128 * 128 * 2;
+  static constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + DS_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr uint32_t IDESC_S = make_idesc(128, 128, false, false);
+  static constexpr uint32_t IDESC_DQ = make_idesc(128, HD, false, true);
+};
+
+template <int HD>
+__global__ void __launch_bounds__(192)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
+                   const AttnBwdParams p) {
+  using C = DqCfg<HD>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* q_s = smem;
+  unsigned char* do_s = q_s + C::TILE_BYTES;
+  unsigned char* kv_s = do_s + C::TILE_BYTES;
+  unsigned char* ds_s = kv_s + C::KV_STAGES * 2 * C::TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_s + C::DS_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = bars + 3;
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* ds_ready = bars + 6;
+  uint64_t* dq_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qi = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (p.Hq / p.Hkv);
+  const int row0 = b * p.S + qi * 128;
+  const int ntiles = qi + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_ready, 4);
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) tmem_alloc(tmem_slot, C::TMEM_COLS);
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * C::TILE_BYTES);
+#pragma unroll
+      for (int a = 0; a < C::ATOMS; ++a) {
+        tma_load_2d(q_s + a * 16384, &tmap_qkv, q_full, h * HD + a * 64, row0);
+        tma_load_2d(do_s + a * 16384, &tmap_do, q_full, h * HD + a * 64, row0);
+      }
+      for (int j = 0; j < ntiles; ++j) {
+        const int st = j % C::KV_STAGES;
+        const uint32_t ph = (j / C::KV_STAGES) & 1;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, 11, &g_attn_error)) break;
+        unsigned char* k_s = kv_s + st * 2 * C::TILE_BYTES;
+        unsigned char* v_s = k_s + C::TILE_BYTES;
+        mbar_expect_tx(&kv_full[st], 2 * C::TILE_BYTES);
+        const int krow = b * p.S + j * 128;
+#pragma unroll
+        for (int a = 0; a < C::ATOMS; ++a) {
+          tma_load_2d(k_s + a * 16384, &tmap_qkv, &kv_full[st], (p.Hq + g) * HD + a * 64, krow);
+          tma_load_2d(v_s + a * 16384, &tmap_qkv, &kv_full[st], (p.Hq + p.Hkv + g) * HD + a * 64, krow);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, abort_flag, 12, &g_attn_error);
+      const uint32_t qa = smem_u32(q_s), doa = smem_u32(do_s), dsa = smem_u32(ds_s);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int st = j % C::KV_STAGES;
+        const uint32_t ph = (j / C::KV_STAGES) & 1;
+        if (!mbar_wait(&kv_full[st], ph, abort_flag, 13, &g_attn_error)) { ok = false; break; }
+        fence_after();
+        const uint32_t ka = smem_u32(kv_s + st * 2 * C::TILE_BYTES), va = ka + C::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tS, make_desc(qa + off, 16, 1024), make_desc(ka + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tDP, make_desc(doa + off, 16, 1024), make_desc(va + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(ds_ready, j & 1, abort_flag, 14, &g_attn_error)) { ok = false; break; }
+        fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tDQ, make_desc(dsa + aoff, 16, 1024), make_desc(ka + kk * 2048, 16384, 1024), C::IDESC_DQ,
+                    (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(dq_done);
+        umma_commit(&kv_empty[st]);
+      }
+    }
+  } else {
+    const int row = threadIdx.x;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const size_t vec = ((size_t)b * p.Hq + h) * p.S + qi * 128 + row;
+    const float lse = p.lse2[vec], Dr = p.D[vec];
+    bool ok = true;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      if (!mbar_wait(sdp_full, j & 1, abort_flag, 15, &g_attn_error)) { ok = false; break; }
+      if (j > 0 && !mbar_wait(dq_done, (j - 1) & 1, abort_flag, 16, &g_attn_error)) { ok = false; break; }
+      fence_after();
+      const bool diag = (j == qi);
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tS + lane_addr + c4 * 32, rs);
+        tmem_ld32(tDP + lane_addr + c4 * 32, rd);
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse);
+          float p1 = exp2f(__uint_as_float(rs[i + 1]) * p.scale_log2 - lse);
+          if (diag && (c4 * 32 + i) > row) p0 = 0.f;
+          if (diag && (c4 * 32 + i + 1) > row) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(rd[i]) - Dr), d1 = p1 * (__uint_as_float(rd[i + 1]) - Dr);
+          __nv_bfloat162 hh = __floats2bfloat162_rn(d0, d1);
+          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+        unsigned char* atom = ds_s + (c4 >> 1) * 16384;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t col = (c4 & 1) * 32 + q * 8;
+          *reinterpret_cast<uint4*>(atom + swz128(row, col)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+        }
+      }
+      fence_before();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+    }
+    if (ok && mbar_wait(dq_done, (ntiles - 1) & 1, abort_flag, 17, &g_attn_error)) {
+      fence_after();
+      __nv_bfloat16* op = p.dqkv + (size_t)(row0 + row) * p.ld_dqkv + h * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tDQ + lane_addr + c * 32, r);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t o[4];
+#pragma unroll
+          for (int k2 = 0; k2 < 4; ++k2) {
+            __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * k2]) * p.scale, __uint_as_float(r[8 * q + 2 * k2 + 1]) * p.scale);
+            o[k2] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+          *reinterpret_cast<uint4*>(op + c * 32 + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+  }
+
+  fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = gtimer();
+    while (gtimer() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---- dK, dV: one CTA per (key tile, KV head, batch); loops over the query heads of the group and the query
+// tiles at or after the key tile.  Scores are computed transposed (S^T = K Q^T, dP^T = V dO^T) so that a thread
+// owns a key row and P^T, dS^T go to shared memory as K-major operands; dV += P^T dO and dK += dS^T Q take dO and
+// Q as MN-major operands.
+template <int HD>
+struct DkvCfg {
+  static constexpr int ATOMS = HD / 64;
+  static constexpr int TILE_BYTES = 128 * HD * 2;
+  static constexpr int Q_STAGES = (HD <= 64) ? 2 : 1;
+  static constexpr int PT_BYTES = 128 * 128 * 2;
+  static constexpr int SMEM_BYTES = 2 * TILE_BYTES + Q_STAGES * 2 * TILE_BYTES + 2 * PT_BYTES + 2 * 2 * 128 * 4 + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr uint32_t IDESC_S = make_idesc(128, 128, false, false);
+  static constexpr uint32_t IDESC_DKV = make_idesc(128, HD, false, true);
+};
+
+template <int HD>
+__global__ void __launch_bounds__(192)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
+                    const AttnBwdParams p) {
+  using C = DkvCfg<HD>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* k_s = smem;
+  unsigned char* v_s = k_s + C::TILE_BYTES;
+  unsigned char* qdo_s = v_s + C::TILE_BYTES;                       // [stage][Q | dO]
+  unsigned char* pt_s = qdo_s + C::Q_STAGES * 2 * C::TILE_BYTES;
+  unsigned char* dst_s = pt_s + C::PT_BYTES;
+  float* vec_s = reinterpret_cast<float*>(dst_s + C::PT_BYTES);     // [2 parities][lse | D][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(vec_s) + 2 * 2 * 128 * 4);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 3;
+  uint64_t* st_full = bars + 5;
+  uint64_t* pt_ready = bars + 6;
+  uint64_t* dkv_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kj = blockIdx.x;                                        // key tile (small index = most work, runs first)
+  const int g = blockIdx.y, b = blockIdx.z;
+  const int rep = p.Hq / p.Hkv;
+  const int nq = p.S / 128;
+  const int per_head = nq - kj;                                     // query tiles kj..nq-1
+  const int niter = rep * per_head;
+  const int krow0 = b * p.S + kj * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+    mbar_init(st_full, 1);
+    mbar_init(pt_ready, 4);
+    mbar_init(dkv_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) tmem_alloc(tmem_slot, C::TMEM_COLS);
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tST = tmem_base, tDPT = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 256 + HD;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * C::TILE_BYTES);
+#pragma unroll
+      for (int a = 0; a < C::ATOMS; ++a) {
+        tma_load_2d(k_s + a * 16384, &tmap_qkv, kv_full, (p.Hq + g) * HD + a * 64, krow0);
+        tma_load_2d(v_s + a * 16384, &tmap_qkv, kv_full, (p.Hq + p.Hkv + g) * HD + a * 64, krow0);
+      }
+      for (int it = 0; it < niter; ++it) {
+        const int h = g * rep + it / per_head, qi = kj + it % per_head;
+        const int st = it % C::Q_STAGES;
+        const uint32_t ph = (it / C::Q_STAGES) & 1;
+        if (!mbar_wait(&qdo_empty[st], ph ^ 1, abort_flag, 21, &g_attn_error)) break;
+        unsigned char* q_s = qdo_s + st * 2 * C::TILE_BYTES;
+        unsigned char* do_s = q_s + C::TILE_BYTES;
+        mbar_expect_tx(&qdo_full[st], 2 * C::TILE_BYTES);
+        const int qrow = b * p.S + qi * 128;
+#pragma unroll
+        for (int a = 0; a < C::ATOMS; ++a) {
+          tma_load_2d(q_s + a * 16384, &tmap_qkv, &qdo_full[st], h * HD + a * 64, qrow);
+          tma_load_2d(do_s + a * 16384, &tmap_do, &qdo_full[st], h * HD + a * 64, qrow);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      bool ok = mbar_wait(kv_full, 0, abort_flag, 22, &g_attn_error);
+      const uint32_t ka = smem_u32(k_s), va = smem_u32(v_s), pta = smem_u32(pt_s), dsta = smem_u32(dst_s);
+      for (int it = 0; it < niter && ok; ++it) {
+        const int st = it % C::Q_STAGES;
+        const uint32_t ph = (it / C::Q_STAGES) & 1;
+        if (!mbar_wait(&qdo_full[st], ph, abort_flag, 23, &g_attn_error)) { ok = false; break; }
+        fence_after();
+        const uint32_t qa = smem_u32(qdo_s + st * 2 * C::TILE_BYTES), doa = qa + C::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tST, make_desc(ka + off, 16, 1024), make_desc(qa + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tDPT, make_desc(va + off, 16, 1024), make_desc(doa + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(st_full);
+        if (!mbar_wait(pt_ready, it & 1, abort_flag, 24, &g_attn_error)) { ok = false; break; }
+        fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tDV, make_desc(pta + aoff, 16, 1024), make_desc(doa + kk * 2048, 16384, 1024), C::IDESC_DKV,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
+          umma_bf16(tDK, make_desc(dsta + aoff, 16, 1024), make_desc(qa + kk * 2048, 16384, 1024), C::IDESC_DKV,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(dkv_done);
+        umma_commit(&qdo_empty[st]);
+      }
+    }
+  } else {
+    const int row = threadIdx.x;                                    // key row within the tile
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < niter && ok; ++it) {
+      const int h = g * rep + it / per_head, qi = kj + it % per_head;
+      // per-query statistics of this (head, query tile): read straight from global memory (warp-uniform
+      // addresses, served by L1), so that no thread barrier is needed inside a loop that may be abandoned
+      const float* lse_v = p.lse2 + ((size_t)b * p.Hq + h) * p.S + qi * 128;
+      const float* d_v = p.D + ((size_t)b * p.Hq + h) * p.S + qi * 128;
+      if (!mbar_wait(st_full, it & 1, abort_flag, 25, &g_attn_error)) { ok = false; break; }
+      if (it > 0 && !mbar_wait(dkv_done, (it - 1) & 1, abort_flag, 26, &g_attn_error)) { ok = false; break; }
+      fence_after();
+      const bool diag = (qi == kj);
+#pragma unroll 1
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tST + lane_addr + c4 * 32, rs);
+        tmem_ld32(tDPT + lane_addr + c4 * 32, rd);
+        uint32_t pk[16], dk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int c0 = c4 * 32 + i;                               // query index within the tile
+          float p0 = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - __ldg(lse_v + c0));
+          float p1 = exp2f(__uint_as_float(rs[i + 1]) * p.scale_log2 - __ldg(lse_v + c0 + 1));
+          if (diag && c0 < row) p0 = 0.f;                           // causal: query must not precede the key
+          if (diag && (c0 + 1) < row) p1 = 0.f;
+          const float d0 = p0 * (__uint_as_float(rd[i]) - __ldg(d_v + c0)), d1 = p1 * (__uint_as_float(rd[i + 1]) - __ldg(d_v + c0 + 1));
+          __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd2 = __floats2bfloat162_rn(d0, d1);
+          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
+          dk[i >> 1] = *reinterpret_cast<uint32_t*>(&hd2);
+        }
+        unsigned char* atom_p = pt_s + (c4 >> 1) * 16384;
+        unsigned char* atom_d = dst_s + (c4 >> 1) * 16384;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off = swz128(row, (c4 & 1) * 32 + q * 8);
+          *reinterpret_cast<uint4*>(atom_p + off) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+          *reinterpret_cast<uint4*>(atom_d + off) = make_uint4(dk[4 * q], dk[4 * q + 1], dk[4 * q + 2], dk[4 * q + 3]);
+        }
+      }
+      fence_before();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pt_ready);
+    }
+    if (ok && mbar_wait(dkv_done, (niter - 1) & 1, abort_flag, 27, &g_attn_error)) {
+      fence_after();
+      __nv_bfloat16* dvp = p.dqkv + (size_t)(krow0 + row) * p.ld_dqkv + (p.Hq + p.Hkv + g) * HD;
+      __nv_bfloat16* dkp = p.dqkv + (size_t)(krow0 + row) * p.ld_dqkv + (p.Hq + g) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32], r2[32];
+        tmem_ld32(tDV + lane_addr + c * 32, r);
+        tmem_ld32(tDK + lane_addr + c * 32, r2);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t o[4], o2[4];
+#pragma unroll
+          for (int k2 = 0; k2 < 4; ++k2) {
+            __nv_bfloat162 hv = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * k2]), __uint_as_float(r[8 * q + 2 * k2 + 1]));
+            __nv_bfloat162 hk = __floats2bfloat162_rn(__uint_as_float(r2[8 * q + 2 * k2]) * p.scale, __uint_as_float(r2[8 * q + 2 * k2 + 1]) * p.scale);
+            o[k2] = *reinterpret_cast<uint32_t*>(&hv);
+            o2[k2] = *reinterpret_cast<uint32_t*>(&hk);
+          }
+          *reinterpret_cast<uint4*>(dvp + c * 32 + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(dkp + c * 32 + q * 8) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+        }
+      }
+    }
+  }
+
+  fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = gtimer();
+    while (gtimer() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -301,6 +742,45 @@ int zen_attn_fwd(const void* qkv, void* out, float* lse2, int B, int S, int Hq, 
   if (hd == 64) return launch_fwd<64>(tm, p, st);
   if (hd == 128) return launch_fwd<128>(tm, p, st);
   return launch_fwd<256>(tm, p, st);
+}
+
+// Causal attention backward.  dout / out: bf16 [B*S, Hq*hd] (row stride ld_o); lse2 from the forward; Dbuf: fp32
+// scratch [B, Hq, S]; dqkv: bf16 [B*S, (Hq + 2*Hkv)*hd] (row stride ld_qkv), fully overwritten.  hd in {64, 128}.
+int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse2, float* Dbuf, void* dqkv, int B,
+                 int S, int Hq, int Hkv, int hd, int ld_qkv, int ld_o, float scale, void* stream) {
+  if (S % 128 || Hq % Hkv || (hd != 64 && hd != 128)) return -2;
+  if ((ld_qkv % 8) || (ld_o % 8) || (reinterpret_cast<uintptr_t>(qkv) % 16) || (reinterpret_cast<uintptr_t>(dout) % 16) ||
+      (reinterpret_cast<uintptr_t>(dqkv) % 16) || (reinterpret_cast<uintptr_t>(out) % 16)) return -3;
+  cudaStream_t st = (cudaStream_t)stream;
+  CUtensorMap tq, tdo;
+  int rc = attn_make_map(qkv, (uint64_t)(Hq + 2 * Hkv) * hd, (uint64_t)B * S, (uint64_t)ld_qkv, &tq);
+  if (rc) return rc;
+  rc = attn_make_map(dout, (uint64_t)Hq * hd, (uint64_t)B * S, (uint64_t)ld_o, &tdo);
+  if (rc) return rc;
+  {
+    const long warps = (long)B * S * Hq;
+    long blocks = (warps + 7) / 8;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    attn_bwd_prep_kernel<<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, Dbuf, B, S, Hq, hd, ld_o);
+  }
+  AttnBwdParams p{(__nv_bfloat16*)dqkv, lse2, Dbuf, B, S, Hq, Hkv, ld_qkv, scale * 1.4426950408889634f, scale};
+  dim3 gq(S / 128, Hq, B), gk(S / 128, Hkv, B);
+#define LAUNCH_BWD(HD_)                                                                                              \
+  do {                                                                                                               \
+    static bool attr = false;                                                                                        \
+    if (!attr) {                                                                                                     \
+      cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_kernel<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<HD_>::SMEM_BYTES); \
+      if (e != cudaSuccess) return (int)e;                                                                           \
+      e = cudaFuncSetAttribute(attn_bwd_dkv_kernel<HD_>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<HD_>::SMEM_BYTES); \
+      if (e != cudaSuccess) return (int)e;                                                                           \
+      attr = true;                                                                                                   \
+    }                                                                                                                \
+    attn_bwd_dq_kernel<HD_><<<gq, 192, DqCfg<HD_>::SMEM_BYTES, st>>>(tq, tdo, p);                                    \
+    attn_bwd_dkv_kernel<HD_><<<gk, 192, DkvCfg<HD_>::SMEM_BYTES, st>>>(tq, tdo, p);                                  \
+  } while (0)
+  if (hd == 64) LAUNCH_BWD(64); else LAUNCH_BWD(128);
+#undef LAUNCH_BWD
+  return (int)cudaGetLastError();
 }
 
 int zen_attn_error() {

@@ -34,7 +34,7 @@ def have_kernel(seq, hq, hkv, hd, dtype) -> bool:
     return kernel_covers(seq, hq, hkv, hd, dtype, backward=True) and HAVE_BWD
 
 
-HAVE_BWD = False
+HAVE_BWD = True
 
 
 def attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale):
@@ -46,6 +46,18 @@ def attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale):
                                     qkv.stride(0), out.stride(0), ctypes.c_float(scale), _native.stream_ptr())
     _native.check(rc, "zen_attn_fwd")
     return out, lse2
+
+
+def attention_bwd_kernel(dout, qkv, out, lse2, bsz, seq, hq, hkv, hd, scale):
+    """tcgen05 backward: gradient of the fused qkv buffer (dQ kernel + dK/dV kernel, no atomics)."""
+    dout = dout if (dout.is_contiguous() and dout.data_ptr() % 16 == 0) else dout.contiguous()
+    dqkv = torch.empty_like(qkv)
+    dbuf = torch.empty(bsz, hq, seq, dtype=torch.float32, device=qkv.device)
+    rc = _native.lib().zen_attn_bwd(_native.ptr(qkv), _native.ptr(out), _native.ptr(dout), _native.ptr(lse2), _native.ptr(dbuf),
+                                    _native.ptr(dqkv), bsz, seq, hq, hkv, hd, qkv.stride(0), out.stride(0),
+                                    ctypes.c_float(scale), _native.stream_ptr())
+    _native.check(rc, "zen_attn_bwd")
+    return dqkv
 
 
 def attention_error() -> int:
@@ -75,13 +87,19 @@ def reference_attention(qkv, bsz, seq, hq, hkv, hd, scale):
 def attention_fwd(qkv, bsz, seq, hq, hkv, hd, scale):
     if not qkv.is_cuda:
         return reference_attention(qkv, bsz, seq, hq, hkv, hd, scale), ()
+    if have_kernel(seq, hq, hkv, hd, qkv.dtype) and qkv.is_contiguous():
+        out, lse2 = attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale)
+        return out, (lse2,)
     q, k, v = _split(qkv, bsz, seq, hq, hkv, hd)
     o = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale, enable_gqa=(hq != hkv))
     return o.transpose(1, 2).reshape(bsz * seq, hq * hd), ()
 
 
 def attention_bwd(dout, qkv, out, saved, bsz, seq, hq, hkv, hd, scale):
-    """Gradient w.r.t. the fused qkv buffer (recomputes the forward under autograd)."""
+    """Gradient w.r.t. the fused qkv buffer: the tcgen05 kernels when the forward saved its statistics, else a
+    recomputation under autograd."""
+    if len(saved) == 1 and qkv.is_cuda:
+        return attention_bwd_kernel(dout, qkv, out, saved[0], bsz, seq, hq, hkv, hd, scale)
     with torch.enable_grad():
         x = qkv.detach().requires_grad_(True)
         if not qkv.is_cuda:
