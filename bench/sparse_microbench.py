@@ -69,6 +69,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--with_reference", action="store_true",
+                    help="also time the reference's own zen_sparse_comm (NCCL + its kernels, bf16 only) from baseline/_ref")
     args = ap.parse_args()
     dtype = {"bf16": torch.bfloat16, "fp32": torch.float32}[args.dtype]
     method = int(args.method) if args.method.isdigit() else args.method
@@ -117,6 +119,20 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         P = world
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        ref_lba = None
+        if args.with_reference and dtype == torch.bfloat16:
+            root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+            sys.path.insert(0, os.path.join(root, "baseline", "shims"))
+            sys.path.insert(0, os.path.join(root, "baseline", "_ref"))
+            try:
+                import logging
+
+                import comm as ref_comm
+
+                ref_lba = ref_comm.LoadBalanceAllreduce(dist.group.WORLD, list(range(world)), logging.getLogger("ref"))
+            except Exception as ex:  # reference not installed on this box
+                if rank == 0:
+                    print(json.dumps({"reference": f"unavailable: {type(ex).__name__}: {ex}"}), flush=True)
         for ln in args.log2n:
             n = 1 << ln
             for d in args.density:
@@ -140,8 +156,21 @@ def main():
                 ms_s, ms_d, stm, err = t.tolist()
                 nnz = int((x != 0).sum())
                 rec_bytes_out = nnz * 8 * (P - 1) / P
+                ref_ms = {}
+                if ref_lba is not None:
+                    xr = x.clone()
+                    xr[0] = 0                      # the reference cannot transmit position 0
+                    for mth in (3, 2, 1):
+                        try:
+                            dist.barrier()
+                            tm = time_fn(lambda: ref_lba.zen_sparse_comm(xr, mth), max(2, args.iters // 2), 1, flush)
+                            tt = torch.tensor([tm], device=dev, dtype=torch.float64)
+                            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                            ref_ms[f"reference_m{mth}_ms"] = float(tt.item())
+                        except Exception as ex:
+                            ref_ms[f"reference_m{mth}_ms"] = f"failed: {type(ex).__name__}"
                 row = dict(mode="nvlink", P=P, log2n=ln, density=d, dtype=args.dtype, dist=args.dist, overlap=args.overlap,
-                           method=str(method), sparse_ms=ms_s, dense_nccl_ms=ms_d, speedup=ms_d / ms_s,
+                           method=str(method), sparse_ms=ms_s, dense_nccl_ms=ms_d, speedup=ms_d / ms_s, **ref_ms,
                            eff_GBps=n * x.element_size() / ms_s / 1e6, max_err=err, status=int(stm),
                            push_bytes_per_rank=rec_bytes_out)
                 if rank == 0:

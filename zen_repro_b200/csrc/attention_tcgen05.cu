@@ -45,7 +45,7 @@ struct FwdCfg {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(192, (HD <= 64) ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
   using C = FwdCfg<HD>;
   extern __shared__ unsigned char smem_raw[];
@@ -147,46 +147,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
       if (j > 0 && !mbar_wait(o_full, (j - 1) & 1, abort_flag, 6, &g_attn_error)) { ok = false; break; }
       fence_after();
       const bool diag = (j == qi);
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_addr + c4 * 32, r);
+      // the whole score row of this thread (128 values) in registers: one tensor-memory round trip
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld32_nowait(tS + lane_addr, r0);
+      tmem_ld32_nowait(tS + lane_addr + 32, r1);
+      tmem_ld32_nowait(tS + lane_addr + 64, r2);
+      tmem_ld32_nowait(tS + lane_addr + 96, r3);
+      tmem_wait_ld();
+      if (diag) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]) * p.scale_log2;
-          if (diag && (c4 * 32 + i) > row) v = -INFINITY;
-          mx = fmaxf(mx, v);
+          if (i > row) r0[i] = 0xff800000u;
+          if (32 + i > row) r1[i] = 0xff800000u;
+          if (64 + i > row) r2[i] = 0xff800000u;
+          if (96 + i > row) r3[i] = 0xff800000u;
         }
       }
-      const float m_new = fmaxf(m, mx);
-      const float alpha = exp2f(m - m_new);
-      float rowsum = 0.f;
-#pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t r[32];
-        tmem_ld32(tS + lane_addr + c4 * 32, r);
-        uint32_t pk[16];
+      float x0 = -INFINITY, x1 = -INFINITY, x2 = -INFINITY, x3 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float v0 = __uint_as_float(r[i]) * p.scale_log2, v1 = __uint_as_float(r[i + 1]) * p.scale_log2;
-          float e0 = exp2f(v0 - m_new), e1 = exp2f(v1 - m_new);
-          if (diag && (c4 * 32 + i) > row) e0 = 0.f;
-          if (diag && (c4 * 32 + i + 1) > row) e1 = 0.f;
-          rowsum += e0 + e1;
-          __nv_bfloat162 hh = __floats2bfloat162_rn(e0, e1);
-          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
-        }
-        unsigned char* atom = p_s + (c4 >> 1) * 16384;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t col = (c4 & 1) * 32 + q * 8;
-          *reinterpret_cast<uint4*>(atom + swz128(row, col)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-        }
+      for (int i = 0; i < 32; ++i) {
+        x0 = fmaxf(x0, __uint_as_float(r0[i])); x1 = fmaxf(x1, __uint_as_float(r1[i]));
+        x2 = fmaxf(x2, __uint_as_float(r2[i])); x3 = fmaxf(x3, __uint_as_float(r3[i]));
       }
-      l = l * alpha + rowsum;
+      const float mx = fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)) * p.scale_log2;
+      // lazy maximum: keep the old reference unless the row maximum grew by more than 2^8; P stays below 256,
+      // the final normalisation is exact either way, and O is rescaled only on such jumps
+      const bool need = mx > m + 8.f;
+      const float m_new = need ? mx : m;
+      const float alpha = need ? ex2f(m - m_new) : 1.f;
+      const float cs = p.scale_log2, nm = -m_new;
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#define ZEN_SOFTMAX_CHUNK(RR, C4, SUM)                                                                  \
+      {                                                                                                 \
+        uint32_t pk[16];                                                                                \
+        _Pragma("unroll") for (int i = 0; i < 32; i += 2) {                                             \
+          const float e0 = ex2f(fmaf(__uint_as_float(RR[i]), cs, nm));                                  \
+          const float e1 = ex2f(fmaf(__uint_as_float(RR[i + 1]), cs, nm));                              \
+          SUM += e0 + e1;                                                                               \
+          pk[i >> 1] = pack_bf16(e0, e1);                                                               \
+        }                                                                                               \
+        unsigned char* atom = p_s + ((C4) >> 1) * 16384;                                                \
+        _Pragma("unroll") for (int q = 0; q < 4; ++q)                                                   \
+          *reinterpret_cast<uint4*>(atom + swz128(row, ((C4) & 1) * 32 + q * 8)) =                      \
+              make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);                       \
+      }
+      ZEN_SOFTMAX_CHUNK(r0, 0, s0)
+      ZEN_SOFTMAX_CHUNK(r1, 1, s1)
+      ZEN_SOFTMAX_CHUNK(r2, 2, s2)
+      ZEN_SOFTMAX_CHUNK(r3, 3, s3)
+#undef ZEN_SOFTMAX_CHUNK
+      l = l * alpha + ((s0 + s1) + (s2 + s3));
       m = m_new;
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t r[32];
@@ -404,28 +416,37 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
       if (j > 0 && !mbar_wait(dq_done, (j - 1) & 1, abort_flag, 16, &g_attn_error)) { ok = false; break; }
       fence_after();
       const bool diag = (j == qi);
+      const float cs = p.scale_log2, nl = -lse;
 #pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t rs[32], rd[32];
-        tmem_ld32(tS + lane_addr + c4 * 32, rs);
-        tmem_ld32(tDP + lane_addr + c4 * 32, rd);
-        uint32_t pk[16];
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t sa[32], sb[32], da[32], db[32];
+        tmem_ld32_nowait(tS + lane_addr + hf * 64, sa);
+        tmem_ld32_nowait(tS + lane_addr + hf * 64 + 32, sb);
+        tmem_ld32_nowait(tDP + lane_addr + hf * 64, da);
+        tmem_ld32_nowait(tDP + lane_addr + hf * 64 + 32, db);
+        tmem_wait_ld();
+        if (diag) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse);
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * p.scale_log2 - lse);
-          if (diag && (c4 * 32 + i) > row) p0 = 0.f;
-          if (diag && (c4 * 32 + i + 1) > row) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rd[i]) - Dr), d1 = p1 * (__uint_as_float(rd[i + 1]) - Dr);
-          __nv_bfloat162 hh = __floats2bfloat162_rn(d0, d1);
-          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+          for (int i = 0; i < 32; ++i) {
+            if (hf * 64 + i > row) sa[i] = 0xff800000u;
+            if (hf * 64 + 32 + i > row) sb[i] = 0xff800000u;
+          }
         }
-        unsigned char* atom = ds_s + (c4 >> 1) * 16384;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t col = (c4 & 1) * 32 + q * 8;
-          *reinterpret_cast<uint4*>(atom + swz128(row, col)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+#define ZEN_DS_CHUNK(SS, DD, COL0)                                                                      \
+        {                                                                                               \
+          uint32_t pk[16];                                                                              \
+          _Pragma("unroll") for (int i = 0; i < 32; i += 2) {                                           \
+            const float p0 = ex2f(fmaf(__uint_as_float(SS[i]), cs, nl));                                \
+            const float p1 = ex2f(fmaf(__uint_as_float(SS[i + 1]), cs, nl));                            \
+            pk[i >> 1] = pack_bf16(p0 * (__uint_as_float(DD[i]) - Dr), p1 * (__uint_as_float(DD[i + 1]) - Dr)); \
+          }                                                                                             \
+          _Pragma("unroll") for (int q = 0; q < 4; ++q)                                                 \
+            *reinterpret_cast<uint4*>(ds_s + hf * 16384 + swz128(row, (COL0) + q * 8)) =                \
+                make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);                     \
         }
+        ZEN_DS_CHUNK(sa, da, 0)
+        ZEN_DS_CHUNK(sb, db, 32)
+#undef ZEN_DS_CHUNK
       }
       fence_before();
       fence_async_smem();
@@ -607,32 +628,43 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
       if (it > 0 && !mbar_wait(dkv_done, (it - 1) & 1, abort_flag, 26, &g_attn_error)) { ok = false; break; }
       fence_after();
       const bool diag = (qi == kj);
+      const float cs = p.scale_log2;
 #pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t rs[32], rd[32];
-        tmem_ld32(tST + lane_addr + c4 * 32, rs);
-        tmem_ld32(tDPT + lane_addr + c4 * 32, rd);
-        uint32_t pk[16], dk[16];
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t sa[32], sb[32], da[32], db[32];
+        tmem_ld32_nowait(tST + lane_addr + hf * 64, sa);
+        tmem_ld32_nowait(tST + lane_addr + hf * 64 + 32, sb);
+        tmem_ld32_nowait(tDPT + lane_addr + hf * 64, da);
+        tmem_ld32_nowait(tDPT + lane_addr + hf * 64 + 32, db);
+        tmem_wait_ld();
+        if (diag) {                                                // causal: a query must not precede the key
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int c0 = c4 * 32 + i;                               // query index within the tile
-          float p0 = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - __ldg(lse_v + c0));
-          float p1 = exp2f(__uint_as_float(rs[i + 1]) * p.scale_log2 - __ldg(lse_v + c0 + 1));
-          if (diag && c0 < row) p0 = 0.f;                           // causal: query must not precede the key
-          if (diag && (c0 + 1) < row) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rd[i]) - __ldg(d_v + c0)), d1 = p1 * (__uint_as_float(rd[i + 1]) - __ldg(d_v + c0 + 1));
-          __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd2 = __floats2bfloat162_rn(d0, d1);
-          pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hp);
-          dk[i >> 1] = *reinterpret_cast<uint32_t*>(&hd2);
+          for (int i = 0; i < 32; ++i) {
+            if (hf * 64 + i < row) sa[i] = 0xff800000u;
+            if (hf * 64 + 32 + i < row) sb[i] = 0xff800000u;
+          }
         }
-        unsigned char* atom_p = pt_s + (c4 >> 1) * 16384;
-        unsigned char* atom_d = dst_s + (c4 >> 1) * 16384;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t off = swz128(row, (c4 & 1) * 32 + q * 8);
-          *reinterpret_cast<uint4*>(atom_p + off) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-          *reinterpret_cast<uint4*>(atom_d + off) = make_uint4(dk[4 * q], dk[4 * q + 1], dk[4 * q + 2], dk[4 * q + 3]);
+#define ZEN_DKV_CHUNK(SS, DD, COL0)                                                                     \
+        {                                                                                               \
+          uint32_t pk[16], dk[16];                                                                      \
+          _Pragma("unroll") for (int i = 0; i < 32; i += 2) {                                           \
+            const int c0 = hf * 64 + (COL0) + i;                                                        \
+            const float2 ls = __ldg(reinterpret_cast<const float2*>(lse_v + c0));                       \
+            const float2 dd = __ldg(reinterpret_cast<const float2*>(d_v + c0));                         \
+            const float p0 = ex2f(fmaf(__uint_as_float(SS[i]), cs, -ls.x));                             \
+            const float p1 = ex2f(fmaf(__uint_as_float(SS[i + 1]), cs, -ls.y));                         \
+            pk[i >> 1] = pack_bf16(p0, p1);                                                             \
+            dk[i >> 1] = pack_bf16(p0 * (__uint_as_float(DD[i]) - dd.x), p1 * (__uint_as_float(DD[i + 1]) - dd.y)); \
+          }                                                                                             \
+          _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                               \
+            const uint32_t off = hf * 16384 + swz128(row, (COL0) + q * 8);                              \
+            *reinterpret_cast<uint4*>(pt_s + off) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]); \
+            *reinterpret_cast<uint4*>(dst_s + off) = make_uint4(dk[4 * q], dk[4 * q + 1], dk[4 * q + 2], dk[4 * q + 3]); \
+          }                                                                                             \
         }
+        ZEN_DKV_CHUNK(sa, da, 0)
+        ZEN_DKV_CHUNK(sb, db, 32)
+#undef ZEN_DKV_CHUNK
       }
       fence_before();
       fence_async_smem();

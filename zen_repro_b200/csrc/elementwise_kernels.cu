@@ -329,7 +329,7 @@ norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res, const T
   }
 }
 
-template <typename T, bool kLayer, int NV>
+template <typename T, bool kLayer, int NV, bool kParams>
 __global__ void __launch_bounds__(NORMW_WARPS * 32)
 norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __restrict__ wgt,
                      const float* __restrict__ rstd_in, const float* __restrict__ mean_in, const T* __restrict__ dres,
@@ -339,12 +339,12 @@ norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T*
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
   const int nv = cols / 8;
-  float aw[NV][8], ab[kLayer ? NV : 1][8];
+  float aw[kParams ? NV : 1][8], ab[(kLayer && kParams) ? NV : 1][8];
   float wv[NV][8];
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { aw[j][i] = 0.f; if (kLayer) ab[j][i] = 0.f; wv[j][i] = 0.f; }
+    for (int i = 0; i < 8; ++i) { if (kParams) { aw[j][i] = 0.f; if (kLayer) ab[j][i] = 0.f; } wv[j][i] = 0.f; }
     if (lane + 32 * j < nv) {
       Vec8<T>::load(wgt + (size_t)(lane + 32 * j) * 8, wv[j]);
       if (!kLayer && unit_offset) {
@@ -375,8 +375,7 @@ norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T*
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           xh[i] = (xh[i] - mean) * rstd;
-          aw[j][i] += d[i] * xh[i];
-          if (kLayer) ab[j][i] += d[i];
+          if (kParams) { aw[j][i] += d[i] * xh[i]; if (kLayer) ab[j][i] += d[i]; }
           const float g = d[i] * wv[j][i];
           s1 += g;
           s2 += g * xh[i];
@@ -403,6 +402,7 @@ norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T*
       }
     }
   }
+  if (!kParams) return;
   // fold the warps' partial dw / db through shared memory, one warp at a time (fixed order)
   float* sdw = sm_acc;
   float* sdb = sm_acc + cols;
@@ -425,6 +425,30 @@ norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T*
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
     part_dw[(size_t)blockIdx.x * cols + c] = sdw[c];
     if (kLayer && part_db) part_db[(size_t)blockIdx.x * cols + c] = sdb[c];
+  }
+}
+
+// Parameter gradients of a norm, column-sum style: CTA b covers rows [32 b, 32 b + 32) and every column (a thread
+// owns 8 columns, loads are coalesced along the row): part_dw[b][c] = sum_r dy * xhat, part_db[b][c] = sum_r dy.
+template <typename T, bool kLayer>
+__global__ void __launch_bounds__(256)
+norm_dwdb_partial_kernel(const T* __restrict__ dy, const T* __restrict__ h, const float* __restrict__ rstd_in,
+                         const float* __restrict__ mean_in, float* __restrict__ part_dw, float* __restrict__ part_db,
+                         int rows, int cols) {
+  const int r0 = blockIdx.x * 32, r1 = min(rows, r0 + 32);
+  for (int c8 = threadIdx.x * 8; c8 < cols; c8 += blockDim.x * 8) {
+    float aw[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ab[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 4
+    for (int r = r0; r < r1; ++r) {
+      float d[8], x[8];
+      Vec8<T>::load(dy + (size_t)r * cols + c8, d);
+      Vec8<T>::load(h + (size_t)r * cols + c8, x);
+      const float rs = rstd_in[r], mu = kLayer ? mean_in[r] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { aw[i] += d[i] * (x[i] - mu) * rs; ab[i] += d[i]; }
+    }
+    Vec8<float>::store(part_dw + (size_t)blockIdx.x * cols + c8, aw);
+    if (kLayer && part_db) Vec8<float>::store(part_db + (size_t)blockIdx.x * cols + c8, ab);
   }
 }
 
@@ -838,11 +862,12 @@ inline int cap_grid(size_t want, int mult) {
 extern "C" {
 
 // Rows of at most NORMW_MAXCOLS columns use the warp-per-row kernels, wider rows the CTA-per-row kernels.
+
 #define NORMW_MAXCOLS 1024
 static inline bool norm_warp_path(int cols, int dtype) { (void)dtype; return cols <= NORMW_MAXCOLS; }
 
 // Number of per-CTA partial rows the norm backward writes (the caller sizes its scratch with this).
-int zen_norm_bwd_parts(int rows) { return cap_grid((size_t)(rows + NORMW_WARPS - 1) / NORMW_WARPS, 3); }
+int zen_norm_bwd_parts(int rows) { const int a = cap_grid((size_t)rows, 2), b = (rows + 31) / 32; return a > b ? a : b; }
 
 #define NORM_NV_DISPATCH(cols, ...)                                   \
   if (cols <= NORM_THREADS * 8) { constexpr int NV = 1; __VA_ARGS__; } \
@@ -885,16 +910,20 @@ int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd
                  int unit_offset, int accumulate, int dtype, void* stream) {
   if (cols % 8 || cols > NORM_THREADS * NORM_MAXV * 8) return -2;
   cudaStream_t st = (cudaStream_t)stream;
-  const int grid = zen_norm_bwd_parts(rows);
+  const int grid = cap_grid((size_t)rows, 2);
   if (norm_warp_path(cols, dtype)) {
-    const size_t smem = (size_t)2 * cols * sizeof(float);
+    // dh by warp-per-row (light on registers, many rows in flight), then dw / db by a column-sum pass
+    const int g1 = cap_grid((size_t)(rows + NORMW_WARPS - 1) / NORMW_WARPS, 8);
+    const int parts = (rows + 31) / 32;
     DISPATCH_T(dtype, {
       NORMW_NV_DISPATCH(cols, {
-        if (layer) norm_bwd_warp_kernel<T, true, NV><<<grid, NORMW_WARPS * 32, smem, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
-        else norm_bwd_warp_kernel<T, false, NV><<<grid, NORMW_WARPS * 32, smem, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+        if (layer) norm_bwd_warp_kernel<T, true, NV, false><<<g1, NORMW_WARPS * 32, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+        else norm_bwd_warp_kernel<T, false, NV, false><<<g1, NORMW_WARPS * 32, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
       });
-      colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, grid, cols, accumulate);
-      if (layer && db) colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_db, (T*)db, grid, cols, accumulate);
+      if (layer) norm_dwdb_partial_kernel<T, true><<<parts, 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols);
+      else norm_dwdb_partial_kernel<T, false><<<parts, 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols);
+      colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate);
+      if (layer && db) colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_db, (T*)db, parts, cols, accumulate);
     });
     return (int)cudaGetLastError();
   }
