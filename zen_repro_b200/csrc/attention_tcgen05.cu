@@ -38,7 +38,10 @@ struct FwdCfg {
   static constexpr int TILE_BYTES = 128 * HD * 2;
   static constexpr int KV_STAGES = (HD <= 128) ? 2 : 1;
   static constexpr int P_BYTES = 128 * 128 * 2;
-  static constexpr int SMEM_BYTES = TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + P_BYTES + 1024 + 256;
+  // No slack for re-aligning the base: the kernel has no static shared memory, so its dynamic window starts at the
+  // CTA's shared-memory base, which is 1024-byte aligned; the kernel checks this and gives up cleanly otherwise.
+  // (With the slack, two hd = 64 CTAs would miss the per-SM capacity by 512 bytes.)
+  static constexpr int SMEM_BYTES = TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + P_BYTES + 256;
   static constexpr int TMEM_COLS = (HD <= 128) ? 256 : 512;
   static constexpr uint32_t IDESC_S = make_idesc(128, 128, false, false);
   static constexpr uint32_t IDESC_PV = make_idesc(128, HD, false, true);
@@ -48,8 +51,12 @@ template <int HD>
 __global__ void __launch_bounds__(192, (HD <= 64) ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
   using C = FwdCfg<HD>;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw;
+  if ((smem_u32(smem_raw) & 1023u) != 0u) {          // uniform over the CTA: nothing has been allocated yet
+    if (threadIdx.x == 0) atomicCAS(&g_attn_error, 0, 99);
+    return;
+  }
   unsigned char* q_s = smem;
   unsigned char* kv_s = q_s + C::TILE_BYTES;                       // [stage][K | V]
   unsigned char* p_s = kv_s + C::KV_STAGES * 2 * C::TILE_BYTES;
@@ -306,7 +313,7 @@ struct DqCfg {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(320)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
                    const AttnBwdParams p) {
   using C = DqCfg<HD>;
@@ -337,19 +344,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
     mbar_init(sdp_full, 1);
-    mbar_init(ds_ready, 4);
+    mbar_init(ds_ready, 8);
     mbar_init(dq_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) tmem_alloc(tmem_slot, C::TMEM_COLS);
+  if (warp == 9) tmem_alloc(tmem_slot, C::TMEM_COLS);
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tDP = tmem_base + 128, tDQ = tmem_base + 256;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       mbar_expect_tx(q_full, 2 * C::TILE_BYTES);
 #pragma unroll
@@ -372,7 +379,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag, 12, &g_attn_error);
       const uint32_t qa = smem_u32(q_s), doa = smem_u32(do_s), dsa = smem_u32(ds_s);
@@ -406,8 +413,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
       }
     }
   } else {
-    const int row = threadIdx.x;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    // warps w and w + 4 share the rows of TMEM lane group w & 3 and split the 128 key columns in two halves
+    const int row = (warp & 3) * 32 + lane;
+    const int hf = warp >> 2;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const size_t vec = ((size_t)b * p.Hq + h) * p.S + qi * 128 + row;
     const float lse = p.lse2[vec], Dr = p.D[vec];
     bool ok = true;
@@ -417,8 +426,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
       fence_after();
       const bool diag = (j == qi);
       const float cs = p.scale_log2, nl = -lse;
-#pragma unroll 1
-      for (int hf = 0; hf < 2; ++hf) {
+      {
         uint32_t sa[32], sb[32], da[32], db[32];
         tmem_ld32_nowait(tS + lane_addr + hf * 64, sa);
         tmem_ld32_nowait(tS + lane_addr + hf * 64 + 32, sb);
@@ -457,7 +465,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
       fence_after();
       __nv_bfloat16* op = p.dqkv + (size_t)(row0 + row) * p.ld_dqkv + h * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = hf * (HD / 64); c < (hf + 1) * (HD / 64); ++c) {
         uint32_t r[32];
         tmem_ld32(tDQ + lane_addr + c * 32, r);
 #pragma unroll
@@ -481,7 +489,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
     while (gtimer() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
@@ -504,7 +512,7 @@ struct DkvCfg {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(320)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
                     const AttnBwdParams p) {
   using C = DkvCfg<HD>;
@@ -539,19 +547,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     mbar_init(st_full, 1);
-    mbar_init(pt_ready, 4);
+    mbar_init(pt_ready, 8);
     mbar_init(dkv_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) tmem_alloc(tmem_slot, C::TMEM_COLS);
+  if (warp == 9) tmem_alloc(tmem_slot, C::TMEM_COLS);
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tST = tmem_base, tDPT = tmem_base + 128, tDV = tmem_base + 256, tDK = tmem_base + 256 + HD;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * C::TILE_BYTES);
 #pragma unroll
@@ -575,7 +583,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       bool ok = mbar_wait(kv_full, 0, abort_flag, 22, &g_attn_error);
       const uint32_t ka = smem_u32(k_s), va = smem_u32(v_s), pta = smem_u32(pt_s), dsta = smem_u32(dst_s);
@@ -615,8 +623,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
       }
     }
   } else {
-    const int row = threadIdx.x;                                    // key row within the tile
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const int row = (warp & 3) * 32 + lane;                         // key row within the tile
+    const int hf = warp >> 2;                                       // which 64-query half this warp handles
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     for (int it = 0; it < niter && ok; ++it) {
       const int h = g * rep + it / per_head, qi = kj + it % per_head;
@@ -629,8 +638,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
       fence_after();
       const bool diag = (qi == kj);
       const float cs = p.scale_log2;
-#pragma unroll 1
-      for (int hf = 0; hf < 2; ++hf) {
+      {
         uint32_t sa[32], sb[32], da[32], db[32];
         tmem_ld32_nowait(tST + lane_addr + hf * 64, sa);
         tmem_ld32_nowait(tST + lane_addr + hf * 64 + 32, sb);
@@ -676,7 +684,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
       __nv_bfloat16* dvp = p.dqkv + (size_t)(krow0 + row) * p.ld_dqkv + (p.Hq + p.Hkv + g) * HD;
       __nv_bfloat16* dkp = p.dqkv + (size_t)(krow0 + row) * p.ld_dqkv + (p.Hq + g) * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = hf * (HD / 64); c < (hf + 1) * (HD / 64); ++c) {
         uint32_t r[32], r2[32];
         tmem_ld32(tDV + lane_addr + c * 32, r);
         tmem_ld32(tDK + lane_addr + c * 32, r2);
@@ -704,7 +712,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
     while (gtimer() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
@@ -807,8 +815,8 @@ int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float
       if (e != cudaSuccess) return (int)e;                                                                           \
       attr = true;                                                                                                   \
     }                                                                                                                \
-    attn_bwd_dq_kernel<HD_><<<gq, 192, DqCfg<HD_>::SMEM_BYTES, st>>>(tq, tdo, p);                                    \
-    attn_bwd_dkv_kernel<HD_><<<gk, 192, DkvCfg<HD_>::SMEM_BYTES, st>>>(tq, tdo, p);                                  \
+    attn_bwd_dq_kernel<HD_><<<gq, 320, DqCfg<HD_>::SMEM_BYTES, st>>>(tq, tdo, p);                                    \
+    attn_bwd_dkv_kernel<HD_><<<gk, 320, DkvCfg<HD_>::SMEM_BYTES, st>>>(tq, tdo, p);                                  \
   } while (0)
   if (hd == 64) LAUNCH_BWD(64); else LAUNCH_BWD(128);
 #undef LAUNCH_BWD
