@@ -53,9 +53,13 @@ def main():
                 a = torch.randn(K, M, device="cuda").bfloat16(); b = torch.randn(K, N, device="cuda").bfloat16()
                 mine, ref = (lambda: G.gemm_tn(a, b)), (lambda: a.t() @ b)
             tm, tr = bench(mine, args.iters, flush), bench(ref, args.iters, flush)
+            pair = {"nt": lambda: G.gemm_nt(a, b, bn=512), "nn": lambda: G.gemm_nn(a, b, bn=512), "tn": lambda: G.gemm_tn(a, b, bn=512)}[mode]
+            one = {"nt": lambda: G.gemm_nt(a, b, bn=256), "nn": lambda: G.gemm_nn(a, b, bn=256), "tn": lambda: G.gemm_tn(a, b, bn=256)}[mode]
+            tp, t1 = bench(pair, args.iters, flush), bench(one, args.iters, flush)
             fl = 2.0 * M * N * K
             print(json.dumps(dict(mode=mode, M=M, N=N, K=K, zen_ms=round(tm, 4), cublas_ms=round(tr, 4),
                                   zen_tflops=round(fl / tm / 1e9, 1), cublas_tflops=round(fl / tr / 1e9, 1),
+                                  pair_tflops=round(fl / tp / 1e9, 1), one256_tflops=round(fl / t1 / 1e9, 1),
                                   err=G.gemm_error())), flush=True)
 
 

@@ -18,7 +18,7 @@ SHAPES = [(128, 128, 64), (128, 256, 128), (256, 512, 256), (1000, 768, 768), (8
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
-@pytest.mark.parametrize("bn", [0, 128, 256])
+@pytest.mark.parametrize("bn", [0, 128, 256, 512])     # 512 selects the CTA-pair kernel
 def test_nt(M, N, K, bn):
     torch.manual_seed(0)
     a = torch.randn(M, K, device="cuda").bfloat16()
@@ -63,3 +63,18 @@ def test_strided_operands_inside_a_wider_buffer():
     w = torch.randn(64, 128, device="cuda").bfloat16()
     _check(G.gemm_nt(q, w), q.float() @ w.float().t(), 128)
     _check(G.gemm_nt(k, w), k.float() @ w.float().t(), 128)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (8192, 2304, 768), (1000, 1300, 264)])
+def test_pair_kernel_all_layouts(M, N, K):
+    torch.manual_seed(4)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(K, N, device="cuda").bfloat16()
+    at = torch.randn(K, M, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    _check(G.gemm_nn(a, b, bias=bias, bn=512), a.float() @ b.float() + bias.float(), K)
+    _check(G.gemm_tn(at, b, bn=512), at.float().t() @ b.float(), K)
+    acc = torch.ones(M, N, device="cuda", dtype=torch.bfloat16)
+    G.gemm_nt(a, b.t().contiguous(), out=acc, accumulate=True, bn=512)
+    _check(acc, a.float() @ b.float() + 1.0, K)
+    assert G.gemm_error() == 0

@@ -1,0 +1,314 @@
+// bf16 GEMM on tcgen05 with CTA pairs (cta_group::2): two CTAs of a cluster share one 256 x 256 output tile.
+//
+//   C[M, N] (+)= A[M, K] * B[N, K]^T (+ bias[N])
+//
+// Each CTA of the pair holds 128 rows of A and 128 of the 256 rows of the B tile; one thread of the leader CTA
+// issues tcgen05.mma.cta_group::2 (M 256 x N 256 x K 16), the hardware reads both CTAs' shared memory and each
+// CTA's tensor memory receives its 128 accumulator rows.  Per SM that halves the shared-memory traffic of B, which
+// is what bounds the single-CTA kernel.  Roles per CTA: warp 0 TMA producer (both CTAs' loads complete on the
+// leader's "full" barrier), warp 1 MMA issuer (leader only; commits are multicast to both CTAs' barriers),
+// warps 2..5 epilogue.  Bounded waits everywhere; a CTA that gives up still joins the final cluster barrier.
+// Operands may be K-major or MN-major as in gemm_tcgen05.cu.
+#include "tc_common.cuh"
+#include "tmap_util.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int BM2 = 128;          // rows per CTA (256 per pair)
+constexpr int BN2 = 256;
+constexpr int BNH = 128;          // B rows held by each CTA
+constexpr int BK2 = 64;
+constexpr int STAGES2 = 6;
+constexpr int STAGE_BYTES2 = BM2 * BK2 * 2 + BNH * BK2 * 2;     // 32 KB per CTA
+constexpr int SMEM_BYTES2 = STAGES2 * STAGE_BYTES2 + 1024 + 256;
+
+__device__ int g_gemm2_error = 0;
+
+struct Gemm2Params {
+  void* C;
+  const void* bias;
+  int M, N, K, ldc;
+  int out_fp32, accumulate;
+  int num_m_pairs, num_n_tiles;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load whose completion is signalled on the pair leader's barrier (same offset, CTA-rank bit cleared).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  const uint32_t bar_leader = smem_u32(bar) & 0xFEFFFFFFu;
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_leader), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this offset in BOTH CTAs of the pair once all previously issued MMAs have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+// Arrive on the leader CTA's copy of a barrier from either CTA of the pair.
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(smem_u32(bar)));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const Gemm2Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE_BYTES2);
+  uint64_t* full = bars;                       // [STAGES2]   used on the leader
+  uint64_t* empty = bars + STAGES2;            // [STAGES2]   one copy per CTA
+  uint64_t* tfull = bars + 2 * STAGES2;        // [2]         one copy per CTA
+  uint64_t* tempty = bars + 2 * STAGES2 + 2;   // [2]         used on the leader, 8 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  constexpr uint32_t IDESC = make_idesc(256, BN2, A_MN, B_MN);
+  constexpr int A_BYTES = BM2 * BK2 * 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int num_tiles = p.num_m_pairs * p.num_n_tiles;
+  const int nkb = (p.K + BK2 - 1) / BK2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, 2 * BN2);
+  fence_before();
+  __syncthreads();
+  cluster_sync_all();                            // both CTAs' barriers exist before anyone signals them
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer (both CTAs)
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int m0 = (tile % p.num_m_pairs) * 256 + (int)cta * BM2;
+        const int n0 = (tile / p.num_m_pairs) * BN2 + (int)cta * BNH;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t ph = (it / STAGES2) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, 1, &g_gemm2_error)) { ok = false; break; }
+          unsigned char* sa = smem + s * STAGE_BYTES2;
+          unsigned char* sb = sa + A_BYTES;
+          if (cta == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES2);
+          const int k0 = kb * BK2;
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tma_a, &full[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM2 / 64; ++j) tma_load_2d_pair(sa + j * 8192, &tma_a, &full[s], m0 + 64 * j, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tma_b, &full[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * 8192, &tma_b, &full[s], n0 + 64 * j, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && cta == 0) {
+      // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tcount) {
+        const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], aph ^ 1, abort_flag, 2, &g_gemm2_error)) { ok = false; break; }
+        fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN2;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t ph = (it / STAGES2) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, 3, &g_gemm2_error)) { ok = false; break; }
+          fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES2);
+          const uint32_t sb = sa + A_BYTES;
+          const uint64_t adesc = A_MN ? make_desc(sa, 8192, 1024) : make_desc(sa, 16, 1024);
+          const uint64_t bdesc = B_MN ? make_desc(sb, 8192, 1024) : make_desc(sb, 16, 1024);
+#pragma unroll
+          for (int j = 0; j < BK2 / 16; ++j) {
+            const uint64_t astep = (uint64_t)((A_MN ? j * 2048 : j * 32) >> 4);
+            const uint64_t bstep = (uint64_t)((B_MN ? j * 2048 : j * 32) >> 4);
+            umma_bf16_pair(d_tmem, adesc + astep, bdesc + bstep, IDESC, (kb | j) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[s]);
+        }
+        if (ok) umma_commit_pair(&tfull[acc]);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- epilogue (warps 2..5, both CTAs)
+    const int grp = warp & 3;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tcount) {
+      const int m0 = (tile % p.num_m_pairs) * 256 + (int)cta * BM2, n0 = (tile / p.num_m_pairs) * BN2;
+      const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], aph, abort_flag, 4, &g_gemm2_error)) { ok = false; break; }
+      fence_after();
+      const int row = m0 + grp * 32 + lane;
+      const uint32_t taddr0 = tmem_base + ((uint32_t)(grp * 32) << 16) + acc * BN2;
+#pragma unroll 1
+      for (int ch = 0; ch < BN2 / 32; ++ch) {
+        uint32_t r[32];
+        tmem_ld32(taddr0 + ch * 32, r);
+        const int col0 = n0 + ch * 32;
+        if (row < p.M && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          const bool fullw = (col0 + 32 <= p.N);
+          if (p.bias) {
+            const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) if (fullw || col0 + i < p.N) v[i] += __bfloat162float(bp[i]);
+          }
+          if (p.out_fp32) {
+            float* cp = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
+            if (fullw && (p.ldc % 4 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (p.accumulate) { const float4 c = *reinterpret_cast<const float4*>(cp + i); o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w; }
+                *reinterpret_cast<float4*>(cp + i) = o;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) cp[i] = p.accumulate ? cp[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
+            if (fullw && (p.ldc % 8 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                if (p.accumulate) {
+                  const uint4 c = *reinterpret_cast<const uint4*>(cp + i);
+                  const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) { v[i + 2 * q] += __uint_as_float(w[q] << 16); v[i + 2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u); }
+                }
+                *reinterpret_cast<uint4*>(cp + i) = make_uint4(pack_bf16(v[i], v[i + 1]), pack_bf16(v[i + 2], v[i + 3]),
+                                                               pack_bf16(v[i + 4], v[i + 5]), pack_bf16(v[i + 6], v[i + 7]));
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (col0 + i < p.N) {
+                  const float o = p.accumulate ? __bfloat162float(cp[i]) + v[i] : v[i];
+                  cp[i] = __float2bfloat16_rn(o);
+                }
+              }
+            }
+          }
+        }
+      }
+      fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tempty[acc]);
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = gtimer();
+    while (gtimer() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();                            // the peer may still be reading this CTA's shared memory / barriers
+  if (warp == 1) {
+    fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * BN2);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+int launch2(const CUtensorMap& ta, const CUtensorMap& tb, Gemm2Params p, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES2);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  p.num_m_pairs = (p.M + 255) / 256;
+  p.num_n_tiles = (p.N + BN2 - 1) / BN2;
+  const int tiles = p.num_m_pairs * p.num_n_tiles;
+  int clusters = zen_tmap::sm_count() / 2;
+  if (tiles < clusters) clusters = tiles;
+  gemm_bf16_2cta_kernel<A_MN, B_MN><<<clusters * 2, 192, SMEM_BYTES2, st>>>(ta, tb, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" {
+
+// Same contract as zen_gemm_bf16 (without the tile choice): C[M,N] (+)= A * B^T (+ bias), CTA-pair kernel.
+int zen_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
+                       int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -2;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn) rc = zen_tmap::get(A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 128, &ta);
+  else rc = zen_tmap::get(A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, 64, &ta);
+  if (rc) return rc;
+  if (!b_mn) rc = zen_tmap::get(B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 128, &tb);
+  else rc = zen_tmap::get(B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64, &tb);
+  if (rc) return rc;
+  Gemm2Params p{C, bias, M, N, K, ldc, out_fp32, accumulate, 0, 0};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, p, st);
+  if (!a_mn && b_mn) return launch2<false, true>(ta, tb, p, st);
+  if (a_mn && !b_mn) return launch2<true, false>(ta, tb, p, st);
+  return launch2<true, true>(ta, tb, p, st);
+}
+
+int zen_gemm2_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm2_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_gemm2_error, &zero, sizeof(int));
+  return v;
+}
+
+}  // extern "C"

@@ -14,6 +14,23 @@ import torch
 from .. import _native
 
 _FORCE_TORCH = os.environ.get("ZEN_GEMM", "") == "torch"
+_PAIR_MODE = os.environ.get("ZEN_GEMM_2CTA", "auto")      # auto | 0 | 1
+
+
+def use_pair_kernel(M: int, N: int, K: int) -> bool:
+    """CTA-pair (256 x 256 tile) kernel when the problem fills the 74 clusters reasonably well."""
+    if _PAIR_MODE == "0":
+        return False
+    if _PAIR_MODE == "1":
+        return M >= 256 and N >= 128
+    if M < 512 or N < 256:
+        return False
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    waves = -(-tiles // 74)
+    eff = tiles / (waves * 74.0)
+    pad = (N / (((N + 255) // 256) * 256.0)) * (M / (((M + 255) // 256) * 256.0))
+    score = eff * pad
+    return score >= 0.8 or (score >= 0.6 and K >= 1024)
 
 
 def _use_kernel(a: torch.Tensor, b: torch.Tensor) -> bool:
@@ -40,6 +57,13 @@ def _launch(a, b, M, N, K, a_mn, b_mn, bias, out, accumulate, out_dtype, bn):
     assert out.dtype in (torch.bfloat16, torch.float32)
     if bias is not None:
         assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == N
+    pair = (bn == 512) or (bn == 0 and use_pair_kernel(M, N, K))
+    if pair:
+        rc = _native.lib().zen_gemm_bf16_2cta(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
+                                              a2.stride(0), b2.stride(0), out.stride(0), int(a_mn), int(b_mn),
+                                              int(out.dtype == torch.float32), int(accumulate), _native.stream_ptr())
+        _native.check(rc, "zen_gemm_bf16_2cta")
+        return out
     rc = _native.lib().zen_gemm_bf16(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
                                      a2.stride(0), b2.stride(0), out.stride(0), int(a_mn), int(b_mn),
                                      int(out.dtype == torch.float32), int(accumulate), bn, _native.stream_ptr())
@@ -92,4 +116,5 @@ def _finish(r, bias, out, accumulate, dtype):
 
 def gemm_error() -> int:
     """Error code of the last tcgen05 kernel that gave up a bounded wait (0 = none)."""
-    return int(_native.lib().zen_gemm_error())
+    lib = _native.lib()
+    return int(lib.zen_gemm_error()) or int(lib.zen_gemm2_error())
