@@ -791,7 +791,13 @@ struct AdamTensor {
 template <typename T>
 __global__ void __launch_bounds__(256)
 adamw_kernel(const AdamTensor* __restrict__ tab, int ntensors, const int32_t* __restrict__ chunk_tensor,
-             uint64_t nchunks, float lr, float b1, float b2, float eps, float bc1, float bc2, float gscale) {
+             uint64_t nchunks, float lr, float b1, float b2, float eps, float bc1, float bc2, float gscale,
+             const int32_t* __restrict__ step_dev) {
+  if (step_dev) {                        // step count kept on the device (CUDA-graph replay): derive the bias corrections here
+    const float t = (float)(*step_dev);
+    bc1 = 1.f - powf(b1, t);
+    bc2 = 1.f - powf(b2, t);
+  }
   for (uint64_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
     const AdamTensor t = tab[chunk_tensor[ch]];
     const uint64_t start = (ch - t.chunk0) * ADAM_CHUNK;
@@ -1018,10 +1024,12 @@ int zen_xent(const void* logits, const int64_t* labels, float* loss, void* dlogi
 
 int zen_adam_tensor_size() { return (int)sizeof(AdamTensor); }
 
+// step_dev (optional): device int32 holding the 1-based step count; when given, bc1 / bc2 are ignored and computed
+// from it inside the kernel, so that a captured launch stays correct across replays.
 int zen_adamw(const void* table, int ntensors, const int32_t* chunk_tensor, uint64_t nchunks, float lr, float b1,
-              float b2, float eps, float bc1, float bc2, float gscale, int dtype, void* stream) {
+              float b2, float eps, float bc1, float bc2, float gscale, const int32_t* step_dev, int dtype, void* stream) {
   const int grid = cap_grid((size_t)nchunks, 8);
-  DISPATCH_T(dtype, adamw_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const AdamTensor*)table, ntensors, chunk_tensor, nchunks, lr, b1, b2, eps, bc1, bc2, gscale));
+  DISPATCH_T(dtype, adamw_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const AdamTensor*)table, ntensors, chunk_tensor, nchunks, lr, b1, b2, eps, bc1, bc2, gscale, step_dev));
   return (int)cudaGetLastError();
 }
 

@@ -33,8 +33,11 @@ struct ZenRowCtx {
   uint32_t* status;
   uint32_t vocab;
   uint32_t pad;
+  const uint32_t* epoch_dev;  // optional: call counter on the device (bumped by zen_row_epoch_bump); overrides `epoch`
   ZenPerm perm;
 };
+
+__device__ __forceinline__ uint32_t row_epoch(const ZenRowCtx& c) { return c.epoch_dev ? *c.epoch_dev : c.epoch; }
 
 namespace {
 
@@ -96,7 +99,7 @@ __device__ __forceinline__ void publish(const ZenRowCtx& c, int which, uint32_t 
     mail->info = (ovf || (st & (ZEN_REC_OVERFLOW | ZEN_PEER_OVERFLOW | ZEN_GATHER_OVERFLOW | ZEN_TIMEOUT))) ? 1u : 0u;
     mail->aux = 0;
     __threadfence_system();
-    zen_st_release_sys(&mail->epoch, c.epoch);
+    zen_st_release_sys(&mail->epoch, row_epoch(c));
   }
   __syncthreads();
   if (!which) { if (threadIdx.x < ZEN_MAX_RANKS) c.cursors[threadIdx.x] = 0; }
@@ -143,7 +146,7 @@ row_reduce_kernel(const ZenRowCtx c, int src_begin, int src_end) {
   uint32_t local_status = 0;
   for (int s = src_begin; s < src_end; ++s) {
     const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_rec_mail) + s;
-    if (threadIdx.x == 0) s_ok = zen_wait_epoch(&mail->epoch, c.epoch, c.wait_ns) ? 1u : 0u;
+    if (threadIdx.x == 0) s_ok = zen_wait_epoch(&mail->epoch, row_epoch(c), c.wait_ns) ? 1u : 0u;
     __syncthreads();
     const bool ok = s_ok != 0;
     __syncthreads();
@@ -240,7 +243,7 @@ row_apply_kernel(const ZenRowCtx c, T* __restrict__ grad, float scale, int overw
   if ((int)threadIdx.x < c.nranks) {
     const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_g_mail) + threadIdx.x;
     uint32_t n = 0;
-    if (zen_wait_epoch(&mail->epoch, c.epoch, c.wait_ns)) {
+    if (zen_wait_epoch(&mail->epoch, row_epoch(c), c.wait_ns)) {
       if (zen_ld_acquire_sys(&mail->info) & 1u) local_status |= ZEN_PEER_OVERFLOW;
       else n = min(zen_ld_acquire_sys(&mail->count), c.cap_g);
     } else {
@@ -291,7 +294,15 @@ int sm_count_r() {
     default: return -1;                                                    \
   }
 
+__global__ void row_epoch_bump_kernel(uint32_t* e) { *e += 1; }
+
 extern "C" {
+
+// Advance the device-side call counter (first launch of every call when the counter lives on the device).
+int zen_row_epoch_bump(uint32_t* epoch_dev, void* stream) {
+  row_epoch_bump_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(epoch_dev);
+  return (int)cudaGetLastError();
+}
 
 int zen_row_ctx_size() { return (int)sizeof(ZenRowCtx); }
 

@@ -34,6 +34,7 @@ class FusedAdamW(torch.optim.Optimizer):
         self.master_weights = master_weights
         self._tables: dict = {}
         self._step = 0
+        self._step_dev = None          # device step counter, used when the step is captured in a CUDA graph
 
     def _init_state(self, p):
         st = self.state[p]
@@ -71,10 +72,16 @@ class FusedAdamW(torch.optim.Optimizer):
         self._tables[(gi, params[0].dtype)] = (key, table, ct, c0)
         return table, ct, c0
 
+    def enable_device_step(self, device):
+        """Keep the step count on the device so that ``step`` can be captured in a CUDA graph and replayed."""
+        self._step_dev = torch.full((1,), self._step, dtype=torch.int32, device=device)
+
     @torch.no_grad()
     def step(self, closure=None, grad_scale: float = 1.0):
         self._step += 1
         t = self._step
+        if self._step_dev is not None:
+            self._step_dev += 1
         for gi, group in enumerate(self.param_groups):
             b1, b2 = group["betas"]
             lr, eps, wd = group["lr"], group["eps"], group["weight_decay"]
@@ -91,7 +98,8 @@ class FusedAdamW(torch.optim.Optimizer):
                     rc = _native.lib().zen_adamw(_native.ptr(table), len(ps), _native.ptr(ct), ctypes.c_uint64(nch),
                                                  ctypes.c_float(lr), ctypes.c_float(b1), ctypes.c_float(b2),
                                                  ctypes.c_float(eps), ctypes.c_float(bc1), ctypes.c_float(bc2),
-                                                 ctypes.c_float(grad_scale), _native.DTYPE_CODE[dtype],
+                                                 ctypes.c_float(grad_scale), _native.ptr(self._step_dev),
+                                                 _native.DTYPE_CODE[dtype],
                                                  _native.stream_ptr())
                     _native.check(rc, "zen_adamw")
             else:

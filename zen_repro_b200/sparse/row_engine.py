@@ -27,7 +27,8 @@ class _RowCtx(ctypes.Structure):
         ("off_rec_val", ctypes.c_uint64), ("off_g_row", ctypes.c_uint64), ("off_g_val", ctypes.c_uint64),
         ("cap_rec", ctypes.c_uint32), ("cap_g", ctypes.c_uint32), ("nslots", ctypes.c_uint32), ("nwords", ctypes.c_uint32),
         ("acc", ctypes.c_void_p), ("bitmap", ctypes.c_void_p), ("list", ctypes.c_void_p), ("cursors", ctypes.c_void_p),
-        ("status", ctypes.c_void_p), ("vocab", ctypes.c_uint32), ("pad", ctypes.c_uint32), ("perm", _Perm),
+        ("status", ctypes.c_void_p), ("vocab", ctypes.c_uint32), ("pad", ctypes.c_uint32),
+        ("epoch_dev", ctypes.c_void_p), ("perm", _Perm),
     ]
 
 
@@ -116,9 +117,20 @@ class RowSparseAllReduce:
         self.region = make_symmetric(self.plan.sym_bytes, group, backend)
         self.state = RowRank(self.plan, self.region, wait_ms)
         self.deterministic, self.epoch = deterministic, 0
+        self._epoch_dev = None
+
+    def enable_device_epoch(self):
+        """Keep the call counter on the device (bumped by a one-thread kernel at the start of each call), so that a
+        captured sequence of calls stays in step with the peers when the graph is replayed."""
+        dev = self.state.acc.device
+        self._epoch_dev = torch.full((1,), self.epoch, dtype=torch.int32, device=dev)
+        self.state.ctx.epoch_dev = self._epoch_dev.data_ptr()
 
     def __call__(self, rows, count, vals, grad, scale=1.0, overwrite=False):
         self.epoch += 1
+        if self._epoch_dev is not None:
+            _native.check(self.state.lib.zen_row_epoch_bump(_native.ptr(self._epoch_dev), _native.stream_ptr()),
+                          "zen_row_epoch_bump")
         e, s = self.epoch, self.state
         s.push(rows, count, vals, e)
         s.reduce(vals.dtype, e, self.deterministic)

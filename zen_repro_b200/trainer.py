@@ -42,6 +42,8 @@ class TrainConfig:
     data_pool: int = 8                # pre-generated pinned batches that the stream cycles through (0 = generate per step)
     overlap: bool = True
     fused_tp: bool = True             # TP all-reduces fused into the GEMM epilogues (peer memory) instead of NCCL
+    cuda_graph: bool = False          # capture forward + backward + sync + optimizer once, then replay it every step
+    graph_warmup: int = 3             # eager steps before the capture
 
     def to_dict(self):
         return dataclasses.asdict(self)
@@ -81,7 +83,14 @@ class Trainer:
                         hook.engine_for(b.buffer.numel(), self.device)
             self.model.module.register_comm_hook(None, hook)
         self.step_count = 0
-        self._ids_dev = None
+        self._graph = None
+        self._static_ids = self._static_loss = None
+        self.graph_ok = (cfg.cuda_graph and self.device.type == "cuda" and cfg.method == 0 and cfg.tp == 1)
+        if self.graph_ok:
+            self.optimizer.enable_device_step(self.device)
+            emb = self.model.module.embedding_sync
+            if emb is not None and emb._engine is not None:
+                emb._engine.enable_device_epoch()
 
     @property
     def tokens_per_step(self) -> int:
@@ -95,7 +104,36 @@ class Trainer:
             labels = batch["labels"].to(self.device, non_blocking=True) if batch["labels"] is not batch["input_ids"] else ids
         return self.step_device(ids, labels, read_loss)
 
+    def _capture(self, ids: torch.Tensor):
+        """Capture one full training step (forward, backward, gradient synchronisation, AdamW, zero-grad) in a CUDA
+        graph.  Everything the step reads at run time lives on the device: the token buffer, the optimizer's step
+        count and the sparse engine's call counter."""
+        self._static_ids = ids.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(self.cfg.graph_warmup):
+                self._eager_step(self._static_ids, self._static_ids)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._static_loss = self._eager_step(self._static_ids, self._static_ids)
+        self._graph = g
+
     def step_device(self, ids: torch.Tensor, labels: torch.Tensor, read_loss: bool = False):
+        if self.graph_ok and labels is ids:
+            if self._graph is None:
+                self._capture(ids)
+            self._static_ids.copy_(ids, non_blocking=True)
+            self._graph.replay()
+            self.step_count += 1
+            return float(self._static_loss.item()) if read_loss else self._static_loss
+        loss = self._eager_step(ids, labels)
+        self.step_count += 1
+        return float(loss.item()) if read_loss else loss
+
+    def _eager_step(self, ids: torch.Tensor, labels: torch.Tensor):
         with trace_range("forward"):
             loss = self.model(ids, labels)
         with trace_range("backward"):
@@ -103,8 +141,7 @@ class Trainer:
         with trace_range("optimizer_step"):
             self.optimizer.step()
             self.model.module.zero_grad()
-        self.step_count += 1
-        return float(loss.item()) if read_loss else loss.detach()
+        return loss.detach()
 
     def bytes_per_step(self, batch: dict) -> tuple[int, int]:
         h2d = batch["input_ids"].numel() * batch["input_ids"].element_size()
