@@ -93,6 +93,8 @@ def run_zen(args):
     e.record()
     barrier()
     launches = _native.launch_count() - l0
+    if trainer._graph is not None:         # replayed steps: the kernels were recorded once, at capture
+        launches += trainer.graph_launches_per_step * args.steps
     ms = s.elapsed_time(e)
     # end to end through the public API: pinned host batch -> device, step, loss -> host
     e2e = None
@@ -135,12 +137,23 @@ def run_zen(args):
 
 def main():
     args = parse()
-    if args.impl == "reference":
-        from baseline.reference_arm import run_reference
+    try:
+        if args.impl == "reference":
+            from baseline.reference_arm import run_reference
 
-        run_reference(args, MODELS[args.config])
-    else:
-        run_zen(args)
+            run_reference(args, MODELS[args.config])
+        else:
+            run_zen(args)
+    except SystemExit:
+        raise
+    except BaseException:
+        # leave at once: a rank that lingers in teardown after an error keeps its peers waiting in a collective
+        import traceback
+
+        traceback.print_exc()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(1)
 
 
 if __name__ == "__main__":

@@ -361,25 +361,25 @@ zen_gather_push_kernel(const ZenSparseCtx c) {
     }
     const uint32_t woff = incl - __popc(word);
     {
-      // phase A: every lane lists the set bits of its own word (shared memory only)
-      uint32_t w = word;
+      // Stream the accumulator: a lane whose bitmap word is non-empty loads its 32 slots as eight independent
+      // 16-byte vectors, clears them, and appends the touched ones (in slot order) to the CTA's staging run.
       uint32_t r = (coff - gbase) + woff;
-      const uint32_t slot0 = ch * 1024 + lane * 32;
-      while (w) {
-        s_idx[mis_i + r] = slot0 + (uint32_t)(__ffs(w) - 1);
-        w &= w - 1;
-        ++r;
-      }
-    }
-    __syncthreads();
-    {
-      // phase B: the whole CTA fetches and clears the listed slots, independent loads in flight
-      const uint32_t n = gend - gbase;
-      for (uint32_t i = tid; i < n; i += blockDim.x) {
-        const uint32_t slot = s_idx[mis_i + i];
-        const float a = c.acc[slot];
-        c.acc[slot] = 0.f;
-        s_val[mis_v + i] = ZenVal<T>::from_f(a);
+      if (word) {
+        float f[32];
+        float4* ap = reinterpret_cast<float4*>(c.acc + (size_t)ch * 1024 + (size_t)lane * 32);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) *reinterpret_cast<float4*>(&f[4 * k]) = ap[k];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ap[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        const uint32_t slot0 = ch * 1024 + lane * 32;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if ((word >> i) & 1u) {
+            s_val[mis_v + r] = ZenVal<T>::from_f(f[i]);
+            if (fmt == ZEN_FMT_COO) s_idx[mis_i + r] = slot0 + i;
+            ++r;
+          }
+        }
       }
     }
     __syncthreads();
@@ -485,37 +485,45 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
     }
     const uint32_t coff = bm ? reinterpret_cast<const uint32_t*>(base + c.off_g_off)[(uint64_t)o * (c.nchunks + 1) + ch] : 0u;
     const uint32_t woff = coff + incl - __popc(word);
-    // lanes 0..15 each invert the permutation for one 64-slot group of this chunk
-    uint64_t my_out = ~0ull;
-    if (lane < 16) {
-      const uint32_t slot0 = ch * 1024 + lane * 64;
-      if (slot0 < c.nslots) {
-        const uint32_t pb = o * c.perm.sb + (slot0 >> c.perm.lg);
-        const uint32_t blk = zen_perm_inv(c.perm, pb);
-        my_out = ((uint64_t)blk << c.perm.lg) + (slot0 & (G - 1u));
-      }
-    }
+    // four passes of 256 slots: every lane produces 8 consecutive output elements (one or two 16-byte stores)
 #pragma unroll
-    for (int jb = 0; jb < 16; ++jb) {
-      const uint64_t obase = __shfl_sync(0xffffffffu, my_out, jb);
-      const int wsel = 2 * jb + (lane >> 4);
+    for (int it = 0; it < 4; ++it) {
+      const int wsel = it * 8 + (lane >> 2);
       const uint32_t w = __shfl_sync(0xffffffffu, word, wsel);
       const uint32_t wo = __shfl_sync(0xffffffffu, woff, wsel);
-      if (obase == ~0ull) continue;
-      const int b0 = (2 * lane) & 31;
-      const uint64_t e = obase + 2 * lane;
-      T v0 = ZenVal<T>::from_f(0.f), v1 = v0;
-      if ((w >> b0) & 1u) v0 = gval[wo + __popc(w & ((1u << b0) - 1u))];
-      if ((w >> (b0 + 1)) & 1u) v1 = gval[wo + __popc(w & ((2u << b0) - 1u))];
-      if (e + 1 < N) {
+      const uint32_t slot0 = ch * 1024 + it * 256 + lane * 8;
+      if (slot0 >= c.nslots) continue;
+      const uint32_t blk = zen_perm_inv(c.perm, o * c.perm.sb + (slot0 >> c.perm.lg));
+      const uint64_t e = ((uint64_t)blk << c.perm.lg) + (slot0 & (G - 1u));
+      if (e >= N) continue;
+      const uint32_t sh = (lane & 3) * 8;
+      const uint32_t byte = (w >> sh) & 0xffu;
+      const uint32_t off0 = wo + __popc(w & ((1u << sh) - 1u));
+      T v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i] = ZenVal<T>::from_f(0.f);
+        if ((byte >> i) & 1u) v[i] = gval[off0 + __popc(byte & ((1u << i) - 1u))];
+      }
+      if (e + 8 <= N) {
         if (sizeof(T) == 2) {
-          uint32_t pk = (ZenVal<T>::bits(v1) << 16) | ZenVal<T>::bits(v0);
-          *reinterpret_cast<uint32_t*>(out + e) = pk;
+          uint4 pk;
+          pk.x = ZenVal<T>::bits(v[0]) | (ZenVal<T>::bits(v[1]) << 16);
+          pk.y = ZenVal<T>::bits(v[2]) | (ZenVal<T>::bits(v[3]) << 16);
+          pk.z = ZenVal<T>::bits(v[4]) | (ZenVal<T>::bits(v[5]) << 16);
+          pk.w = ZenVal<T>::bits(v[6]) | (ZenVal<T>::bits(v[7]) << 16);
+          *reinterpret_cast<uint4*>(out + e) = pk;
         } else {
-          out[e] = v0; out[e + 1] = v1;
+          uint4 lo, hi;
+          lo.x = ZenVal<T>::bits(v[0]); lo.y = ZenVal<T>::bits(v[1]); lo.z = ZenVal<T>::bits(v[2]); lo.w = ZenVal<T>::bits(v[3]);
+          hi.x = ZenVal<T>::bits(v[4]); hi.y = ZenVal<T>::bits(v[5]); hi.z = ZenVal<T>::bits(v[6]); hi.w = ZenVal<T>::bits(v[7]);
+          reinterpret_cast<uint4*>(out + e)[0] = lo;
+          reinterpret_cast<uint4*>(out + e)[1] = hi;
         }
-      } else if (e < N) {
-        out[e] = v0;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (e + i < N) out[e + i] = v[i];
       }
     }
   }

@@ -164,6 +164,7 @@ class ZenDDP(nn.Module):
         with trace_range(f"bucket{b.index}"):
             if self.comm_stream is not None:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
+                self._comm_used = True
                 with torch.cuda.stream(self.comm_stream):
                     b.future = hook(self._hook_state, gb)
             else:
@@ -176,7 +177,8 @@ class ZenDDP(nn.Module):
             for b in self.buckets:
                 if not b.launched:           # parameters without a gradient this step, or undeclared uses
                     self._launch(b)
-            ctx = torch.cuda.stream(self.comm_stream) if self.comm_stream is not None else _null()
+            used = self.comm_stream is not None and getattr(self, "_comm_used", False)
+            ctx = torch.cuda.stream(self.comm_stream) if used else _null()
             with ctx:
                 for b in self.buckets:
                     if b.future is not None:
@@ -186,8 +188,9 @@ class ZenDDP(nn.Module):
                         if res is not b.buffer and res.data_ptr() != b.buffer.data_ptr():
                             b.buffer.copy_(res.reshape(-1))
                         b.future = None
-            if self.comm_stream is not None:
+            if used:                      # join only a stream that was forked from this one during the step
                 torch.cuda.current_stream().wait_stream(self.comm_stream)
+                self._comm_used = False
             if hasattr(self.module, "sync_replicated_grads"):
                 self.module.sync_replicated_grads()
             if self.embedding_sync is not None:

@@ -152,7 +152,7 @@ class SparseRank:
         _native.check(rc, "zen_gather_push")
 
     def densify(self, out: torch.Tensor, epoch: int, fmt: int = FMT_AUTO):
-        assert out.is_contiguous() and out.numel() == self.plan.numel and out.data_ptr() % 4 == 0
+        assert out.is_contiguous() and out.numel() == self.plan.numel and out.data_ptr() % 16 == 0
         rc = self.lib.zen_densify(self._prep(epoch, fmt), _native.ptr(out), _native.DTYPE_CODE[out.dtype],
                                   _native.stream_ptr())
         _native.check(rc, "zen_densify")

@@ -84,6 +84,7 @@ class Trainer:
             self.model.module.register_comm_hook(None, hook)
         self.step_count = 0
         self._graph = None
+        self.graph_launches_per_step = 0
         self._static_ids = self._static_loss = None
         self.graph_ok = (cfg.cuda_graph and self.device.type == "cuda" and cfg.method == 0 and cfg.tp == 1)
         if self.graph_ok:
@@ -116,9 +117,13 @@ class Trainer:
                 self._eager_step(self._static_ids, self._static_ids)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from . import _native
+
         g = torch.cuda.CUDAGraph()
+        before = _native.launch_count()
         with torch.cuda.graph(g):
             self._static_loss = self._eager_step(self._static_ids, self._static_ids)
+        self.graph_launches_per_step = _native.launch_count() - before      # this library's kernels inside the graph
         self._graph = g
 
     def step_device(self, ids: torch.Tensor, labels: torch.Tensor, read_loss: bool = False):
