@@ -132,7 +132,13 @@ def run_zen(args):
     if rank == 0:
         print(json.dumps(out), flush=True)
     if dist.is_initialized():
-        dist.destroy_process_group()
+        dist.barrier()
+        torch.cuda.synchronize()
+    # leave without tearing down NCCL: a captured graph still references its communicator, and destroying the
+    # process group under it can block at exit
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def main():
