@@ -139,6 +139,54 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
   if (tid < ZEN_MAX_RANKS) { qn[tid] = 0; qvalid[tid] = 0; }
   __syncthreads();
 
+  constexpr int RAWW = sizeof(Raw8<T>) / 4;                           // words per staged vector (4 or 8)
+  __shared__ uint32_t wbuf[K1_WARPS][64][RAWW + 1];                   // per-warp staging: {first element, raw vector}
+  uint32_t wcnt = 0;                                                  // staged vectors of this warp (warp-uniform)
+
+  // Records of one 8-element vector starting at element e32: choose the owner, reserve queue space, write them.
+  auto emit = [&](uint32_t e32, const Raw8<T>& vec) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      bool keep = vec.nonzero(i);
+      if (use_thr) keep = keep && (fabsf(vec.value(i)) >= thr);
+      m |= keep ? (1u << i) : 0u;
+    }
+    if (!m) return;
+    uint32_t owner = 0, slot0 = e32;
+    if (!kBroadcast) {
+      const uint32_t pb = zen_perm_fwd(c.perm, e32 >> c.perm.lg);
+      owner = zen_owner_of(c.perm, pb, c.nranks);
+      slot0 = ((pb - owner * c.perm.sb) << c.perm.lg) + (e32 & (c.perm.block - 1u));
+    }
+    const uint32_t cnt = __popc(m);
+    uint32_t k = atomicAdd(&qn[owner], cnt);
+    bool direct = false;
+    if (k + cnt > K1_QCAP) {
+      if (k <= K1_QCAP) qvalid[owner] = k;                            // exactly one lane per overflow sees this
+      direct = true;
+      k = atomicAdd(&c.cursors[owner], cnt);                          // reserve directly in the destination
+    }
+    while (m) {
+      const int i = __ffs(m) - 1;
+      m &= m - 1;
+      const uint2 rec = make_uint2(slot0 + i, vec.bits(i));
+      if (!direct) {
+        q[owner * K1_QCAP + k] = rec;
+      } else if (k < c.cap_rec) {
+        if (kBroadcast) {
+          for (int p = 0; p < c.nranks; ++p)
+            reinterpret_cast<uint2*>(c.sym[p] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
+        } else {
+          reinterpret_cast<uint2*>(c.sym[owner] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
+        }
+      } else {
+        local_status |= ZEN_REC_OVERFLOW;
+      }
+      ++k;
+    }
+  };
+
   for (uint64_t it = blockIdx.x; it < ncta_it; it += gridDim.x) {
     Raw8<T> v[K1_U];
 #pragma unroll
@@ -146,54 +194,59 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
       const uint64_t e0 = (it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp) * 256 + (uint64_t)lane * 8;
       if (e0 < N) v[u].load(g, e0, N, aligned != 0); else v[u].zero();
     }
+    const bool last_it = (it + gridDim.x >= ncta_it);
+    // Vectors that hold a nonzero are first compacted into this warp's staging list (a ballot and one shared-memory
+    // store), and the expensive part -- owner lookup, queue reservation, record writes -- runs on 32 staged vectors
+    // at a time with every lane busy, instead of once per warp-load for the two or three lanes that have work.
 #pragma unroll
     for (int u = 0; u < K1_U; ++u) {
-      if (!v[u].any()) continue;
-      uint32_t m = 0;
+      const bool has = v[u].any();
+      const uint32_t bal = __ballot_sync(0xffffffffu, has);
+      if (!bal) continue;
+      if (has) {
+        uint32_t* ent = wbuf[warp][wcnt + __popc(bal & ((1u << lane) - 1u))];
+        ent[0] = (uint32_t)((it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp) * 256) + lane * 8;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        bool keep = v[u].nonzero(i);
-        if (use_thr) keep = keep && (fabsf(v[u].value(i)) >= thr);
-        m |= keep ? (1u << i) : 0u;
+        for (int k = 0; k < RAWW; ++k) ent[1 + k] = v[u].w[k];
       }
-      if (!m) continue;
-      const uint32_t e32 = (uint32_t)((it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp) * 256) + lane * 8;
-      uint32_t owner = 0, slot0 = e32;
-      if (!kBroadcast) {
-        const uint32_t pb = zen_perm_fwd(c.perm, e32 >> c.perm.lg);
-        owner = zen_owner_of(c.perm, pb, c.nranks);
-        slot0 = ((pb - owner * c.perm.sb) << c.perm.lg) + (e32 & (c.perm.block - 1u));
-      }
-      const uint32_t cnt = __popc(m);
-      uint32_t k = atomicAdd(&qn[owner], cnt);
-      bool direct = false;
-      if (k + cnt > K1_QCAP) {
-        if (k <= K1_QCAP) qvalid[owner] = k;                          // exactly one lane per overflow sees this
-        direct = true;
-        k = atomicAdd(&c.cursors[owner], cnt);                        // reserve directly in the destination
-      }
-      while (m) {
-        const int i = __ffs(m) - 1;
-        m &= m - 1;
-        const uint2 rec = make_uint2(slot0 + i, v[u].bits(i));
-        if (!direct) {
-          q[owner * K1_QCAP + k] = rec;
-        } else if (k < c.cap_rec) {
-          if (kBroadcast) {
-            for (int p = 0; p < c.nranks; ++p)
-              reinterpret_cast<uint2*>(c.sym[p] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
-          } else {
-            reinterpret_cast<uint2*>(c.sym[owner] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
-          }
-        } else {
-          local_status |= ZEN_REC_OVERFLOW;
+      wcnt += __popc(bal);
+      if (wcnt >= 32) {
+        __syncwarp();
+        {
+          Raw8<T> r;
+          const uint32_t* ent = wbuf[warp][lane];
+#pragma unroll
+          for (int k = 0; k < RAWW; ++k) r.w[k] = ent[1 + k];
+          emit(ent[0], r);
         }
-        ++k;
+        const uint32_t rest = wcnt - 32;
+        uint32_t tmp[RAWW + 1];
+        if (lane < rest) {
+#pragma unroll
+          for (int k = 0; k <= RAWW; ++k) tmp[k] = wbuf[warp][32 + lane][k];
+        }
+        __syncwarp();
+        if (lane < rest) {
+#pragma unroll
+          for (int k = 0; k <= RAWW; ++k) wbuf[warp][lane][k] = tmp[k];
+        }
+        __syncwarp();
+        wcnt = rest;
       }
+    }
+    if (last_it && wcnt) {                               // leftovers of this warp: drain with the lanes that have one
+      __syncwarp();
+      if (lane < wcnt) {
+        Raw8<T> r;
+        const uint32_t* ent = wbuf[warp][lane];
+#pragma unroll
+        for (int k = 0; k < RAWW; ++k) r.w[k] = ent[1 + k];
+        emit(ent[0], r);
+      }
+      wcnt = 0;
     }
     __syncthreads();
     // flush phase: warp w drains queue w when it holds a worthwhile run (or on the last iteration)
-    const bool last_it = (it + gridDim.x >= ncta_it);
     if (warp < nq) {
       uint32_t n = qn[warp];
       const bool overflowed = n > K1_QCAP;
