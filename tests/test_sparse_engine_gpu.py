@@ -139,3 +139,31 @@ def test_owner_map_kernel_matches_python():
     _native.check(lib.zen_owner_map(_native.ptr(out), ctypes.c_uint64(n), ctypes.byref(ps), 1, ctypes.c_uint32(table), P,
                                     _native.stream_ptr()), "owner_map")
     assert torch.equal(out.cpu().long(), zen_poly3_owner(torch.arange(n), table, P))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sampled_threshold_kernels(dtype):
+    import ctypes
+
+    from zen_repro_b200 import _native
+    from zen_repro_b200.parallel.hooks import sampled_threshold
+
+    dev = torch.device("cuda")
+    lib = _native.lib()
+    # exact k-th largest against torch.topk
+    torch.manual_seed(0)
+    v = torch.rand(100003, device=dev) * 5
+    hist = torch.zeros(2048, dtype=torch.int32, device=dev)
+    state = torch.zeros(2, dtype=torch.int32, device=dev)
+    out = torch.empty(1, device=dev)
+    for k in (1, 17, 5000, 100003):
+        _native.check(lib.zen_select_kth(_native.ptr(v), ctypes.c_uint32(v.numel()), ctypes.c_uint32(k), _native.ptr(hist),
+                                         _native.ptr(state), _native.ptr(out), _native.stream_ptr()), "select")
+        want = torch.topk(v, k, sorted=True)[0][-1]
+        assert float(out) == float(want), (k, float(out), float(want))
+        assert int(hist.abs().sum()) == 0
+    # the sampled threshold keeps about top_k percent
+    g = torch.randn(1 << 21, device=dev).to(dtype)
+    thr = sampled_threshold(g, 5)
+    frac = float((g.abs().float() >= thr).float().mean())
+    assert 0.04 < frac < 0.06, frac

@@ -811,3 +811,91 @@ int zen_sparse_balance(const void* in, uint64_t n, int dtype, int32_t* table, ui
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Sampled top-k threshold (the sparsifier of train.py:56-73 without a sort and without leaving the device):
+//   zen_sample_abs       |x| at `nsamples` pseudo-random positions (counter-based hash, with replacement)
+//   zen_select_kth       k-th largest of the (gathered) samples by a three-pass radix select on the float bits
+// The result is one device float that zen_partition_push consumes as its threshold.
+__device__ __forceinline__ uint32_t zen_mix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+  return x;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+zen_sample_abs_kernel(const T* __restrict__ x, uint64_t n, float* __restrict__ out, uint32_t nsamples, uint32_t seed) {
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < nsamples; i += gridDim.x * blockDim.x) {
+    const uint64_t r = ((uint64_t)zen_mix32(i * 2u + seed) << 32) | zen_mix32(i * 2u + 1u + seed * 0x9e3779b9u);
+    out[i] = fabsf(ZenVal<T>::to_f(x[r % n]));
+  }
+}
+
+// Histogram of bits [shift, shift + nbits) of the samples whose higher bits equal `prefix` (prefix_bits of them).
+__global__ void __launch_bounds__(256)
+zen_select_hist_kernel(const float* __restrict__ v, uint32_t n, uint32_t* __restrict__ hist, const uint32_t* __restrict__ state,
+                       int pass) {
+  __shared__ uint32_t sh[2048];
+  for (int i = threadIdx.x; i < 2048; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  // state[0] = prefix found so far (high bits), state[1] = remaining rank k (1-based among the candidates)
+  const uint32_t prefix = state[0];
+  const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
+  const int nbits = pass == 2 ? 10 : 11;
+  const int hi_shift = shift + nbits;                                  // bits above the current digit
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const uint32_t b = __float_as_uint(v[i]) & 0x7fffffffu;
+    if (pass == 0 || (b >> hi_shift) == prefix) atomicAdd(&sh[(b >> shift) & ((1u << nbits) - 1u)], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2048; i += blockDim.x)
+    if (sh[i]) atomicAdd(&hist[i], sh[i]);
+}
+
+// One CTA: walk the histogram from the top bin down to the bin holding the k-th largest; update state; clear hist.
+__global__ void __launch_bounds__(1024)
+zen_select_pick_kernel(uint32_t* __restrict__ hist, uint32_t* __restrict__ state, float* __restrict__ out, int pass) {
+  __shared__ uint32_t cnt[2048];
+  const int nbins = pass == 2 ? 1024 : 2048;
+  for (int i = threadIdx.x; i < 2048; i += blockDim.x) { cnt[i] = i < nbins ? hist[i] : 0u; hist[i] = 0u; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t k = state[1], acc = 0;
+    int bin = 0;
+    for (int i = nbins - 1; i >= 0; --i) {
+      if (acc + cnt[i] >= k) { bin = i; break; }
+      acc += cnt[i];
+    }
+    const int nbits = pass == 2 ? 10 : 11;
+    state[0] = (state[0] << nbits) | (uint32_t)bin;
+    state[1] = k - acc;
+    if (pass == 2) *out = __uint_as_float(state[0]);
+  }
+}
+
+__global__ void zen_select_init_kernel(uint32_t* state, uint32_t k) { state[0] = 0u; state[1] = k; }
+
+extern "C" {
+
+int zen_sample_abs(const void* x, uint64_t n, float* out, uint32_t nsamples, uint32_t seed, int dtype, void* stream) {
+  if (n == 0 || nsamples == 0) return -1;
+  const int grid = grid_for(nsamples, 256, sm_count() * 4);
+  DISPATCH_DTYPE(dtype, zen_sample_abs_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)x, n, out, nsamples, seed));
+  return (int)cudaGetLastError();
+}
+
+// k-th largest (1-based) of v[0..n) (non-negative floats) -> *out.  hist: 2048 zeroed uint32 (left zeroed),
+// state: 2 uint32 scratch.  Seven small launches, no host synchronisation.
+int zen_select_kth(const float* v, uint32_t n, uint32_t k, uint32_t* hist, uint32_t* state, float* out, void* stream) {
+  if (n == 0 || k == 0 || k > n) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  zen_select_init_kernel<<<1, 1, 0, st>>>(state, k);
+  const int grid = grid_for(n, 256 * 8, sm_count() * 2);
+  for (int pass = 0; pass < 3; ++pass) {
+    zen_select_hist_kernel<<<grid, 256, 0, st>>>(v, n, hist, state, pass);
+    zen_select_pick_kernel<<<1, 1024, 0, st>>>(hist, state, out, pass);
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -18,10 +18,41 @@ import math
 import torch
 import torch.distributed as dist
 
+from .. import _native
 from ..sparse import torch_pipeline
 from ..utils.trace import trace_range
 
 SMALL_BUCKET = 4096
+_select_state: dict = {}
+_sample_calls = [0]
+
+
+def _sampled_threshold_cuda(flat: torch.Tensor, ns: int, top_k: float, group) -> torch.Tensor:
+    """Kernel path: hash-sampled |g|, optional all-gather over the TP group, radix select of the k-th largest.
+    Everything stays on the device; the returned one-element float tensor feeds the partition kernel."""
+    import ctypes
+
+    lib = _native.lib()
+    dev = flat.device
+    st = _select_state.get(dev)
+    if st is None:
+        st = (torch.zeros(2048, dtype=torch.int32, device=dev), torch.zeros(2, dtype=torch.int32, device=dev))
+        _select_state[dev] = st
+    hist, state = st
+    _sample_calls[0] += 1
+    sample = torch.empty(ns, dtype=torch.float32, device=dev)
+    _native.check(lib.zen_sample_abs(_native.ptr(flat), ctypes.c_uint64(flat.numel()), _native.ptr(sample), ctypes.c_uint32(ns),
+                                     ctypes.c_uint32(_sample_calls[0] * 2654435761 & 0xFFFFFFFF),
+                                     _native.DTYPE_CODE[flat.dtype], _native.stream_ptr()), "zen_sample_abs")
+    if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+        gathered = torch.empty(dist.get_world_size(group) * ns, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(gathered, sample, group=group)
+        sample = gathered
+    k = max(1, int(sample.numel() * top_k // 100))
+    out = torch.empty(1, dtype=torch.float32, device=dev)
+    _native.check(lib.zen_select_kth(_native.ptr(sample), ctypes.c_uint32(sample.numel()), ctypes.c_uint32(k), _native.ptr(hist),
+                                     _native.ptr(state), _native.ptr(out), _native.stream_ptr()), "zen_select_kth")
+    return out
 
 
 def sampled_threshold(tensor: torch.Tensor, top_k: float, group=None, generator=None) -> torch.Tensor | None:
@@ -31,6 +62,8 @@ def sampled_threshold(tensor: torch.Tensor, top_k: float, group=None, generator=
     if numel <= SMALL_BUCKET:
         return None
     ns = math.ceil(0.01 * numel)
+    if flat.is_cuda and flat.dtype in _native.DTYPE_CODE and generator is None:
+        return _sampled_threshold_cuda(flat, ns, top_k, group)
     pos = torch.randint(0, numel, (ns,), device=flat.device, generator=generator)
     sample = flat[pos].abs()
     if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
