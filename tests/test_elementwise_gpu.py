@@ -142,7 +142,7 @@ def test_cuda_graph_step_matches_eager_steps():
     def run(graph):
         torch.manual_seed(0)
         t = Trainer(TrainConfig(model="gpt2", num_layers=2, micro_batch=2, seq_len=256, lr=1e-3, data_pool=4, cuda_graph=graph,
-                                graph_warmup=0), init_dist=False)
+                                graph_warmup=2), init_dist=False)
         ids = [next(t.data)["input_ids"].cuda() for _ in range(4)]
         out = [float(t.step_device(i, i, read_loss=True)) for i in ids + ids]
         return out, t
@@ -153,3 +153,24 @@ def test_cuda_graph_step_matches_eager_steps():
     assert graph[-1] < graph[0]
     for a, b in zip(eager, graph):
         assert abs(a - b) < 0.05, (eager, graph)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_vocab_parallel_xent_kernels(dtype):
+    g = torch.Generator().manual_seed(5)
+    rows, vl, valid, start = 33, 1000, 993, 2000
+    buf = (torch.randn(rows, vl + 0, generator=g) * 3).to(dtype)
+    labels = torch.randint(1500, 3500, (rows,), generator=g)
+    labels[1] = -100
+    labels[2] = start + 5
+    m0, s0, t0 = E.xent_partial(buf, labels, valid, start)
+    m1, s1, t1 = E.xent_partial(buf.to(DEV), labels.to(DEV), valid, start)
+    torch.testing.assert_close(m1.cpu(), m0, atol=1e-5, rtol=0)
+    torch.testing.assert_close(s1.cpu(), s0, atol=1e-2, rtol=1e-3)
+    torch.testing.assert_close(t1.cpu(), t0, atol=1e-5, rtol=0)
+    lse = m0 + s0.log() + 0.3
+    scale = torch.tensor([0.25])
+    d0 = E.xent_apply_(buf.clone(), labels, lse, valid, start, grad_scale_dev=scale)
+    d1 = E.xent_apply_(buf.to(DEV), labels.to(DEV), lse.to(DEV), valid, start, grad_scale_dev=scale.to(DEV))
+    torch.testing.assert_close(d1.cpu().float(), d0.float(), atol=2e-3, rtol=2e-2)
+    assert float(d1[1].abs().max()) == 0.0 and float(d1[:, valid:].abs().max()) == 0.0

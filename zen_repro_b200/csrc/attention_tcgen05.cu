@@ -496,9 +496,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
 }
 
 // ---- dK, dV: one CTA per (key tile, KV head, batch); loops over the query heads of the group and the query
-// tiles at or after the key tile.  Scores are computed transposed (S^T = K Q^T, dP^T = V dO^T) so that a thread
-// owns a key row and P^T, dS^T go to shared memory as K-major operands; dV += P^T dO and dK += dS^T Q take dO and
-// Q as MN-major operands.
+// tiles at or after the key tile.  S = Q K^T and dP = dO V^T are computed as in the dQ kernel (a thread owns a
+// query row, so its log-sum-exp and D are scalars); P and dS are stored [query][key] and the products
+// dV += P^T dO, dK += dS^T Q read them transposed as MN-major A operands, with dO and Q as MN-major B operands.
 template <int HD>
 struct DkvCfg {
   static constexpr int ATOMS = HD / 64;
@@ -508,7 +508,7 @@ struct DkvCfg {
   static constexpr int SMEM_BYTES = 2 * TILE_BYTES + Q_STAGES * 2 * TILE_BYTES + 2 * PT_BYTES + 2 * 2 * 128 * 4 + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
   static constexpr uint32_t IDESC_S = make_idesc(128, 128, false, false);
-  static constexpr uint32_t IDESC_DKV = make_idesc(128, HD, false, true);
+  static constexpr uint32_t IDESC_DKV = make_idesc(128, HD, true, true);   // A = P / dS read transposed (MN-major)
 };
 
 template <int HD>
@@ -596,26 +596,26 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tST, make_desc(ka + off, 16, 1024), make_desc(qa + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+          umma_bf16(tST, make_desc(qa + off, 16, 1024), make_desc(ka + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tDPT, make_desc(va + off, 16, 1024), make_desc(doa + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+          umma_bf16(tDPT, make_desc(doa + off, 16, 1024), make_desc(va + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
         }
         umma_commit(st_full);
         if (!mbar_wait(pt_ready, it & 1, abort_flag, 24, &g_attn_error)) { ok = false; break; }
         fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tDV, make_desc(pta + aoff, 16, 1024), make_desc(doa + kk * 2048, 16384, 1024), C::IDESC_DKV,
+          // P is stored [query row][key] (as the dQ kernel stores dS); read as an MN-major A operand it is P^T:
+          // M = keys (two 64-key groups 16 KB apart), K = queries (16 rows of 128 bytes per step)
+          umma_bf16(tDV, make_desc(pta + kk * 2048, 16384, 1024), make_desc(doa + kk * 2048, 16384, 1024), C::IDESC_DKV,
                     (it > 0 || kk > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t aoff = (kk >> 2) * 16384 + (kk & 3) * 32;
-          umma_bf16(tDK, make_desc(dsta + aoff, 16, 1024), make_desc(qa + kk * 2048, 16384, 1024), C::IDESC_DKV,
+          umma_bf16(tDK, make_desc(dsta + kk * 2048, 16384, 1024), make_desc(qa + kk * 2048, 16384, 1024), C::IDESC_DKV,
                     (it > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(dkv_done);
@@ -623,16 +623,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
       }
     }
   } else {
-    const int row = (warp & 3) * 32 + lane;                         // key row within the tile
-    const int hf = warp >> 2;                                       // which 64-query half this warp handles
+    const int row = (warp & 3) * 32 + lane;                         // query row in the loop, key row in the epilogue
+    const int hf = warp >> 2;                                       // which 64-key half of the score columns
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     for (int it = 0; it < niter && ok; ++it) {
       const int h = g * rep + it / per_head, qi = kj + it % per_head;
-      // per-query statistics of this (head, query tile): read straight from global memory (warp-uniform
-      // addresses, served by L1), so that no thread barrier is needed inside a loop that may be abandoned
-      const float* lse_v = p.lse2 + ((size_t)b * p.Hq + h) * p.S + qi * 128;
-      const float* d_v = p.D + ((size_t)b * p.Hq + h) * p.S + qi * 128;
+      // inside the loop a thread owns QUERY row `row` of tile qi (scores are computed as in the dQ kernel), so its
+      // softmax statistics are two scalars
+      const size_t vec = ((size_t)b * p.Hq + h) * p.S + qi * 128 + row;
+      const float nl = -p.lse2[vec], Dr = p.D[vec];
       if (!mbar_wait(st_full, it & 1, abort_flag, 25, &g_attn_error)) { ok = false; break; }
       if (it > 0 && !mbar_wait(dkv_done, (it - 1) & 1, abort_flag, 26, &g_attn_error)) { ok = false; break; }
       fence_after();
@@ -645,24 +645,21 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
         tmem_ld32_nowait(tDPT + lane_addr + hf * 64, da);
         tmem_ld32_nowait(tDPT + lane_addr + hf * 64 + 32, db);
         tmem_wait_ld();
-        if (diag) {                                                // causal: a query must not precede the key
+        if (diag) {                                                // causal: key column beyond the query row
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if (hf * 64 + i < row) sa[i] = 0xff800000u;
-            if (hf * 64 + 32 + i < row) sb[i] = 0xff800000u;
+            if (hf * 64 + i > row) sa[i] = 0xff800000u;
+            if (hf * 64 + 32 + i > row) sb[i] = 0xff800000u;
           }
         }
 #define ZEN_DKV_CHUNK(SS, DD, COL0)                                                                     \
         {                                                                                               \
           uint32_t pk[16], dk[16];                                                                      \
           _Pragma("unroll") for (int i = 0; i < 32; i += 2) {                                           \
-            const int c0 = hf * 64 + (COL0) + i;                                                        \
-            const float2 ls = __ldg(reinterpret_cast<const float2*>(lse_v + c0));                       \
-            const float2 dd = __ldg(reinterpret_cast<const float2*>(d_v + c0));                         \
-            const float p0 = ex2f(fmaf(__uint_as_float(SS[i]), cs, -ls.x));                             \
-            const float p1 = ex2f(fmaf(__uint_as_float(SS[i + 1]), cs, -ls.y));                         \
+            const float p0 = ex2f(fmaf(__uint_as_float(SS[i]), cs, nl));                                \
+            const float p1 = ex2f(fmaf(__uint_as_float(SS[i + 1]), cs, nl));                            \
             pk[i >> 1] = pack_bf16(p0, p1);                                                             \
-            dk[i >> 1] = pack_bf16(p0 * (__uint_as_float(DD[i]) - dd.x), p1 * (__uint_as_float(DD[i + 1]) - dd.y)); \
+            dk[i >> 1] = pack_bf16(p0 * (__uint_as_float(DD[i]) - Dr), p1 * (__uint_as_float(DD[i + 1]) - Dr)); \
           }                                                                                             \
           _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                               \
             const uint32_t off = hf * 16384 + swz128(row, (COL0) + q * 8);                              \

@@ -773,6 +773,56 @@ xent_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels, fl
   }
 }
 
+// Vocabulary-parallel cross-entropy, two kernels around the small cross-rank reductions:
+//   xent_partial_kernel : per row, max and sum-exp over this rank's vocabulary shard (columns >= valid_cols are
+//                         padding and ignored), plus the target logit when the label falls in the shard
+//   xent_apply_kernel   : dlogits = (exp(x - lse) - onehot) * scale in place, with the global lse of each row
+template <typename T>
+__global__ void __launch_bounds__(512)
+xent_partial_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels, float* __restrict__ rowmax,
+                    float* __restrict__ sumexp, float* __restrict__ target, int rows, int valid_cols, int ld,
+                    int64_t vocab_start, int64_t ignore_index) {
+  __shared__ float sh[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* lp = logits + (size_t)row * ld;
+    float m = -INFINITY, s = 0.f;
+    for (int c = threadIdx.x; c < valid_cols; c += blockDim.x) {
+      const float x = ZenVal<T>::to_f(lp[c]);
+      const float nm = fmaxf(m, x);
+      s = s * __expf(m - nm) + __expf(x - nm);
+      m = nm;
+    }
+    const float gm = block_max(m, sh);
+    s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+    const float gs = block_sum(s, sh);
+    if (threadIdx.x == 0) {
+      rowmax[row] = gm;
+      sumexp[row] = gs;
+      const int64_t lab = labels[row] - vocab_start;
+      target[row] = (labels[row] != ignore_index && lab >= 0 && lab < valid_cols) ? ZenVal<T>::to_f(lp[lab]) : 0.f;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+xent_apply_kernel(T* __restrict__ logits, const int64_t* __restrict__ labels, const float* __restrict__ lse,
+                  int rows, int cols, int valid_cols, int ld, float gscale_host, const float* __restrict__ gscale_dev,
+                  int64_t vocab_start, int64_t ignore_index) {
+  const float gscale = gscale_dev ? gscale_host * (*gscale_dev) : gscale_host;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    T* lp = logits + (size_t)row * ld;
+    const bool valid = labels[row] != ignore_index;
+    const int64_t lab = labels[row] - vocab_start;
+    const float l = lse[row], sc = valid ? gscale : 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      float pr = (c < valid_cols) ? __expf(ZenVal<T>::to_f(lp[c]) - l) : 0.f;
+      if (c == lab) pr -= 1.f;
+      lp[c] = ZenVal<T>::from_f(pr * sc);
+    }
+  }
+}
+
 // --------------------------------------------------------------------------------------------
 // Multi-tensor AdamW.  One table entry per tensor; CTAs walk a flat list of 64K-element chunks.
 struct AdamTensor {
@@ -1019,6 +1069,18 @@ int zen_rows_add(void* grad, const int32_t* rows, const int32_t* count, const vo
 int zen_xent(const void* logits, const int64_t* labels, float* loss, void* dlogits, int rows, int vocab, int ld,
              float gscale, const float* gscale_dev, int64_t ignore_index, int dtype, void* stream) {
   DISPATCH_T(dtype, xent_kernel<T><<<cap_grid((size_t)rows, 8), 512, 0, (cudaStream_t)stream>>>((const T*)logits, labels, loss, (T*)dlogits, rows, vocab, ld, gscale, gscale_dev, ignore_index));
+  return (int)cudaGetLastError();
+}
+
+int zen_xent_partial(const void* logits, const int64_t* labels, float* rowmax, float* sumexp, float* target, int rows,
+                     int valid_cols, int ld, int64_t vocab_start, int64_t ignore_index, int dtype, void* stream) {
+  DISPATCH_T(dtype, xent_partial_kernel<T><<<cap_grid((size_t)rows, 8), 512, 0, (cudaStream_t)stream>>>((const T*)logits, labels, rowmax, sumexp, target, rows, valid_cols, ld, vocab_start, ignore_index));
+  return (int)cudaGetLastError();
+}
+
+int zen_xent_apply(void* logits, const int64_t* labels, const float* lse, int rows, int cols, int valid_cols, int ld,
+                   float gscale, const float* gscale_dev, int64_t vocab_start, int64_t ignore_index, int dtype, void* stream) {
+  DISPATCH_T(dtype, xent_apply_kernel<T><<<cap_grid((size_t)rows, 8), 512, 0, (cudaStream_t)stream>>>((T*)logits, labels, lse, rows, cols, valid_cols, ld, gscale, gscale_dev, vocab_start, ignore_index));
   return (int)cudaGetLastError();
 }
 

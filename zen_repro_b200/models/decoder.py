@@ -214,24 +214,10 @@ class DecoderLM(nn.Module):
         return logits[..., : self.cfg.vocab_size]
 
     def _vocab_parallel_loss(self, y, labels):
-        """Cross-entropy over vocabulary shards: local max / sum-exp / target logit, three small all-reduces."""
-        g = self.tp_group
-        y = O.copy_to_tp(y, g)
-        logits = O.linear(y, self.head_weight(), None, "out_in").float()
-        col = torch.arange(self.vocab_local, device=logits.device) + self.vocab_start
-        logits = logits.masked_fill(col[None, :] >= self.cfg.vocab_size, float("-inf"))
-        m = logits.max(dim=-1).values.detach()
-        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=g)
-        e = (logits - m[:, None]).exp()
-        s = O.reduce_from_tp(e.sum(-1), g)
-        valid = labels != -100
-        lo = self.vocab_start
-        mine = valid & (labels >= lo) & (labels < lo + self.vocab_local)
-        idx = torch.where(mine, labels - lo, torch.zeros_like(labels))
-        tgt = logits.gather(1, idx[:, None]).squeeze(1) * mine
-        tgt = O.reduce_from_tp(tgt, g)
-        loss = (s.log() + m - tgt) * valid
-        return loss.sum() / valid.sum().clamp(min=1)
+        """Cross-entropy over vocabulary shards; the hidden-state gradient is the sum over the group of each shard's
+        dlogits @ W_local (the input of this function is replicated, so that sum is its full gradient)."""
+        return O.vocab_parallel_lm_head_loss(y, self.head_weight(), labels, self.tp_group, self.vocab_start,
+                                             self.cfg.vocab_size, tp_ws=getattr(self, "tp_ws", None))
 
     def sync_replicated_grads(self):
         """Sum over the TP group the gradients of weights that are replicated but see only part of the work: the

@@ -285,6 +285,69 @@ def lm_head_loss(h, weight, labels, ignore_index=-100, chunk_tokens=8192, unit_g
     return LMHeadLossFn.apply(h, weight, labels, ignore_index, chunk_tokens, unit_grad)
 
 
+class VocabParallelLMHeadLossFn(torch.autograd.Function):
+    """LM head + cross-entropy with the vocabulary sharded over the tensor-parallel group.  Per chunk of tokens: local
+    logits GEMM, local max / sum-exp / target logit (one kernel), three [tokens]-sized all-reduces, dlogits in place
+    (one kernel), then dW_local = dlogits^T h and the partial dh = dlogits W_local, which is summed over the group
+    (fused into the GEMM epilogue when a workspace is given).  Unit incoming gradient assumed, as in LMHeadLossFn."""
+
+    @staticmethod
+    def forward(ctx, h, weight, labels, group, vocab_start, vocab_size, ignore_index, chunk_tokens, tp_ws):
+        h2 = h.reshape(-1, h.shape[-1])
+        lab = labels.reshape(-1)
+        T = h2.shape[0]
+        Vl = weight.shape[0]
+        valid_cols = max(0, min(Vl, vocab_size - vocab_start))
+        inv = 1.0 / (lab != ignore_index).sum().clamp_(min=1).to(torch.float32).reshape(1)
+        vpad = (Vl + 7) // 8 * 8
+        dh = torch.empty_like(h2)
+        direct = _claim(weight)
+        if not direct:
+            _declare_autograd_use(weight)
+        dw = weight.grad if direct else torch.zeros(weight.shape, dtype=weight.dtype, device=h2.device)
+        loss_sum = torch.zeros((), dtype=torch.float32, device=h2.device)
+        for s in range(0, T, chunk_tokens):
+            e = min(T, s + chunk_tokens)
+            buf = torch.empty(e - s, vpad, dtype=h2.dtype, device=h2.device)
+            logits = buf[:, :Vl]
+            G.gemm_nt(h2[s:e], weight, out=logits)
+            m, se, tgt = E.xent_partial(logits, lab[s:e], valid_cols, vocab_start, ignore_index)
+            gm = m.clone()
+            dist.all_reduce(gm, op=dist.ReduceOp.MAX, group=group)
+            se = se * torch.exp(m - gm)
+            packed = torch.stack([se, tgt])
+            dist.all_reduce(packed, group=group)
+            lse = gm + packed[0].log()
+            valid = lab[s:e] != ignore_index
+            loss_sum += ((lse - packed[1]) * valid).sum()
+            E.xent_apply_(logits, lab[s:e], lse, valid_cols, vocab_start, grad_scale_dev=inv, ignore_index=ignore_index)
+            if tp_ws is not None and tp_ws.fits(e - s, h2.shape[1]):
+                tp_ws.gemm_ar_nn(logits, weight, out=dh[s:e])
+            else:
+                part = G.gemm_nn(logits, weight)
+                dist.all_reduce(part, group=group)
+                dh[s:e] = part
+            G.gemm_tn(logits, h2[s:e], out=dw, accumulate=True)
+        ctx.save_for_backward(dh, dw if not direct else dh)
+        ctx.cfg = (h.shape, direct)
+        ctx.wp = weight
+        return loss_sum * inv.squeeze(0)
+
+    @staticmethod
+    def backward(ctx, g):
+        dh, dw = ctx.saved_tensors
+        hshape, direct = ctx.cfg
+        if direct:
+            ctx.wp.zen_ready(ctx.wp)
+            return (dh.view(hshape),) + (None,) * 8
+        return (dh.view(hshape), dw) + (None,) * 7
+
+
+def vocab_parallel_lm_head_loss(h, weight, labels, group, vocab_start, vocab_size, ignore_index=-100, chunk_tokens=8192,
+                                tp_ws=None):
+    return VocabParallelLMHeadLossFn.apply(h, weight, labels, group, vocab_start, vocab_size, ignore_index, chunk_tokens, tp_ws)
+
+
 class AttentionFn(torch.autograd.Function):
     """Causal self-attention over a fused qkv projection [B*S, (Hq + 2 Hkv) * hd] -> [B*S, Hq * hd]."""
 

@@ -330,3 +330,48 @@ def cross_entropy(logits, labels, *, grad_scale: float | None = None, ignore_ind
                                 _code(lg), _native.stream_ptr())
     _native.check(rc, "zen_xent")
     return loss, d
+
+
+# ----------------------------------------------------------------------------- vocabulary-parallel cross entropy
+def xent_partial(logits, labels, valid_cols: int, vocab_start: int, ignore_index: int = -100):
+    """Per-row (max, sum-exp, target logit) over this rank's vocabulary shard ``logits[:, :valid_cols]``."""
+    rows = logits.shape[0]
+    if not logits.is_cuda:
+        lf = logits[:, :valid_cols].float()
+        m = lf.max(-1).values if valid_cols else torch.full((rows,), float("-inf"))
+        s = (lf - m[:, None]).exp().sum(-1)
+        lab = labels - vocab_start
+        mine = (labels != ignore_index) & (lab >= 0) & (lab < valid_cols)
+        tgt = torch.where(mine, lf.gather(1, lab.clamp(0, max(valid_cols - 1, 0))[:, None]).squeeze(1), torch.zeros(rows))
+        return m, s, tgt
+    m = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    s2 = torch.empty_like(m)
+    tgt = torch.empty_like(m)
+    rc = _native.lib().zen_xent_partial(_native.ptr(logits), _native.ptr(labels), _native.ptr(m), _native.ptr(s2), _native.ptr(tgt),
+                                        rows, valid_cols, logits.stride(0), ctypes.c_int64(vocab_start),
+                                        ctypes.c_int64(ignore_index), _code(logits), _native.stream_ptr())
+    _native.check(rc, "zen_xent_partial")
+    return m, s2, tgt
+
+
+def xent_apply_(logits, labels, lse, valid_cols: int, vocab_start: int, grad_scale_dev=None, grad_scale: float = 1.0,
+                ignore_index: int = -100):
+    """In place: logits <- (exp(logits - lse) - onehot(label - vocab_start)) * scale; padding columns get zero."""
+    rows, cols = logits.shape
+    if not logits.is_cuda:
+        lf = logits.float()
+        pr = (lf - lse[:, None]).exp()
+        pr[:, valid_cols:] = 0
+        lab = labels - vocab_start
+        mine = (labels != ignore_index) & (lab >= 0) & (lab < cols)
+        pr[mine, lab[mine]] -= 1.0
+        sc = grad_scale * (float(grad_scale_dev) if grad_scale_dev is not None else 1.0)
+        pr = pr * sc * (labels != ignore_index)[:, None]
+        logits.copy_(pr.to(logits.dtype))
+        return logits
+    rc = _native.lib().zen_xent_apply(_native.ptr(logits), _native.ptr(labels), _native.ptr(lse), rows, cols, valid_cols,
+                                      logits.stride(0), ctypes.c_float(grad_scale), _native.ptr(grad_scale_dev),
+                                      ctypes.c_int64(vocab_start), ctypes.c_int64(ignore_index), _code(logits),
+                                      _native.stream_ptr())
+    _native.check(rc, "zen_xent_apply")
+    return logits

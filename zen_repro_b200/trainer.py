@@ -43,7 +43,7 @@ class TrainConfig:
     overlap: bool = True
     fused_tp: bool = True             # TP all-reduces fused into the GEMM epilogues (peer memory) instead of NCCL
     cuda_graph: bool = False          # capture forward + backward + sync + optimizer once, then replay it every step
-    graph_warmup: int = 3             # eager steps before the capture
+    graph_warmup: int = 2             # real steps launched from the host before the capture
 
     def to_dict(self):
         return dataclasses.asdict(self)
@@ -110,12 +110,6 @@ class Trainer:
         graph.  Everything the step reads at run time lives on the device: the token buffer, the optimizer's step
         count and the sparse engine's call counter."""
         self._static_ids = ids.clone()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(self.cfg.graph_warmup):
-                self._eager_step(self._static_ids, self._static_ids)
-        torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         from . import _native
 
@@ -127,8 +121,8 @@ class Trainer:
         self._graph = g
 
     def step_device(self, ids: torch.Tensor, labels: torch.Tensor, read_loss: bool = False):
-        if self.graph_ok and labels is ids:
-            if self._graph is None:
+        if self.graph_ok and labels is ids and self.step_count >= self.cfg.graph_warmup:
+            if self._graph is None:        # the first steps ran eagerly (tables, scratch and peers are set up): record now
                 self._capture(ids)
             self._static_ids.copy_(ids, non_blocking=True)
             self._graph.replay()
