@@ -838,6 +838,19 @@ struct AdamTensor {
 };
 #define ADAM_CHUNK 65536
 
+// One AdamW element update.  The square root and the quotient use the approximate units (about 2 ulp): the update is
+// rounded to bf16 (or added to an fp32 master) right after, and the exact sequences cost several times the
+// instructions, enough to show against the 22 bytes per element this kernel moves.
+__device__ __forceinline__ void adam_update(float& p, float& m, float& v, float g, float b1, float b2, float eps,
+                                            float ibc1, float isb2, float decay, float lr) {
+  m = b1 * m + (1.f - b1) * g;
+  v = b2 * v + (1.f - b2) * g * g;
+  float sq;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(sq) : "f"(v));
+  const float den = fmaf(sq, isb2, eps);
+  p = fmaf(-lr, __fdividef(m * ibc1, den), p * decay);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 adamw_kernel(const AdamTensor* __restrict__ tab, int ntensors, const int32_t* __restrict__ chunk_tensor,
@@ -848,6 +861,7 @@ adamw_kernel(const AdamTensor* __restrict__ tab, int ntensors, const int32_t* __
     bc1 = 1.f - powf(b1, t);
     bc2 = 1.f - powf(b2, t);
   }
+  const float ibc1 = 1.f / bc1, isb2 = rsqrtf(bc2);
   for (uint64_t ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
     const AdamTensor t = tab[chunk_tensor[ch]];
     const uint64_t start = (ch - t.chunk0) * ADAM_CHUNK;
@@ -855,35 +869,55 @@ adamw_kernel(const AdamTensor* __restrict__ tab, int ntensors, const int32_t* __
     T* p = reinterpret_cast<T*>(t.param);
     const T* g = reinterpret_cast<const T*>(t.grad);
     const float decay = 1.f - lr * t.wd;
-    for (uint64_t i = start + (uint64_t)threadIdx.x * 8; i < end; i += 256 * 8) {
-      if (i + 8 <= end) {
-        float pv[8], gv[8], mv[8], vv[8];
-        if (t.master) Vec8<float>::load(t.master + i, pv); else Vec8<T>::load(p + i, pv);
-        Vec8<T>::load(g + i, gv);
-        Vec8<float>::load(t.m + i, mv);
-        Vec8<float>::load(t.v + i, vv);
+    // two 8-element vectors per thread and trip, all loads issued before the arithmetic
+    for (uint64_t i0 = start + (uint64_t)threadIdx.x * 8; i0 < end; i0 += 2 * 256 * 8) {
+      const uint64_t i1 = i0 + 256 * 8;
+      if (i1 + 8 <= end) {
+        float pv[2][8], gv[2][8], mv[2][8], vv[2][8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float gg = gv[k] * gscale;
-          mv[k] = b1 * mv[k] + (1.f - b1) * gg;
-          vv[k] = b2 * vv[k] + (1.f - b2) * gg * gg;
-          const float den = __fsqrt_rn(vv[k] / bc2) + eps;
-          pv[k] = pv[k] * decay - lr * __fdiv_rn(mv[k] / bc1, den);
+        for (int u = 0; u < 2; ++u) {
+          const uint64_t i = u ? i1 : i0;
+          if (t.master) Vec8<float>::load(t.master + i, pv[u]); else Vec8<T>::load(p + i, pv[u]);
+          Vec8<T>::load(g + i, gv[u]);
+          Vec8<float>::load(t.m + i, mv[u]);
+          Vec8<float>::load(t.v + i, vv[u]);
         }
-        Vec8<float>::store(t.m + i, mv);
-        Vec8<float>::store(t.v + i, vv);
-        if (t.master) Vec8<float>::store(t.master + i, pv);
-        Vec8<T>::store(p + i, pv);
-      } else {
-        for (uint64_t k = i; k < end; ++k) {
-          float pv = t.master ? t.master[k] : ZenVal<T>::to_f(p[k]);
-          const float gg = ZenVal<T>::to_f(g[k]) * gscale;
-          const float mm = b1 * t.m[k] + (1.f - b1) * gg;
-          const float vv = b2 * t.v[k] + (1.f - b2) * gg * gg;
-          pv = pv * decay - lr * __fdiv_rn(mm / bc1, __fsqrt_rn(vv / bc2) + eps);
-          t.m[k] = mm; t.v[k] = vv;
-          if (t.master) t.master[k] = pv;
-          p[k] = ZenVal<T>::from_f(pv);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint64_t i = u ? i1 : i0;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) adam_update(pv[u][k], mv[u][k], vv[u][k], gv[u][k] * gscale, b1, b2, eps, ibc1, isb2, decay, lr);
+          Vec8<float>::store(t.m + i, mv[u]);
+          Vec8<float>::store(t.v + i, vv[u]);
+          if (t.master) Vec8<float>::store(t.master + i, pv[u]);
+          Vec8<T>::store(p + i, pv[u]);
+        }
+        continue;
+      }
+      for (int u = 0; u < 2; ++u) {
+        const uint64_t i = u ? i1 : i0;
+        if (i >= end) break;
+        if (i + 8 <= end) {
+          float pv[8], gv[8], mv[8], vv[8];
+          if (t.master) Vec8<float>::load(t.master + i, pv); else Vec8<T>::load(p + i, pv);
+          Vec8<T>::load(g + i, gv);
+          Vec8<float>::load(t.m + i, mv);
+          Vec8<float>::load(t.v + i, vv);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) adam_update(pv[k], mv[k], vv[k], gv[k] * gscale, b1, b2, eps, ibc1, isb2, decay, lr);
+          Vec8<float>::store(t.m + i, mv);
+          Vec8<float>::store(t.v + i, vv);
+          if (t.master) Vec8<float>::store(t.master + i, pv);
+          Vec8<T>::store(p + i, pv);
+        } else {
+          for (uint64_t k = i; k < end; ++k) {
+            float pv = t.master ? t.master[k] : ZenVal<T>::to_f(p[k]);
+            float mm = t.m[k], vv = t.v[k];
+            adam_update(pv, mm, vv, ZenVal<T>::to_f(g[k]) * gscale, b1, b2, eps, ibc1, isb2, decay, lr);
+            t.m[k] = mm; t.v[k] = vv;
+            if (t.master) t.master[k] = pv;
+            p[k] = ZenVal<T>::from_f(pv);
+          }
         }
       }
     }

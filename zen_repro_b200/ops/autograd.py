@@ -15,22 +15,22 @@ from . import gemm as G
 from . import attention as A
 
 
-def _claim(p) -> bool:
+def _claim(p, needed: bool) -> bool:
     """Called in forward.  True when this op will ADD its gradient for ``p`` straight into ``p.grad`` (a bucket
     view of the data-parallel reducer) and signal ``p.zen_ready``; the claim is counted so that the reducer knows
-    how many such signals to expect before the parameter's bucket may be sent."""
-    if p is None or not getattr(p, "zen_direct_grad", False) or p.grad is None:
-        return False
-    if not (torch.is_grad_enabled() and p.requires_grad):
+    how many such signals to expect before the parameter's bucket may be sent.  ``needed`` is the op's
+    ``ctx.needs_input_grad`` entry for ``p``: grad mode itself is always off inside ``Function.forward``, so this is
+    what tells a recorded forward from one under ``no_grad`` (the first pass of a checkpointed block)."""
+    if p is None or not needed or not getattr(p, "zen_direct_grad", False) or p.grad is None:
         return False
     p.zen_expected = getattr(p, "zen_expected", 0) + 1
     return True
 
 
-def _declare_autograd_use(p) -> None:
+def _declare_autograd_use(p, needed: bool) -> None:
     """Called in forward by an op whose gradient for ``p`` travels through autograd although other ops write
     theirs directly: the reducer then also waits for the accumulate-grad hook of ``p``."""
-    if p is not None and getattr(p, "zen_direct_grad", False) and torch.is_grad_enabled() and p.requires_grad:
+    if p is not None and needed and getattr(p, "zen_direct_grad", False):
         p.zen_autograd_use = True
 
 
@@ -56,7 +56,7 @@ class LinearFn(torch.autograd.Function):
             y = G.gemm_nn(x2, weight, bias=bias)
         ctx.save_for_backward(x2, weight)
         ctx.params = (weight, bias)
-        ctx.direct = (_claim(weight), _claim(bias))
+        ctx.direct = (_claim(weight, ctx.needs_input_grad[1]), _claim(bias, ctx.needs_input_grad[2]))
         ctx.xshape = x.shape
         return y if x.dim() == 2 else y.view(*x.shape[:-1], n)
 
@@ -104,8 +104,9 @@ class NormFn(torch.autograd.Function):
         ctx.save_for_backward(h, weight, rstd, mean if mean is not None else rstd)
         ctx.cfg = (layer, unit_offset, bias is not None, residual is not None)
         ctx.params = (weight, bias)
-        cw = _claim(weight)
-        ctx.direct = cw and (bias is None or _claim(bias))
+        # both or neither: the kernel produces the two column sums together
+        both = ctx.needs_input_grad[2] and (bias is None or ctx.needs_input_grad[3])
+        ctx.direct = both and _claim(weight, True) and (bias is None or _claim(bias, True))
         return y, h
 
     @staticmethod
@@ -153,9 +154,7 @@ class ActFn(torch.autograd.Function):
         kind = ctx.kind
         d2 = dout.reshape(-1, dout.shape[-1])
         if kind in ("swiglu", "geglu"):
-            inner = x2.shape[1] // 2
-            da, db = E.act_bwd(x2[:, :inner], x2[:, inner:], d2, kind)
-            dx = torch.cat([da.view(-1, inner), db.view(-1, inner)], dim=1)
+            dx = E.act_bwd_gated(x2, d2, kind)
         else:
             dx, _ = E.act_bwd(x2, None, d2, kind)
         return dx.view(ctx.xshape), None
@@ -200,7 +199,7 @@ class EmbeddingFn(torch.autograd.Function):
     def forward(ctx, ids, wte, wpe, seq, pos_offset, scale, sparse_sink, vocab_start):
         local = ids - vocab_start if vocab_start else ids
         if sparse_sink is None:
-            _declare_autograd_use(wte)
+            _declare_autograd_use(wte, ctx.needs_input_grad[1])
         out = E.embedding_fwd(local, wte, wpe, seq=seq, pos_offset=pos_offset, scale=scale)
         ctx.save_for_backward(local)
         ctx.cfg = (wte.shape, wte.dtype, wpe.shape if wpe is not None else None, seq, pos_offset, scale, sparse_sink)
@@ -245,9 +244,9 @@ class LMHeadLossFn(torch.autograd.Function):
         V = weight.shape[0]
         vpad = (V + 7) // 8 * 8
         dh = torch.empty_like(h2)
-        direct = unit_grad and _claim(weight)
+        direct = unit_grad and _claim(weight, ctx.needs_input_grad[1])
         if not direct:
-            _declare_autograd_use(weight)
+            _declare_autograd_use(weight, ctx.needs_input_grad[1])
         nchunks = (T + chunk_tokens - 1) // chunk_tokens
         if direct:
             dw = weight.grad
@@ -301,9 +300,9 @@ class VocabParallelLMHeadLossFn(torch.autograd.Function):
         inv = 1.0 / (lab != ignore_index).sum().clamp_(min=1).to(torch.float32).reshape(1)
         vpad = (Vl + 7) // 8 * 8
         dh = torch.empty_like(h2)
-        direct = _claim(weight)
+        direct = _claim(weight, ctx.needs_input_grad[1])
         if not direct:
-            _declare_autograd_use(weight)
+            _declare_autograd_use(weight, ctx.needs_input_grad[1])
         dw = weight.grad if direct else torch.zeros(weight.shape, dtype=weight.dtype, device=h2.device)
         loss_sum = torch.zeros((), dtype=torch.float32, device=h2.device)
         for s in range(0, T, chunk_tokens):

@@ -201,6 +201,30 @@ def act_bwd(a, b, dout, kind: str):
     return da.view(a.shape), (db.view(a.shape) if db is not None else None)
 
 
+def act_bwd_gated(x: torch.Tensor, dout: torch.Tensor, kind: str) -> torch.Tensor:
+    """Gradient of the gated activation with respect to the fused [rows, 2 * inner] input (gate | up), written straight
+    into one [rows, 2 * inner] tensor: the kernel reads the two halves through the row stride and stores the two
+    gradients the same way, so nothing is copied or concatenated."""
+    inner = x.shape[1] // 2
+    if not x.is_cuda:
+        da, db = act_bwd(x[:, :inner], x[:, inner:], dout, kind)
+        return torch.cat([da, db], dim=1)
+    assert x.dim() == 2 and x.stride(1) == 1
+    d2 = _c(dout).view(-1, inner)
+    rows, ld = x.shape[0], x.stride(0)
+    dx = torch.empty(rows, 2 * inner, dtype=x.dtype, device=x.device)
+    if ld == 2 * inner:
+        rc = _native.lib().zen_act_bwd(_native.ptr(x), _native.ptr(x[:, inner:]), _native.ptr(d2), _native.ptr(dx),
+                                       _native.ptr(dx[:, inner:]), rows, inner, ld, ld, _ACT[kind], _code(x),
+                                       _native.stream_ptr())
+        _native.check(rc, "zen_act_bwd")
+        return dx
+    da, db = act_bwd(x[:, :inner], x[:, inner:], dout, kind)
+    dx[:, :inner].copy_(da)
+    dx[:, inner:].copy_(db)
+    return dx
+
+
 # ----------------------------------------------------------------------------- RoPE
 def rope_(x: torch.Tensor, seq: int, theta: float = 10000.0, inverse: bool = False, pos0: int = 0) -> torch.Tensor:
     """In-place rotary embedding (rotate-half) on x[tokens, heads, hd]; token t has position pos0 + t % seq."""

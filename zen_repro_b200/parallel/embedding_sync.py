@@ -54,6 +54,8 @@ class EmbeddingRowSync:
 
     def sync_into(self, grad: torch.Tensor, zero_first: bool = False):
         if self._pending is None:
+            if zero_first:
+                grad.zero_()
             return grad
         rows, count, vals = self._pending
         self._pending = None

@@ -210,9 +210,7 @@ class ZenDDP(nn.Module):
     def zero_grad(self, set_to_none: bool = False) -> None:
         for b in self.buckets:
             b.buffer.zero_()
-        for p in self._sparse_only:
-            if p.grad is not None:
-                p.grad.zero_()
+        # gradients of row-sparse-only parameters are rebuilt from zero by the embedding sync of the next step
 
 
 class _null:
