@@ -56,6 +56,28 @@ def test_bias_accumulate_fp32_out():
     assert G.gemm_error() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (1000, 1304, 200), (8192, 768, 768), (384, 50257, 128)])
+def test_pair_kernel_store_through_shared_memory(M, N, K):
+    """Plain bf16 output of the CTA-pair kernel goes through TMA stores: edges are clipped, padding columns of a wider
+    buffer stay untouched, the bias is added."""
+    torch.manual_seed(6)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    ld = (N + 7) // 8 * 8 + 8
+    buf = torch.full((M + 1, ld), 7.0, device="cuda", dtype=torch.bfloat16)
+    out = buf[:M, :N]
+    G.gemm_nt(a, b, bias=bias, out=out, bn=512)
+    _check(out, a.float() @ b.float().t() + bias.float(), K)
+    assert bool((buf[:M, N:] == 7.0).all()) and bool((buf[M] == 7.0).all())
+    # the caller may give up the columns to the next multiple of 8 (an odd N then takes the store path too)
+    G.gemm_nt(a, b, bias=bias, out=out, bn=512, pad_ok=True)
+    _check(out, a.float() @ b.float().t() + bias.float(), K)
+    n8 = (N + 7) // 8 * 8
+    assert bool((buf[:M, n8:] == 7.0).all()) and bool((buf[M] == 7.0).all())
+    assert G.gemm_error() == 0
+
+
 def test_strided_operands_inside_a_wider_buffer():
     torch.manual_seed(3)
     buf = torch.randn(256, 3 * 128, device="cuda").bfloat16()
@@ -77,4 +99,28 @@ def test_pair_kernel_all_layouts(M, N, K):
     acc = torch.ones(M, N, device="cuda", dtype=torch.bfloat16)
     G.gemm_nt(a, b.t().contiguous(), out=acc, accumulate=True, bn=512)
     _check(acc, a.float() @ b.float() + 1.0, K)
+    assert G.gemm_error() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(768, 2304, 8192), (768, 768, 8192), (3072, 768, 4096), (700, 1000, 2112)])
+def test_split_k_weight_gradient_shapes(M, N, K, monkeypatch):
+    """Few output tiles and a long K: the K slices meet through the workspace, summed in slice order."""
+    monkeypatch.setattr(G, "_SPLITK_MIN_K", 2048)          # the default only splits much longer K
+    torch.manual_seed(5)
+    assert G.split_k_choice(M, N, K) > 1
+    at = torch.randn(K, M, device="cuda").bfloat16()
+    b = torch.randn(K, N, device="cuda").bfloat16()
+    want = at.float().t() @ b.float()
+    got = G.gemm_tn(at, b)
+    _check(got, want, K)
+    again = G.gemm_tn(at, b)                       # same slices, same order: bit-identical, counters were left at zero
+    assert torch.equal(got, again)
+    acc = torch.ones(M, N, device="cuda", dtype=torch.bfloat16)
+    G.gemm_tn(at, b, out=acc, accumulate=True)
+    _check(acc, want + 1.0, K)
+    acc32 = torch.full((M, N), 2.0, device="cuda", dtype=torch.float32)
+    G.gemm_tn(at, b, out=acc32, accumulate=True)
+    _check(acc32, want + 2.0, K)
+    a = at.t().contiguous()
+    _check(G.gemm_nt(a, b.t().contiguous()), want, K)
     assert G.gemm_error() == 0

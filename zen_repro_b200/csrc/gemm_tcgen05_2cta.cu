@@ -21,8 +21,10 @@ constexpr int BN2 = 256;
 constexpr int BNH = 128;          // B rows held by each CTA
 constexpr int BK2 = 64;
 constexpr int STAGES2 = 6;
+constexpr int MAX_SPLITS = 3;      // K slices per output tile at most (the last slice to arrive holds the others' partials in registers)
 constexpr int STAGE_BYTES2 = BM2 * BK2 * 2 + BNH * BK2 * 2;     // 32 KB per CTA
-constexpr int SMEM_BYTES2 = STAGES2 * STAGE_BYTES2 + 1024 + 256;
+constexpr int EPI_STAGE_BYTES = 4 * 2 * 4096;   // per epilogue warp two [32 rows][64 bf16] boxes for the TMA store
+constexpr int SMEM_BYTES2 = STAGES2 * STAGE_BYTES2 + EPI_STAGE_BYTES + 1024 + 256;
 
 __device__ int g_gemm2_error = 0;
 
@@ -32,6 +34,12 @@ struct Gemm2Params {
   int M, N, K, ldc;
   int out_fp32, accumulate;
   int num_m_pairs, num_n_tiles;
+  // split-K: a work unit is (output tile, K slice).  Every unit stores its fp32 partial tile in `ws`; per 32-row
+  // group a counter tells the last unit to arrive, which sums the slices in slice order and writes the output.
+  int splits, kb_per_split;
+  float* ws;                        // [splits * tiles][2 CTAs][8 column chunks][128 rows][32] floats
+  int* counters;                    // [tiles][2 CTAs][4 row groups][2], zero between launches
+  int tma_store;                    // bf16 output written through shared memory and TMA stores (full lines, async)
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -79,12 +87,23 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const Gemm2Params p) {
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                      const __grid_constant__ CUtensorMap tma_c, const Gemm2Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES2 * STAGE_BYTES2);
+  unsigned char* epi_stage = smem + STAGES2 * STAGE_BYTES2;              // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + EPI_STAGE_BYTES);
   uint64_t* full = bars;                       // [STAGES2]   used on the leader
   uint64_t* empty = bars + STAGES2;            // [STAGES2]   one copy per CTA
   uint64_t* tfull = bars + 2 * STAGES2;        // [2]         one copy per CTA
@@ -98,6 +117,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const uint32_t cta = cluster_ctarank();
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
   const int num_tiles = p.num_m_pairs * p.num_n_tiles;
+  const int num_units = num_tiles * p.splits;
   const int nkb = (p.K + BK2 - 1) / BK2;
 
   if (threadIdx.x == 0) {
@@ -118,10 +138,12 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       // ---------------------------------------------------------------- TMA producer (both CTAs)
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
+        const int tile = unit % num_tiles, ks = unit / num_tiles;
         const int m0 = (tile % p.num_m_pairs) * 256 + (int)cta * BM2;
         const int n0 = (tile / p.num_m_pairs) * BN2 + (int)cta * BNH;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int kb0 = ks * p.kb_per_split, kb1 = min(nkb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES2;
           const uint32_t ph = (it / STAGES2) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, 1, &g_gemm2_error)) { ok = false; break; }
@@ -149,12 +171,13 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       // ---------------------------------------------------------------- MMA issuer (leader CTA only)
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tcount) {
+      for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++tcount) {
         const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
         if (!mbar_wait(&tempty[acc], aph ^ 1, abort_flag, 2, &g_gemm2_error)) { ok = false; break; }
         fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN2;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int kb0 = (unit / num_tiles) * p.kb_per_split, kb1 = min(nkb, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES2;
           const uint32_t ph = (it / STAGES2) & 1;
           if (!mbar_wait(&full[s], ph, abort_flag, 3, &g_gemm2_error)) { ok = false; break; }
@@ -167,7 +190,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           for (int j = 0; j < BK2 / 16; ++j) {
             const uint64_t astep = (uint64_t)((A_MN ? j * 2048 : j * 32) >> 4);
             const uint64_t bstep = (uint64_t)((B_MN ? j * 2048 : j * 32) >> 4);
-            umma_bf16_pair(d_tmem, adesc + astep, bdesc + bstep, IDESC, (kb | j) != 0 ? 1u : 0u);
+            umma_bf16_pair(d_tmem, adesc + astep, bdesc + bstep, IDESC, (kb != kb0 || j != 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty[s]);
         }
@@ -179,17 +202,197 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     const int grp = warp & 3;
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tcount) {
+    for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++tcount) {
+      const int tile = unit % num_tiles, ks = unit / num_tiles;
       const int m0 = (tile % p.num_m_pairs) * 256 + (int)cta * BM2, n0 = (tile / p.num_m_pairs) * BN2;
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aph, abort_flag, 4, &g_gemm2_error)) { ok = false; break; }
       fence_after();
       const int row = m0 + grp * 32 + lane;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(grp * 32) << 16) + acc * BN2;
+      const bool split = p.splits > 1;
+      if (split && !p.tma_store) {
+        // store this K slice's partial tile and count in.  Every slice but the last to arrive for these 32 rows is
+        // done then; the last one adds the others' partials to its own accumulator, in slice order, below.
+        float* wp = p.ws + ((size_t)(ks * num_tiles + tile) * 2 + cta) * (BM2 * BN2) + (size_t)(grp * 32 + lane) * 32;
+#pragma unroll 1
+        for (int ch = 0; ch < BN2 / 32; ch += 2) {
+          uint32_t r[32], r2[32];
+          tmem_ld32_nowait(taddr0 + ch * 32, r);
+          tmem_ld32_nowait(taddr0 + ch * 32 + 32, r2);
+          tmem_wait_ld();
+          float4* dst = reinterpret_cast<float4*>(wp + (size_t)ch * (BM2 * 32));
+          float4* dst2 = reinterpret_cast<float4*>(wp + (size_t)(ch + 1) * (BM2 * 32));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+            dst2[i] = make_float4(__uint_as_float(r2[4 * i]), __uint_as_float(r2[4 * i + 1]), __uint_as_float(r2[4 * i + 2]), __uint_as_float(r2[4 * i + 3]));
+          }
+        }
+        __threadfence();
+        __syncwarp();
+        int* cnt = p.counters + (tile * 2 + (int)cta) * 4 + grp;
+        int old = 0;
+        if (lane == 0) {
+          old = atomicAdd(cnt, 1);
+          if (old == p.splits - 1) *cnt = 0;           // every slice has arrived: ready for the next launch
+        }
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old != p.splits - 1) {
+          fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_leader(&tempty[acc]);
+          continue;
+        }
+        __threadfence();
+      }
+      if (p.tma_store) {
+        // bf16 output: each warp turns its 32 rows into [32][64] boxes in shared memory (the swizzled layout of the
+        // tensor map) and one lane stores each box with TMA: whole lines, clipped at the matrix edge, no waiting.
+        // With two K slices each slice finishes half of the columns: it hands the other half of its accumulator to
+        // the peer through the workspace, waits (bounded) for the peer's half and adds it to its own.
+        unsigned char* stg = epi_stage + grp * 8192;
+        int cb_lo = 0, cb_hi = BN2 / 64;
+        const float* peer = nullptr;
+        if (split) {
+          const int other = 1 - ks;
+          float* wp = p.ws + ((size_t)(ks * num_tiles + tile) * 2 + cta) * (BM2 * BN2) + (size_t)(grp * 32 + lane) * 32;
+#pragma unroll 1
+          for (int ch = other * 4; ch < other * 4 + 4; ch += 2) {
+            uint32_t r[32], r2[32];
+            tmem_ld32_nowait(taddr0 + ch * 32, r);
+            tmem_ld32_nowait(taddr0 + ch * 32 + 32, r2);
+            tmem_wait_ld();
+            float4* dst = reinterpret_cast<float4*>(wp + (size_t)ch * (BM2 * 32));
+            float4* dst2 = reinterpret_cast<float4*>(wp + (size_t)(ch + 1) * (BM2 * 32));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+              dst2[i] = make_float4(__uint_as_float(r2[4 * i]), __uint_as_float(r2[4 * i + 1]), __uint_as_float(r2[4 * i + 2]), __uint_as_float(r2[4 * i + 3]));
+            }
+          }
+          __threadfence();
+          __syncwarp();
+          // flags[..][ks] = 1: "slice ks has published its half"; the consumer clears it for the next launch
+          int* flags = p.counters + ((tile * 2 + (int)cta) * 4 + grp) * 2;
+          int got = 1;
+          if (lane == 0) {
+            atomicExch(flags + ks, 1);
+            const uint64_t t0 = gtimer();
+            while (atomicAdd(flags + other, 0) == 0) {
+              if (*abort_flag || gtimer() - t0 > WAIT_NS) { got = 0; break; }
+            }
+            if (got) atomicExch(flags + other, 0);
+            else { *abort_flag = 5; atomicCAS(&g_gemm2_error, 0, 5); }
+          }
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (!got) { ok = false; break; }
+          __threadfence();
+          peer = p.ws + ((size_t)(other * num_tiles + tile) * 2 + cta) * (BM2 * BN2) + (size_t)(grp * 32 + lane) * 32;
+          cb_lo = ks * 2;
+          cb_hi = ks * 2 + 2;
+        }
+#pragma unroll 1
+        for (int cb = cb_lo; cb < cb_hi; ++cb) {
+          unsigned char* st = stg + (cb & 1) * 4096;
+          uint32_t ra[32], rb[32];
+          tmem_ld32_nowait(taddr0 + cb * 64, ra);
+          tmem_ld32_nowait(taddr0 + cb * 64 + 32, rb);
+          float4 oa[8], ob[8];
+          if (split) {
+            const float4* qa = reinterpret_cast<const float4*>(peer + (size_t)(2 * cb) * (BM2 * 32));
+            const float4* qb = reinterpret_cast<const float4*>(peer + (size_t)(2 * cb + 1) * (BM2 * 32));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { oa[i] = __ldcg(qa + i); ob[i] = __ldcg(qb + i); }
+          }
+          if (lane == 0) bulk_wait_read<1>();          // the store that read this buffer two boxes ago is done
+          __syncwarp();
+          tmem_wait_ld();
+          if (split) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              ra[4 * i] = __float_as_uint(__uint_as_float(ra[4 * i]) + oa[i].x);
+              ra[4 * i + 1] = __float_as_uint(__uint_as_float(ra[4 * i + 1]) + oa[i].y);
+              ra[4 * i + 2] = __float_as_uint(__uint_as_float(ra[4 * i + 2]) + oa[i].z);
+              ra[4 * i + 3] = __float_as_uint(__uint_as_float(ra[4 * i + 3]) + oa[i].w);
+              rb[4 * i] = __float_as_uint(__uint_as_float(rb[4 * i]) + ob[i].x);
+              rb[4 * i + 1] = __float_as_uint(__uint_as_float(rb[4 * i + 1]) + ob[i].y);
+              rb[4 * i + 2] = __float_as_uint(__uint_as_float(rb[4 * i + 2]) + ob[i].z);
+              rb[4 * i + 3] = __float_as_uint(__uint_as_float(rb[4 * i + 3]) + ob[i].w);
+            }
+          }
+          const int col0 = n0 + cb * 64;
+          if (p.bias) {
+            const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (col0 + i < p.N) ra[i] = __float_as_uint(__uint_as_float(ra[i]) + __bfloat162float(bp[i]));
+              if (col0 + 32 + i < p.N) rb[i] = __float_as_uint(__uint_as_float(rb[i]) + __bfloat162float(bp[32 + i]));
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            *reinterpret_cast<uint4*>(st + swz128(lane, q * 8)) =
+                make_uint4(pack_bf16(__uint_as_float(ra[8 * q]), __uint_as_float(ra[8 * q + 1])),
+                           pack_bf16(__uint_as_float(ra[8 * q + 2]), __uint_as_float(ra[8 * q + 3])),
+                           pack_bf16(__uint_as_float(ra[8 * q + 4]), __uint_as_float(ra[8 * q + 5])),
+                           pack_bf16(__uint_as_float(ra[8 * q + 6]), __uint_as_float(ra[8 * q + 7])));
+            *reinterpret_cast<uint4*>(st + swz128(lane, 32 + q * 8)) =
+                make_uint4(pack_bf16(__uint_as_float(rb[8 * q]), __uint_as_float(rb[8 * q + 1])),
+                           pack_bf16(__uint_as_float(rb[8 * q + 2]), __uint_as_float(rb[8 * q + 3])),
+                           pack_bf16(__uint_as_float(rb[8 * q + 4]), __uint_as_float(rb[8 * q + 5])),
+                           pack_bf16(__uint_as_float(rb[8 * q + 6]), __uint_as_float(rb[8 * q + 7])));
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (col0 < p.N && m0 + grp * 32 < p.M) tma_store_2d(&tma_c, st, col0, m0 + grp * 32);
+            bulk_commit();
+          }
+        }
+        fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_leader(&tempty[acc]);
+        continue;
+      }
 #pragma unroll 1
       for (int ch = 0; ch < BN2 / 32; ++ch) {
         uint32_t r[32];
-        tmem_ld32(taddr0 + ch * 32, r);
+        if (split) {
+          // the other slices' partials of this chunk first (independent loads, all in flight together), then the
+          // own accumulator; the sum runs over slice indices whichever slice arrived last
+          float4 buf[MAX_SPLITS][8];
+          const float* src = p.ws + ((size_t)tile * 2 + cta) * (BM2 * BN2) + (size_t)ch * (BM2 * 32) + (size_t)(grp * 32 + lane) * 32;
+#pragma unroll
+          for (int sidx = 0; sidx < MAX_SPLITS; ++sidx) {
+            if (sidx < p.splits && sidx != ks) {
+              const float4* q = reinterpret_cast<const float4*>(src + (size_t)sidx * num_tiles * 2 * (BM2 * BN2));
+#pragma unroll
+              for (int i = 0; i < 8; ++i) buf[sidx][i] = __ldcg(q + i);
+            }
+          }
+          tmem_ld32(taddr0 + ch * 32, r);
+          float a[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) a[i] = 0.f;
+#pragma unroll
+          for (int sidx = 0; sidx < MAX_SPLITS; ++sidx) {
+            if (sidx < p.splits) {
+              const bool own = (sidx == ks);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                a[4 * i] += own ? __uint_as_float(r[4 * i]) : buf[sidx][i].x;
+                a[4 * i + 1] += own ? __uint_as_float(r[4 * i + 1]) : buf[sidx][i].y;
+                a[4 * i + 2] += own ? __uint_as_float(r[4 * i + 2]) : buf[sidx][i].z;
+                a[4 * i + 3] += own ? __uint_as_float(r[4 * i + 3]) : buf[sidx][i].w;
+              }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(a[i]);
+        } else {
+          tmem_ld32(taddr0 + ch * 32, r);
+        }
         const int col0 = n0 + ch * 32;
         if (row < p.M && col0 < p.N) {
           float v[32];
@@ -245,6 +448,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&tempty[acc]);
     }
+    if (p.tma_store && lane == 0) bulk_wait_all();     // shared memory stays valid until the last store has read it
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -263,7 +467,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 }
 
 template <bool A_MN, bool B_MN>
-int launch2(const CUtensorMap& ta, const CUtensorMap& tb, Gemm2Params p, cudaStream_t st) {
+int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, Gemm2Params p, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES2);
@@ -272,10 +476,10 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, Gemm2Params p, cudaStr
   }
   p.num_m_pairs = (p.M + 255) / 256;
   p.num_n_tiles = (p.N + BN2 - 1) / BN2;
-  const int tiles = p.num_m_pairs * p.num_n_tiles;
+  const int tiles = p.num_m_pairs * p.num_n_tiles * p.splits;
   int clusters = zen_tmap::sm_count() / 2;
   if (tiles < clusters) clusters = tiles;
-  gemm_bf16_2cta_kernel<A_MN, B_MN><<<clusters * 2, 192, SMEM_BYTES2, st>>>(ta, tb, p);
+  gemm_bf16_2cta_kernel<A_MN, B_MN><<<clusters * 2, 192, SMEM_BYTES2, st>>>(ta, tb, tc, p);
   return (int)cudaGetLastError();
 }
 
@@ -284,9 +488,36 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, Gemm2Params p, cudaStr
 extern "C" {
 
 // Same contract as zen_gemm_bf16 (without the tile choice): C[M,N] (+)= A * B^T (+ bias), CTA-pair kernel.
+// splits > 1 cuts K into that many slices per output tile (for outputs with too few tiles to fill the GPU and a
+// long K, the weight-gradient shape): `ws` must hold splits * tiles * 2 * 128 * 256 floats and `counters`
+// tiles * 16 ints that are zero on entry (the kernel leaves them zero); both are caller-owned and used in stream
+// order.  The slices are summed in slice order, so the result does not depend on timing.
+// n_store: 0, or a width in [N, ldc] that the kernel may write (columns N.. receive zeros).
+int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                              int ldb, int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, int splits, float* ws,
+                              uint64_t ws_floats, int* counters, int n_counters, int n_store, void* stream);
+
 int zen_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
                        int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, void* stream) {
+  return zen_gemm_bf16_2cta_splitk(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, 1, nullptr, 0,
+                                   nullptr, 0, 0, stream);
+}
+
+int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                              int ldb, int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, int splits, float* ws,
+                              uint64_t ws_floats, int* counters, int n_counters, int n_store, void* stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
+  const int nkb = (K + BK2 - 1) / BK2;
+  if (splits < 1) splits = 1;
+  if (splits > MAX_SPLITS) splits = MAX_SPLITS;
+  if (splits > nkb) splits = nkb;
+  int kb_per = (nkb + splits - 1) / splits;
+  splits = (nkb + kb_per - 1) / kb_per;                     // no empty slice
+  if (splits > 1) {
+    const uint64_t tiles = (uint64_t)((M + 255) / 256) * ((N + BN2 - 1) / BN2);
+    if (!ws || !counters || ws_floats < tiles * splits * 2 * BM2 * BN2 || (uint64_t)n_counters < tiles * 16) return -4;
+    if (reinterpret_cast<uintptr_t>(ws) % 16) return -2;
+  }
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -2;
   CUtensorMap ta, tb;
   int rc;
@@ -296,12 +527,23 @@ int zen_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* bias, 
   if (!b_mn) rc = zen_tmap::get(B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 128, &tb);
   else rc = zen_tmap::get(B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64, &tb);
   if (rc) return rc;
-  Gemm2Params p{C, bias, M, N, K, ldc, out_fp32, accumulate, 0, 0};
+  // Plain bf16 output with a TMA-compatible layout: store through shared memory.  The stored width must be a
+  // multiple of 8 columns (16 bytes); a caller whose buffer has spare columns after N may allow them to be written
+  // (with zeros) by passing n_store = N rounded up.
+  if (n_store < N || n_store > ldc) n_store = N;
+  const int tma_store = (!out_fp32 && !accumulate && splits <= 2 && (ldc % 8) == 0 && (n_store % 8) == 0 &&
+                         (reinterpret_cast<uintptr_t>(C) % 16) == 0) ? 1 : 0;
+  CUtensorMap tc = ta;
+  if (tma_store) {
+    rc = zen_tmap::get(C, (uint64_t)n_store, (uint64_t)M, (uint64_t)ldc, 64, 32, &tc);
+    if (rc) return rc;
+  }
+  Gemm2Params p{C, bias, M, N, K, ldc, out_fp32, accumulate, 0, 0, splits, kb_per, ws, counters, tma_store};
   cudaStream_t st = (cudaStream_t)stream;
-  if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, p, st);
-  if (!a_mn && b_mn) return launch2<false, true>(ta, tb, p, st);
-  if (a_mn && !b_mn) return launch2<true, false>(ta, tb, p, st);
-  return launch2<true, true>(ta, tb, p, st);
+  if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, tc, p, st);
+  if (!a_mn && b_mn) return launch2<false, true>(ta, tb, tc, p, st);
+  if (a_mn && !b_mn) return launch2<true, false>(ta, tb, tc, p, st);
+  return launch2<true, true>(ta, tb, tc, p, st);
 }
 
 int zen_gemm2_error() {

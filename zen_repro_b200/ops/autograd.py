@@ -27,6 +27,15 @@ def _claim(p, needed: bool) -> bool:
     return True
 
 
+def _take_fresh(p) -> bool:
+    """True once per step for a parameter whose bucket view is known to hold zeros (the reducer marks it at
+    ``zero_grad``): the first direct writer may then overwrite instead of accumulate, which lets the GEMM skip
+    reading the old values."""
+    fresh = getattr(p, "zen_fresh", False)
+    p.zen_fresh = False
+    return fresh
+
+
 def _declare_autograd_use(p, needed: bool) -> None:
     """Called in forward by an op whose gradient for ``p`` travels through autograd although other ops write
     theirs directly: the reducer then also waits for the accumulate-grad hook of ``p``."""
@@ -78,7 +87,7 @@ class LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             a, b = (dy2, x2) if ctx.layout == "out_in" else (x2, dy2)
             if ctx.direct[0]:
-                G.gemm_tn(a, b, out=wp.grad, accumulate=True)
+                G.gemm_tn(a, b, out=wp.grad, accumulate=not _take_fresh(wp))
                 wp.zen_ready(wp)
             else:
                 dw = G.gemm_tn(a, b)
@@ -254,15 +263,16 @@ class LMHeadLossFn(torch.autograd.Function):
             dw = torch.zeros(weight.shape, dtype=torch.float32 if (h2.is_cuda and nchunks > 1) else weight.dtype,
                              device=h2.device)
         loss_sum = torch.zeros((), dtype=torch.float32, device=h2.device)
+        fresh = direct and _take_fresh(weight)
         for s in range(0, T, chunk_tokens):
             e = min(T, s + chunk_tokens)
             buf = torch.empty(e - s, vpad, dtype=h2.dtype, device=h2.device)
             logits = buf[:, :V]
-            G.gemm_nt(h2[s:e], weight, out=logits)
+            G.gemm_nt(h2[s:e], weight, out=logits, pad_ok=True)
             loss, dl = E.cross_entropy(logits, lab[s:e], grad_scale=1.0, grad_scale_dev=inv, ignore_index=ignore_index)
             loss_sum += loss.sum()
             G.gemm_nn(dl, weight, out=dh[s:e])
-            G.gemm_tn(dl, h2[s:e], out=dw, accumulate=True)
+            G.gemm_tn(dl, h2[s:e], out=dw, accumulate=not (fresh and s == 0))
         ctx.save_for_backward(dh, dw if not direct else dh)
         ctx.cfg = (h.shape, weight.dtype, direct, unit_grad)
         ctx.wp = weight
@@ -305,11 +315,12 @@ class VocabParallelLMHeadLossFn(torch.autograd.Function):
             _declare_autograd_use(weight, ctx.needs_input_grad[1])
         dw = weight.grad if direct else torch.zeros(weight.shape, dtype=weight.dtype, device=h2.device)
         loss_sum = torch.zeros((), dtype=torch.float32, device=h2.device)
+        fresh = direct and _take_fresh(weight)
         for s in range(0, T, chunk_tokens):
             e = min(T, s + chunk_tokens)
             buf = torch.empty(e - s, vpad, dtype=h2.dtype, device=h2.device)
             logits = buf[:, :Vl]
-            G.gemm_nt(h2[s:e], weight, out=logits)
+            G.gemm_nt(h2[s:e], weight, out=logits, pad_ok=True)
             m, se, tgt = E.xent_partial(logits, lab[s:e], valid_cols, vocab_start, ignore_index)
             gm = m.clone()
             dist.all_reduce(gm, op=dist.ReduceOp.MAX, group=group)
@@ -326,7 +337,7 @@ class VocabParallelLMHeadLossFn(torch.autograd.Function):
                 part = G.gemm_nn(logits, weight)
                 dist.all_reduce(part, group=group)
                 dh[s:e] = part
-            G.gemm_tn(logits, h2[s:e], out=dw, accumulate=True)
+            G.gemm_tn(logits, h2[s:e], out=dw, accumulate=not (fresh and s == 0))
         ctx.save_for_backward(dh, dw if not direct else dh)
         ctx.cfg = (h.shape, direct)
         ctx.wp = weight

@@ -7,6 +7,7 @@ no operand is ever transposed in memory.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -33,6 +34,39 @@ def use_pair_kernel(M: int, N: int, K: int) -> bool:
     return score >= 0.8 or (score >= 0.6 and K >= 1024)
 
 
+_SPLITK = os.environ.get("ZEN_GEMM_SPLITK", "auto")       # auto | 0
+_WS_FLOATS = 74 * 2 * 128 * 256                            # one fp32 partial tile per CTA of one full wave
+_N_COUNTERS = 4096
+_ws_cache: dict = {}
+# below this K the extra pass over the partial tiles costs more than the idle clusters
+_SPLITK_MIN_K = int(os.environ.get("ZEN_GEMM_SPLITK_MIN_K", "4096"))
+
+
+def split_k_choice(M: int, N: int, K: int) -> int:
+    """Number of K slices for the CTA-pair kernel, or 1.  Splitting pays when the output has far fewer 256 x 256
+    tiles than the 74 clusters and K is long: the weight-gradient products of a transformer layer."""
+    if _SPLITK == "0" or _PAIR_MODE == "0" or M < 256 or N < 256 or K < _SPLITK_MIN_K:
+        return 1
+    tm, tn = (M + 255) // 256, (N + 255) // 256
+    tiles = tm * tn
+    if (M * N) / (tiles * 65536.0) < 0.75 or tiles > 37:
+        return 1
+    splits = min(74 // tiles, (K // 64) // 8, 2)          # two slices: the fast store path of the kernel
+    return splits if splits >= 2 and tiles * splits * 2 * 128 * 256 <= _WS_FLOATS and tiles * 16 <= _N_COUNTERS else 1
+
+
+def _splitk_workspace(device):
+    """fp32 partial tiles and arrival counters for the split-K kernel, one pair per device and stream: the
+    kernel's slices meet through them, so two launches may share them only in stream order."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    w = _ws_cache.get(key)
+    if w is None:
+        w = (torch.empty(_WS_FLOATS, dtype=torch.float32, device=device),
+             torch.zeros(_N_COUNTERS, dtype=torch.int32, device=device))
+        _ws_cache[key] = w
+    return w
+
+
 def _use_kernel(a: torch.Tensor, b: torch.Tensor) -> bool:
     return (a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and not _FORCE_TORCH)
 
@@ -48,7 +82,7 @@ def _rowmajor(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
-def _launch(a, b, M, N, K, a_mn, b_mn, bias, out, accumulate, out_dtype, bn):
+def _launch(a, b, M, N, K, a_mn, b_mn, bias, out, accumulate, out_dtype, bn, pad_ok=False):
     a2, b2 = _rowmajor(a), _rowmajor(b)
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
@@ -57,11 +91,22 @@ def _launch(a, b, M, N, K, a_mn, b_mn, bias, out, accumulate, out_dtype, bn):
     assert out.dtype in (torch.bfloat16, torch.float32)
     if bias is not None:
         assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == N
+    splits = split_k_choice(M, N, K) if bn == 0 else 1
+    if splits > 1:
+        ws, cnt = _splitk_workspace(a.device)
+        rc = _native.lib().zen_gemm_bf16_2cta_splitk(
+            _native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K, a2.stride(0), b2.stride(0),
+            out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), splits,
+            _native.ptr(ws), ctypes.c_uint64(ws.numel()), _native.ptr(cnt), cnt.numel(), 0, _native.stream_ptr())
+        _native.check(rc, "zen_gemm_bf16_2cta_splitk")
+        return out
     pair = (bn == 512) or (bn == 0 and use_pair_kernel(M, N, K))
     if pair:
-        rc = _native.lib().zen_gemm_bf16_2cta(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
-                                              a2.stride(0), b2.stride(0), out.stride(0), int(a_mn), int(b_mn),
-                                              int(out.dtype == torch.float32), int(accumulate), _native.stream_ptr())
+        n_store = min((N + 7) // 8 * 8, out.stride(0)) if pad_ok else 0
+        rc = _native.lib().zen_gemm_bf16_2cta_splitk(
+            _native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K, a2.stride(0), b2.stride(0),
+            out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), 1, None,
+            ctypes.c_uint64(0), None, 0, n_store, _native.stream_ptr())
         _native.check(rc, "zen_gemm_bf16_2cta")
         return out
     rc = _native.lib().zen_gemm_bf16(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
@@ -71,14 +116,15 @@ def _launch(a, b, M, N, K, a_mn, b_mn, bias, out, accumulate, out_dtype, bn):
     return out
 
 
-def gemm_nt(a, b, bias=None, out=None, accumulate=False, out_dtype=None, bn=0):
-    """a[M,K] @ b[N,K]^T (+ bias[N])."""
+def gemm_nt(a, b, bias=None, out=None, accumulate=False, out_dtype=None, bn=0, pad_ok=False):
+    """a[M,K] @ b[N,K]^T (+ bias[N]).  ``pad_ok``: ``out`` is the first N columns of a wider buffer whose columns up to
+    the next multiple of 8 may be overwritten (with zeros); lets an odd N use the full-line store path."""
     M, K = a.shape[-2] if a.dim() == 2 else a.numel() // a.shape[-1], a.shape[-1]
     N = b.shape[0]
     if not _use_kernel(a, b):
         r = a.reshape(-1, K).float() @ b.float().t()
         return _finish(r, bias, out, accumulate, out_dtype or a.dtype)
-    return _launch(a, b, M, N, K, False, False, bias, out, accumulate, out_dtype, bn)
+    return _launch(a, b, M, N, K, False, False, bias, out, accumulate, out_dtype, bn, pad_ok)
 
 
 def gemm_nn(a, b, bias=None, out=None, accumulate=False, out_dtype=None, bn=0):

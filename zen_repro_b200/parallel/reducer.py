@@ -210,6 +210,8 @@ class ZenDDP(nn.Module):
     def zero_grad(self, set_to_none: bool = False) -> None:
         for b in self.buckets:
             b.buffer.zero_()
+            for p in b.params:
+                p.zen_fresh = True              # the view holds zeros: the first direct writer may overwrite
         # gradients of row-sparse-only parameters are rebuilt from zero by the embedding sync of the next step
 
 
