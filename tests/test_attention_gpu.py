@@ -37,7 +37,7 @@ def test_forward(B, S, hq, hkv, hd):
 
 
 @pytest.mark.parametrize("B,S,hq,hkv,hd", [(1, 128, 1, 1, 64), (2, 384, 4, 4, 64), (1, 1024, 12, 12, 64), (1, 256, 8, 2, 128),
-                                           (2, 512, 4, 1, 128)])
+                                           (2, 512, 4, 1, 128), (1, 128, 1, 1, 256), (2, 384, 4, 1, 256), (1, 512, 2, 2, 256)])
 def test_backward(B, S, hq, hkv, hd):
     torch.manual_seed(1)
     qkv = (torch.randn(B * S, (hq + 2 * hkv) * hd, device="cuda") * 0.7).bfloat16()

@@ -715,6 +715,252 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
   }
 }
 
+// ---- head_dim 256 backward.  The accumulators of dK and dV alone would fill tensor memory (2 x 256 columns) and a
+// 128-row tile of each of Q, K, V, dO would overflow shared memory, so the work is cut differently: one kernel
+// template, run in three modes, always with a RESIDENT 128-row operand pair and a STREAMED side in 64-row tiles:
+//
+//   mode     resident (128 rows)   streamed (64 rows)   S' [128 x 64]        weights W'        accumulator [128 x 256]
+//   BWD_DQ   Q, dO  (query tile)   K, V  (key tiles)     Q K^T, dP = dO V^T   dS  (row stats)   dQ += dS K
+//   BWD_DK   K, V   (key tile)     Q, dO (query tiles)   K Q^T, dP' = V dO^T  dS^T (col stats)  dK += dS^T Q
+//   BWD_DV   K      (key tile)     Q, dO (query tiles)   K Q^T                P^T (col stats)   dV += P^T dO
+//
+// A softmax thread owns one resident row; W' is written to shared memory as a K-major [128][64] operand and the
+// streamed tile serves as the MN-major B operand of the accumulating product.  Tensor memory: S' 64 + dP' 64 +
+// accumulator 256 columns.  The scores are computed in each of the three launches (3 x the exponentials of a fused
+// kernel), which is the price of fitting hd = 256 on chip.
+enum { BWD_DQ = 0, BWD_DK = 1, BWD_DV = 2 };
+
+struct Bwd256Cfg {
+  static constexpr int HD = 256;
+  static constexpr int RES_BYTES = 128 * HD * 2;        // 64 KB: four [128][64] atoms
+  static constexpr int STR_BYTES = 64 * HD * 2;         // 32 KB: four [64][64] atoms
+  static constexpr int W_BYTES = 128 * 64 * 2;
+  static constexpr int SMEM_BYTES = 2 * RES_BYTES + 2 * STR_BYTES + W_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr uint32_t IDESC_S = make_idesc(128, 64, false, false);
+  static constexpr uint32_t IDESC_ACC = make_idesc(128, 256, false, true);
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(320)
+attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_constant__ CUtensorMap tmap_do128,
+                   const __grid_constant__ CUtensorMap tmap_qkv64, const __grid_constant__ CUtensorMap tmap_do64,
+                   const AttnBwdParams p) {
+  using C = Bwd256Cfg;
+  constexpr int HD = C::HD;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* r1_s = smem;
+  unsigned char* r2_s = r1_s + C::RES_BYTES;
+  unsigned char* t1_s = r2_s + C::RES_BYTES;
+  unsigned char* t2_s = t1_s + C::STR_BYTES;
+  unsigned char* w_s = t2_s + C::STR_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(w_s + C::W_BYTES);
+  uint64_t* r_full = bars;
+  uint64_t* t_full = bars + 1;
+  uint64_t* t_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;
+  uint64_t* w_ready = bars + 4;
+  uint64_t* acc_done = bars + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z;
+  const int rep = p.Hq / p.Hkv;
+  // resident tile index (heavy tiles first), head of the resident operand, and the iteration space
+  const int ri = (MODE == BWD_DQ) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int hres = blockIdx.y;                               // query head (dQ) or KV head (dK / dV)
+  const int g = (MODE == BWD_DQ) ? hres / rep : hres;
+  const int nq64 = p.S / 64;
+  const int per_head = (MODE == BWD_DQ) ? 2 * ri + 2 : nq64 - 2 * ri;   // streamed tiles per head
+  const int niter = (MODE == BWD_DQ) ? per_head : rep * per_head;
+  const int rrow0 = b * p.S + ri * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(r_full, 1);
+    mbar_init(t_full, 1);
+    mbar_init(t_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(w_ready, 8);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) tmem_alloc(tmem_slot, C::TMEM_COLS);
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tACC = tmem_base + 128;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      mbar_expect_tx(r_full, (MODE == BWD_DV ? 1 : 2) * C::RES_BYTES);
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        if (MODE == BWD_DQ) {
+          tma_load_2d(r1_s + a * 16384, &tmap_qkv128, r_full, hres * HD + a * 64, rrow0);
+          tma_load_2d(r2_s + a * 16384, &tmap_do128, r_full, hres * HD + a * 64, rrow0);
+        } else {
+          tma_load_2d(r1_s + a * 16384, &tmap_qkv128, r_full, (p.Hq + g) * HD + a * 64, rrow0);
+          if (MODE == BWD_DK) tma_load_2d(r2_s + a * 16384, &tmap_qkv128, r_full, (p.Hq + p.Hkv + g) * HD + a * 64, rrow0);
+        }
+      }
+      for (int it = 0; it < niter; ++it) {
+        if (!mbar_wait(t_empty, (it & 1) ^ 1, abort_flag, 31, &g_attn_error)) break;
+        mbar_expect_tx(t_full, 2 * C::STR_BYTES);
+        if (MODE == BWD_DQ) {
+          const int krow = b * p.S + it * 64;
+#pragma unroll
+          for (int a = 0; a < 4; ++a) {
+            tma_load_2d(t1_s + a * 8192, &tmap_qkv64, t_full, (p.Hq + g) * HD + a * 64, krow);
+            tma_load_2d(t2_s + a * 8192, &tmap_qkv64, t_full, (p.Hq + p.Hkv + g) * HD + a * 64, krow);
+          }
+        } else {
+          const int h = g * rep + it / per_head, t = 2 * ri + it % per_head;
+          const int qrow = b * p.S + t * 64;
+#pragma unroll
+          for (int a = 0; a < 4; ++a) {
+            tma_load_2d(t1_s + a * 8192, &tmap_qkv64, t_full, h * HD + a * 64, qrow);
+            tma_load_2d(t2_s + a * 8192, &tmap_do64, t_full, h * HD + a * 64, qrow);
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      bool ok = mbar_wait(r_full, 0, abort_flag, 32, &g_attn_error);
+      const uint32_t r1a = smem_u32(r1_s), r2a = smem_u32(r2_s), t1a = smem_u32(t1_s), t2a = smem_u32(t2_s), wa = smem_u32(w_s);
+      for (int it = 0; it < niter && ok; ++it) {
+        if (!mbar_wait(t_full, it & 1, abort_flag, 33, &g_attn_error)) { ok = false; break; }
+        fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t roff = (kk >> 2) * 16384 + (kk & 3) * 32, toff = (kk >> 2) * 8192 + (kk & 3) * 32;
+          umma_bf16(tS, make_desc(r1a + roff, 16, 1024), make_desc(t1a + toff, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+        }
+        if (MODE != BWD_DV) {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk) {
+            const uint32_t roff = (kk >> 2) * 16384 + (kk & 3) * 32, toff = (kk >> 2) * 8192 + (kk & 3) * 32;
+            umma_bf16(tDP, make_desc(r2a + roff, 16, 1024), make_desc(t2a + toff, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(w_ready, it & 1, abort_flag, 34, &g_attn_error)) { ok = false; break; }
+        fence_after();
+        const uint32_t tba = (MODE == BWD_DV) ? t2a : t1a;    // streamed tile as the MN-major B operand
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_bf16(tACC, make_desc(wa + kk * 32, 16, 1024), make_desc(tba + kk * 2048, 8192, 1024), C::IDESC_ACC,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(acc_done);
+        umma_commit(t_empty);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warps: thread = resident row,
+    // warps w and w + 4 split the 64 streamed columns in halves of 32
+    const int row = (warp & 3) * 32 + lane;
+    const int hf = warp >> 2;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const float cs = p.scale_log2;
+    float nl_row = 0.f, d_row = 0.f;
+    if (MODE == BWD_DQ) {
+      const size_t vec = ((size_t)b * p.Hq + hres) * p.S + ri * 128 + row;
+      nl_row = -p.lse2[vec];
+      d_row = p.D[vec];
+    }
+    bool ok = true;
+    for (int it = 0; it < niter && ok; ++it) {
+      const int h = (MODE == BWD_DQ) ? hres : g * rep + it / per_head;
+      const int t = (MODE == BWD_DQ) ? it : 2 * ri + it % per_head;         // streamed 64-row tile index
+      if (!mbar_wait(sdp_full, it & 1, abort_flag, 35, &g_attn_error)) { ok = false; break; }
+      if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, abort_flag, 36, &g_attn_error)) { ok = false; break; }
+      fence_after();
+      uint32_t sa[32], da[32];
+      tmem_ld32_nowait(tS + lane_addr + hf * 32, sa);
+      if (MODE != BWD_DV) tmem_ld32_nowait(tDP + lane_addr + hf * 32, da);
+      tmem_wait_ld();
+      // causal mask: key index against query index (resident row is the query in dQ, the key otherwise)
+      const int res_idx = ri * 128 + row, str0 = t * 64 + hf * 32;
+      const bool need_mask = (MODE == BWD_DQ) ? (str0 + 31 > ri * 128) : (str0 < ri * 128 + 128);
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool dead = (MODE == BWD_DQ) ? (str0 + i > res_idx) : (res_idx > str0 + i);
+          if (dead) sa[i] = 0xff800000u;
+        }
+      }
+      const float* lse_c = p.lse2 + ((size_t)b * p.Hq + h) * p.S + str0;      // per-column statistics (dK / dV)
+      const float* d_c = p.D + ((size_t)b * p.Hq + h) * p.S + str0;
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float w0, w1;
+        if (MODE == BWD_DQ) {
+          const float p0 = ex2f(fmaf(__uint_as_float(sa[i]), cs, nl_row));
+          const float p1 = ex2f(fmaf(__uint_as_float(sa[i + 1]), cs, nl_row));
+          w0 = p0 * (__uint_as_float(da[i]) - d_row);
+          w1 = p1 * (__uint_as_float(da[i + 1]) - d_row);
+        } else {
+          const float p0 = ex2f(fmaf(__uint_as_float(sa[i]), cs, -__ldg(lse_c + i)));
+          const float p1 = ex2f(fmaf(__uint_as_float(sa[i + 1]), cs, -__ldg(lse_c + i + 1)));
+          if (MODE == BWD_DK) {
+            w0 = p0 * (__uint_as_float(da[i]) - __ldg(d_c + i));
+            w1 = p1 * (__uint_as_float(da[i + 1]) - __ldg(d_c + i + 1));
+          } else {
+            w0 = p0;
+            w1 = p1;
+          }
+        }
+        pk[i >> 1] = pack_bf16(w0, w1);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<uint4*>(w_s + swz128(row, hf * 32 + q * 8)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+      fence_before();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(w_ready);
+    }
+    if (ok && mbar_wait(acc_done, (niter - 1) & 1, abort_flag, 37, &g_attn_error)) {
+      fence_after();
+      const int col_base = (MODE == BWD_DQ) ? hres * HD : (MODE == BWD_DK ? (p.Hq + g) * HD : (p.Hq + p.Hkv + g) * HD);
+      const float osc = (MODE == BWD_DV) ? 1.f : p.scale;
+      __nv_bfloat16* op = p.dqkv + (size_t)(rrow0 + row) * p.ld_dqkv + col_base;
+#pragma unroll 1
+      for (int c = hf * 4; c < hf * 4 + 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tACC + lane_addr + c * 32, r);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t o[4];
+#pragma unroll
+          for (int k2 = 0; k2 < 4; ++k2)
+            o[k2] = pack_bf16(__uint_as_float(r[8 * q + 2 * k2]) * osc, __uint_as_float(r[8 * q + 2 * k2 + 1]) * osc);
+          *reinterpret_cast<uint4*>(op + c * 32 + q * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+  }
+
+  fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = gtimer();
+    while (gtimer() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 9) {
+    fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -732,13 +978,13 @@ EncodeTiledFn attn_get_encode() {
   return fn;
 }
 
-// bf16 [rows, cols] row-major (row stride ld elements) with a {64, 128} box and 128-byte swizzle.
-int attn_make_map(const void* ptr, uint64_t cols, uint64_t rows, uint64_t ld, CUtensorMap* out) {
+// bf16 [rows, cols] row-major (row stride ld elements) with a {64, box_rows} box and 128-byte swizzle.
+int attn_make_map(const void* ptr, uint64_t cols, uint64_t rows, uint64_t ld, CUtensorMap* out, uint32_t box_rows = 128) {
   EncodeTiledFn enc = attn_get_encode();
   if (!enc) return -10;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {64, 128};
+  cuuint32_t box[2] = {64, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -782,10 +1028,10 @@ int zen_attn_fwd(const void* qkv, void* out, float* lse2, int B, int S, int Hq, 
 }
 
 // Causal attention backward.  dout / out: bf16 [B*S, Hq*hd] (row stride ld_o); lse2 from the forward; Dbuf: fp32
-// scratch [B, Hq, S]; dqkv: bf16 [B*S, (Hq + 2*Hkv)*hd] (row stride ld_qkv), fully overwritten.  hd in {64, 128}.
+// scratch [B, Hq, S]; dqkv: bf16 [B*S, (Hq + 2*Hkv)*hd] (row stride ld_qkv), fully overwritten.  hd in {64, 128, 256}.
 int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse2, float* Dbuf, void* dqkv, int B,
                  int S, int Hq, int Hkv, int hd, int ld_qkv, int ld_o, float scale, void* stream) {
-  if (S % 128 || Hq % Hkv || (hd != 64 && hd != 128)) return -2;
+  if (S % 128 || Hq % Hkv || (hd != 64 && hd != 128 && hd != 256)) return -2;
   if ((ld_qkv % 8) || (ld_o % 8) || (reinterpret_cast<uintptr_t>(qkv) % 16) || (reinterpret_cast<uintptr_t>(dout) % 16) ||
       (reinterpret_cast<uintptr_t>(dqkv) % 16) || (reinterpret_cast<uintptr_t>(out) % 16)) return -3;
   cudaStream_t st = (cudaStream_t)stream;
@@ -802,6 +1048,25 @@ int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float
   }
   AttnBwdParams p{(__nv_bfloat16*)dqkv, lse2, Dbuf, B, S, Hq, Hkv, ld_qkv, scale * 1.4426950408889634f, scale};
   dim3 gq(S / 128, Hq, B), gk(S / 128, Hkv, B);
+  if (hd == 256) {
+    CUtensorMap tq64, tdo64;
+    rc = attn_make_map(qkv, (uint64_t)(Hq + 2 * Hkv) * hd, (uint64_t)B * S, (uint64_t)ld_qkv, &tq64, 64);
+    if (rc) return rc;
+    rc = attn_make_map(dout, (uint64_t)Hq * hd, (uint64_t)B * S, (uint64_t)ld_o, &tdo64, 64);
+    if (rc) return rc;
+    static bool attr256 = false;
+    if (!attr256) {
+      cudaError_t e = cudaFuncSetAttribute(attn_bwd256_kernel<BWD_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd256Cfg::SMEM_BYTES);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd256_kernel<BWD_DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd256Cfg::SMEM_BYTES);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd256_kernel<BWD_DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, Bwd256Cfg::SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      attr256 = true;
+    }
+    attn_bwd256_kernel<BWD_DQ><<<gq, 320, Bwd256Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, p);
+    attn_bwd256_kernel<BWD_DK><<<gk, 320, Bwd256Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, p);
+    attn_bwd256_kernel<BWD_DV><<<gk, 320, Bwd256Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, p);
+    return (int)cudaGetLastError();
+  }
 #define LAUNCH_BWD(HD_)                                                                                              \
   do {                                                                                                               \
     static bool attr = false;                                                                                        \

@@ -24,7 +24,7 @@ def kernel_covers(seq, hq, hkv, hd, dtype, backward: bool = False) -> bool:
     """Shapes the tcgen05 attention kernels handle."""
     if dtype != torch.bfloat16 or seq % 128 or hq % hkv:
         return False
-    return hd in ((64, 128) if backward else (64, 128, 256))
+    return hd in (64, 128, 256)
 
 
 def have_kernel(seq, hq, hkv, hd, dtype) -> bool:
