@@ -296,6 +296,8 @@ struct AttnBwdParams {
   int ld_dqkv;
   float scale_log2;
   float scale;
+  float* part;            // hd 256, hsplit > 1: fp32 partial dK | dV, each [hsplit][B*S][Hkv * 256]
+  int hsplit;             // CTAs that share one KV head (each takes Hq / Hkv / hsplit query heads)
 };
 
 // ---- dQ: one CTA per (query tile, head, batch).  Per key tile: S = Q K^T and dP = dO V^T into tensor memory,
@@ -770,11 +772,15 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
   const int rep = p.Hq / p.Hkv;
   // resident tile index (heavy tiles first), head of the resident operand, and the iteration space
   const int ri = (MODE == BWD_DQ) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-  const int hres = blockIdx.y;                               // query head (dQ) or KV head (dK / dV)
+  const int hs = (MODE == BWD_DQ) ? 1 : p.hsplit;
+  const int hres = (MODE == BWD_DQ) ? (int)blockIdx.y : (int)blockIdx.y / hs;   // query head (dQ) or KV head (dK / dV)
+  const int hpart = (MODE == BWD_DQ) ? 0 : (int)blockIdx.y % hs;
   const int g = (MODE == BWD_DQ) ? hres / rep : hres;
+  const int reph = rep / hs;                                 // query heads this CTA walks (dK / dV)
+  const int h0 = g * rep + hpart * reph;
   const int nq64 = p.S / 64;
   const int per_head = (MODE == BWD_DQ) ? 2 * ri + 2 : nq64 - 2 * ri;   // streamed tiles per head
-  const int niter = (MODE == BWD_DQ) ? per_head : rep * per_head;
+  const int niter = (MODE == BWD_DQ) ? per_head : reph * per_head;
   const int rrow0 = b * p.S + ri * 128;
 
   if (threadIdx.x == 0) {
@@ -819,7 +825,7 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
             tma_load_2d(t2_s + a * 8192, &tmap_qkv64, t_full, (p.Hq + p.Hkv + g) * HD + a * 64, krow);
           }
         } else {
-          const int h = g * rep + it / per_head, t = 2 * ri + it % per_head;
+          const int h = h0 + it / per_head, t = 2 * ri + it % per_head;
           const int qrow = b * p.S + t * 64;
 #pragma unroll
           for (int a = 0; a < 4; ++a) {
@@ -876,7 +882,7 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
     }
     bool ok = true;
     for (int it = 0; it < niter && ok; ++it) {
-      const int h = (MODE == BWD_DQ) ? hres : g * rep + it / per_head;
+      const int h = (MODE == BWD_DQ) ? hres : h0 + it / per_head;
       const int t = (MODE == BWD_DQ) ? it : 2 * ri + it % per_head;         // streamed 64-row tile index
       if (!mbar_wait(sdp_full, it & 1, abort_flag, 35, &g_attn_error)) { ok = false; break; }
       if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, abort_flag, 36, &g_attn_error)) { ok = false; break; }
@@ -932,10 +938,22 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
       const int col_base = (MODE == BWD_DQ) ? hres * HD : (MODE == BWD_DK ? (p.Hq + g) * HD : (p.Hq + p.Hkv + g) * HD);
       const float osc = (MODE == BWD_DV) ? 1.f : p.scale;
       __nv_bfloat16* op = p.dqkv + (size_t)(rrow0 + row) * p.ld_dqkv + col_base;
+      float* pp = nullptr;
+      if (MODE != BWD_DQ && hs > 1) {
+        const size_t rows_all = (size_t)p.B * p.S, wid = (size_t)p.Hkv * HD;
+        pp = p.part + (MODE == BWD_DV ? (size_t)hs * rows_all * wid : 0) + ((size_t)hpart * rows_all + rrow0 + row) * wid + (size_t)g * HD;
+      }
 #pragma unroll 1
       for (int c = hf * 4; c < hf * 4 + 4; ++c) {
         uint32_t r[32];
         tmem_ld32(tACC + lane_addr + c * 32, r);
+        if (pp) {                                            // several CTAs share this KV head: fp32 partials, summed later
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<float4*>(pp + c * 32 + q * 4) = make_float4(__uint_as_float(r[4 * q]) * osc, __uint_as_float(r[4 * q + 1]) * osc,
+                                                                        __uint_as_float(r[4 * q + 2]) * osc, __uint_as_float(r[4 * q + 3]) * osc);
+          continue;
+        }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           uint32_t o[4];
@@ -958,6 +976,29 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
   if (warp == 9) {
     fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// dK and dV of the head-split hd = 256 backward: sum the hsplit fp32 partials in order, write bf16 into dqkv.
+__global__ void __launch_bounds__(256)
+attn_bwd256_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dqkv, int rows, int Hq, int Hkv,
+                          int hsplit, int ld) {
+  const size_t wid = (size_t)Hkv * 256, per = (size_t)rows * wid;
+  const size_t nvec = 2 * per / 8;
+  for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (size_t)gridDim.x * blockDim.x) {
+    const size_t e = v * 8;
+    const int which = (int)(e / per);                      // 0 = dK, 1 = dV
+    const size_t off = e % per;
+    const size_t row = off / wid;
+    const int col = (int)(off % wid);
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int sidx = 0; sidx < hsplit; ++sidx) {
+      const float4* q = reinterpret_cast<const float4*>(part + ((size_t)which * hsplit + sidx) * per + off);
+      const float4 x = __ldcs(q), y = __ldcs(q + 1);
+      a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w; a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
+    }
+    __nv_bfloat16* dst = dqkv + row * ld + (size_t)(Hq + which * Hkv) * 256 + col;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(a[0], a[1]), pack_bf16(a[2], a[3]), pack_bf16(a[4], a[5]), pack_bf16(a[6], a[7]));
   }
 }
 
@@ -1029,8 +1070,11 @@ int zen_attn_fwd(const void* qkv, void* out, float* lse2, int B, int S, int Hq, 
 
 // Causal attention backward.  dout / out: bf16 [B*S, Hq*hd] (row stride ld_o); lse2 from the forward; Dbuf: fp32
 // scratch [B, Hq, S]; dqkv: bf16 [B*S, (Hq + 2*Hkv)*hd] (row stride ld_qkv), fully overwritten.  hd in {64, 128, 256}.
+// part / hsplit (hd 256 only): with hsplit > 1 the query heads of a KV head are spread over hsplit CTAs whose fp32
+// partial dK / dV go to `part` (2 * hsplit * B*S * Hkv*256 floats) and are summed by a last kernel; hsplit divides
+// Hq / Hkv.  Pass hsplit <= 1 (part unused) to let one CTA walk all heads of its group.
 int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse2, float* Dbuf, void* dqkv, int B,
-                 int S, int Hq, int Hkv, int hd, int ld_qkv, int ld_o, float scale, void* stream) {
+                 int S, int Hq, int Hkv, int hd, int ld_qkv, int ld_o, float scale, float* part, int hsplit, void* stream) {
   if (S % 128 || Hq % Hkv || (hd != 64 && hd != 128 && hd != 256)) return -2;
   if ((ld_qkv % 8) || (ld_o % 8) || (reinterpret_cast<uintptr_t>(qkv) % 16) || (reinterpret_cast<uintptr_t>(dout) % 16) ||
       (reinterpret_cast<uintptr_t>(dqkv) % 16) || (reinterpret_cast<uintptr_t>(out) % 16)) return -3;
@@ -1046,7 +1090,9 @@ int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float
     if (blocks > 148 * 16) blocks = 148 * 16;
     attn_bwd_prep_kernel<<<(int)blocks, 256, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, Dbuf, B, S, Hq, hd, ld_o);
   }
-  AttnBwdParams p{(__nv_bfloat16*)dqkv, lse2, Dbuf, B, S, Hq, Hkv, ld_qkv, scale * 1.4426950408889634f, scale};
+  if (hsplit < 1 || hd != 256 || !part) hsplit = 1;
+  if ((Hq / Hkv) % hsplit) return -2;
+  AttnBwdParams p{(__nv_bfloat16*)dqkv, lse2, Dbuf, B, S, Hq, Hkv, ld_qkv, scale * 1.4426950408889634f, scale, part, hsplit};
   dim3 gq(S / 128, Hq, B), gk(S / 128, Hkv, B);
   if (hd == 256) {
     CUtensorMap tq64, tdo64;
@@ -1063,8 +1109,15 @@ int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float
       attr256 = true;
     }
     attn_bwd256_kernel<BWD_DQ><<<gq, 320, Bwd256Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, p);
-    attn_bwd256_kernel<BWD_DK><<<gk, 320, Bwd256Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, p);
-    attn_bwd256_kernel<BWD_DV><<<gk, 320, Bwd256Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, p);
+    dim3 gks(S / 128, Hkv * hsplit, B);
+    attn_bwd256_kernel<BWD_DK><<<gks, 320, Bwd256Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, p);
+    attn_bwd256_kernel<BWD_DV><<<gks, 320, Bwd256Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, p);
+    if (hsplit > 1) {
+      const size_t nvec = (size_t)2 * B * S * Hkv * 256 / 8;
+      size_t blocks = (nvec + 255) / 256;
+      if (blocks > 148 * 8) blocks = 148 * 8;
+      attn_bwd256_reduce_kernel<<<(int)blocks, 256, 0, st>>>(part, (__nv_bfloat16*)dqkv, B * S, Hq, Hkv, hsplit, ld_qkv);
+    }
     return (int)cudaGetLastError();
   }
 #define LAUNCH_BWD(HD_)                                                                                              \

@@ -53,9 +53,17 @@ def attention_bwd_kernel(dout, qkv, out, lse2, bsz, seq, hq, hkv, hd, scale):
     dout = dout if (dout.is_contiguous() and dout.data_ptr() % 16 == 0) else dout.contiguous()
     dqkv = torch.empty_like(qkv)
     dbuf = torch.empty(bsz, hq, seq, dtype=torch.float32, device=qkv.device)
+    hsplit, part = 1, None
+    rep = hq // hkv
+    if hd == 256 and rep > 1:
+        # few KV heads (MQA / GQA): spread the query heads of a group over several CTAs until the GPU is covered
+        base = hkv * bsz * (seq // 128)
+        hsplit = next((d for d in range(1, rep + 1) if rep % d == 0 and base * d >= 2 * 148), rep)
+        if hsplit > 1:
+            part = torch.empty(2 * hsplit * bsz * seq * hkv * 256, dtype=torch.float32, device=qkv.device)
     rc = _native.lib().zen_attn_bwd(_native.ptr(qkv), _native.ptr(out), _native.ptr(dout), _native.ptr(lse2), _native.ptr(dbuf),
                                     _native.ptr(dqkv), bsz, seq, hq, hkv, hd, qkv.stride(0), out.stride(0),
-                                    ctypes.c_float(scale), _native.stream_ptr())
+                                    ctypes.c_float(scale), _native.ptr(part), hsplit, _native.stream_ptr())
     _native.check(rc, "zen_attn_bwd")
     return dqkv
 
