@@ -144,6 +144,45 @@ def check_gemm_allreduce(rank, world, dev):
     print(f"OK gemm_allreduce rank{rank}", flush=True)
 
 
+def check_gemm_rs_ag(rank, world, dev):
+    """GEMM fused with a reduce-scatter of its output rows, and with an all-gather of its input rows, against NCCL."""
+    from zen_repro_b200.ops import gemm as G
+    from zen_repro_b200.parallel.tp_fused import FusedTPWorkspace
+
+    ws = FusedTPWorkspace(None, 4096, 4096, wait_ms=1000.0)
+    for (M, N, K) in [(256, 384, 320), (4096, 768, 1536), (2048, 4096, 512), (512, 130, 72)]:
+        for rep in range(3):
+            g = torch.Generator().manual_seed(2000 * rep + rank)
+            a = torch.randn(M, K, generator=g).bfloat16().to(dev)
+            w = torch.randn(N, K, generator=g).bfloat16().to(dev)
+            bias = torch.randn(N, generator=torch.Generator().manual_seed(9)).bfloat16().to(dev)
+            # reduce-scatter: this rank's rows of the summed product
+            assert ws.fits_rs(M, N)
+            got = ws.gemm_rs_nt(a, w, bias)
+            full = a.float() @ w.float().t()
+            dist.all_reduce(full)
+            rpr = M // world
+            want = full[rank * rpr:(rank + 1) * rpr] + bias.float()
+            assert ws.check() == 0 and G.gemm_error() == 0
+            assert got.shape == (rpr, N)
+            assert (got.float() - want).abs().max().item() <= 0.02 * want.abs().max().item() + 0.05, ("rs", M, N, K)
+            got_nn = ws.gemm_rs_nn(a, w.t().contiguous())
+            assert (got_nn.float() + bias.float() - want).abs().max().item() <= 0.02 * want.abs().max().item() + 0.1
+            # all-gather of the input rows, then the product with this rank's own weight
+            assert ws.fits_ag(M, K)
+            rows = [torch.empty_like(a) for _ in range(world)]
+            dist.all_gather(rows, a)
+            want2 = torch.cat(rows).float() @ w.float().t() + bias.float()
+            got2 = ws.ag_gemm_nt(a, w, bias)
+            assert ws.check() == 0 and G.gemm_error() == 0
+            assert got2.shape == (world * M, N)
+            assert (got2.float() - want2).abs().max().item() <= 0.02 * want2.abs().max().item() + 0.05, ("ag", M, N, K)
+            got3 = ws.ag_gemm_nn(a, w.t().contiguous())
+            assert (got3.float() + bias.float() - want2).abs().max().item() <= 0.02 * want2.abs().max().item() + 0.1
+    ws.close()
+    print(f"OK gemm_rs_ag rank{rank}", flush=True)
+
+
 def check_tp_trainer(rank, world, dev):
     """TP = 2 training with fused GEMM + all-reduce tracks the NCCL-based TP path."""
     from zen_repro_b200.trainer import TrainConfig, Trainer
@@ -157,7 +196,7 @@ def check_tp_trainer(rank, world, dev):
     print(f"OK tp_trainer rank{rank} {out[True]}", flush=True)
 
 
-CHECKS = {"gemm_ar": check_gemm_allreduce, "tp_trainer": check_tp_trainer,"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
+CHECKS = {"gemm_ar": check_gemm_allreduce, "gemm_rs_ag": check_gemm_rs_ag, "tp_trainer": check_tp_trainer,"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
           "hook": check_zen_hook, "departed": check_departed_rank}
 
 if __name__ == "__main__":

@@ -58,7 +58,44 @@ struct GemmParams {
   uint64_t slot_elems;        // elements per (parity, slot)
   int recv_ld;                // row stride of exchanged partial tiles
   uint32_t* status;           // device word: bit 2 set when a peer wait timed out
+  // ---- collective flavour of the fused kernel ----
+  // 0: all-reduce of C (every rank gets the sum).
+  // 1: reduce-scatter of C over rows: A is [M, K], rank r ends up with rows [r * rows_per_rank, ...) of the sum in
+  //    C[rows_per_rank, N]; partial tiles of rows owned by a peer are pushed to that peer only, and those tiles run
+  //    first so that they are on their way while this rank computes its own rows.
+  // 2: all-gather of A over rows: this rank holds rows [rank * rows_per_rank, ...) of A (a_local); the epilogue warps
+  //    of the first CTAs push it chunk by chunk (128 rows) into the peer's gather region at kernel start, tiles of local
+  //    rows run first, and the producer waits (bounded) for a chunk's flag before it loads a tile of gathered rows
+  //    through a tensor map over this rank's own region, never over peer memory.
+  int coll_mode;
+  int rows_per_rank;
+  const __nv_bfloat16* a_local;
+  int lda_local;
 };
+
+constexpr int COLL_AR = 0, COLL_RS = 1, COLL_AG = 2;
+
+// Tile index -> coordinates.  owner: rank whose rows the tile covers; m0: first row in the full row space; mloc:
+// first row relative to the owner's block; fidx: index of the tile among the owner's tiles (flag slot).
+struct TileCoord { int m0, n0, owner, mloc, fidx; };
+template <int BN>
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int tile) {
+  TileCoord t;
+  if (p.npeers == 0 || p.coll_mode == COLL_AR) {
+    t.m0 = (tile % p.num_m_tiles) * BM;
+    t.n0 = (tile / p.num_m_tiles) * BN;
+    t.owner = p.rank; t.mloc = t.m0; t.fidx = tile;
+    return t;
+  }
+  const int tpr = p.rows_per_rank / BM, per_owner = tpr * p.num_n_tiles, nranks = p.npeers + 1;
+  const int rel = tile / per_owner, within = tile % per_owner;
+  t.owner = (p.rank + rel + (p.coll_mode == COLL_RS ? 1 : 0)) % nranks;   // RS: peers' rows first; AG: own rows first
+  t.mloc = (within % tpr) * BM;
+  t.n0 = (within / tpr) * BN;
+  t.m0 = t.owner * p.rows_per_rank + t.mloc;
+  t.fidx = within;
+  return t;
+}
 
 // ------------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -187,7 +224,8 @@ struct Cfg {
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_g, const GemmParams p) {
   using C = Cfg<BN, A_MN, B_MN>;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -221,8 +259,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       // ------------------------------------------------------------------ TMA producer
       uint32_t it = 0;
       bool ok = true;
+      const bool ag = p.npeers > 0 && p.coll_mode == COLL_AG;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.num_m_tiles) * BM, n0 = (tile / p.num_m_tiles) * BN;
+        const TileCoord tc = decode_tile<BN>(p, tile);
+        const int n0 = tc.n0;
+        int m0 = tc.m0;
+        const CUtensorMap* amap = &tma_a;
+        if (ag) {
+          m0 = tc.mloc;                             // row inside the local shard or inside the gathered copy
+          if (tc.owner != p.rank) {
+            // rows of a peer: its epilogue warps push them into this rank's gather region; wait for the chunk
+            amap = &tma_g;
+            const uint32_t* f = p.my_flags + (size_t)(p.epoch & 1u) * p.npeers * p.max_tiles + tc.mloc / BM;
+            const uint64_t t0 = gtimer();
+            bool got = ld_acquire_sys_u32(f) == p.epoch;
+            while (!got) {
+              for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f) == p.epoch;
+              if (!got && (gtimer() - t0 > p.wait_ns || *abort_flag)) break;
+            }
+            if (!got) { atomicOr(p.status, 4u); *abort_flag = 6; atomicCAS(&g_gemm_error, 0, 6); ok = false; break; }
+            asm volatile("fence.proxy.async;" ::: "memory");      // the peer's stores, then this rank's TMA reads
+          }
+        }
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % C::STAGES;
           const uint32_t ph = (it / C::STAGES) & 1;
@@ -232,7 +290,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           mbar_expect_tx(&full[s], C::STAGE_BYTES);
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_2d(sa, &tma_a, &full[s], k0, m0);
+            tma_load_2d(sa, amap, &full[s], k0, m0);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tma_a, &full[s], m0 + 64 * j, k0);
@@ -281,18 +339,44 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int grp = warp & 3;                   // TMEM lane quarter this warp may read
     uint32_t tcount = 0;
     bool ok = true;
+    const uint32_t par = p.epoch & 1u;
+    const bool rs = p.npeers > 0 && p.coll_mode == COLL_RS, ag = p.npeers > 0 && p.coll_mode == COLL_AG;
+    if (ag) {
+      // ---- all-gather: push this rank's rows to the peer, one 128-row chunk per CTA, while the first tiles
+      // (local rows) are in their main loops.  The gathered copy is dense [rows_per_rank, K].
+      const int et = threadIdx.x - 64;
+      const int nchunks = p.rows_per_rank / BM, vec_per_row = p.K / 8;
+      for (int c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        for (int pe = 0; pe < p.npeers; ++pe) {
+          __nv_bfloat16* dst = p.peer_recv[pe] + ((size_t)par * p.npeers + p.peer_slot_of_me[pe]) * p.slot_elems + (size_t)c * BM * p.K;
+          const __nv_bfloat16* src = p.a_local + (size_t)c * BM * p.lda_local;
+          for (int v = et; v < BM * vec_per_row; v += 128) {
+            const int r = v / vec_per_row, cv = v % vec_per_row;
+            *reinterpret_cast<uint4*>(dst + (size_t)r * p.K + cv * 8) = *reinterpret_cast<const uint4*>(src + (size_t)r * p.lda_local + cv * 8);
+          }
+        }
+        __threadfence_system();
+        epilogue_barrier();
+        if (et < p.npeers)
+          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + c, p.epoch);
+      }
+    }
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-      const int m0 = (tile % p.num_m_tiles) * BM, n0 = (tile / p.num_m_tiles) * BN;
+      const TileCoord tc = decode_tile<BN>(p, tile);
+      const int m0 = tc.m0, n0 = tc.n0;
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aph, abort_flag, 4)) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + grp * 32 + lane;
+      const int row = m0 + grp * 32 + lane;     // row in the full row space (bounds)
+      const int xrow = rs ? tc.mloc + grp * 32 + lane : row;    // row inside an exchange slot / inside C
+      const int ftile = tc.fidx;
+      const bool mine = tc.owner == p.rank;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(grp * 32) << 16) + acc * BN;
-      const uint32_t par = p.epoch & 1u;
-      if (p.npeers > 0) {
-        // ---- fused all-reduce, step 1: push this rank's partial tile (bf16) into every peer's exchange region
+      if (p.npeers > 0 && !ag) {
+        // ---- step 1: push this rank's partial tile (bf16) into the exchange region of every peer (all-reduce) or of
+        // the rank that owns these rows (reduce-scatter; nothing to push for own rows)
 #pragma unroll 1
-        for (int ch = 0; ch < BN / 32; ++ch) {
+        for (int ch = 0; ch < ((rs && mine) ? 0 : BN / 32); ++ch) {
           uint32_t r[32];
           tmem_ld32(taddr0 + ch * 32, r);
           const int col0 = n0 + ch * 32;
@@ -304,8 +388,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               o[q] = *reinterpret_cast<uint32_t*>(&h);
             }
             for (int pe = 0; pe < p.npeers; ++pe) {
+              if (rs && p.peer_rank[pe] != tc.owner) continue;
               __nv_bfloat16* dst = p.peer_recv[pe] + ((size_t)par * p.npeers + p.peer_slot_of_me[pe]) * p.slot_elems +
-                                   (size_t)row * p.recv_ld + col0;
+                                   (size_t)xrow * p.recv_ld + col0;
               if (col0 + 32 <= p.N) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
@@ -320,11 +405,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         __threadfence_system();
         epilogue_barrier();
         const int et = threadIdx.x - 64;                                   // 0..127 among the epilogue threads
-        if (et < p.npeers)
-          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + tile, p.epoch);
+        if (et < p.npeers && !(rs && (mine || p.peer_rank[et] != tc.owner)))
+          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + ftile, p.epoch);
+        if (rs && !mine) {                       // a peer's rows: pushed, nothing to write here
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[acc]);
+          continue;
+        }
         // ---- step 2: bounded wait for every peer's partial of this tile
         if (et < p.npeers) {
-          const uint32_t* f = p.my_flags + ((size_t)par * p.npeers + et) * p.max_tiles + tile;
+          const uint32_t* f = p.my_flags + ((size_t)par * p.npeers + et) * p.max_tiles + ftile;
           const uint64_t t0 = gtimer();
           bool got = ld_acquire_sys_u32(f) == p.epoch;
           while (!got) {
@@ -344,7 +435,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (p.npeers > 0) {
+          if (p.npeers > 0 && !ag) {
             // step 3: sum the bf16-rounded partials of all ranks in rank order, so every rank gets the same bits
             float own[32];
 #pragma unroll
@@ -362,7 +453,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 own_added = true;
               }
               if (pe == p.npeers) break;
-              const __nv_bfloat16* src = p.my_recv + ((size_t)par * p.npeers + pe) * p.slot_elems + (size_t)row * p.recv_ld + col0;
+              const __nv_bfloat16* src = p.my_recv + ((size_t)par * p.npeers + pe) * p.slot_elems + (size_t)xrow * p.recv_ld + col0;
               if (col0 + 32 <= p.N) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -385,7 +476,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int i = 0; i < 32; ++i) if (fullw || col0 + i < p.N) v[i] += __bfloat162float(bp[i]);
           }
           if (p.out_fp32) {
-            float* cp = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
+            float* cp = reinterpret_cast<float*>(p.C) + (size_t)xrow * p.ldc + col0;
             if (fullw && (p.ldc % 4 == 0)) {
 #pragma unroll
               for (int i = 0; i < 32; i += 4) {
@@ -399,7 +490,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 if (col0 + i < p.N) cp[i] = p.accumulate ? cp[i] + v[i] : v[i];
             }
           } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)xrow * p.ldc + col0;
             if (fullw && (p.ldc % 8 == 0)) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
@@ -518,7 +609,7 @@ int sm_count_g() {
 }
 
 template <int BN, bool A_MN, bool B_MN>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t st) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tg, GemmParams p, cudaStream_t st) {
   using C = Cfg<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -530,7 +621,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStrea
   p.num_n_tiles = (p.N + BN - 1) / BN;
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < sm_count_g() ? tiles : sm_count_g();
-  gemm_bf16_kernel<BN, A_MN, B_MN><<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, p);
+  gemm_bf16_kernel<BN, A_MN, B_MN><<<grid, NUM_THREADS, C::SMEM_BYTES, st>>>(ta, tb, tg, p);
   return (int)cudaGetLastError();
 }
 
@@ -550,6 +641,7 @@ struct ZenGemmArCtx {
 };
 namespace {
 thread_local const ZenGemmArCtx* g_ar_next = nullptr;
+thread_local int g_coll_next = 0;                // COLL_* of the launch that follows on this thread
 void fill_ar(GemmParams& p, const ZenGemmArCtx& c) {
   p.npeers = c.nranks - 1;
   p.rank = c.rank;
@@ -589,24 +681,51 @@ int zen_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
     const long c256 = ((t256 + sms - 1) / sms) * 2, c128 = (t128 + sms - 1) / sms;
     bn = (N <= 128 || c128 < c256) ? 128 : 256;
   }
-  CUtensorMap ta, tb;
+  GemmParams p{};
+  p.C = C; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
+  if (g_ar_next) {
+    fill_ar(p, *g_ar_next);
+    p.coll_mode = g_coll_next;
+    g_ar_next = nullptr;
+    g_coll_next = 0;
+  }
+  const bool ag = p.npeers > 0 && p.coll_mode == COLL_AG, rs = p.npeers > 0 && p.coll_mode == COLL_RS;
+  int a_rows = M;
+  if (ag || rs) {
+    const int nranks = p.npeers + 1;
+    if (M % nranks || (M / nranks) % BM) return -6;
+    p.rows_per_rank = M / nranks;
+    if (rs) p.recv_ld = (N + 7) / 8 * 8;
+    if (ag) {
+      // A is this rank's row block; the peer's block arrives in this rank's own region
+      if (a_mn || nranks != 2 || (K % 8) || (uint64_t)p.rows_per_rank * K > p.slot_elems ||
+          (uint32_t)(p.rows_per_rank / BM) > p.max_tiles) return -7;
+      p.a_local = reinterpret_cast<const __nv_bfloat16*>(A);
+      p.lda_local = lda;
+      a_rows = p.rows_per_rank;
+    }
+  }
+  CUtensorMap ta, tb, tg;
   int rc;
-  if (!a_mn) rc = get_map(A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 128, &ta);
+  if (!a_mn) rc = get_map(A, (uint64_t)K, (uint64_t)a_rows, (uint64_t)lda, 64, 128, &ta);
   else rc = get_map(A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, 64, &ta);
   if (rc) return rc;
   if (!b_mn) rc = get_map(B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, (uint32_t)bn, &tb);
   else rc = get_map(B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64, &tb);
   if (rc) return rc;
-  GemmParams p{};
-  p.C = C; p.bias = bias; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
-  if (g_ar_next) { fill_ar(p, *g_ar_next); g_ar_next = nullptr; }
+  tg = ta;
+  if (ag) {
+    const __nv_bfloat16* gsrc = p.my_recv + (size_t)(p.epoch & 1u) * p.npeers * p.slot_elems;
+    rc = get_map(gsrc, (uint64_t)K, (uint64_t)p.rows_per_rank, (uint64_t)K, 64, 128, &tg);
+    if (rc) return rc;
+  }
   cudaStream_t st = (cudaStream_t)stream;
-#define LAUNCH(BN_)                                                        \
-  do {                                                                     \
-    if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, p, st);   \
-    if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, p, st);     \
-    if (a_mn && !b_mn) return launch<BN_, true, false>(ta, tb, p, st);     \
-    return launch<BN_, true, true>(ta, tb, p, st);                         \
+#define LAUNCH(BN_)                                                            \
+  do {                                                                         \
+    if (!a_mn && !b_mn) return launch<BN_, false, false>(ta, tb, tg, p, st);   \
+    if (!a_mn && b_mn) return launch<BN_, false, true>(ta, tb, tg, p, st);     \
+    if (a_mn && !b_mn) return launch<BN_, true, false>(ta, tb, tg, p, st);     \
+    return launch<BN_, true, true>(ta, tb, tg, p, st);                         \
   } while (0)
   if (bn == 256) LAUNCH(256);
   LAUNCH(128);
@@ -631,6 +750,28 @@ int zen_gemm_bf16_ar(const void* A, const void* B, void* C, const void* bias, in
   if (ctx->nranks > 1) g_ar_next = ctx;
   const int rc = zen_gemm_bf16(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, bn, stream);
   g_ar_next = nullptr;
+  return rc;
+}
+
+// The same kernel with the collective chosen by `mode`: 0 = all-reduce (as zen_gemm_bf16_ar), 1 = reduce-scatter of
+// the output over rows (A [M, K], C [M / nranks, N] = this rank's rows of the sum), 2 = all-gather of A over rows
+// (A is this rank's [M / nranks, K] block, C [M, N]; two ranks).  M / nranks must be a multiple of 128.  Capacity:
+// mode 1 needs (M / nranks) * round_up(N, 8) <= slot_elems, mode 2 needs (M / nranks) * K <= slot_elems.
+int zen_gemm_bf16_coll(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
+                       int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, int bn, const ZenGemmArCtx* ctx,
+                       int mode, void* stream) {
+  if (mode == COLL_AR) return zen_gemm_bf16_ar(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, bn, ctx, stream);
+  if (!ctx || ctx->nranks < 2 || ctx->nranks > 8 || (mode != COLL_RS && mode != COLL_AG)) return -3;
+  if (bn == 0) bn = 128;
+  const int rpr = M / ctx->nranks;
+  if (mode == COLL_RS && (uint64_t)rpr * (uint64_t)((N + 7) / 8 * 8) > ctx->slot_elems) return -4;
+  const uint64_t tiles = (uint64_t)((rpr + 127) / 128) * ((N + bn - 1) / bn);
+  if (tiles > ctx->max_tiles) return -5;
+  g_ar_next = ctx;
+  g_coll_next = mode;
+  const int rc = zen_gemm_bf16(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, bn, stream);
+  g_ar_next = nullptr;
+  g_coll_next = 0;
   return rc;
 }
 

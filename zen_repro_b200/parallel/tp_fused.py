@@ -1,4 +1,5 @@
-"""Workspace and entry points of the GEMM fused with a tensor-parallel all-reduce.
+"""Workspace and entry points of the GEMMs fused with a tensor-parallel collective (all-reduce, reduce-scatter of
+the output rows, all-gather of the input rows).
 
 ``FusedTPWorkspace`` owns the symmetric exchange region of one TP group (two parities of partial-tile
 buffers and per-tile flags per peer) and the call counter that every rank advances in lockstep.
@@ -50,20 +51,51 @@ class FusedTPWorkspace:
     def fits(self, M: int, N: int) -> bool:
         return M * ((N + 7) // 8 * 8) <= self.slot_elems and ((M + 127) // 128) * ((N + 127) // 128) <= self.max_tiles
 
-    def _call(self, a, b, M, N, K, a_mn, b_mn, bias, out, out_dtype):
+    def _call(self, a, b, M, N, K, a_mn, b_mn, bias, out, out_dtype, mode: int = 0):
+        """mode 0: all-reduce of the product; 1: reduce-scatter over rows (out has M / P rows); 2: all-gather of the
+        rows of ``a`` (``a`` is this rank's M / P rows, out has M rows)."""
         from ..ops.gemm import _rowmajor
 
         a2, b2 = _rowmajor(a), _rowmajor(b)
         if out is None:
-            out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
+            out = torch.empty(M // self.P if mode == 1 else M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
         self.epoch += 1
         self.ctx.epoch = self.epoch
-        rc = _native.lib().zen_gemm_bf16_ar(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
-                                            a2.stride(0), b2.stride(0), out.stride(0), int(a_mn), int(b_mn),
-                                            int(out.dtype == torch.float32), 0, 128, ctypes.byref(self.ctx),
-                                            _native.stream_ptr())
-        _native.check(rc, "zen_gemm_bf16_ar")
+        rc = _native.lib().zen_gemm_bf16_coll(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
+                                              a2.stride(0), b2.stride(0), out.stride(0), int(a_mn), int(b_mn),
+                                              int(out.dtype == torch.float32), 0, 128, ctypes.byref(self.ctx), mode,
+                                              _native.stream_ptr())
+        _native.check(rc, "zen_gemm_bf16_coll")
         return out
+
+    def fits_rs(self, M: int, N: int) -> bool:
+        rpr = M // self.P
+        return (M % self.P == 0 and rpr % 128 == 0 and rpr * ((N + 7) // 8 * 8) <= self.slot_elems
+                and (rpr // 128) * ((N + 127) // 128) <= self.max_tiles)
+
+    def fits_ag(self, rows_local: int, K: int) -> bool:
+        return self.P == 2 and rows_local % 128 == 0 and K % 8 == 0 and rows_local * K <= self.slot_elems
+
+    def gemm_rs_nt(self, a, b, bias=None, out=None):
+        """reduce_scatter over rows of a[M,K] @ b[N,K]^T: this rank's M / P rows of the sum over the group (+ bias)."""
+        K = a.shape[-1]
+        return self._call(a, b, a.numel() // K, b.shape[0], K, False, False, bias, out, None, mode=1)
+
+    def gemm_rs_nn(self, a, b, bias=None, out=None):
+        """reduce_scatter over rows of a[M,K] @ b[K,N]."""
+        K = a.shape[-1]
+        return self._call(a, b, a.numel() // K, b.shape[1], K, False, True, bias, out, None, mode=1)
+
+    def ag_gemm_nt(self, a_local, b, bias=None, out=None):
+        """all_gather(a_local over rows)[M,K] @ b[N,K]^T: every rank passes its M / P rows; the kernel pushes them to the
+        peer and multiplies local rows first, gathered rows as they arrive."""
+        K = a_local.shape[-1]
+        return self._call(a_local, b, self.P * (a_local.numel() // K), b.shape[0], K, False, False, bias, out, None, mode=2)
+
+    def ag_gemm_nn(self, a_local, b, bias=None, out=None):
+        """all_gather(a_local over rows)[M,K] @ b[K,N]."""
+        K = a_local.shape[-1]
+        return self._call(a_local, b, self.P * (a_local.numel() // K), b.shape[1], K, False, True, bias, out, None, mode=2)
 
     def gemm_ar_nt(self, a, b, bias=None, out=None):
         """all_reduce(a[M,K] @ b[N,K]^T) (+ bias, added once after the sum)."""
