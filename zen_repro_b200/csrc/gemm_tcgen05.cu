@@ -211,6 +211,109 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+// Second half of a deferred tile (all 128 epilogue threads): bounded wait for the peers' partials of tile `tile`,
+// then C = bias + sum over ranks, in rank order, of the bf16 partials (own partial already in C).  Rows are walked
+// with consecutive threads on consecutive 16-byte vectors, four rows in flight per thread.
+template <int BN>
+__device__ __forceinline__ bool finish_tile(const GemmParams& p, int tile, uint32_t par, volatile int* abort_flag) {
+  const TileCoord tc = decode_tile<BN>(p, tile);
+  const int et = threadIdx.x - 64;
+  const bool rs = p.coll_mode == COLL_RS;
+  if (et < p.npeers) {
+    const uint32_t* f = p.my_flags + ((size_t)par * p.npeers + et) * p.max_tiles + tc.fidx;
+    const uint64_t t0 = gtimer();
+    bool got = ld_acquire_sys_u32(f) == p.epoch;
+    while (!got) {
+      for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f) == p.epoch;
+      if (!got && (gtimer() - t0 > p.wait_ns || *abort_flag)) break;
+    }
+    if (!got) { atomicOr(p.status, 4u); *abort_flag = 5; atomicCAS(&g_gemm_error, 0, 5); }
+  }
+  epilogue_barrier();
+  if (*abort_flag) return false;
+  constexpr int VPR = BN / 8, RPP = 128 / VPR;       // vectors per row, rows per pass of the 128 threads
+  const int cv = et % VPR, col = tc.n0 + cv * 8;
+  const bool vec_ok = (p.ldc % 8) == 0 && col + 8 <= p.N;
+  __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C);
+  const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(p.bias);
+  for (int r0 = et / VPR; r0 < BM; r0 += 4 * RPP) {
+    float v[4][8];
+    uint4 own[4];
+    bool live[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int r = r0 + u * RPP;
+      live[u] = r < BM && tc.m0 + r < p.M && col < p.N;
+      if (live[u] && vec_ok) own[u] = *reinterpret_cast<const uint4*>(C + (size_t)((rs ? tc.mloc : tc.m0) + r) * p.ldc + col);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
+    }
+    bool own_added = false;
+    for (int pe = 0; pe <= p.npeers; ++pe) {
+      if (!own_added && (pe == p.npeers || p.peer_rank[pe] > p.rank)) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (!live[u]) continue;
+          const int xr = (rs ? tc.mloc : tc.m0) + r0 + u * RPP;
+          if (vec_ok) {
+            const uint32_t w[4] = {own[u].x, own[u].y, own[u].z, own[u].w};
+#pragma unroll
+            for (int k2 = 0; k2 < 4; ++k2) { v[u][2 * k2] += __uint_as_float(w[k2] << 16); v[u][2 * k2 + 1] += __uint_as_float(w[k2] & 0xffff0000u); }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) if (col + i < p.N) v[u][i] += __bfloat162float(C[(size_t)xr * p.ldc + col + i]);
+          }
+        }
+        own_added = true;
+      }
+      if (pe == p.npeers) break;
+      uint4 pv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int xr = (rs ? tc.mloc : tc.m0) + r0 + u * RPP;
+        const __nv_bfloat16* src = p.my_recv + ((size_t)par * p.npeers + pe) * p.slot_elems + (size_t)xr * p.recv_ld + col;
+        if (live[u] && vec_ok) pv[u] = ld_cg_v4(src);
+        else if (live[u]) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) if (col + i < p.N) v[u][i] += __bfloat162float(*reinterpret_cast<const volatile __nv_bfloat16*>(src + i));
+        }
+      }
+      if (vec_ok) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (!live[u]) continue;
+          const uint32_t w[4] = {pv[u].x, pv[u].y, pv[u].z, pv[u].w};
+#pragma unroll
+          for (int k2 = 0; k2 < 4; ++k2) { v[u][2 * k2] += __uint_as_float(w[k2] << 16); v[u][2 * k2 + 1] += __uint_as_float(w[k2] & 0xffff0000u); }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (!live[u]) continue;
+      const int xr = (rs ? tc.mloc : tc.m0) + r0 + u * RPP;
+      if (bias) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) if (col + i < p.N) v[u][i] += __bfloat162float(bias[col + i]);
+      }
+      __nv_bfloat16* cp = C + (size_t)xr * p.ldc + col;
+      if (vec_ok) {
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(v[u][2 * q], v[u][2 * q + 1]);
+          o[q] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(cp) = make_uint4(o[0], o[1], o[2], o[3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) if (col + i < p.N) cp[i] = __float2bfloat16_rn(v[u][i]);
+      }
+    }
+  }
+  return true;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -361,6 +464,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + c, p.epoch);
       }
     }
+    // Deferred reduction (bf16 output, no accumulation): a tile's epilogue pushes the partial to the peers, stores
+    // the own partial in C and moves on; the sum over ranks for that tile is taken one tile later (after the next
+    // tile's push), when the peers' partials have normally arrived, so that no epilogue stalls on NVLink latency.
+    const bool deferred = p.npeers > 0 && !ag && !p.out_fp32 && !p.accumulate;
+    int pending = -1;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
       const TileCoord tc = decode_tile<BN>(p, tile);
       const int m0 = tc.m0, n0 = tc.n0;
@@ -376,7 +484,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         // ---- step 1: push this rank's partial tile (bf16) into the exchange region of every peer (all-reduce) or of
         // the rank that owns these rows (reduce-scatter; nothing to push for own rows)
 #pragma unroll 1
-        for (int ch = 0; ch < ((rs && mine) ? 0 : BN / 32); ++ch) {
+        for (int ch = 0; ch < ((rs && mine && !deferred) ? 0 : BN / 32); ++ch) {
           uint32_t r[32];
           tmem_ld32(taddr0 + ch * 32, r);
           const int col0 = n0 + ch * 32;
@@ -386,6 +494,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int q = 0; q < 16; ++q) {
               __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
               o[q] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            if (deferred && (!rs || mine)) {      // own partial waits in C for the peers' (summed by finish_tile)
+              __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)xrow * p.ldc + col0;
+              if (col0 + 32 <= p.N && (p.ldc % 8) == 0) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(cp + 8 * q) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (col0 + i < p.N) cp[i] = __ushort_as_bfloat16((unsigned short)((o[i >> 1] >> ((i & 1) * 16)) & 0xffffu));
+              }
             }
             for (int pe = 0; pe < p.npeers; ++pe) {
               if (rs && p.peer_rank[pe] != tc.owner) continue;
@@ -407,6 +526,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int et = threadIdx.x - 64;                                   // 0..127 among the epilogue threads
         if (et < p.npeers && !(rs && (mine || p.peer_rank[et] != tc.owner)))
           st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + ftile, p.epoch);
+        if (deferred) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[acc]);
+          if (pending >= 0 && !finish_tile<BN>(p, pending, par, abort_flag)) { ok = false; break; }
+          pending = (!rs || mine) ? tile : -1;
+          continue;
+        }
         if (rs && !mine) {                       // a peer's rows: pushed, nothing to write here
           tc_fence_before();
           __syncwarp();
@@ -524,6 +651,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
+    if (ok && pending >= 0) finish_tile<BN>(p, pending, par, abort_flag);
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -744,7 +872,7 @@ int zen_gemm_bf16_ar(const void* A, const void* B, void* C, const void* bias, in
                      void* stream) {
   if (!ctx || ctx->nranks < 1 || ctx->nranks > 8) return -3;
   if ((uint64_t)M * (uint64_t)((N + 7) / 8 * 8) > ctx->slot_elems) return -4;
-  if (bn == 0) bn = 128;
+  if (bn == 0) bn = (N >= 1024 && N % 256 == 0) ? 256 : 128;
   const uint64_t tiles = (uint64_t)((M + 127) / 128) * ((N + bn - 1) / bn);
   if (tiles > ctx->max_tiles) return -5;
   if (ctx->nranks > 1) g_ar_next = ctx;
@@ -762,7 +890,7 @@ int zen_gemm_bf16_coll(const void* A, const void* B, void* C, const void* bias, 
                        int mode, void* stream) {
   if (mode == COLL_AR) return zen_gemm_bf16_ar(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, bn, ctx, stream);
   if (!ctx || ctx->nranks < 2 || ctx->nranks > 8 || (mode != COLL_RS && mode != COLL_AG)) return -3;
-  if (bn == 0) bn = 128;
+  if (bn == 0) bn = (N >= 1024 && N % 256 == 0) ? 256 : 128;
   const int rpr = M / ctx->nranks;
   if (mode == COLL_RS && (uint64_t)rpr * (uint64_t)((N + 7) / 8 * 8) > ctx->slot_elems) return -4;
   const uint64_t tiles = (uint64_t)((rpr + 127) / 128) * ((N + bn - 1) / bn);

@@ -63,7 +63,7 @@ class FusedTPWorkspace:
         self.ctx.epoch = self.epoch
         rc = _native.lib().zen_gemm_bf16_coll(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
                                               a2.stride(0), b2.stride(0), out.stride(0), int(a_mn), int(b_mn),
-                                              int(out.dtype == torch.float32), 0, 128, ctypes.byref(self.ctx), mode,
+                                              int(out.dtype == torch.float32), 0, 0, ctypes.byref(self.ctx), mode,
                                               _native.stream_ptr())
         _native.check(rc, "zen_gemm_bf16_coll")
         return out
