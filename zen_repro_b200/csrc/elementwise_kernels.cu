@@ -435,11 +435,23 @@ __global__ void __launch_bounds__(256)
 norm_dwdb_partial_kernel(const T* __restrict__ dy, const T* __restrict__ h, const float* __restrict__ rstd_in,
                          const float* __restrict__ mean_in, float* __restrict__ part_dw, float* __restrict__ part_db,
                          int rows, int cols) {
+  // Narrow matrices (fewer 8-column vectors than threads): the threads form `groups` row groups that walk
+  // interleaved rows of the CTA's 32 and meet in shared memory, group by group, so that no thread idles.
+  __shared__ float red_w[2048], red_b[2048];
   const int r0 = blockIdx.x * 32, r1 = min(rows, r0 + 32);
-  for (int c8 = threadIdx.x * 8; c8 < cols; c8 += blockDim.x * 8) {
+  const int vpr = cols / 8;
+  const int groups = vpr < 256 ? 256 / vpr : 1;
+  const int g = groups > 1 ? threadIdx.x / vpr : 0;
+  const int first = groups > 1 ? (threadIdx.x % vpr) * 8 : threadIdx.x * 8;
+  const int stride = groups > 1 ? cols : 256 * 8;            // grouped threads own exactly one vector
+  if (g >= groups) {                                         // leftover threads (256 not a multiple of vpr)
+    for (int k = 1; k < groups; ++k) { __syncthreads(); __syncthreads(); }
+    return;
+  }
+  for (int c8 = first; c8 < cols; c8 += stride) {
     float aw[8] = {0, 0, 0, 0, 0, 0, 0, 0}, ab[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll 4
-    for (int r = r0; r < r1; ++r) {
+    for (int r = r0 + g; r < r1; r += groups) {
       float d[8], x[8];
       Vec8<T>::load(dy + (size_t)r * cols + c8, d);
       Vec8<T>::load(h + (size_t)r * cols + c8, x);
@@ -447,8 +459,22 @@ norm_dwdb_partial_kernel(const T* __restrict__ dy, const T* __restrict__ h, cons
 #pragma unroll
       for (int i = 0; i < 8; ++i) { aw[i] += d[i] * (x[i] - mu) * rs; ab[i] += d[i]; }
     }
-    Vec8<float>::store(part_dw + (size_t)blockIdx.x * cols + c8, aw);
-    if (kLayer && part_db) Vec8<float>::store(part_db + (size_t)blockIdx.x * cols + c8, ab);
+    for (int k = 1; k < groups; ++k) {                       // fold group k into group 0, in group order
+      if (g == k) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { red_w[c8 + i] = aw[i]; red_b[c8 + i] = ab[i]; }
+      }
+      __syncthreads();
+      if (g == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { aw[i] += red_w[c8 + i]; ab[i] += red_b[c8 + i]; }
+      }
+      __syncthreads();
+    }
+    if (g == 0) {
+      Vec8<float>::store(part_dw + (size_t)blockIdx.x * cols + c8, aw);
+      if (kLayer && part_db) Vec8<float>::store(part_db + (size_t)blockIdx.x * cols + c8, ab);
+    }
   }
 }
 
@@ -478,17 +504,39 @@ colreduce_kernel(const float* __restrict__ part, T* __restrict__ out, int nparts
 #define COLSUM_ROWS 32
 template <typename T>
 __global__ void __launch_bounds__(256) colsum_partial_kernel(const T* __restrict__ a, float* __restrict__ part, int rows, int cols) {
+  __shared__ float red[2048];                                // see norm_dwdb_partial_kernel: row groups for narrow matrices
   const int r0 = blockIdx.x * COLSUM_ROWS, r1 = min(rows, r0 + COLSUM_ROWS);
-  for (int c8 = threadIdx.x * 8; c8 < cols; c8 += blockDim.x * 8) {
+  const int vpr = cols / 8;
+  const int groups = vpr < 256 ? 256 / vpr : 1;
+  const int g = groups > 1 ? threadIdx.x / vpr : 0;
+  const int first = groups > 1 ? (threadIdx.x % vpr) * 8 : threadIdx.x * 8;
+  const int stride = groups > 1 ? cols : 256 * 8;
+  if (g >= groups) {
+    for (int k = 1; k < groups; ++k) { __syncthreads(); __syncthreads(); }
+    return;
+  }
+  for (int c8 = first; c8 < cols; c8 += stride) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll 8
-    for (int r = r0; r < r1; ++r) {
+    for (int r = r0 + g; r < r1; r += groups) {
       float v[8];
       Vec8<T>::load(a + (size_t)r * cols + c8, v);
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] += v[i];
     }
-    Vec8<float>::store(part + (size_t)blockIdx.x * cols + c8, acc);
+    for (int k = 1; k < groups; ++k) {
+      if (g == k) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) red[c8 + i] = acc[i];
+      }
+      __syncthreads();
+      if (g == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += red[c8 + i];
+      }
+      __syncthreads();
+    }
+    if (g == 0) Vec8<float>::store(part + (size_t)blockIdx.x * cols + c8, acc);
   }
 }
 

@@ -31,7 +31,7 @@ def use_pair_kernel(M: int, N: int, K: int) -> bool:
     eff = tiles / (waves * 74.0)
     pad = (N / (((N + 255) // 256) * 256.0)) * (M / (((M + 255) // 256) * 256.0))
     score = eff * pad
-    return score >= 0.8 or (score >= 0.6 and K >= 1024)
+    return score >= 0.6
 
 
 _SPLITK = os.environ.get("ZEN_GEMM_SPLITK", "auto")       # auto | 0
