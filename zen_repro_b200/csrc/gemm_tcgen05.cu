@@ -183,6 +183,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -314,13 +327,24 @@ __device__ __forceinline__ bool finish_tile(const GemmParams& p, int tile, uint3
   return true;
 }
 
+// Column slices per 128-row chunk of the all-gather push: as many as the grid can work on at once (same value on
+// every rank: same shapes, same grid), within the flag capacity.
+__device__ __forceinline__ int ag_slices(int grid, int nchunks, uint32_t max_tiles) {
+  int n = grid / nchunks;
+  if (n < 1) n = 1;
+  if (n > 16) n = 16;
+  while (n > 1 && (uint32_t)(nchunks * n) > max_tiles) --n;
+  return n;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int XCHG_BYTES = 4 * 4096;          // per epilogue warp a [32 rows][64 bf16] staging box (peer pushes)
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + XCHG_BYTES;
   static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) |
                                     ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 };
@@ -373,12 +397,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if (tc.owner != p.rank) {
             // rows of a peer: its epilogue warps push them into this rank's gather region; wait for the chunk
             amap = &tma_g;
-            const uint32_t* f = p.my_flags + (size_t)(p.epoch & 1u) * p.npeers * p.max_tiles + tc.mloc / BM;
+            const int nslices = ag_slices(gridDim.x, p.rows_per_rank / BM, p.max_tiles);
+            const uint32_t* f = p.my_flags + (size_t)(p.epoch & 1u) * p.npeers * p.max_tiles + (tc.mloc / BM) * nslices;
             const uint64_t t0 = gtimer();
-            bool got = ld_acquire_sys_u32(f) == p.epoch;
-            while (!got) {
-              for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f) == p.epoch;
-              if (!got && (gtimer() - t0 > p.wait_ns || *abort_flag)) break;
+            bool got = true;
+            for (int sl = 0; sl < nslices && got; ++sl) {               // every column slice of the chunk
+              got = ld_acquire_sys_u32(f + sl) == p.epoch;
+              while (!got) {
+                for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f + sl) == p.epoch;
+                if (!got && (gtimer() - t0 > p.wait_ns || *abort_flag)) break;
+              }
             }
             if (!got) { atomicOr(p.status, 4u); *abort_flag = 6; atomicCAS(&g_gemm_error, 0, 6); ok = false; break; }
             asm volatile("fence.proxy.async;" ::: "memory");      // the peer's stores, then this rank's TMA reads
@@ -449,19 +477,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       // (local rows) are in their main loops.  The gathered copy is dense [rows_per_rank, K].
       const int et = threadIdx.x - 64;
       const int nchunks = p.rows_per_rank / BM, vec_per_row = p.K / 8;
-      for (int c = blockIdx.x; c < nchunks; c += gridDim.x) {
+      const int nslices = ag_slices(gridDim.x, nchunks, p.max_tiles);
+      const int vps = (vec_per_row + nslices - 1) / nslices;          // 16-byte vectors per row and slice
+      // work item = (128-row chunk, column slice); every CTA takes the items b, b + grid, ...
+      for (int item = blockIdx.x; item < nchunks * nslices; item += gridDim.x) {
+        const int c = item % nchunks, sl = item / nchunks;
+        const int v0 = sl * vps, v1 = min(vec_per_row, v0 + vps), w = v1 - v0;
         for (int pe = 0; pe < p.npeers; ++pe) {
           __nv_bfloat16* dst = p.peer_recv[pe] + ((size_t)par * p.npeers + p.peer_slot_of_me[pe]) * p.slot_elems + (size_t)c * BM * p.K;
           const __nv_bfloat16* src = p.a_local + (size_t)c * BM * p.lda_local;
-          for (int v = et; v < BM * vec_per_row; v += 128) {
-            const int r = v / vec_per_row, cv = v % vec_per_row;
-            *reinterpret_cast<uint4*>(dst + (size_t)r * p.K + cv * 8) = *reinterpret_cast<const uint4*>(src + (size_t)r * p.lda_local + cv * 8);
+          for (int v = et; v < BM * w; v += 4 * 128) {
+            uint4 x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int vv = v + u * 128;
+              if (vv < BM * w) x[u] = *reinterpret_cast<const uint4*>(src + (size_t)(vv / w) * p.lda_local + (v0 + vv % w) * 8);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int vv = v + u * 128;
+              if (vv < BM * w) *reinterpret_cast<uint4*>(dst + (size_t)(vv / w) * p.K + (v0 + vv % w) * 8) = x[u];
+            }
           }
         }
         __threadfence_system();
         epilogue_barrier();
         if (et < p.npeers)
-          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + c, p.epoch);
+          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + c * nslices + sl, p.epoch);
       }
     }
     // Deferred reduction (bf16 output, no accumulation): a tile's epilogue pushes the partial to the peers, stores
@@ -483,8 +525,54 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       if (p.npeers > 0 && !ag) {
         // ---- step 1: push this rank's partial tile (bf16) into the exchange region of every peer (all-reduce) or of
         // the rank that owns these rows (reduce-scatter; nothing to push for own rows)
+        // Whole-line version (deferred mode, 16-byte-aligned rows, N a multiple of 8): a thread's 64 columns go
+        // through a swizzled [32][64] box in shared memory and come back transposed, so that every store instruction
+        // of the warp writes four complete 128-byte lines instead of 32 pieces of 16 bytes in 32 different rows,
+        // which is what NVLink packets and the L2 want.
+        const bool staged = deferred && (p.ldc % 8) == 0 && (p.N % 8) == 0;
+        if (staged) {
+          unsigned char* stg = smem + C::STAGES * C::STAGE_BYTES + 256 + grp * 4096;
+          const bool keep = !rs || mine;
+          __nv_bfloat16* Cb = reinterpret_cast<__nv_bfloat16*>(p.C);
 #pragma unroll 1
-        for (int ch = 0; ch < ((rs && mine && !deferred) ? 0 : BN / 32); ++ch) {
+          for (int cb = 0; cb < BN / 64; ++cb) {
+            uint32_t ra[32], rb[32];
+            tmem_ld32_nowait(taddr0 + cb * 64, ra);
+            tmem_ld32_nowait(taddr0 + cb * 64 + 32, rb);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t o[4], o2[4];
+#pragma unroll
+              for (int k2 = 0; k2 < 4; ++k2) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(ra[8 * q + 2 * k2]), __uint_as_float(ra[8 * q + 2 * k2 + 1]));
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(rb[8 * q + 2 * k2]), __uint_as_float(rb[8 * q + 2 * k2 + 1]));
+                o[k2] = *reinterpret_cast<uint32_t*>(&h);
+                o2[k2] = *reinterpret_cast<uint32_t*>(&h2);
+              }
+              *reinterpret_cast<uint4*>(stg + lane * 128 + ((q ^ (lane & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<uint4*>(stg + lane * 128 + (((4 + q) ^ (lane & 7)) << 4)) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = it * 4 + (lane >> 3), c = lane & 7;
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + r * 128 + ((c ^ (r & 7)) << 4));
+              const int grow = m0 + grp * 32 + r, col = n0 + cb * 64 + c * 8;
+              if (grow < p.M && col < p.N) {
+                const size_t xr = (size_t)((rs ? tc.mloc : m0) + grp * 32 + r);
+                if (keep) *reinterpret_cast<uint4*>(Cb + xr * p.ldc + col) = v;
+                for (int pe = 0; pe < p.npeers; ++pe) {
+                  if (rs && p.peer_rank[pe] != tc.owner) continue;
+                  *reinterpret_cast<uint4*>(p.peer_recv[pe] + ((size_t)par * p.npeers + p.peer_slot_of_me[pe]) * p.slot_elems + xr * p.recv_ld + col) = v;
+                }
+              }
+            }
+            __syncwarp();
+          }
+        }
+#pragma unroll 1
+        for (int ch = 0; ch < ((staged || (rs && mine && !deferred)) ? 0 : BN / 32); ++ch) {
           uint32_t r[32];
           tmem_ld32(taddr0 + ch * 32, r);
           const int col0 = n0 + ch * 32;
