@@ -440,7 +440,7 @@ norm_dwdb_partial_kernel(const T* __restrict__ dy, const T* __restrict__ h, cons
   __shared__ float red_w[2048], red_b[2048];
   const int r0 = blockIdx.x * 32, r1 = min(rows, r0 + 32);
   const int vpr = cols / 8;
-  const int groups = vpr < 256 ? 256 / vpr : 1;
+  const int groups = vpr <= 128 ? 256 / vpr : 1;
   const int g = groups > 1 ? threadIdx.x / vpr : 0;
   const int first = groups > 1 ? (threadIdx.x % vpr) * 8 : threadIdx.x * 8;
   const int stride = groups > 1 ? cols : 256 * 8;            // grouped threads own exactly one vector
@@ -507,10 +507,24 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const T* __restrict
   __shared__ float red[2048];                                // see norm_dwdb_partial_kernel: row groups for narrow matrices
   const int r0 = blockIdx.x * COLSUM_ROWS, r1 = min(rows, r0 + COLSUM_ROWS);
   const int vpr = cols / 8;
-  const int groups = vpr < 256 ? 256 / vpr : 1;
-  const int g = groups > 1 ? threadIdx.x / vpr : 0;
-  const int first = groups > 1 ? (threadIdx.x % vpr) * 8 : threadIdx.x * 8;
-  const int stride = groups > 1 ? cols : 256 * 8;
+  const int groups = vpr <= 128 ? 256 / vpr : 1;
+  if (groups == 1) {                                          // wide matrix: every thread has columns of its own
+    for (int c8 = threadIdx.x * 8; c8 < cols; c8 += blockDim.x * 8) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 8
+      for (int r = r0; r < r1; ++r) {
+        float v[8];
+        Vec8<T>::load(a + (size_t)r * cols + c8, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[i];
+      }
+      Vec8<float>::store(part + (size_t)blockIdx.x * cols + c8, acc);
+    }
+    return;
+  }
+  const int g = threadIdx.x / vpr;
+  const int first = (threadIdx.x % vpr) * 8;
+  const int stride = cols;
   if (g >= groups) {
     for (int k = 1; k < groups; ++k) { __syncthreads(); __syncthreads(); }
     return;
