@@ -59,6 +59,33 @@ def test_backward(B, S, hq, hkv, hd):
         assert rel < 0.02, (name, float(rel))
 
 
+@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("B,S,hq,hkv", [(1, 256, 2, 2), (2, 1024, 4, 4), (1, 512, 4, 2)])
+def test_backward_hd64_both_kernel_families(variant, B, S, hq, hkv):
+    """head_dim 64 has two backward implementations (128 x 128 tiles, one CTA per SM; 64-row streamed tiles, two CTAs per
+    SM with dK and dV from one pass): both must agree with autograd."""
+    from zen_repro_b200 import _native
+
+    hd = 64
+    old = _native.lib().zen_attn_bwd64_variant(variant)
+    try:
+        torch.manual_seed(3)
+        qkv = (torch.randn(B * S, (hq + 2 * hkv) * hd, device="cuda") * 0.7).bfloat16()
+        dout = (torch.randn(B * S, hq * hd, device="cuda") * 0.5).bfloat16()
+        scale = 1.0 / math.sqrt(hd)
+        out, lse2 = A.attention_fwd_kernel(qkv, B, S, hq, hkv, hd, scale)
+        dqkv = A.attention_bwd_kernel(dout, qkv, out, lse2, B, S, hq, hkv, hd, scale)
+        torch.cuda.synchronize()
+        assert A.attention_error() == 0
+        x = qkv.float().requires_grad_(True)
+        want, _ = _ref(x, B, S, hq, hkv, hd, scale)
+        (g,) = torch.autograd.grad(want, x, dout.float())
+        rel = (dqkv.float() - g).norm() / g.norm()
+        assert rel < 0.02, float(rel)
+    finally:
+        _native.lib().zen_attn_bwd64_variant(old)
+
+
 def test_autograd_path_uses_the_kernels():
     from zen_repro_b200.ops import autograd as O
 

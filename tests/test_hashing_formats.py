@@ -70,3 +70,29 @@ def test_coo_and_format_choice():
     assert formats.choose_index_format(10, 100000) == "coo"
     assert formats.choose_index_format(5000, 100000) == "bitmap"
     assert formats.choose_index_format(60000, 100000) == "dense"
+
+
+def test_murmur3_known_vectors_and_split_k_choice():
+    from zen_repro_b200.sparse.hashing import fmix32, murmur3_32
+
+    # published verification values of MurmurHash3_x86_32 for 4-byte keys
+    keys = torch.tensor([0x00000000, 0xFFFFFFFF, 0x87654321], dtype=torch.int64)
+    got = murmur3_32(keys, 0).tolist()
+    assert got == [0x2362F9DE, 0x76293B50, 0xF55B516B], [hex(v) for v in got]
+    assert int(murmur3_32(torch.tensor([0x87654321]), 0x5082EDEE)) == 0x2362F9DE
+    assert int(fmix32(torch.tensor([0]))) == 0
+    # spreads consecutive indices over 8 owners within a few percent
+    own = murmur3_32(torch.arange(1 << 16), 0) % 8
+    cnt = torch.bincount(own, minlength=8).float()
+    assert float(cnt.max() / cnt.mean()) < 1.05
+
+
+def test_split_k_choice_is_limited_to_weight_gradient_shapes():
+    from zen_repro_b200.ops import gemm as G
+
+    assert G.split_k_choice(768, 2304, 8192) == 2          # 27 tiles, long K
+    assert G.split_k_choice(768, 768, 8192) == 2
+    assert G.split_k_choice(8192, 2304, 768) == 1          # plenty of tiles
+    assert G.split_k_choice(768, 2304, 1024) == 1          # short K
+    assert G.split_k_choice(4096, 4096, 8192) == 1
+    assert G.split_k_choice(100, 2304, 8192) == 1          # too narrow for a 256-row pair tile

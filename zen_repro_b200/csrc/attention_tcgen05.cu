@@ -979,6 +979,262 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
   }
 }
 
+// ---- head_dim 64 backward, same resident / streamed scheme as the hd = 256 kernel but small enough for TWO CTAs per
+// SM (96 KB of shared memory, 256 tensor-memory columns each), so that one CTA's softmax pass overlaps the other's MMAs
+// and prologue, with a two-stage ring for the streamed tiles.  Modes: RS_DQ (resident Q, dO; streamed K, V; dQ += dS K)
+// and RS_DKV (resident K, V; streamed Q, dO; dK += dS^T Q and dV += P^T dO from one pass over the scores:
+// S' 64 + dP' 64 + dK 64 + dV 64 columns).
+enum { RS_DQ = 0, RS_DKV = 1 };
+
+struct Rs64Cfg {
+  static constexpr int HD = 64;
+  static constexpr int STAGES = 2;
+  static constexpr int RES_BYTES = 128 * HD * 2;        // one [128][64] atom
+  static constexpr int STR_BYTES = 64 * HD * 2;         // one [64][64] atom
+  static constexpr int W_BYTES = 128 * 64 * 2;
+  static constexpr int SMEM_BYTES = 2 * RES_BYTES + STAGES * 2 * STR_BYTES + 2 * W_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = 256;
+  static constexpr uint32_t IDESC_S = make_idesc(128, 64, false, false);
+  static constexpr uint32_t IDESC_ACC = make_idesc(128, 64, false, true);
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(320, 2)
+attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_constant__ CUtensorMap tmap_do128,
+                  const __grid_constant__ CUtensorMap tmap_qkv64, const __grid_constant__ CUtensorMap tmap_do64,
+                  const __grid_constant__ CUtensorMap tmap_o128, const AttnBwdParams p) {
+  using C = Rs64Cfg;
+  constexpr int HD = C::HD;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* r1_s = smem;
+  unsigned char* r2_s = r1_s + C::RES_BYTES;
+  unsigned char* t_s = r2_s + C::RES_BYTES;                       // [stage][T1 | T2]
+  unsigned char* w1_s = t_s + C::STAGES * 2 * C::STR_BYTES;       // dS (dQ mode) or dS^T
+  unsigned char* w2_s = w1_s + C::W_BYTES;                        // P^T (dK/dV mode)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(w2_s + C::W_BYTES);
+  uint64_t* r_full = bars;
+  uint64_t* t_full = bars + 1;                                    // [2]
+  uint64_t* t_empty = bars + 3;                                   // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* w_ready = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z;
+  const int rep = p.Hq / p.Hkv;
+  const int ri = (MODE == RS_DQ) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int hres = blockIdx.y;
+  const int g = (MODE == RS_DQ) ? hres / rep : hres;
+  const int nq64 = p.S / 64;
+  const int per_head = (MODE == RS_DQ) ? 2 * ri + 2 : nq64 - 2 * ri;
+  const int niter = (MODE == RS_DQ) ? per_head : rep * per_head;
+  const int rrow0 = b * p.S + ri * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(r_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 1); }
+    mbar_init(sdp_full, 1);
+    mbar_init(w_ready, 8);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 9) tmem_alloc(tmem_slot, C::TMEM_COLS);
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tDP = tmem_base + 64, tA1 = tmem_base + 128, tA2 = tmem_base + 192;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      mbar_expect_tx(r_full, (MODE == RS_DQ ? 3 : 2) * C::RES_BYTES);
+      if (MODE == RS_DQ) {
+        tma_load_2d(r1_s, &tmap_qkv128, r_full, hres * HD, rrow0);
+        tma_load_2d(r2_s, &tmap_do128, r_full, hres * HD, rrow0);
+        tma_load_2d(w2_s, &tmap_o128, r_full, hres * HD, rrow0);     // O tile: D = rowsum(dO * O) is computed here
+      } else {
+        tma_load_2d(r1_s, &tmap_qkv128, r_full, (p.Hq + g) * HD, rrow0);
+        tma_load_2d(r2_s, &tmap_qkv128, r_full, (p.Hq + p.Hkv + g) * HD, rrow0);
+      }
+      for (int it = 0; it < niter; ++it) {
+        const int st = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1;
+        if (!mbar_wait(&t_empty[st], ph ^ 1, abort_flag, 41, &g_attn_error)) break;
+        unsigned char* t1 = t_s + st * 2 * C::STR_BYTES;
+        unsigned char* t2 = t1 + C::STR_BYTES;
+        mbar_expect_tx(&t_full[st], 2 * C::STR_BYTES);
+        if (MODE == RS_DQ) {
+          const int krow = b * p.S + it * 64;
+          tma_load_2d(t1, &tmap_qkv64, &t_full[st], (p.Hq + g) * HD, krow);
+          tma_load_2d(t2, &tmap_qkv64, &t_full[st], (p.Hq + p.Hkv + g) * HD, krow);
+        } else {
+          const int h = g * rep + it / per_head, t = 2 * ri + it % per_head;
+          const int qrow = b * p.S + t * 64;
+          tma_load_2d(t1, &tmap_qkv64, &t_full[st], h * HD, qrow);
+          tma_load_2d(t2, &tmap_do64, &t_full[st], h * HD, qrow);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      bool ok = mbar_wait(r_full, 0, abort_flag, 42, &g_attn_error);
+      const uint32_t r1a = smem_u32(r1_s), r2a = smem_u32(r2_s), w1a = smem_u32(w1_s), w2a = smem_u32(w2_s);
+      for (int it = 0; it < niter && ok; ++it) {
+        const int st = it % C::STAGES;
+        const uint32_t ph = (it / C::STAGES) & 1;
+        if (!mbar_wait(&t_full[st], ph, abort_flag, 43, &g_attn_error)) { ok = false; break; }
+        fence_after();
+        const uint32_t t1a = smem_u32(t_s + st * 2 * C::STR_BYTES), t2a = t1a + C::STR_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_bf16(tS, make_desc(r1a + kk * 32, 16, 1024), make_desc(t1a + kk * 32, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_bf16(tDP, make_desc(r2a + kk * 32, 16, 1024), make_desc(t2a + kk * 32, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
+        umma_commit(sdp_full);
+        if (!mbar_wait(w_ready, it & 1, abort_flag, 44, &g_attn_error)) { ok = false; break; }
+        fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)           // dQ += dS K   or   dK += dS^T Q   (streamed tile 1 as MN-major B)
+          umma_bf16(tA1, make_desc(w1a + kk * 32, 16, 1024), make_desc(t1a + kk * 2048, 8192, 1024), C::IDESC_ACC,
+                    (it > 0 || kk > 0) ? 1u : 0u);
+        if (MODE == RS_DKV) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)         // dV += P^T dO
+            umma_bf16(tA2, make_desc(w2a + kk * 32, 16, 1024), make_desc(t2a + kk * 2048, 8192, 1024), C::IDESC_ACC,
+                      (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(acc_done);
+        umma_commit(&t_empty[st]);
+      }
+    }
+  } else {
+    const int row = (warp & 3) * 32 + lane;
+    const int hf = warp >> 2;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    const float cs = p.scale_log2;
+    float nl_row = 0.f, d_row = 0.f;
+    bool ok = true;
+    if (MODE == RS_DQ) {
+      const size_t vec = ((size_t)b * p.Hq + hres) * p.S + ri * 128 + row;
+      nl_row = -p.lse2[vec];
+      // D of this query row from the dO and O tiles in shared memory (both warps of the lane group compute it, one
+      // stores it for the dK / dV kernel that runs after this one)
+      ok = mbar_wait(r_full, 0, abort_flag, 48, &g_attn_error);
+      if (ok) {
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+          const uint4 x = *reinterpret_cast<const uint4*>(r2_s + swz128(row, c8 * 8));
+          const uint4 y = *reinterpret_cast<const uint4*>(w2_s + swz128(row, c8 * 8));
+          const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            d_row += __uint_as_float(xw[i] << 16) * __uint_as_float(yw[i] << 16);
+            d_row += __uint_as_float(xw[i] & 0xffff0000u) * __uint_as_float(yw[i] & 0xffff0000u);
+          }
+        }
+        if (hf == 0) const_cast<float*>(p.D)[vec] = d_row;
+      }
+    }
+    for (int it = 0; it < niter && ok; ++it) {
+      const int h = (MODE == RS_DQ) ? hres : g * rep + it / per_head;
+      const int t = (MODE == RS_DQ) ? it : 2 * ri + it % per_head;
+      if (!mbar_wait(sdp_full, it & 1, abort_flag, 45, &g_attn_error)) { ok = false; break; }
+      if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, abort_flag, 46, &g_attn_error)) { ok = false; break; }
+      fence_after();
+      uint32_t sa[32], da[32];
+      tmem_ld32_nowait(tS + lane_addr + hf * 32, sa);
+      tmem_ld32_nowait(tDP + lane_addr + hf * 32, da);
+      tmem_wait_ld();
+      const int res_idx = ri * 128 + row, str0 = t * 64 + hf * 32;
+      const bool need_mask = (MODE == RS_DQ) ? (str0 + 31 > ri * 128) : (str0 < ri * 128 + 128);
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const bool dead = (MODE == RS_DQ) ? (str0 + i > res_idx) : (res_idx > str0 + i);
+          if (dead) sa[i] = 0xff800000u;
+        }
+      }
+      const float* lse_c = p.lse2 + ((size_t)b * p.Hq + h) * p.S + str0;
+      const float* d_c = p.D + ((size_t)b * p.Hq + h) * p.S + str0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t pk[4], dk[4];
+        float lv[8], dv[8];
+        if (MODE != RS_DQ) {              // statistics of the 8 streamed queries of this vector (same for every thread)
+          const float4 l0 = __ldg(reinterpret_cast<const float4*>(lse_c + 8 * q)), l1 = __ldg(reinterpret_cast<const float4*>(lse_c + 8 * q + 4));
+          const float4 e0 = __ldg(reinterpret_cast<const float4*>(d_c + 8 * q)), e1 = __ldg(reinterpret_cast<const float4*>(d_c + 8 * q + 4));
+          lv[0] = l0.x; lv[1] = l0.y; lv[2] = l0.z; lv[3] = l0.w; lv[4] = l1.x; lv[5] = l1.y; lv[6] = l1.z; lv[7] = l1.w;
+          dv[0] = e0.x; dv[1] = e0.y; dv[2] = e0.z; dv[3] = e0.w; dv[4] = e1.x; dv[5] = e1.y; dv[6] = e1.z; dv[7] = e1.w;
+        }
+#pragma unroll
+        for (int k2 = 0; k2 < 4; ++k2) {
+          const int i = 8 * q + 2 * k2;
+          float p0, p1, w0, w1;
+          if (MODE == RS_DQ) {
+            p0 = ex2f(fmaf(__uint_as_float(sa[i]), cs, nl_row));
+            p1 = ex2f(fmaf(__uint_as_float(sa[i + 1]), cs, nl_row));
+            w0 = p0 * (__uint_as_float(da[i]) - d_row);
+            w1 = p1 * (__uint_as_float(da[i + 1]) - d_row);
+          } else {
+            p0 = ex2f(fmaf(__uint_as_float(sa[i]), cs, -lv[2 * k2]));
+            p1 = ex2f(fmaf(__uint_as_float(sa[i + 1]), cs, -lv[2 * k2 + 1]));
+            w0 = p0 * (__uint_as_float(da[i]) - dv[2 * k2]);
+            w1 = p1 * (__uint_as_float(da[i + 1]) - dv[2 * k2 + 1]);
+          }
+          dk[k2] = pack_bf16(w0, w1);
+          pk[k2] = pack_bf16(p0, p1);
+        }
+        const uint32_t off = swz128(row, hf * 32 + q * 8);
+        *reinterpret_cast<uint4*>(w1_s + off) = make_uint4(dk[0], dk[1], dk[2], dk[3]);
+        if (MODE == RS_DKV) *reinterpret_cast<uint4*>(w2_s + off) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      fence_before();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(w_ready);
+    }
+    if (ok && mbar_wait(acc_done, (niter - 1) & 1, abort_flag, 47, &g_attn_error)) {
+      fence_after();
+      // 64 accumulator columns = two chunks of 32: the two warps of a lane group take one chunk each
+      uint32_t r[32], r2[32];
+      tmem_ld32_nowait(tA1 + lane_addr + hf * 32, r);
+      if (MODE == RS_DKV) tmem_ld32_nowait(tA2 + lane_addr + hf * 32, r2);
+      tmem_wait_ld();
+      const int col1 = (MODE == RS_DQ) ? hres * HD : (p.Hq + g) * HD;
+      __nv_bfloat16* o1 = p.dqkv + (size_t)(rrow0 + row) * p.ld_dqkv + col1 + hf * 32;
+      __nv_bfloat16* o2 = p.dqkv + (size_t)(rrow0 + row) * p.ld_dqkv + (p.Hq + p.Hkv + g) * HD + hf * 32;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t a[4], c[4];
+#pragma unroll
+        for (int k2 = 0; k2 < 4; ++k2) {
+          a[k2] = pack_bf16(__uint_as_float(r[8 * q + 2 * k2]) * p.scale, __uint_as_float(r[8 * q + 2 * k2 + 1]) * p.scale);
+          if (MODE == RS_DKV) c[k2] = pack_bf16(__uint_as_float(r2[8 * q + 2 * k2]), __uint_as_float(r2[8 * q + 2 * k2 + 1]));
+        }
+        *reinterpret_cast<uint4*>(o1 + q * 8) = make_uint4(a[0], a[1], a[2], a[3]);
+        if (MODE == RS_DKV) *reinterpret_cast<uint4*>(o2 + q * 8) = make_uint4(c[0], c[1], c[2], c[3]);
+      }
+    }
+  }
+
+  fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = gtimer();
+    while (gtimer() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 9) {
+    fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // dK and dV of the head-split hd = 256 backward: sum the hsplit fp32 partials in order, write bf16 into dqkv.
 __global__ void __launch_bounds__(256)
 attn_bwd256_reduce_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dqkv, int rows, int Hq, int Hkv,
@@ -1049,7 +1305,17 @@ int launch_fwd(const CUtensorMap& tm, const AttnParams& p, cudaStream_t st) {
 
 }  // namespace
 
+int g_bwd64_variant = 1;       // 0: the 128 x 128 tile kernels; 1: two-CTAs-per-SM kernels with 64-row streamed tiles;
+                               // 2: that dQ kernel with the 128 x 128 tile dK/dV kernel
+
 extern "C" {
+
+// Which head_dim 64 backward runs (see g_bwd64_variant); returns the previous choice.
+int zen_attn_bwd64_variant(int v) {
+  const int old = g_bwd64_variant;
+  if (v >= 0 && v <= 2) g_bwd64_variant = v;
+  return old;
+}
 
 // Causal attention forward.  qkv: bf16 [B*S, (Hq + 2*Hkv) * hd] with row stride ld_qkv (elements, multiple of 8,
 // base 16-byte aligned); out: bf16 [B*S, Hq*hd] (row stride ld_out); lse2: fp32 [B, Hq, S].
@@ -1084,7 +1350,7 @@ int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float
   if (rc) return rc;
   rc = attn_make_map(dout, (uint64_t)Hq * hd, (uint64_t)B * S, (uint64_t)ld_o, &tdo);
   if (rc) return rc;
-  {
+  if (!(hd == 64 && g_bwd64_variant >= 1)) {       // the hd 64 dQ kernel of variants 1 and 2 computes D itself
     const long warps = (long)B * S * Hq;
     long blocks = (warps + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
@@ -1094,6 +1360,35 @@ int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float
   if ((Hq / Hkv) % hsplit) return -2;
   AttnBwdParams p{(__nv_bfloat16*)dqkv, lse2, Dbuf, B, S, Hq, Hkv, ld_qkv, scale * 1.4426950408889634f, scale, part, hsplit};
   dim3 gq(S / 128, Hq, B), gk(S / 128, Hkv, B);
+  if (hd == 64 && g_bwd64_variant >= 1) {
+    CUtensorMap tq64, tdo64, to128;
+    rc = attn_make_map(out, (uint64_t)Hq * hd, (uint64_t)B * S, (uint64_t)ld_o, &to128);
+    if (rc) return rc;
+    rc = attn_make_map(qkv, (uint64_t)(Hq + 2 * Hkv) * hd, (uint64_t)B * S, (uint64_t)ld_qkv, &tq64, 64);
+    if (rc) return rc;
+    rc = attn_make_map(dout, (uint64_t)Hq * hd, (uint64_t)B * S, (uint64_t)ld_o, &tdo64, 64);
+    if (rc) return rc;
+    static bool attr64 = false;
+    if (!attr64) {
+      cudaError_t e = cudaFuncSetAttribute(attn_bwd64_kernel<RS_DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, Rs64Cfg::SMEM_BYTES);
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd64_kernel<RS_DKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, Rs64Cfg::SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      attr64 = true;
+    }
+    attn_bwd64_kernel<RS_DQ><<<gq, 320, Rs64Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, to128, p);
+    if (g_bwd64_variant == 1) {
+      attn_bwd64_kernel<RS_DKV><<<gk, 320, Rs64Cfg::SMEM_BYTES, st>>>(tq, tdo, tq64, tdo64, to128, p);
+    } else {
+      static bool attr_old = false;
+      if (!attr_old) {
+        cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkv_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<64>::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        attr_old = true;
+      }
+      attn_bwd_dkv_kernel<64><<<gk, 320, DkvCfg<64>::SMEM_BYTES, st>>>(tq, tdo, p);
+    }
+    return (int)cudaGetLastError();
+  }
   if (hd == 256) {
     CUtensorMap tq64, tdo64;
     rc = attn_make_map(qkv, (uint64_t)(Hq + 2 * Hkv) * hd, (uint64_t)B * S, (uint64_t)ld_qkv, &tq64, 64);

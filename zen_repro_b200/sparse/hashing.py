@@ -124,6 +124,38 @@ def zen_poly3(idx: torch.Tensor, seed: int) -> torch.Tensor:
     return h & m
 
 
+def _rotl32(x: torch.Tensor, r: int) -> torch.Tensor:
+    m = 0xFFFFFFFF
+    return ((x << r) | (x >> (32 - r))) & m
+
+
+def fmix32(h: torch.Tensor) -> torch.Tensor:
+    """Finaliser of MurmurHash3 (functions_cuda_kernel.cu:27-36 in the reference, unused there)."""
+    m = 0xFFFFFFFF
+    h = h & m
+    h = h ^ (h >> 16)
+    h = (h * 0x85EBCA6B) & m
+    h = h ^ (h >> 13)
+    h = (h * 0xC2B2AE35) & m
+    return h ^ (h >> 16)
+
+
+def murmur3_32(idx: torch.Tensor, seed: int = 0) -> torch.Tensor:
+    """MurmurHash3_x86_32 of each index taken as one little-endian 4-byte key (int64 tensor out, values < 2^32).
+    The reference carries this hash as dead code next to the polynomial it actually uses
+    (functions_cuda_kernel.cu:12-77); here it is an alternative integer mixer for experiments with the balancer."""
+    m = 0xFFFFFFFF
+    k = idx.to(torch.int64) & m
+    k = (k * 0xCC9E2D51) & m
+    k = _rotl32(k, 15)
+    k = (k * 0x1B873593) & m
+    h = torch.full_like(k, seed & m) ^ k
+    h = _rotl32(h, 13)
+    h = (h * 5 + 0xE6546B64) & m
+    h = h ^ 4                                   # key length in bytes
+    return fmix32(h)
+
+
 def zen_poly3_owner(idx: torch.Tensor, table_size: int, parts: int) -> torch.Tensor:
     """Owner of ``idx`` under the reference balancer: first probe decides the partition."""
     per = table_size // parts
