@@ -1305,7 +1305,7 @@ int launch_fwd(const CUtensorMap& tm, const AttnParams& p, cudaStream_t st) {
 
 }  // namespace
 
-int g_bwd64_variant = 0;       // 0: the 128 x 128 tile kernels; 1: two-CTAs-per-SM kernels with 64-row streamed tiles;
+int g_bwd64_variant = 2;       // 0: the 128 x 128 tile kernels; 1: two-CTAs-per-SM kernels with 64-row streamed tiles;
                                // 2: that dQ kernel with the 128 x 128 tile dK/dV kernel
 
 extern "C" {
