@@ -124,3 +124,26 @@ def test_split_k_weight_gradient_shapes(M, N, K, monkeypatch):
     a = at.t().contiguous()
     _check(G.gemm_nt(a, b.t().contiguous()), want, K)
     assert G.gemm_error() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 128, 64), (8192, 768, 768), (1000, 1304, 200), (512, 50257, 128)])
+def test_pair_kernel_with_128_wide_tiles(M, N, K):
+    """The CTA-pair kernel with 256 x 128 tiles (chosen when 256-wide tiles fill the GPU unevenly), all layouts."""
+    from zen_repro_b200 import _native
+
+    old = _native.lib().zen_gemm2_force_bn(128)
+    try:
+        torch.manual_seed(7)
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(K, N, device="cuda").bfloat16()
+        at = torch.randn(K, M, device="cuda").bfloat16()
+        bias = torch.randn(N, device="cuda").bfloat16()
+        _check(G.gemm_nn(a, b, bias=bias, bn=512), a.float() @ b.float() + bias.float(), K)
+        _check(G.gemm_nt(a, b.t().contiguous(), bn=512), a.float() @ b.float(), K)
+        _check(G.gemm_tn(at, b, bn=512), at.float().t() @ b.float(), K)
+        acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
+        G.gemm_nn(a, b, out=acc, accumulate=True, bn=512)
+        _check(acc, a.float() @ b.float() + 1.0, K)
+        assert G.gemm_error() == 0
+    finally:
+        _native.lib().zen_gemm2_force_bn(old)

@@ -17,14 +17,17 @@ namespace {
 using namespace tc;
 
 constexpr int BM2 = 128;          // rows per CTA (256 per pair)
-constexpr int BN2 = 256;
-constexpr int BNH = 128;          // B rows held by each CTA
+// N extent of the pair tile: 256 (default) or 128 (for outputs whose 256-wide tiles quantise badly over the 74 CTA
+// pairs, e.g. 96 tiles = 1.3 waves); each CTA holds BN / 2 rows of the B tile.
 constexpr int BK2 = 64;
-constexpr int STAGES2 = 6;
+template <int BN> struct PairCfg {
+  static constexpr int BNH = BN / 2;
+  static constexpr int STAGES = (BN == 256) ? 6 : 8;
+  static constexpr int STAGE_BYTES = 128 * 64 * 2 + BNH * 64 * 2;      // A rows of this CTA + its half of B
+};
 constexpr int MAX_SPLITS = 3;      // K slices per output tile at most (the last slice to arrive holds the others' partials in registers)
-constexpr int STAGE_BYTES2 = BM2 * BK2 * 2 + BNH * BK2 * 2;     // 32 KB per CTA
 constexpr int EPI_STAGE_BYTES = 4 * 2 * 4096;   // per epilogue warp two [32 rows][64 bf16] boxes for the TMA store
-constexpr int SMEM_BYTES2 = STAGES2 * STAGE_BYTES2 + EPI_STAGE_BYTES + 1024 + 256;
+template <int BN> constexpr int pair_smem_bytes() { return PairCfg<BN>::STAGES * PairCfg<BN>::STAGE_BYTES + EPI_STAGE_BYTES + 1024 + 256; }
 
 __device__ int g_gemm2_error = 0;
 
@@ -96,10 +99,11 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int BN2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                       const __grid_constant__ CUtensorMap tma_c, const Gemm2Params p) {
+  constexpr int BNH = PairCfg<BN2>::BNH, STAGES2 = PairCfg<BN2>::STAGES, STAGE_BYTES2 = PairCfg<BN2>::STAGE_BYTES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* epi_stage = smem + STAGES2 * STAGE_BYTES2;              // 1024-byte aligned
@@ -258,7 +262,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           const int other = 1 - ks;
           float* wp = p.ws + ((size_t)(ks * num_tiles + tile) * 2 + cta) * (BM2 * BN2) + (size_t)(grp * 32 + lane) * 32;
 #pragma unroll 1
-          for (int ch = other * 4; ch < other * 4 + 4; ch += 2) {
+          for (int ch = other * (BN2 / 64); ch < (other + 1) * (BN2 / 64); ch += 2) {
             uint32_t r[32], r2[32];
             tmem_ld32_nowait(taddr0 + ch * 32, r);
             tmem_ld32_nowait(taddr0 + ch * 32 + 32, r2);
@@ -289,8 +293,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           if (!got) { ok = false; break; }
           __threadfence();
           peer = p.ws + ((size_t)(other * num_tiles + tile) * 2 + cta) * (BM2 * BN2) + (size_t)(grp * 32 + lane) * 32;
-          cb_lo = ks * 2;
-          cb_hi = ks * 2 + 2;
+          cb_lo = ks * (BN2 / 128);
+          cb_hi = cb_lo + BN2 / 128;
         }
 #pragma unroll 1
         for (int cb = cb_lo; cb < cb_hi; ++cb) {
@@ -466,11 +470,11 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   }
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int BN2>
 int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, Gemm2Params p, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES2);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes<BN2>());
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
@@ -479,11 +483,22 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
   const int tiles = p.num_m_pairs * p.num_n_tiles * p.splits;
   int clusters = zen_tmap::sm_count() / 2;
   if (tiles < clusters) clusters = tiles;
-  gemm_bf16_2cta_kernel<A_MN, B_MN><<<clusters * 2, 192, SMEM_BYTES2, st>>>(ta, tb, tc, p);
+  gemm_bf16_2cta_kernel<A_MN, B_MN, BN2><<<clusters * 2, 192, pair_smem_bytes<BN2>(), st>>>(ta, tb, tc, p);
   return (int)cudaGetLastError();
 }
 
 }  // namespace
+
+int g_force_bn = 0;
+
+// 256-wide pair tiles.  The 128-wide variant exists for outputs whose 256-wide tiles fill the 74 CTA pairs unevenly
+// (96 tiles = 1.3 waves), but measured on 8192 x 768 outputs it lost (662 vs 858 TFLOP/s at K = 3072, 410 vs 472 at
+// K = 768): with half the columns per tile the A rows are fetched twice as often and the kernel is bound by that
+// traffic, not by the idle third of the second wave.  It is therefore only taken when forced.
+int pick_pair_bn(int M, int N) {
+  (void)M; (void)N;
+  return g_force_bn ? g_force_bn : 256;
+}
 
 extern "C" {
 
@@ -513,9 +528,10 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
   if (splits > nkb) splits = nkb;
   int kb_per = (nkb + splits - 1) / splits;
   splits = (nkb + kb_per - 1) / kb_per;                     // no empty slice
+  const int bn = (splits > 1) ? 256 : pick_pair_bn(M, N);
   if (splits > 1) {
-    const uint64_t tiles = (uint64_t)((M + 255) / 256) * ((N + BN2 - 1) / BN2);
-    if (!ws || !counters || ws_floats < tiles * splits * 2 * BM2 * BN2 || (uint64_t)n_counters < tiles * 16) return -4;
+    const uint64_t tiles = (uint64_t)((M + 255) / 256) * ((N + 255) / 256);
+    if (!ws || !counters || ws_floats < tiles * splits * 2 * BM2 * 256 || (uint64_t)n_counters < tiles * 16) return -4;
     if (reinterpret_cast<uintptr_t>(ws) % 16) return -2;
   }
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -2;
@@ -524,7 +540,7 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
   if (!a_mn) rc = zen_tmap::get(A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 128, &ta);
   else rc = zen_tmap::get(A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, 64, &ta);
   if (rc) return rc;
-  if (!b_mn) rc = zen_tmap::get(B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, 128, &tb);
+  if (!b_mn) rc = zen_tmap::get(B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, (uint32_t)(bn / 2), &tb);
   else rc = zen_tmap::get(B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64, &tb);
   if (rc) return rc;
   // Plain bf16 output with a TMA-compatible layout: store through shared memory.  The stored width must be a
@@ -540,10 +556,23 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
   }
   Gemm2Params p{C, bias, M, N, K, ldc, out_fp32, accumulate, 0, 0, splits, kb_per, ws, counters, tma_store};
   cudaStream_t st = (cudaStream_t)stream;
-  if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, tc, p, st);
-  if (!a_mn && b_mn) return launch2<false, true>(ta, tb, tc, p, st);
-  if (a_mn && !b_mn) return launch2<true, false>(ta, tb, tc, p, st);
-  return launch2<true, true>(ta, tb, tc, p, st);
+#define LAUNCH2(BN_)                                                            \
+  do {                                                                          \
+    if (!a_mn && !b_mn) return launch2<false, false, BN_>(ta, tb, tc, p, st);   \
+    if (!a_mn && b_mn) return launch2<false, true, BN_>(ta, tb, tc, p, st);     \
+    if (a_mn && !b_mn) return launch2<true, false, BN_>(ta, tb, tc, p, st);     \
+    return launch2<true, true, BN_>(ta, tb, tc, p, st);                         \
+  } while (0)
+  if (bn == 128) LAUNCH2(128);
+  LAUNCH2(256);
+#undef LAUNCH2
+}
+
+// 0 = choose the N tile per call, 128 / 256 = force it (tests, measurements); returns the previous setting.
+int zen_gemm2_force_bn(int bn) {
+  const int old = g_force_bn;
+  if (bn == 0 || bn == 128 || bn == 256) g_force_bn = bn;
+  return old;
 }
 
 int zen_gemm2_error() {
