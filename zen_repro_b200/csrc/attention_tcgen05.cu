@@ -992,7 +992,7 @@ struct Rs64Cfg {
   static constexpr int RES_BYTES = 128 * HD * 2;        // one [128][64] atom
   static constexpr int STR_BYTES = 64 * HD * 2;         // one [64][64] atom
   static constexpr int W_BYTES = 128 * 64 * 2;
-  static constexpr int SMEM_BYTES = 2 * RES_BYTES + STAGES * 2 * STR_BYTES + 2 * W_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = 2 * RES_BYTES + STAGES * 2 * STR_BYTES + 2 * W_BYTES + STAGES * 512 + 1024 + 256;
   static constexpr int TMEM_COLS = 256;
   static constexpr uint32_t IDESC_S = make_idesc(128, 64, false, false);
   static constexpr uint32_t IDESC_ACC = make_idesc(128, 64, false, true);
@@ -1012,7 +1012,8 @@ attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_
   unsigned char* t_s = r2_s + C::RES_BYTES;                       // [stage][T1 | T2]
   unsigned char* w1_s = t_s + C::STAGES * 2 * C::STR_BYTES;       // dS (dQ mode) or dS^T
   unsigned char* w2_s = w1_s + C::W_BYTES;                        // P^T (dK/dV mode)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(w2_s + C::W_BYTES);
+  float* stats_s = reinterpret_cast<float*>(w2_s + C::W_BYTES);   // [stage][lse | D][64]: statistics of the streamed queries
+  uint64_t* bars = reinterpret_cast<uint64_t*>(w2_s + C::W_BYTES + C::STAGES * 512);
   uint64_t* r_full = bars;
   uint64_t* t_full = bars + 1;                                    // [2]
   uint64_t* t_empty = bars + 3;                                   // [2]
@@ -1066,7 +1067,7 @@ attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_
         if (!mbar_wait(&t_empty[st], ph ^ 1, abort_flag, 41, &g_attn_error)) break;
         unsigned char* t1 = t_s + st * 2 * C::STR_BYTES;
         unsigned char* t2 = t1 + C::STR_BYTES;
-        mbar_expect_tx(&t_full[st], 2 * C::STR_BYTES);
+        mbar_expect_tx(&t_full[st], 2 * C::STR_BYTES + (MODE == RS_DKV ? 512 : 0));
         if (MODE == RS_DQ) {
           const int krow = b * p.S + it * 64;
           tma_load_2d(t1, &tmap_qkv64, &t_full[st], (p.Hq + g) * HD, krow);
@@ -1076,6 +1077,10 @@ attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_
           const int qrow = b * p.S + t * 64;
           tma_load_2d(t1, &tmap_qkv64, &t_full[st], h * HD, qrow);
           tma_load_2d(t2, &tmap_do64, &t_full[st], h * HD, qrow);
+          // log-sum-exp and D of these 64 queries ride on the same barrier (256 bytes each)
+          const size_t sv = ((size_t)b * p.Hq + h) * p.S + t * 64;
+          bulk_load_1d(stats_s + st * 128, p.lse2 + sv, 256, &t_full[st]);
+          bulk_load_1d(stats_s + st * 128 + 64, p.D + sv, 256, &t_full[st]);
         }
       }
     }
@@ -1159,15 +1164,20 @@ attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_
           if (dead) sa[i] = 0xff800000u;
         }
       }
-      const float* lse_c = p.lse2 + ((size_t)b * p.Hq + h) * p.S + str0;
-      const float* d_c = p.D + ((size_t)b * p.Hq + h) * p.S + str0;
+      const int sst = it % C::STAGES;
+      if (MODE != RS_DQ) {                // the statistics arrived with the tile; this wait is over already (acquire)
+        if (!mbar_wait(&t_full[sst], (it / C::STAGES) & 1, abort_flag, 49, &g_attn_error)) { ok = false; break; }
+      }
+      const float* lse_c = stats_s + sst * 128 + hf * 32;
+      const float* d_c = lse_c + 64;
+      (void)h;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint32_t pk[4], dk[4];
         float lv[8], dv[8];
         if (MODE != RS_DQ) {              // statistics of the 8 streamed queries of this vector (same for every thread)
-          const float4 l0 = __ldg(reinterpret_cast<const float4*>(lse_c + 8 * q)), l1 = __ldg(reinterpret_cast<const float4*>(lse_c + 8 * q + 4));
-          const float4 e0 = __ldg(reinterpret_cast<const float4*>(d_c + 8 * q)), e1 = __ldg(reinterpret_cast<const float4*>(d_c + 8 * q + 4));
+          const float4 l0 = *reinterpret_cast<const float4*>(lse_c + 8 * q), l1 = *reinterpret_cast<const float4*>(lse_c + 8 * q + 4);
+          const float4 e0 = *reinterpret_cast<const float4*>(d_c + 8 * q), e1 = *reinterpret_cast<const float4*>(d_c + 8 * q + 4);
           lv[0] = l0.x; lv[1] = l0.y; lv[2] = l0.z; lv[3] = l0.w; lv[4] = l1.x; lv[5] = l1.y; lv[6] = l1.z; lv[7] = l1.w;
           dv[0] = e0.x; dv[1] = e0.y; dv[2] = e0.z; dv[3] = e0.w; dv[4] = e1.x; dv[5] = e1.y; dv[6] = e1.z; dv[7] = e1.w;
         }

@@ -48,8 +48,16 @@ def attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale):
     return out, lse2
 
 
+_BWD64 = os.environ.get("ZEN_ATTN_BWD64", "")      # "", or 0 / 1 / 2: which head_dim 64 backward kernels run (measurements)
+_bwd64_applied = False
+
+
 def attention_bwd_kernel(dout, qkv, out, lse2, bsz, seq, hq, hkv, hd, scale):
     """tcgen05 backward: gradient of the fused qkv buffer (dQ kernel + dK/dV kernel, no atomics)."""
+    global _bwd64_applied
+    if _BWD64 and not _bwd64_applied:
+        _native.lib().zen_attn_bwd64_variant(int(_BWD64))
+        _bwd64_applied = True
     dout = dout if (dout.is_contiguous() and dout.data_ptr() % 16 == 0) else dout.contiguous()
     dqkv = torch.empty_like(qkv)
     dbuf = torch.empty(bsz, hq, seq, dtype=torch.float32, device=qkv.device)
