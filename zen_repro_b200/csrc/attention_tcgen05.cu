@@ -737,7 +737,7 @@ struct Bwd256Cfg {
   static constexpr int RES_BYTES = 128 * HD * 2;        // 64 KB: four [128][64] atoms
   static constexpr int STR_BYTES = 64 * HD * 2;         // 32 KB: four [64][64] atoms
   static constexpr int W_BYTES = 128 * 64 * 2;
-  static constexpr int SMEM_BYTES = 2 * RES_BYTES + 2 * STR_BYTES + W_BYTES + 1024 + 256;
+  static constexpr int SMEM_BYTES = 2 * RES_BYTES + 2 * STR_BYTES + W_BYTES + 512 + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
   static constexpr uint32_t IDESC_S = make_idesc(128, 64, false, false);
   static constexpr uint32_t IDESC_ACC = make_idesc(128, 256, false, true);
@@ -757,7 +757,8 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
   unsigned char* t1_s = r2_s + C::RES_BYTES;
   unsigned char* t2_s = t1_s + C::STR_BYTES;
   unsigned char* w_s = t2_s + C::STR_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(w_s + C::W_BYTES);
+  float* stats_s = reinterpret_cast<float*>(w_s + C::W_BYTES);      // [lse | D][64] of the streamed queries (dK / dV)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(w_s + C::W_BYTES + 512);
   uint64_t* r_full = bars;
   uint64_t* t_full = bars + 1;
   uint64_t* t_empty = bars + 2;
@@ -816,7 +817,7 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
       }
       for (int it = 0; it < niter; ++it) {
         if (!mbar_wait(t_empty, (it & 1) ^ 1, abort_flag, 31, &g_attn_error)) break;
-        mbar_expect_tx(t_full, 2 * C::STR_BYTES);
+        mbar_expect_tx(t_full, 2 * C::STR_BYTES + (MODE == BWD_DQ ? 0 : 512));
         if (MODE == BWD_DQ) {
           const int krow = b * p.S + it * 64;
 #pragma unroll
@@ -832,6 +833,10 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
             tma_load_2d(t1_s + a * 8192, &tmap_qkv64, t_full, h * HD + a * 64, qrow);
             tma_load_2d(t2_s + a * 8192, &tmap_do64, t_full, h * HD + a * 64, qrow);
           }
+          // log-sum-exp and D of these 64 queries ride on the same barrier (256 bytes each)
+          const size_t sv = ((size_t)b * p.Hq + h) * p.S + t * 64;
+          bulk_load_1d(stats_s, p.lse2 + sv, 256, t_full);
+          bulk_load_1d(stats_s + 64, p.D + sv, 256, t_full);
         }
       }
     }
@@ -901,8 +906,12 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
           if (dead) sa[i] = 0xff800000u;
         }
       }
-      const float* lse_c = p.lse2 + ((size_t)b * p.Hq + h) * p.S + str0;      // per-column statistics (dK / dV)
-      const float* d_c = p.D + ((size_t)b * p.Hq + h) * p.S + str0;
+      if (MODE != BWD_DQ) {               // the statistics arrived with the tile; this wait is over already (acquire)
+        if (!mbar_wait(t_full, it & 1, abort_flag, 38, &g_attn_error)) { ok = false; break; }
+      }
+      const float* lse_c = stats_s + hf * 32;                               // per-column statistics (dK / dV)
+      const float* d_c = lse_c + 64;
+      (void)h;
       uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
@@ -913,11 +922,11 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
           w0 = p0 * (__uint_as_float(da[i]) - d_row);
           w1 = p1 * (__uint_as_float(da[i + 1]) - d_row);
         } else {
-          const float p0 = ex2f(fmaf(__uint_as_float(sa[i]), cs, -__ldg(lse_c + i)));
-          const float p1 = ex2f(fmaf(__uint_as_float(sa[i + 1]), cs, -__ldg(lse_c + i + 1)));
+          const float p0 = ex2f(fmaf(__uint_as_float(sa[i]), cs, -lse_c[i]));
+          const float p1 = ex2f(fmaf(__uint_as_float(sa[i + 1]), cs, -lse_c[i + 1]));
           if (MODE == BWD_DK) {
-            w0 = p0 * (__uint_as_float(da[i]) - __ldg(d_c + i));
-            w1 = p1 * (__uint_as_float(da[i + 1]) - __ldg(d_c + i + 1));
+            w0 = p0 * (__uint_as_float(da[i]) - d_c[i]);
+            w1 = p1 * (__uint_as_float(da[i + 1]) - d_c[i + 1]);
           } else {
             w0 = p0;
             w1 = p1;
