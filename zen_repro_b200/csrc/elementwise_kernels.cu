@@ -160,76 +160,7 @@ norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __r
   }
 }
 
-// Norm backward.  dh = grad through the norm (+ dres, the gradient arriving on the residual stream).
-// Per-CTA partial sums of dw (and db) go to part_dw/part_db [gridDim.x][cols] (fp32 scratch) and are
-// folded by colreduce_kernel.
-template <typename T, bool kLayer, int NV>
-__global__ void __launch_bounds__(NORM_THREADS)
-norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __restrict__ wgt,
-                const float* __restrict__ rstd_in, const float* __restrict__ mean_in, const T* __restrict__ dres,
-                T* __restrict__ dh, float* __restrict__ part_dw, float* __restrict__ part_db, int rows, int cols,
-                int unit_offset) {
-  __shared__ float sh[32];
-  const int nv = cols / 8;
-  float aw[NV][8], ab[NV][8];
-#pragma unroll
-  for (int j = 0; j < NV; ++j)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { aw[j][i] = 0.f; ab[j][i] = 0.f; }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const size_t base = (size_t)row * cols;
-    const float rstd = rstd_in[row];
-    const float mean = kLayer ? mean_in[row] : 0.f;
-    float g[NV][8], xh[NV][8];
-    float s1 = 0.f, s2 = 0.f;                       // sum(g), sum(g * xhat)
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      const int v = threadIdx.x + j * NORM_THREADS;
-      if (v < nv) {
-        float d[8], w[8];
-        Vec8<T>::load(dy + base + (size_t)v * 8, d);
-        Vec8<T>::load(h + base + (size_t)v * 8, xh[j]);
-        Vec8<T>::load(wgt + (size_t)v * 8, w);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          xh[j][i] = (xh[j][i] - mean) * rstd;
-          aw[j][i] += d[i] * xh[j][i];
-          ab[j][i] += d[i];
-          g[j][i] = d[i] * (kLayer ? w[i] : (unit_offset ? 1.f + w[i] : w[i]));
-          s1 += g[j][i];
-          s2 += g[j][i] * xh[j][i];
-        }
-      }
-    }
-    s2 = block_sum(s2, sh) / cols;
-    if (kLayer) s1 = block_sum(s1, sh) / cols; else s1 = 0.f;
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      const int v = threadIdx.x + j * NORM_THREADS;
-      if (v < nv) {
-        float o[8];
-        if (dres) Vec8<T>::load(dres + base + (size_t)v * 8, o);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float t = rstd * (g[j][i] - s1 - xh[j][i] * s2);
-          o[i] = dres ? o[i] + t : t;
-        }
-        Vec8<T>::store(dh + base + (size_t)v * 8, o);
-      }
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < NV; ++j) {
-    const int v = threadIdx.x + j * NORM_THREADS;
-    if (v < nv) {
-      Vec8<float>::store(part_dw + (size_t)blockIdx.x * cols + (size_t)v * 8, aw[j]);
-      if (kLayer && part_db) Vec8<float>::store(part_db + (size_t)blockIdx.x * cols + (size_t)v * 8, ab[j]);
-    }
-  }
-}
-
-// ---- warp-per-row variants for narrow rows (cols <= 256 * NV): no block barriers, many rows in flight per SM.
-// Rows are kept as raw 16-byte vectors (8 registers per vector for fp32, 4 for 16-bit types) and unpacked on use.
+// Rows kept as raw 16-byte vectors (8 registers per vector for fp32, 4 for 16-bit types) and unpacked on use.
 template <typename T> struct Pack;
 template <> struct Pack<float> {
   struct raw_t { float4 a, b; };
@@ -255,6 +186,86 @@ template <> struct Pack<__half> {
   }
 };
 
+// Norm backward.  dh = grad through the norm (+ dres, the gradient arriving on the residual stream).
+// Per-CTA partial sums of dw (and db) go to part_dw/part_db [gridDim.x][cols] (fp32 scratch) and are
+// folded by colreduce_kernel.
+template <typename T, bool kLayer, int NV, bool kParams>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __restrict__ wgt,
+                const float* __restrict__ rstd_in, const float* __restrict__ mean_in, const T* __restrict__ dres,
+                T* __restrict__ dh, float* __restrict__ part_dw, float* __restrict__ part_db, int rows, int cols,
+                int unit_offset) {
+  __shared__ float sh[32];
+  const int nv = cols / 8;
+  // kParams = false: only dh here (the parameter gradients come from norm_dwdb_partial_kernel), which frees the
+  // 16 * NV accumulator registers and lets several CTAs share an SM
+  float aw[kParams ? NV : 1][8], ab[kParams ? NV : 1][8];
+  if (kParams) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { aw[j][i] = 0.f; ab[j][i] = 0.f; }
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = (size_t)row * cols;
+    const float rstd = rstd_in[row];
+    const float mean = kLayer ? mean_in[row] : 0.f;
+    float g[NV][8], xh[NV][8];
+    typename Pack<T>::raw_t rres[NV];               // residual-stream gradient, fetched with the first loads
+    float s1 = 0.f, s2 = 0.f;                       // sum(g), sum(g * xhat)
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nv && dres) rres[j] = Pack<T>::load(dres + base + (size_t)v * 8);
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nv) {
+        float d[8], w[8];
+        Vec8<T>::load(dy + base + (size_t)v * 8, d);
+        Vec8<T>::load(h + base + (size_t)v * 8, xh[j]);
+        Vec8<T>::load(wgt + (size_t)v * 8, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[j][i] = (xh[j][i] - mean) * rstd;
+          if (kParams) { aw[j][i] += d[i] * xh[j][i]; ab[j][i] += d[i]; }
+          g[j][i] = d[i] * (kLayer ? w[i] : (unit_offset ? 1.f + w[i] : w[i]));
+          s1 += g[j][i];
+          s2 += g[j][i] * xh[j][i];
+        }
+      }
+    }
+    s2 = block_sum(s2, sh) / cols;
+    if (kLayer) s1 = block_sum(s1, sh) / cols; else s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int v = threadIdx.x + j * NORM_THREADS;
+      if (v < nv) {
+        float o[8];
+        if (dres) Pack<T>::unpack(rres[j], o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float t = rstd * (g[j][i] - s1 - xh[j][i] * s2);
+          o[i] = dres ? o[i] + t : t;
+        }
+        Vec8<T>::store(dh + base + (size_t)v * 8, o);
+      }
+    }
+  }
+  if (!kParams) return;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int v = threadIdx.x + j * NORM_THREADS;
+    if (v < nv) {
+      Vec8<float>::store(part_dw + (size_t)blockIdx.x * cols + (size_t)v * 8, aw[j]);
+      if (kLayer && part_db) Vec8<float>::store(part_db + (size_t)blockIdx.x * cols + (size_t)v * 8, ab[j]);
+    }
+  }
+}
+
+// ---- warp-per-row variants for narrow rows (cols <= 256 * NV): no block barriers, many rows in flight per SM.
+// Rows are kept as raw 16-byte vectors (8 registers per vector for fp32, 4 for 16-bit types) and unpacked on use.
 #define NORMW_WARPS 8
 
 template <typename T, bool kLayer, int NV>
@@ -434,16 +445,17 @@ template <typename T, bool kLayer>
 __global__ void __launch_bounds__(256)
 norm_dwdb_partial_kernel(const T* __restrict__ dy, const T* __restrict__ h, const float* __restrict__ rstd_in,
                          const float* __restrict__ mean_in, float* __restrict__ part_dw, float* __restrict__ part_db,
-                         int rows, int cols) {
+                         int rows, int cols, int rows_per_cta) {
+  // Wide matrices: blockIdx.y selects a 2048-column slice (one vector per thread), blockIdx.x a group of rows.
   // Narrow matrices (fewer 8-column vectors than threads): the threads form `groups` row groups that walk
   // interleaved rows of the CTA's 32 and meet in shared memory, group by group, so that no thread idles.
   __shared__ float red_w[2048], red_b[2048];
-  const int r0 = blockIdx.x * 32, r1 = min(rows, r0 + 32);
+  const int r0 = blockIdx.x * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
   const int vpr = cols / 8;
   const int groups = vpr <= 128 ? 256 / vpr : 1;
   const int g = groups > 1 ? threadIdx.x / vpr : 0;
-  const int first = groups > 1 ? (threadIdx.x % vpr) * 8 : threadIdx.x * 8;
-  const int stride = groups > 1 ? cols : 256 * 8;            // grouped threads own exactly one vector
+  const int first = groups > 1 ? (threadIdx.x % vpr) * 8 : (blockIdx.y * 256 + threadIdx.x) * 8;
+  const int stride = cols;                                   // every thread owns exactly one vector
   if (g >= groups) {                                         // leftover threads (256 not a multiple of vpr)
     for (int k = 1; k < groups; ++k) { __syncthreads(); __syncthreads(); }
     return;
@@ -644,6 +656,39 @@ rope_kernel(T* __restrict__ x, int tokens, int heads, int hd, int ld, int seq, i
     const float a = ZenVal<T>::to_f(p[j]), b = ZenVal<T>::to_f(p[j + half]);
     p[j] = ZenVal<T>::from_f(a * c - b * s);
     p[j + half] = ZenVal<T>::from_f(b * c + a * s);
+  }
+}
+
+// Vectorised form for hd / 2 a multiple of 8: a thread owns 8 consecutive frequencies of one token, computes their
+// sines and cosines once and walks all heads with 16-byte loads and stores (the scalar kernel above recomputes the
+// trigonometry for every head and moves two bytes per access).
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(T* __restrict__ x, int tokens, int heads, int hd, int ld, int seq, int pos0, float log2_theta, float sign) {
+  const int half = hd / 2, vph = half / 8;
+  const size_t n = (size_t)tokens * vph;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+    const int jv = (int)(idx % vph);
+    const int t = (int)(idx / vph);
+    const float pos = (float)(pos0 + t % seq);
+    float c[8], sn[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float inv_freq = exp2f(-log2_theta * (2.f * (jv * 8 + i) / hd));
+      sincosf(pos * inv_freq, &sn[i], &c[i]);
+      sn[i] *= sign;
+    }
+    T* p = x + (size_t)t * ld + jv * 8;
+#pragma unroll 4
+    for (int hh = 0; hh < heads; ++hh) {
+      float a[8], b[8], oa[8], ob[8];
+      Vec8<T>::load(p + (size_t)hh * hd, a);
+      Vec8<T>::load(p + (size_t)hh * hd + half, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { oa[i] = a[i] * c[i] - b[i] * sn[i]; ob[i] = b[i] * c[i] + a[i] * sn[i]; }
+      Vec8<T>::store(p + (size_t)hh * hd, oa);
+      Vec8<T>::store(p + (size_t)hh * hd + half, ob);
+    }
   }
 }
 
@@ -1019,7 +1064,7 @@ extern "C" {
 static inline bool norm_warp_path(int cols, int dtype) { (void)dtype; return cols <= NORMW_MAXCOLS; }
 
 // Number of per-CTA partial rows the norm backward writes (the caller sizes its scratch with this).
-int zen_norm_bwd_parts(int rows) { const int a = cap_grid((size_t)rows, 2), b = (rows + 31) / 32; return a > b ? a : b; }
+int zen_norm_bwd_parts(int rows) { const int a = cap_grid((size_t)rows, 2), b = (rows + 7) / 8; return a > b ? a : b; }
 
 #define NORM_NV_DISPATCH(cols, ...)                                   \
   if (cols <= NORM_THREADS * 8) { constexpr int NV = 1; __VA_ARGS__; } \
@@ -1072,20 +1117,31 @@ int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd
         if (layer) norm_bwd_warp_kernel<T, true, NV, false><<<g1, NORMW_WARPS * 32, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
         else norm_bwd_warp_kernel<T, false, NV, false><<<g1, NORMW_WARPS * 32, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
       });
-      if (layer) norm_dwdb_partial_kernel<T, true><<<parts, 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols);
-      else norm_dwdb_partial_kernel<T, false><<<parts, 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols);
+      if (layer) norm_dwdb_partial_kernel<T, true><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, 32);
+      else norm_dwdb_partial_kernel<T, false><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, 32);
       colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate);
       if (layer && db) colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_db, (T*)db, parts, cols, accumulate);
     });
     return (int)cudaGetLastError();
   }
+  (void)grid;
+  // wide rows: dh by one CTA per row (no parameter accumulators, so several CTAs fit an SM), then dw / db by the
+  // column-sum pass, as on the warp path
+  const int g2 = cap_grid((size_t)rows, 6);
+  // rows per CTA of the column-sum pass: 32, fewer when that would leave SMs idle (the partial buffer holds
+  // zen_norm_bwd_parts(rows) rows)
+  int rpc = 32;
+  while (rpc > 8 && (rows + rpc - 1) / rpc < 4 * sm_count_e() && (rows + rpc / 2 - 1) / (rpc / 2) <= zen_norm_bwd_parts(rows)) rpc /= 2;
+  const int parts = (rows + rpc - 1) / rpc;
   DISPATCH_T(dtype, {
     NORM_NV_DISPATCH(cols, {
-      if (layer) norm_bwd_kernel<T, true, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
-      else norm_bwd_kernel<T, false, NV><<<grid, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+      if (layer) norm_bwd_kernel<T, true, NV, false><<<g2, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
+      else norm_bwd_kernel<T, false, NV, false><<<g2, NORM_THREADS, 0, st>>>((const T*)dy, (const T*)h, (const T*)w, rstd, mean, (const T*)dres, (T*)dh, part_dw, part_db, rows, cols, unit_offset);
     });
-    colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, grid, cols, accumulate);
-    if (layer && db) colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_db, (T*)db, grid, cols, accumulate);
+    if (layer) norm_dwdb_partial_kernel<T, true><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, rpc);
+    else norm_dwdb_partial_kernel<T, false><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, rpc);
+    colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate);
+    if (layer && db) colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_db, (T*)db, parts, cols, accumulate);
   });
   return (int)cudaGetLastError();
 }
@@ -1125,6 +1181,12 @@ int zen_rope(void* x, int tokens, int heads, int hd, int ld, int seq, int pos0, 
   if (hd % 2) return -2;
   const size_t n = (size_t)tokens * heads * (hd / 2);
   const int grid = cap_grid((n + 255) / 256, 16);
+  if ((hd / 2) % 8 == 0 && (ld % 8) == 0 && (reinterpret_cast<uintptr_t>(x) % 16) == 0) {
+    const size_t nvec = (size_t)tokens * (hd / 16);
+    const int gv = cap_grid((nvec + 255) / 256, 16);
+    DISPATCH_T(dtype, rope_vec_kernel<T><<<gv, 256, 0, (cudaStream_t)stream>>>((T*)x, tokens, heads, hd, ld, seq, pos0, log2f(theta), inverse ? -1.f : 1.f));
+    return (int)cudaGetLastError();
+  }
   DISPATCH_T(dtype, rope_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((T*)x, tokens, heads, hd, ld, seq, pos0, log2f(theta), inverse ? -1.f : 1.f));
   return (int)cudaGetLastError();
 }
