@@ -42,6 +42,7 @@ def parse():
     ap.add_argument("--num_layers", type=int, default=None)
     ap.add_argument("--micro_batch", type=int, default=None)
     ap.add_argument("--no_e2e", action="store_true")
+    ap.add_argument("--sequence_parallel", action="store_true", help="TP layers with the residual stream sharded over tokens")
     ap.add_argument("--no_graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     return ap.parse_args()
 
@@ -65,7 +66,7 @@ def run_zen(args):
     if preset["tp"] > world:
         preset["tp"] = 1
     cfg = TrainConfig(method=args.method, top_k=args.top_k, num_layers=args.num_layers, data_pool=max(4, min(8, args.steps)),
-                      cuda_graph=not args.no_graph, **preset)
+                      cuda_graph=not args.no_graph, sequence_parallel=args.sequence_parallel, **preset)
     trainer = Trainer(cfg, init_dist=False)
     dev = trainer.device
     rank = dist.get_rank() if dist.is_initialized() else 0
@@ -123,7 +124,7 @@ def run_zen(args):
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic Zipf tokens, random-init weights", "impl": "zen",
         "config": {"model": cfg.model, "global_batch": cfg.micro_batch * trainer.plugin.dp_size, "seq_len": cfg.seq_len,
-                   "parallelism": f"dp{trainer.plugin.dp_size}" + (f"xtp{cfg.tp}" if cfg.tp > 1 else ""),
+                   "parallelism": f"dp{trainer.plugin.dp_size}" + (f"xtp{cfg.tp}" if cfg.tp > 1 else "") + ("+sp" if (cfg.tp > 1 and cfg.sequence_parallel) else ""),
                    "method": cfg.method, "sparse_embedding": cfg.sparse_embedding and cfg.method == 0,
                    "num_layers": trainer.model_cfg.num_layers, "cuda_graph": bool(trainer._graph is not None),
                    "l2": "per-step working set (weights + activations, > 1 GB) exceeds the 126 MB L2"},

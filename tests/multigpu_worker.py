@@ -196,7 +196,23 @@ def check_tp_trainer(rank, world, dev):
     print(f"OK tp_trainer rank{rank} {out[True]}", flush=True)
 
 
-CHECKS = {"gemm_ar": check_gemm_allreduce, "gemm_rs_ag": check_gemm_rs_ag, "tp_trainer": check_tp_trainer,"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
+def check_sp_trainer(rank, world, dev):
+    """TP = 2 with the residual stream sharded over tokens (all-gather + GEMM, GEMM + reduce-scatter kernels) tracks
+    the all-reduce form of the same model."""
+    from zen_repro_b200.trainer import TrainConfig, Trainer
+
+    out = {}
+    for sp in (True, False):
+        t = Trainer(TrainConfig(model="meta-llama/Llama-3.2-3B", num_layers=2, micro_batch=1, seq_len=256, tp=2, lr=1e-4,
+                                data_pool=0, fused_tp=True, sequence_parallel=sp), init_dist=False)
+        out[sp] = [t.step(next(t.data)) for _ in range(4)]
+        ws = t.model.unwrap().tp_ws
+        assert ws is None or ws.check() == 0
+    assert all(abs(a - b) < 0.05 for a, b in zip(out[True], out[False])), out
+    print(f"OK sp_trainer rank{rank} {out[True]}", flush=True)
+
+
+CHECKS = {"gemm_ar": check_gemm_allreduce, "sp_trainer": check_sp_trainer, "gemm_rs_ag": check_gemm_rs_ag, "tp_trainer": check_tp_trainer,"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
           "hook": check_zen_hook, "departed": check_departed_rank}
 
 if __name__ == "__main__":

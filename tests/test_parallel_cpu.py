@@ -63,7 +63,7 @@ def test_zen_hook_trains_on_two_ranks():
     torch.testing.assert_close(torch.as_tensor(out[0][1]), torch.as_tensor(out[1][1]), atol=0, rtol=0)
 
 
-def _tp_worker(rank, world, name):
+def _tp_worker(rank, world, name, sequence_parallel=False):
     import torch.distributed as dist
 
     from zen_repro_b200.models.sharding import shard_state_dict
@@ -77,6 +77,8 @@ def _tp_worker(rank, world, name):
     g = dist.group.WORLD
     sh = build_model(cfg, tp_group=g, dtype=torch.float32)
     sh.load_state_dict(shard_state_dict(full.state_dict(), cfg, rank, world))
+    if sequence_parallel:
+        sh.enable_sequence_parallel()
     got = sh(ids, ids)
     got.backward()
     sh.sync_replicated_grads()
@@ -90,6 +92,16 @@ def _tp_worker(rank, world, name):
 @pytest.mark.parametrize("name", ["tiny-llama", "tiny-gpt2", "tiny-gemma"])
 def test_tensor_parallel_matches_single_rank(name):
     for want, got, gerr, lerr in run_gloo(_tp_worker, 2, name):
+        assert got == pytest.approx(want, rel=1e-5, abs=1e-5)
+        assert gerr < 1e-4
+        assert lerr < 1e-4
+
+
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-gpt2", "tiny-gemma"])
+def test_sequence_parallel_matches_single_rank(name):
+    """Residual stream sharded over the tokens of the TP group: all-gather before the column-parallel projections,
+    reduce-scatter after the row-parallel ones, partial norm / bias gradients summed over the group."""
+    for want, got, gerr, lerr in run_gloo(_tp_worker, 2, name, True):
         assert got == pytest.approx(want, rel=1e-5, abs=1e-5)
         assert gerr < 1e-4
         assert lerr < 1e-4

@@ -63,10 +63,13 @@ class Block(nn.Module):
             self.norm1_b = self.norm2_b = self.qkv_b = self.o_b = self.up_b = self.down_b = None
 
     tp_ws = None        # FusedTPWorkspace shared by all blocks of a model (set by DecoderLM.enable_fused_tp)
+    sequence_parallel = False   # residual stream sharded over the tokens of the TP group (DecoderLM.enable_sequence_parallel)
 
     def forward(self, x, res, bsz: int, seq: int):
         cfg, g = self.cfg, self.tp_group
         rank, tp = _tp(g)
+        if self.sequence_parallel and tp > 1:
+            return self._forward_sp(x, res, bsz, seq)
         ws = self.tp_ws if (tp > 1 and x.is_cuda and x.dtype == torch.bfloat16) else None
         if ws is not None and ws.fits(x.shape[0], cfg.hidden_size):
             return self._forward_fused_tp(x, res, bsz, seq, ws)
@@ -110,6 +113,31 @@ def _block_forward_fused_tp(self, x, res, bsz, seq, ws):
 
 
 Block._forward_fused_tp = _block_forward_fused_tp
+
+
+def _block_forward_sp(self, x, res, bsz, seq):
+    """Sequence-parallel block: x and res hold this rank's T / P token rows.  Norms run on the shard; the
+    column-parallel projections gather the tokens inside the GEMM (all-gather + GEMM), attention and the activation see
+    all tokens and this rank's heads / inner columns; the row-parallel projections return this rank's rows of the sum
+    (GEMM + reduce-scatter).  The reference's ColossalAI plugin has this mode too (enable_sequence_parallelism) but
+    train.py:117-123 leaves it off."""
+    cfg, g = self.cfg, self.tp_group
+    ws = self.tp_ws if (x.is_cuda and x.dtype == torch.bfloat16) else None
+    lay = cfg.weight_layout
+    y, h = O.fused_norm(x, res, self.norm1_w, self.norm1_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
+    qkv = O.sp_linear(y, self.qkv_w, self.qkv_b, lay, "ag", g, ws)
+    if not cfg.learned_positions:
+        qkv = O.rope_qkv(qkv, self.hq, self.hkv, cfg.head_dim, seq, cfg.rope_theta)
+    a = O.attention(qkv, bsz, seq, self.hq, self.hkv, cfg.head_dim)
+    o = O.sp_linear(a, self.o_w, self.o_b, lay, "rs", g, ws)
+    y2, h2 = O.fused_norm(o, h, self.norm2_w, self.norm2_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
+    u = O.sp_linear(y2, self.up_w, self.up_b, lay, "ag", g, ws)
+    m = O.activation(u, cfg.act)
+    dn = O.sp_linear(m, self.down_w, self.down_b, lay, "rs", g, ws)
+    return dn, h2
+
+
+Block._forward_sp = _block_forward_sp
 
 
 class DecoderLM(nn.Module):
@@ -160,6 +188,22 @@ class DecoderLM(nn.Module):
             self.tp_ws = ws
         return self
 
+    def enable_sequence_parallel(self, on: bool = True):
+        """Shard the residual stream over the tokens of the TP group (tokens per step must divide by the group size).
+        Norm parameters and the biases of row-parallel layers then see only this rank's tokens; their gradients are
+        summed over the group by ``sync_replicated_grads``."""
+        _, tp = _tp(self.tp_group)
+        self.sequence_parallel = bool(on) and tp > 1
+        for b in self.blocks:
+            b.sequence_parallel = self.sequence_parallel
+        return self
+
+    def _sp_partial_params(self):
+        ps = [self.norm_f_w, self.norm_f_b]
+        for b in self.blocks:
+            ps += [b.norm1_w, b.norm2_w, b.norm1_b, b.norm2_b, b.o_b, b.down_b]
+        return [p for p in ps if p is not None]
+
     def head_weight(self):
         return self.wte if self.lm_head is None else self.lm_head
 
@@ -173,12 +217,18 @@ class DecoderLM(nn.Module):
         else:
             x = O.embedding(ids, self.wte, self.wpe, seq, cfg.pos_offset, cfg.embed_scale, self.sparse_sink)
         res = None
+        sp = getattr(self, "sequence_parallel", False) and tp > 1
+        if sp:
+            assert ids.numel() % tp == 0, "sequence parallelism needs the token count to divide by the TP size"
+            x = O.scatter_to_sp(x, self.tp_group)
         for blk in self.blocks:
             if cfg.grad_checkpoint and torch.is_grad_enabled():
                 x, res = checkpoint(blk, x, res, bsz, seq, use_reentrant=False)
             else:
                 x, res = blk(x, res, bsz, seq)
         y, _ = O.fused_norm(x, res, self.norm_f_w, self.norm_f_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
+        if sp:
+            y = O.gather_from_sp(y, self.tp_group)
         if labels is None:
             return self._logits(y).view(bsz, seq, -1)
         if shift_labels:
@@ -226,6 +276,11 @@ class DecoderLM(nn.Module):
         _, tp = _tp(self.tp_group)
         if tp == 1:
             return
+        if getattr(self, "sequence_parallel", False):
+            # parameters applied to this rank's token rows only: their gradients are partial sums over the group
+            for p in self._sp_partial_params():
+                if p.grad is not None:
+                    dist.all_reduce(p.grad, group=self.tp_group)
         for b in self.blocks:
             if not b.kv_replicated or b.qkv_w.grad is None:
                 continue

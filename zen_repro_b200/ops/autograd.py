@@ -415,6 +415,151 @@ class _ReduceFromTP(torch.autograd.Function):
         return g, None
 
 
+# ---- sequence parallelism: the residual stream is sharded over the tokens of the TP group ------------------------
+def _gather_rows(x, group):
+    """[T / P, C] on every rank -> [T, C] (rank-major row blocks)."""
+    P = dist.get_world_size(group)
+    x = x.contiguous()
+    out = torch.empty(P * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out, x, group=group)
+    return out
+
+
+def _reduce_scatter_rows(x, group):
+    """[T, C] partial sums on every rank -> this rank's [T / P, C] rows of the sum."""
+    P, r = dist.get_world_size(group), dist.get_rank(group)
+    x = x.contiguous()
+    n = x.shape[0] // P
+    if not x.is_cuda:                      # gloo has no reduce-scatter
+        dist.all_reduce(x, group=group)
+        return x[r * n:(r + 1) * n].clone()
+    out = torch.empty(n, *x.shape[1:], dtype=x.dtype, device=x.device)
+    dist.reduce_scatter_tensor(out, x, group=group)
+    return out
+
+
+class _ScatterToSP(torch.autograd.Function):
+    """Keep this rank's block of token rows (forward); all-gather the row gradients (backward)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        P, r = dist.get_world_size(group), dist.get_rank(group)
+        n = x.shape[0] // P
+        return x[r * n:(r + 1) * n].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return _gather_rows(g, ctx.group), None
+
+
+class _GatherFromSP(torch.autograd.Function):
+    """All-gather the token rows (forward); keep this rank's block of the gradient (backward).  The consumer is a
+    vocabulary-parallel head whose input gradient is already summed over the group, hence identical on every rank."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _gather_rows(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        P, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        n = g.shape[0] // P
+        return g[r * n:(r + 1) * n].contiguous(), None
+
+
+def scatter_to_sp(x, group):
+    return _ScatterToSP.apply(x, group)
+
+
+def gather_from_sp(x, group):
+    return _GatherFromSP.apply(x, group)
+
+
+class SPLinearFn(torch.autograd.Function):
+    """Linear layer of a sequence-parallel block.
+
+    mode "ag" (column-parallel weight): the input is this rank's token rows; y = all_gather(x) @ W^T has all tokens
+    and this rank's output columns.  mode "rs" (row-parallel weight): the input has all tokens and this rank's
+    slice of the contraction; y = reduce_scatter(x @ W^T) is this rank's token rows of the summed product (+ bias,
+    once).  With a ``FusedTPWorkspace`` on CUDA the forward of both and the input gradient of "ag" run as one kernel
+    (``ag_gemm_*`` / ``gemm_rs_*``: GEMM and collective over peer memory); the operand that a weight gradient needs
+    in full (x for "ag", dy for "rs") is all-gathered in backward, as Megatron-style sequence parallelism does."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, layout, mode, group, ws):
+        x2 = x.reshape(-1, x.shape[-1])
+        P = dist.get_world_size(group)
+        out_in = layout == "out_in"
+        n = weight.shape[0] if out_in else weight.shape[1]
+        fused = ws is not None and x2.is_cuda and x2.dtype == torch.bfloat16
+        if mode == "ag":
+            if fused and ws.fits_ag(x2.shape[0], x2.shape[1], n):
+                y = ws.ag_gemm_nt(x2, weight, bias) if out_in else ws.ag_gemm_nn(x2, weight, bias)
+            else:
+                xf = _gather_rows(x2, group)
+                y = G.gemm_nt(xf, weight, bias=bias) if out_in else G.gemm_nn(xf, weight, bias=bias)
+        else:
+            if fused and ws.fits_rs(x2.shape[0], n):
+                y = ws.gemm_rs_nt(x2, weight, bias) if out_in else ws.gemm_rs_nn(x2, weight, bias)
+            else:
+                y = G.gemm_nt(x2, weight) if out_in else G.gemm_nn(x2, weight)
+                y = _reduce_scatter_rows(y, group)
+                if bias is not None:
+                    y = y + bias
+        ctx.save_for_backward(x2, weight)
+        ctx.cfg = (layout, mode, group, ws, bias is not None)
+        ctx.params = (weight, bias)
+        ctx.direct = (_claim(weight, ctx.needs_input_grad[1]), _claim(bias, ctx.needs_input_grad[2]))
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        layout, mode, group, ws, has_bias = ctx.cfg
+        out_in = layout == "out_in"
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        fused = ws is not None and dy2.is_cuda and dy2.dtype == torch.bfloat16
+        dx = dw = db = None
+        wp, bp = ctx.params
+        if mode == "ag":
+            # dx: every rank holds a partial [T, K] (its output columns); this rank needs its token rows of the sum
+            if ctx.needs_input_grad[0]:
+                if fused and ws.fits_rs(dy2.shape[0], x2.shape[1]):
+                    dx = ws.gemm_rs_nn(dy2, weight) if out_in else ws.gemm_rs_nt(dy2, weight)
+                else:
+                    part = G.gemm_nn(dy2, weight) if out_in else G.gemm_nt(dy2, weight)
+                    dx = _reduce_scatter_rows(part, group)
+            xf = _gather_rows(x2, group) if ctx.needs_input_grad[1] else None
+            dyf, db_src = dy2, dy2
+        else:
+            dyf = _gather_rows(dy2, group)
+            if ctx.needs_input_grad[0]:
+                dx = G.gemm_nn(dyf, weight) if out_in else G.gemm_nt(dyf, weight)
+            xf, db_src = x2, dy2                 # the bias gradient of this rank covers its token rows only
+        if ctx.needs_input_grad[1]:
+            a, b = (dyf, xf) if out_in else (xf, dyf)
+            if ctx.direct[0]:
+                G.gemm_tn(a, b, out=wp.grad, accumulate=not _take_fresh(wp))
+                wp.zen_ready(wp)
+            else:
+                dw = G.gemm_tn(a, b)
+        if has_bias and ctx.needs_input_grad[2]:
+            if ctx.direct[1]:
+                E.colsum(db_src, out=bp.grad)
+                bp.zen_ready(bp)
+            else:
+                db = E.colsum(db_src)
+        return dx, dw, db, None, None, None, None
+
+
+def sp_linear(x, weight, bias, layout, mode, group, ws=None):
+    return SPLinearFn.apply(x, weight, bias, layout, mode, group, ws)
+
+
 def copy_to_tp(x, group):
     return x if group is None or dist.get_world_size(group) == 1 else _CopyToTP.apply(x, group)
 

@@ -73,8 +73,13 @@ class FusedTPWorkspace:
         return (M % self.P == 0 and rpr % 128 == 0 and rpr * ((N + 7) // 8 * 8) <= self.slot_elems
                 and (rpr // 128) * ((N + 127) // 128) <= self.max_tiles)
 
-    def fits_ag(self, rows_local: int, K: int) -> bool:
-        return self.P == 2 and rows_local % 128 == 0 and K % 8 == 0 and rows_local * K <= self.slot_elems
+    def fits_ag(self, rows_local: int, K: int, N: int = 0) -> bool:
+        """All-gather + GEMM: two ranks, whole 128-row tiles, the peer's rows fit one exchange slot; with N given also
+        that the per-rank tile count fits the flag rows (the kernel takes 256-wide tiles when N allows)."""
+        if not (self.P == 2 and rows_local % 128 == 0 and K % 8 == 0 and rows_local * K <= self.slot_elems):
+            return False
+        bn = 256 if (N >= 1024 and N % 256 == 0) else 128
+        return N == 0 or (rows_local // 128) * ((N + bn - 1) // bn) <= self.max_tiles
 
     def gemm_rs_nt(self, a, b, bias=None, out=None):
         """reduce_scatter over rows of a[M,K] @ b[N,K]^T: this rank's M / P rows of the sum over the group (+ bias)."""

@@ -42,6 +42,7 @@ class TrainConfig:
     data_pool: int = 8                # pre-generated pinned batches that the stream cycles through (0 = generate per step)
     overlap: bool = True
     fused_tp: bool = True             # TP all-reduces fused into the GEMM epilogues (peer memory) instead of NCCL
+    sequence_parallel: bool = False   # TP with the residual stream sharded over tokens: all-gather + GEMM / GEMM + reduce-scatter
     cuda_graph: bool = False          # capture forward + backward + sync + optimizer once, then replay it every step
     graph_warmup: int = 2             # real steps launched from the host before the capture
 
@@ -69,6 +70,8 @@ class Trainer:
         model.reset_parameters(seed=cfg.seed + 1000 * self.plugin.pg_mesh.tp_rank)
         if cfg.tp > 1 and self.device.type == "cuda" and cfg.fused_tp:
             model.enable_fused_tp(cfg.micro_batch * cfg.seq_len)
+        if cfg.tp > 1 and cfg.sequence_parallel:
+            model.enable_sequence_parallel()
         optimizer = FusedAdamW(model.parameters(), lr=cfg.lr, weight_decay=cfg.weight_decay)
         self.data = ZipfTokenStream(mc.vocab_size, cfg.seq_len, cfg.micro_batch, s=cfg.zipf_s, seed=cfg.seed,
                                     dp_rank=self.plugin.dp_rank, pool=cfg.data_pool)
