@@ -47,6 +47,7 @@ def build_parser():
     p.add_argument("--data", choices=["synthetic", "hf"], default="synthetic")
     p.add_argument("--zipf_s", type=float, default=1.1)
     p.add_argument("--no_sparse_embedding", action="store_true")
+    p.add_argument("--sequence_parallel", action="store_true", help="TP with the residual stream sharded over tokens")
     p.add_argument("--save", type=str, default=None, help="checkpoint directory written at the end")
     p.add_argument("--resume", type=str, default=None, help="checkpoint directory to resume from")
     p.add_argument("--metrics_out", type=str, default=None)
@@ -66,7 +67,7 @@ def main(argv=None):
                       method=args.method, top_k=args.top_k, bucket_cap_mb=args.bucket_cap,
                       sparse_embedding=not args.no_sparse_embedding, grad_checkpoint=args.grad_checkpoint,
                       zipf_s=args.zipf_s, seed=args.seed, num_layers=args.num_hidden_layers, kv_heads=args.kv_heads,
-                      data_pool=0)
+                      data_pool=0, sequence_parallel=args.sequence_parallel)
     trainer = Trainer(cfg, init_dist=False)
     coord = trainer.coordinator
     if args.data == "hf":

@@ -21,8 +21,9 @@ from .reducer import ZenDDP
 
 class HybridParallelPlugin:
     def __init__(self, tp_size: int = 1, pp_size: int = 1, precision: str = "bf16", ddp_bucket_cap_mb: float = 25,
-                 sparse_embedding: bool = True, overlap: bool = True):
+                 sparse_embedding: bool = True, overlap: bool = True, enable_sequence_parallelism: bool = False):
         self.tp_size, self.pp_size, self.precision = tp_size, pp_size, precision
+        self.enable_sequence_parallelism = enable_sequence_parallelism    # same switch as ColossalAI's plugin
         self.ddp_bucket_cap_mb = ddp_bucket_cap_mb
         self.sparse_embedding = sparse_embedding
         self.overlap = overlap
@@ -68,6 +69,8 @@ class Booster:
         if isinstance(model, BoostedModel):
             return model, optimizer, criterion, dataloader, lr_scheduler
         model = model.to(device=pl.device, dtype=pl.dtype)
+        if pl.enable_sequence_parallelism and pl.tp_size > 1 and hasattr(model, "enable_sequence_parallel"):
+            model.enable_sequence_parallel()
         emb_sync = None
         wte = getattr(model, "wte", None)
         if pl.sparse_embedding and wte is not None and pl.tp_size == 1 and max_tokens:
