@@ -116,7 +116,10 @@ def run_zen(args):
     tokens = trainer.tokens_per_step * args.steps
     value = tokens / (ms / 1e3)
     if not args.no_e2e:
-        e2e = {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        e2e = {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": e2e_ms / args.steps,
+               "timed": "host wall clock around K calls of Trainer.step(batch): H2D copy of the pinned host batch, the "
+                        "step, loss.item(); a separate pass over fresh batches, after the device-timed pass"}
     from zen_repro_b200.ops import gemm
 
     out = {
