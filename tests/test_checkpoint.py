@@ -38,3 +38,27 @@ def test_hf_checkpoint_loads_into_transformers(tmp_path):
     ours = a.model.unwrap()(ids, ids)
     theirs = hf(input_ids=ids, labels=ids).loss
     torch.testing.assert_close(ours, theirs, atol=1e-4, rtol=1e-4)
+
+
+def _tp2_save_worker(rank, world, path):
+    t = Trainer(TrainConfig(model="tiny-llama", micro_batch=2, seq_len=16, precision="fp32", lr=1e-2, data_pool=0, tp=2),
+                init_dist=False)
+    for _ in range(2):
+        t.step(next(t.data))
+    save_checkpoint(path, t)
+    return [t.step(next(t.data)) for _ in range(2)]
+
+
+def test_checkpoint_written_with_tp2_resumes_on_one_rank(tmp_path):
+    """Model shards and optimizer moments of a TP = 2 run are joined for a TP = 1 resume; the HF-format file holds the
+    full model either way."""
+    from _dist_util import run_gloo
+
+    want = run_gloo(_tp2_save_worker, 2, str(tmp_path))[0]
+    b = _mk()
+    assert load_checkpoint(str(tmp_path), b) == 2
+    got = [b.step(next(b.data)) for _ in range(2)]
+    assert got == pytest.approx(want, rel=1e-4, abs=1e-4)
+    sd = torch.load(tmp_path / "pytorch_model.bin", weights_only=True)
+    cfg = b.model_cfg
+    assert sd["model.embed_tokens.weight"].shape == (cfg.vocab_size, cfg.hidden_size)
