@@ -118,3 +118,35 @@ def test_mesh_groups():
     res = run_gloo(_mesh_worker, 4)
     assert res[0] == (0, 0, [0, 2], [0, 1])
     assert res[3] == (1, 1, [1, 3], [2, 3])
+
+
+def _heartbeat_worker(rank, world):
+    import time
+
+    import torch.distributed as dist
+
+    from zen_repro_b200.parallel.failure import Heartbeat, PeerLost
+
+    hb = Heartbeat(interval=0.05, timeout=0.6)
+    dist.barrier()
+    assert hb.lost() == []
+    x = torch.ones(4)
+    dist.all_reduce(x)                          # a step with everybody present
+    if rank == world - 1:
+        hb.stop()                               # leaves between steps: nothing of its own is in flight
+        time.sleep(2.5)                         # stays around so that the others' store reads keep working
+        return "left"
+    t0 = time.monotonic()
+    while time.monotonic() - t0 < 5.0:
+        try:
+            hb.assert_alive()                   # what the trainer does before every step
+        except PeerLost as e:
+            return e.ranks                      # noticed on the host; the next collective is never launched
+        time.sleep(0.05)
+    return "not noticed"
+
+
+def test_heartbeat_names_the_rank_that_left_between_steps():
+    res = run_gloo(_heartbeat_worker, 3)
+    assert res[2] == "left"
+    assert res[0] == [2] and res[1] == [2]

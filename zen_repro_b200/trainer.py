@@ -43,6 +43,7 @@ class TrainConfig:
     overlap: bool = True
     fused_tp: bool = True             # TP all-reduces fused into the GEMM epilogues (peer memory) instead of NCCL
     sequence_parallel: bool = False   # TP with the residual stream sharded over tokens: all-gather + GEMM / GEMM + reduce-scatter
+    heartbeat_s: float = 0.0          # > 0: host heartbeat between ranks, checked before every step (PeerLost is raised)
     cuda_graph: bool = False          # capture forward + backward + sync + optimizer once, then replay it every step
     graph_warmup: int = 2             # real steps launched from the host before the capture
 
@@ -86,6 +87,11 @@ class Trainer:
                         hook.engine_for(b.buffer.numel(), self.device)
             self.model.module.register_comm_hook(None, hook)
         self.step_count = 0
+        self.heartbeat = None
+        if cfg.heartbeat_s > 0 and dist.is_initialized() and dist.get_world_size() > 1:
+            from .parallel.failure import Heartbeat
+
+            self.heartbeat = Heartbeat(interval=cfg.heartbeat_s / 4, timeout=cfg.heartbeat_s)
         self._graph = None
         self.graph_launches_per_step = 0
         self._static_ids = self._static_loss = None
@@ -103,6 +109,8 @@ class Trainer:
 
     def step(self, batch: dict, read_loss: bool = True):
         """One optimizer step on a host batch.  Returns the loss as a float (read_loss) or a device tensor."""
+        if self.heartbeat is not None:
+            self.heartbeat.assert_alive()        # a peer that left between steps is noticed here, before any launch
         with trace_range("h2d"):
             ids = batch["input_ids"].to(self.device, non_blocking=True)
             labels = batch["labels"].to(self.device, non_blocking=True) if batch["labels"] is not batch["input_ids"] else ids
