@@ -62,3 +62,9 @@ def test_checkpoint_written_with_tp2_resumes_on_one_rank(tmp_path):
     sd = torch.load(tmp_path / "pytorch_model.bin", weights_only=True)
     cfg = b.model_cfg
     assert sd["model.embed_tokens.weight"].shape == (cfg.vocab_size, cfg.hidden_size)
+
+
+def test_check_health_is_clean_on_cpu():
+    a = _mk()
+    a.step(next(a.data))
+    assert not any(a.check_health().values())

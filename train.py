@@ -97,6 +97,9 @@ def main(argv=None):
             break
     mem = torch.cuda.max_memory_allocated() / 1024 ** 2 if torch.cuda.is_available() else 0.0
     coord.print_on_master(f"Max CUDA memory usage: {mem:.2f} MB")
+    health = trainer.check_health(raise_on_error=False)          # status words of the kernels (0 = clean)
+    if any(health.values()):
+        print(f"[rank {dist.get_rank() if dist.is_initialized() else 0}] kernel status: {health}", flush=True)
     dp = trainer.plugin.dp_size
     header = f"{args.model_name} method {args.method} topk {args.top_k} dp {dp}"
     sec_per_it = None

@@ -86,6 +86,7 @@ class Trainer:
                     if b.buffer.numel() > 4096:
                         hook.engine_for(b.buffer.numel(), self.device)
             self.model.module.register_comm_hook(None, hook)
+            self._hook = hook
         self.step_count = 0
         self.heartbeat = None
         if cfg.heartbeat_s > 0 and dist.is_initialized() and dist.get_world_size() > 1:
@@ -152,6 +153,36 @@ class Trainer:
             self.optimizer.step()
             self.model.module.zero_grad()
         return loss.detach()
+
+    def check_health(self, raise_on_error: bool = True) -> dict:
+        """Read (and clear) the status words that the kernels set instead of faulting: capacity overflow or an expired
+        wait in the sparse engines (element and row granule) and in the fused tensor-parallel GEMMs, and the error
+        codes of the tcgen05 GEMM / attention kernels.  Synchronises the device; meant for every N-th step and the end
+        of a run, not for the hot loop.  Non-zero entries mean that a step used incomplete data."""
+        out = {}
+        if self.device.type != "cuda":
+            return out
+        from .ops import attention as A
+        from .ops import gemm as G
+
+        torch.cuda.synchronize()
+        out["gemm"] = int(G.gemm_error())
+        out["attention"] = int(A.attention_error())
+        emb = getattr(self.model.module, "embedding_sync", None)
+        if emb is not None:
+            out["embedding_rows"] = int(emb.check())
+        hook = getattr(self, "_hook", None)
+        if hook is not None:
+            for numel, eng in hook.state["engines"].items():
+                out[f"sparse_{numel}"] = int(eng.check())
+        ws = getattr(self.model.unwrap(), "tp_ws", None)
+        if ws is not None:
+            out["tp_fused"] = int(ws.check())
+        bad = {k: v for k, v in out.items() if v}
+        if bad and raise_on_error:
+            raise RuntimeError(f"kernel status words report errors: {bad} (1 = record overflow, 2 = gather overflow, "
+                               f"4 = wait expired, 8 = overflow at a peer, 16 = bad argument)")
+        return out
 
     def bytes_per_step(self, batch: dict) -> tuple[int, int]:
         h2d = batch["input_ids"].numel() * batch["input_ids"].element_size()
