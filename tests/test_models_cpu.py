@@ -87,3 +87,20 @@ def test_presets_have_published_sizes():
     assert abs(get_config("gpt2").num_params() / 1e6 - 124.4) < 0.5
     assert abs(get_config("llama-3-8b").num_params() / 1e9 - 8.03) < 0.05
     assert abs(get_config("gemma-2b").num_params() / 1e9 - 2.51) < 0.05
+
+
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-gpt2", "tiny-gemma", "tiny-opt"])
+@pytest.mark.parametrize("tp", [2, 4])
+def test_unshard_inverts_shard(name, tp):
+    """Joining the TP shards of a state dict gives back the full one (fused qkv and gate|up rows go back to their
+    heads / halves, a KV head replicated over ranks is taken once, the padded vocabulary is cut)."""
+    from zen_repro_b200.models.sharding import shard_state_dict, unshard_state_dicts
+
+    cfg = get_config(name)
+    if cfg.num_heads % tp or cfg.intermediate_size % tp:
+        pytest.skip("shape does not divide")
+    sd = build_model(cfg, dtype=torch.float32).state_dict()
+    back = unshard_state_dicts([shard_state_dict(sd, cfg, r, tp) for r in range(tp)], cfg)
+    assert set(back) == set(sd)
+    for k in sd:
+        assert torch.equal(back[k], sd[k]), k
