@@ -150,3 +150,26 @@ def test_heartbeat_names_the_rank_that_left_between_steps():
     res = run_gloo(_heartbeat_worker, 3)
     assert res[2] == "left"
     assert res[0] == [2] and res[1] == [2]
+
+
+def test_gradient_accumulation_over_micro_batches_with_no_sync():
+    """Two micro-batches under ``no_sync`` and a third with synchronisation: the bucket views hold the sum of all three
+    (the first writer after ``zero_grad`` overwrites, every later writer accumulates)."""
+    from zen_repro_b200.parallel.reducer import ZenDDP
+
+    torch.manual_seed(0)
+    a = build_model("tiny-llama", dtype=torch.float32)
+    b = build_model("tiny-llama", dtype=torch.float32)
+    b.load_state_dict(a.state_dict())
+    batches = [torch.randint(0, 1000, (2, 16)) for _ in range(3)]
+    for ids in batches:
+        a(ids, ids).backward()
+    ddp = ZenDDP(b, None, 0.05, None)
+    ddp.zero_grad()
+    with ddp.no_sync():
+        for ids in batches[:2]:
+            ddp(ids, ids).backward()
+    ddp(batches[2], batches[2]).backward()
+    ddp.finalize_grads()
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        torch.testing.assert_close(q.grad, p.grad, atol=1e-5, rtol=1e-4, msg=lambda m, n=n: f"{n}: {m}")
