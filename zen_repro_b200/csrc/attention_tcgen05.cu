@@ -306,7 +306,7 @@ template <int HD>
 struct DqCfg {
   static constexpr int ATOMS = HD / 64;
   static constexpr int TILE_BYTES = 128 * HD * 2;
-  static constexpr int KV_STAGES = (HD <= 64) ? 2 : 1;
+  static constexpr int KV_STAGES = (HD <= 128) ? 2 : 1;     // hd 128: 64 + 128 + 32 KB = 224 KB, still one CTA's worth
   static constexpr int DS_BYTES = 128 * 128 * 2;
   static constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + DS_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
