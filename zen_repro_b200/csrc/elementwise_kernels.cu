@@ -491,9 +491,12 @@ norm_dwdb_partial_kernel(const T* __restrict__ dy, const T* __restrict__ h, cons
 }
 
 // out[c] (+)= sum_p part[p][c], cast to T.  CTA = 32 columns x 32 part-lanes; fixed summation order.
+// blockIdx.y == 1 reduces a second (part, out) pair of the same shape in the same launch (dw and db of a LayerNorm).
 template <typename T>
 __global__ void __launch_bounds__(1024)
-colreduce_kernel(const float* __restrict__ part, T* __restrict__ out, int nparts, int cols, int accumulate) {
+colreduce_kernel(const float* __restrict__ part, T* __restrict__ out, int nparts, int cols, int accumulate,
+                 const float* __restrict__ part2 = nullptr, T* __restrict__ out2 = nullptr) {
+  if (blockIdx.y == 1) { part = part2; out = out2; }
   __shared__ float sh[32][33];
   const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + x;
@@ -1119,8 +1122,8 @@ int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd
       });
       if (layer) norm_dwdb_partial_kernel<T, true><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, 32);
       else norm_dwdb_partial_kernel<T, false><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, 32);
-      colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate);
-      if (layer && db) colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_db, (T*)db, parts, cols, accumulate);
+      if (layer && db) colreduce_kernel<T><<<dim3((cols + 31) / 32, 2), 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate, part_db, (T*)db);
+      else colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate);
     });
     return (int)cudaGetLastError();
   }
@@ -1140,8 +1143,8 @@ int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd
     });
     if (layer) norm_dwdb_partial_kernel<T, true><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, rpc);
     else norm_dwdb_partial_kernel<T, false><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, rpc);
-    colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate);
-    if (layer && db) colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_db, (T*)db, parts, cols, accumulate);
+    if (layer && db) colreduce_kernel<T><<<dim3((cols + 31) / 32, 2), 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate, part_db, (T*)db);
+    else colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate);
   });
   return (int)cudaGetLastError();
 }
