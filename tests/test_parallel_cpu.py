@@ -173,3 +173,24 @@ def test_gradient_accumulation_over_micro_batches_with_no_sync():
     ddp.finalize_grads()
     for (n, p), q in zip(a.named_parameters(), b.parameters()):
         torch.testing.assert_close(q.grad, p.grad, atol=1e-5, rtol=1e-4, msg=lambda m, n=n: f"{n}: {m}")
+
+
+def _verify_worker(rank, world):
+    import torch.distributed as dist
+
+    from zen_repro_b200.parallel.hooks import verified_or_dense
+
+    x = torch.full((8,), float(rank + 1))
+    wrong = torch.zeros(8)                                     # what a sparse call that lost records might return
+    stats = {}
+    ok = verified_or_dense(wrong.clone(), 0, x, None, stats)   # clean status everywhere: the sparse result stands
+    bad = verified_or_dense(wrong.clone(), 4 if rank == 1 else 0, x, None, stats)   # one rank timed out: all fall back
+    return ok.tolist(), bad.tolist(), stats
+
+
+def test_hook_recovery_agrees_on_the_status_and_falls_back_to_dense():
+    res = run_gloo(_verify_worker, 3)
+    for ok, bad, stats in res:
+        assert ok == [0.0] * 8
+        assert bad == [6.0] * 8                                # 1 + 2 + 3 on every rank, also on those that saw no error
+        assert stats["last_status"] == 4 and stats["fallbacks"] == 1

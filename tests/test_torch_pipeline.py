@@ -61,3 +61,51 @@ def test_gloo_two_ranks_zipf_one_percent(method):
 def test_gloo_four_ranks_bf16():
     errs = run_gloo(_worker, 4, 100003, 0.05, 3, "bfloat16")
     assert max(errs) <= 0.07      # one bf16 rounding of a sum of up to four N(0,1) values
+
+
+def _emul_worker(rank, world, faults, density, max_density):
+    import torch.distributed as dist
+
+    from zen_repro_b200.sparse.emulated import EmulatedSparseAllReduce
+
+    n = 1 << 14
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.zeros(n)
+    idx = torch.randperm(n, generator=g)[: int(n * density)]
+    x[idx] = torch.randn(idx.numel(), generator=g)
+    want = x.clone()
+    dist.all_reduce(want)
+    eng = EmulatedSparseAllReduce(n, None, max_density=max_density, wait_s=0.6, faults=faults)
+    got = eng(x, method=3)
+    again = eng(x, method=2)                              # the next call starts from a clean epoch
+    return (float((got - want).abs().max()), eng.last_status if faults else 0, float((again - want).abs().max()),
+            eng.last_fallback)
+
+
+def test_emulated_push_protocol_matches_dense_sum():
+    from _dist_util import run_gloo
+
+    for err, status, err2, fb in run_gloo(_emul_worker, 3, None, 0.01, 0.12):
+        assert err < 1e-5 and err2 < 1e-5 and status == 0 and not fb
+
+
+@pytest.mark.parametrize("faults,bit", [({"mute": [1]}, 4), ({"short": [2]}, 8), ({"slow": {0: 1.5}}, 4)])
+def test_emulated_faults_raise_status_bits_and_fall_back_to_dense(faults, bit):
+    """A peer that never pushes (or pushes late) makes the bounded waits expire (bit 4); a mail that claims fewer
+    records than were sent is flagged as loss at a peer (bit 8).  Every rank sees the agreed status and returns the
+    dense all-reduce instead, so the result is still the exact sum."""
+    from _dist_util import run_gloo
+
+    res = run_gloo(_emul_worker, 3, faults, 0.01, 0.12)
+    for err, status, err2, fb in res:
+        assert status & bit, (status, bit)
+        assert fb and err < 1e-5 and err2 < 1e-5
+
+
+def test_emulated_capacity_overflow_is_reported_not_written_past_the_inbox():
+    from _dist_util import run_gloo
+
+    # 20 % non-zeros against inboxes sized for 1 %: senders truncate and flag, receivers learn of it through the mail
+    res = run_gloo(_emul_worker, 2, {"none": []}, 0.2, 0.01)
+    for err, status, err2, fb in res:
+        assert status & (1 | 8) and fb and err < 1e-5

@@ -112,10 +112,31 @@ def _future(value, like_torch: bool):
     return _Ready(value)
 
 
+def verified_or_dense(out: torch.Tensor, status: int, masked: torch.Tensor, group, stats: dict | None = None) -> torch.Tensor:
+    """The recovery step of the hook's ``verify`` mode: agree on the status word over the data-parallel group (so that
+    every rank takes the same branch) and, when any rank saw overflow or an expired wait, return the dense all-reduce
+    of the thresholded bucket instead of the sparse result."""
+    st = torch.tensor([int(status)], dtype=torch.int32, device=masked.device)
+    dist.all_reduce(st, op=dist.ReduceOp.MAX, group=group)
+    agreed = int(st.item())
+    if stats is not None:
+        stats["last_status"] = agreed
+        stats["fallbacks"] = stats.get("fallbacks", 0) + (1 if agreed else 0)
+    if not agreed:
+        return out
+    dense = masked.clone()
+    dist.all_reduce(dense, group=group)
+    return dense
+
+
 def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, engines: dict | None = None,
-                       skip_first: bool = False, torch_future: bool = True, max_density: float | None = None):
+                       skip_first: bool = False, torch_future: bool = True, max_density: float | None = None,
+                       verify: bool = False):
     """Build the hook.  ``engines`` caches one CUDA ``SparseAllReduce`` per bucket size (create them with
-    ``prepare_engines`` before training so that buffer exchange does not happen inside backward)."""
+    ``prepare_engines`` before training so that buffer exchange does not happen inside backward).  ``verify``: read the
+    engine's status word after every bucket (one device synchronisation per bucket) and replace the result by the dense
+    all-reduce when a capacity overflow or an expired wait was reported; off by default, where the status is left for
+    ``Trainer.check_health``."""
     state = {"skip": skip_first, "engines": engines if engines is not None else {}}
     P = dist.get_world_size(dp_group) if dist.is_initialized() else 1
     density = max_density if max_density is not None else min(1.0, top_k / 100.0 * 2.0 + 0.01)
@@ -143,6 +164,9 @@ def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, e
         if buf.device.type == "cuda" and buf.numel() > SMALL_BUCKET:
             eng = engine_for(buf.numel(), buf.device)
             out = eng(buf, method=method, threshold=thr)
+            if verify:
+                masked = buf if thr is None else torch.where(buf.abs() >= thr.to(buf.dtype), buf, torch.zeros_like(buf))
+                out = verified_or_dense(out, eng.check(), masked, dp_group, state)
         else:
             masked = buf if thr is None else torch.where(buf.abs() >= thr.to(buf.dtype), buf, torch.zeros_like(buf))
             if buf.numel() <= SMALL_BUCKET:
