@@ -13,7 +13,6 @@ tensor parallelism from ColossalAI's shardformer (train.py:117-123, 149-157).
 """
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.distributed as dist

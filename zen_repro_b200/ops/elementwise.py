@@ -8,7 +8,6 @@ tests.  The autograd wrappers that models use live in ``ops/autograd.py``.
 from __future__ import annotations
 
 import ctypes
-import math
 
 import torch
 import torch.nn.functional as F

@@ -10,7 +10,6 @@ ColossalAI's ``HybridAdam`` under the bf16 mixed-precision plugin
 from __future__ import annotations
 
 import ctypes
-import math
 
 import torch
 

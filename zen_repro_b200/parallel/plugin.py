@@ -11,7 +11,6 @@ unpacks (train.py:117-123, 157); the boosted model exposes ``dp_group``, ``tp_gr
 from __future__ import annotations
 
 import torch
-import torch.distributed as dist
 import torch.nn as nn
 
 from .embedding_sync import EmbeddingRowSync

@@ -9,7 +9,7 @@ optimizer, hook registration: train.py:109-185) and runs the same loop body (tra
 from __future__ import annotations
 
 import dataclasses
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
