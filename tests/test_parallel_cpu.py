@@ -194,3 +194,29 @@ def test_hook_recovery_agrees_on_the_status_and_falls_back_to_dense():
         assert ok == [0.0] * 8
         assert bad == [6.0] * 8                                # 1 + 2 + 3 on every rank, also on those that saw no error
         assert stats["last_status"] == 4 and stats["fallbacks"] == 1
+
+
+def _tp_dp_worker(rank, world, sparse_tp):
+    from zen_repro_b200.trainer import TrainConfig, Trainer
+
+    t = Trainer(TrainConfig(model="tiny-llama", micro_batch=2, seq_len=16, precision="fp32", lr=1e-2, data_pool=0, tp=2,
+                            sparse_embedding=True, sparse_embedding_under_tp=sparse_tp, bucket_cap_mb=0.05), init_dist=False)
+    m = t.model.unwrap()
+    assert (m.sparse_sink is not None) == sparse_tp and bool(getattr(m.wte, "zen_sparse_only", False)) == sparse_tp
+    losses = [t.step(next(t.data)) for _ in range(4)]
+    if sparse_tp:
+        assert int(m.sparse_sink.last_count) > 0           # rows went through the sparse sink
+    w = m.wte.detach().clone()
+    return losses, w
+
+
+def test_vocab_sharded_embedding_rows_sync_sparsely_over_dp_under_tp():
+    """TP = 2 x DP = 2 on four CPU ranks: the gradient of the vocabulary-sharded embedding travels over the DP group
+    as sparse rows and training follows the dense synchronisation of the same run."""
+    sparse = run_gloo(_tp_dp_worker, 4, True)
+    dense = run_gloo(_tp_dp_worker, 4, False)
+    for r in range(4):
+        assert sparse[r][0] == pytest.approx(dense[r][0], rel=1e-5, abs=1e-5)
+        torch.testing.assert_close(torch.as_tensor(sparse[r][1]), torch.as_tensor(dense[r][1]), atol=1e-6, rtol=1e-5)
+    # the two DP replicas of a TP coordinate hold the same embedding shard
+    torch.testing.assert_close(torch.as_tensor(sparse[0][1]), torch.as_tensor(sparse[2][1]), atol=0, rtol=0)

@@ -245,7 +245,9 @@ class DecoderLM(nn.Module):
         lo, hi = self.vocab_start, self.vocab_start + self.vocab_local
         mine = (ids >= lo) & (ids < hi)
         local = torch.where(mine, ids - lo, torch.zeros_like(ids))
-        x = O.embedding(local, self.wte, None, seq, 0, cfg.embed_scale, None)
+        # with a sink the lookup gradient leaves as (rows of this vocabulary shard, values); tokens of other shards
+        # map to row 0 with a zero gradient (their output is masked below)
+        x = O.embedding(local, self.wte, None, seq, 0, cfg.embed_scale, self.sparse_sink)
         x = x * mine.unsqueeze(-1).to(x.dtype)
         x = O.reduce_from_tp(x, self.tp_group)
         if self.wpe is not None:

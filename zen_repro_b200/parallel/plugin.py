@@ -20,9 +20,12 @@ from .reducer import ZenDDP
 
 class HybridParallelPlugin:
     def __init__(self, tp_size: int = 1, pp_size: int = 1, precision: str = "bf16", ddp_bucket_cap_mb: float = 25,
-                 sparse_embedding: bool = True, overlap: bool = True, enable_sequence_parallelism: bool = False):
+                 sparse_embedding: bool = True, overlap: bool = True, enable_sequence_parallelism: bool = False,
+                 sparse_embedding_under_tp: bool = False):
         self.tp_size, self.pp_size, self.precision = tp_size, pp_size, precision
         self.enable_sequence_parallelism = enable_sequence_parallelism    # same switch as ColossalAI's plugin
+        # row-sparse synchronisation of the vocabulary-sharded embedding gradient over the DP group when TP > 1
+        self.sparse_embedding_under_tp = sparse_embedding_under_tp
         self.ddp_bucket_cap_mb = ddp_bucket_cap_mb
         self.sparse_embedding = sparse_embedding
         self.overlap = overlap
@@ -72,7 +75,7 @@ class Booster:
             model.enable_sequence_parallel()
         emb_sync = None
         wte = getattr(model, "wte", None)
-        if pl.sparse_embedding and wte is not None and pl.tp_size == 1 and max_tokens:
+        if pl.sparse_embedding and wte is not None and (pl.tp_size == 1 or pl.sparse_embedding_under_tp) and max_tokens:
             emb_sync = EmbeddingRowSync(wte.shape[0], wte.shape[1], max_tokens, pl.dp_group, dtype=pl.dtype,
                                         device=pl.device)
             emb_sync.target_param = wte

@@ -43,6 +43,7 @@ class TrainConfig:
     overlap: bool = True
     fused_tp: bool = True             # TP all-reduces fused into the GEMM epilogues (peer memory) instead of NCCL
     sequence_parallel: bool = False   # TP with the residual stream sharded over tokens: all-gather + GEMM / GEMM + reduce-scatter
+    sparse_embedding_under_tp: bool = False   # TP > 1: sync the vocabulary-sharded embedding gradient as sparse rows over DP
     heartbeat_s: float = 0.0          # > 0: host heartbeat between ranks, checked before every step (PeerLost is raised)
     cuda_graph: bool = False          # capture forward + backward + sync + optimizer once, then replay it every step
     graph_warmup: int = 2             # real steps launched from the host before the capture
@@ -59,7 +60,8 @@ class Trainer:
         self.coordinator = DistCoordinator()
         self.plugin = HybridParallelPlugin(tp_size=cfg.tp, pp_size=1, precision=cfg.precision,
                                            ddp_bucket_cap_mb=cfg.bucket_cap_mb,
-                                           sparse_embedding=cfg.sparse_embedding and cfg.method == 0, overlap=cfg.overlap)
+                                           sparse_embedding=cfg.sparse_embedding and cfg.method == 0, overlap=cfg.overlap,
+                                           sparse_embedding_under_tp=cfg.sparse_embedding_under_tp)
         self.booster = Booster(self.plugin)
         self.device = self.plugin.device
         mc = get_config(cfg.model, num_layers=cfg.num_layers, num_kv_heads=cfg.kv_heads,
