@@ -110,7 +110,7 @@ class _Clocks:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons)}
 
 
-def run_reference(args, preset):
+def run_reference(args, preset, models=None):
     import torch
 
     if not torch.cuda.is_available():
@@ -119,8 +119,6 @@ def run_reference(args, preset):
         _unavailable("needs tensor parallelism from ColossalAI's shardformer, which cannot be installed offline")
     comm, compress_with_allgather = _load_reference()
     import torch.distributed as dist
-    import transformers
-    from torch.nn.parallel import DistributedDataParallel as DDP
 
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -128,9 +126,32 @@ def run_reference(args, preset):
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    out = _measure_reference(args, preset, comm, compress_with_allgather, dev, rank, world, local)
+    if out is None:
+        _unavailable(f"no HuggingFace config for {preset['model']} in the reference arm")
+    if preset["model"] == "gpt2" and models and not getattr(args, "no_extra", False):
+        # the second model of the benchmark, measured in the same process after the headline with the same K and W
+        try:
+            r = _measure_reference(args, models["gemma-2b"], comm, compress_with_allgather, dev, rank, world, local)
+            out["extra"] = {"gemma-2b": {k: r[k] for k in ("value", "unit", "ms_per_step", "config", "e2e")}}
+        except Exception as ex:
+            out["extra"] = {"gemma-2b": {"error": f"{type(ex).__name__}: {ex}"[:300]}}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    dist.destroy_process_group()
+
+
+def _measure_reference(args, preset, comm, compress_with_allgather, dev, rank, world, local):
+    import gc
+
+    import torch
+    import torch.distributed as dist
+    import transformers
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
     cfg = _hf_config(preset["model"])
     if cfg is None:
-        _unavailable(f"no HuggingFace config for {preset['model']} in the reference arm")
+        return None
     if args.num_layers:
         cfg.num_hidden_layers = args.num_layers
     torch.manual_seed(0)
@@ -210,6 +231,7 @@ def run_reference(args, preset):
            "clocks": ck,
            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": mb * seq * 8, "d2h_bytes_per_step": 4},
            "gpu_launches": None}
-    if rank == 0:
-        print(json.dumps(out), flush=True)
-    dist.destroy_process_group()
+    del ddp, model, optimizer, dev_batches, lba, step, custom_comm_hook
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out

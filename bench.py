@@ -10,7 +10,9 @@ Default config: GPT-2 small (12 layers, d 768, 12 heads, vocab 50257), bf16, dat
 the tied token-embedding gradient and dense bucket all-reduce elsewhere.  Weak scaling (per-GPU batch
 fixed).  `value` is device-timed (CUDA events around exactly K optimizer steps, max over ranks);
 `e2e` times the same K steps through ``Trainer.step`` including the pinned-host -> device copy of each
-batch and the device -> host read of each loss.  One JSON line is printed by rank 0.
+batch and the device -> host read of each loss.  One JSON line is printed by rank 0.  With the default
+config the line also carries ``extra``: Gemma-2B (same K and W) and GPT-2 with the framework's own top-k
+hook (``--method 3 --top_k 1``, the reference arm's configuration), measured in the same process afterwards.
 """
 from __future__ import annotations
 
@@ -42,34 +44,42 @@ def parse():
     ap.add_argument("--num_layers", type=int, default=None)
     ap.add_argument("--micro_batch", type=int, default=None)
     ap.add_argument("--no_e2e", action="store_true")
+    ap.add_argument("--no_extra", action="store_true", help="skip the extra configurations measured after the GPT-2 headline")
+    ap.add_argument("--bucket_cap_mb", type=float, default=None)
+    ap.add_argument("--dense_embedding_under_tp", action="store_true",
+                    help="TP runs: keep the vocabulary-sharded embedding gradient in the dense buckets")
     ap.add_argument("--sequence_parallel", action="store_true", help="TP layers with the residual stream sharded over tokens")
     ap.add_argument("--no_graph", action="store_true", help="launch every kernel from the host instead of replaying a CUDA graph")
     return ap.parse_args()
 
 
-def run_zen(args):
+def _measure(args, config_name: str, method: int, top_k: float, e2e_pass: bool) -> dict:
+    """Build a ``Trainer`` for one configuration, run W warm-up steps, device-time exactly K steps (CUDA events, max over
+    ranks) and, with ``e2e_pass``, time K more steps through ``Trainer.step`` from pinned host batches.  The trainer is
+    torn down (graph dropped, peer regions closed) before returning, so that the next configuration starts clean."""
     import torch
     import torch.distributed as dist
 
     from zen_repro_b200 import _native
+    from zen_repro_b200.ops import gemm
     from zen_repro_b200.trainer import TrainConfig, Trainer
     from zen_repro_b200.utils.clocks import ClockSampler
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world > 1 or "RANK" in os.environ:
-        from zen_repro_b200.parallel import launch_from_torch
-
-        launch_from_torch()
-    preset = dict(MODELS[args.config])
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    preset = dict(MODELS[config_name])
     if args.micro_batch:
         preset["micro_batch"] = args.micro_batch
-    if preset["tp"] > world:
+    if preset["tp"] > world or world % preset["tp"]:
         preset["tp"] = 1
-    cfg = TrainConfig(method=args.method, top_k=args.top_k, num_layers=args.num_layers, data_pool=max(4, min(8, args.steps)),
-                      cuda_graph=not args.no_graph, sequence_parallel=args.sequence_parallel, **preset)
+    extra_cfg = {}
+    if args.bucket_cap_mb:
+        extra_cfg["bucket_cap_mb"] = args.bucket_cap_mb
+    cfg = TrainConfig(method=method, top_k=top_k, num_layers=args.num_layers, data_pool=max(4, min(8, args.steps)),
+                      cuda_graph=not args.no_graph, sequence_parallel=args.sequence_parallel,
+                      sparse_embedding_under_tp=preset["tp"] > 1 and not args.dense_embedding_under_tp, **extra_cfg, **preset)
     trainer = Trainer(cfg, init_dist=False)
     dev = trainer.device
-    rank = dist.get_rank() if dist.is_initialized() else 0
 
     def barrier():
         if dist.is_initialized():
@@ -98,8 +108,8 @@ def run_zen(args):
         launches += trainer.graph_launches_per_step * args.steps
     ms = s.elapsed_time(e)
     # end to end through the public API: pinned host batch -> device, step, loss -> host
-    e2e = None
-    if not args.no_e2e:
+    e2e, e2e_ms, h2d, d2h = None, 0.0, 0, 0
+    if e2e_pass:
         batches = [next(trainer.data) for _ in range(args.steps)]
         h2d, d2h = trainer.bytes_per_step(batches[0])
         barrier()
@@ -109,40 +119,70 @@ def run_zen(args):
         barrier()
         e2e_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop() if sampler is not None else None
-    t = torch.tensor([ms, e2e_ms if not args.no_e2e else 0.0], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     if dist.is_initialized():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
+    health = trainer.check_health(raise_on_error=False)
     tokens = trainer.tokens_per_step * args.steps
-    value = tokens / (ms / 1e3)
-    if not args.no_e2e:
+    if e2e_pass:
         e2e = {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "ms_per_step": e2e_ms / args.steps,
                "timed": "host wall clock around K calls of Trainer.step(batch): H2D copy of the pinned host batch, the "
                         "step, loss.item(); a separate pass over fresh batches, after the device-timed pass"}
-    from zen_repro_b200.ops import gemm
-
+    ddp = trainer.model.module
     out = {
-        "metric": "train tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": "train tokens/sec", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic Zipf tokens, random-init weights", "impl": "zen",
         "config": {"model": cfg.model, "global_batch": cfg.micro_batch * trainer.plugin.dp_size, "seq_len": cfg.seq_len,
                    "parallelism": f"dp{trainer.plugin.dp_size}" + (f"xtp{cfg.tp}" if cfg.tp > 1 else "") + ("+sp" if (cfg.tp > 1 and cfg.sequence_parallel) else ""),
-                   "method": cfg.method, "sparse_embedding": cfg.sparse_embedding and cfg.method == 0,
+                   "method": cfg.method, "top_k": cfg.top_k,
+                   # what was actually built, not what was asked for
+                   "embedding_row_sync": ddp.embedding_sync is not None, "bucket_cap_mb": cfg.bucket_cap_mb,
+                   "n_buckets": len(ddp.buckets), "grad_checkpoint": bool(trainer.model_cfg.grad_checkpoint),
                    "num_layers": trainer.model_cfg.num_layers, "cuda_graph": bool(trainer._graph is not None),
                    "l2": "per-step working set (weights + activations, > 1 GB) exceeds the 126 MB L2"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "gemm_error": gemm.gemm_error(),
+        "kernel_status": {k: v for k, v in health.items() if v},
     }
+    trainer.close()
+    del trainer, dev_batches
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_zen(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 or "RANK" in os.environ:
+        from zen_repro_b200.parallel import launch_from_torch
+
+        launch_from_torch()
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    out = _measure(args, args.config, args.method, args.top_k, not args.no_e2e)
+    if args.config == "gpt2" and args.method == 0 and not args.no_extra:
+        # measured in the same process after the headline, same K and W: the second model of the benchmark, and the
+        # framework's own top-k hook in the reference arm's configuration (method 3, top_k 1; train.py:99-100)
+        extra = {}
+        for name, (cfg_name, method, top_k) in {"gemma-2b": ("gemma-2b", 0, 1.0), "gpt2_method3": ("gpt2", 3, 1.0)}.items():
+            try:
+                r = _measure(args, cfg_name, method, top_k, True)
+                extra[name] = {k: r[k] for k in ("value", "unit", "ms_per_step", "config", "e2e", "gpu_launches", "kernel_status")}
+            except Exception as ex:  # a failed extra must not cost the headline
+                extra[name] = {"error": f"{type(ex).__name__}: {ex}"[:300]}
+        out["extra"] = extra
     if rank == 0:
         print(json.dumps(out), flush=True)
     if dist.is_initialized():
         dist.barrier()
         torch.cuda.synchronize()
-    # leave without tearing down NCCL: a captured graph still references its communicator, and destroying the
-    # process group under it can block at exit
-    sys.stdout.flush()
-    sys.stderr.flush()
-    os._exit(0)
+        dist.destroy_process_group()
 
 
 def main():
@@ -151,7 +191,7 @@ def main():
         if args.impl == "reference":
             from baseline.reference_arm import run_reference
 
-            run_reference(args, MODELS[args.config])
+            run_reference(args, MODELS[args.config], MODELS)
         else:
             run_zen(args)
     except SystemExit:

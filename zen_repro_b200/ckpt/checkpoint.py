@@ -42,6 +42,11 @@ def save_checkpoint(path: str, trainer) -> None:
         }
         state["tp_size"] = mesh.tp_size
         torch.save(state, os.path.join(path, f"trainer_state_tp{mesh.tp_rank}.pt"))
+        if mesh.tp_rank == 0:             # shards of an earlier save with a larger TP size would be stale
+            t = mesh.tp_size
+            while os.path.exists(os.path.join(path, f"trainer_state_tp{t}.pt")):
+                os.remove(os.path.join(path, f"trainer_state_tp{t}.pt"))
+                t += 1
         if mesh.tp_size == 1:
             hf = {k: v.cpu() for k, v in model.hf_state_dict().items()}
             torch.save(hf, os.path.join(path, "pytorch_model.bin"))
@@ -62,10 +67,16 @@ def save_checkpoint(path: str, trainer) -> None:
 
 
 def _saved_tp_size(path: str) -> int:
-    n = 0
-    while os.path.exists(os.path.join(path, f"trainer_state_tp{n}.pt")):
-        n += 1
-    return n
+    """Tensor-parallel size recorded in shard 0 (older checkpoints without the field: the number of shard files)."""
+    f0 = os.path.join(path, "trainer_state_tp0.pt")
+    if not os.path.exists(f0):
+        return 0
+    tp = torch.load(f0, map_location="cpu", weights_only=False).get("tp_size")
+    if tp is None:
+        tp = 0
+        while os.path.exists(os.path.join(path, f"trainer_state_tp{tp}.pt")):
+            tp += 1
+    return int(tp)
 
 
 def _resharded_state(path: str, trainer, saved_tp: int) -> dict:
@@ -75,6 +86,10 @@ def _resharded_state(path: str, trainer, saved_tp: int) -> dict:
     mesh, mc = trainer.plugin.pg_mesh, trainer.model_cfg
     states = [torch.load(os.path.join(path, f"trainer_state_tp{t}.pt"), map_location="cpu", weights_only=False)
               for t in range(saved_tp)]
+    for t, st in enumerate(states):      # shards of one save only: a stale file of an earlier save must not be joined in
+        if st.get("tp_size", saved_tp) != saved_tp or st["step"] != states[0]["step"]:
+            raise RuntimeError(f"checkpoint shard {t} in {path} (tp_size {st.get('tp_size')}, step {st['step']}) does not "
+                               f"belong to the save of shard 0 (tp_size {saved_tp}, step {states[0]['step']})")
     names = list(states[0]["model"].keys())                # parameter order = optimizer index order
     out = dict(states[0])
     out["model"] = shard_state_dict(unshard_state_dicts([s["model"] for s in states], mc), mc, mesh.tp_rank, mesh.tp_size)

@@ -528,6 +528,12 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
   if (splits > nkb) splits = nkb;
   int kb_per = (nkb + splits - 1) / splits;
   splits = (nkb + kb_per - 1) / kb_per;                     // no empty slice
+  if (splits > 1) {
+    // The two slices of a tile hand each other half of the columns and wait for it: both must be resident at the
+    // same time, i.e. every (tile, slice) unit needs its own cluster in the one wave that the launch has.
+    const uint64_t units = (uint64_t)((M + 255) / 256) * ((N + 255) / 256) * (uint64_t)splits;
+    if (units > (uint64_t)(zen_tmap::sm_count() / 2)) { splits = 1; kb_per = nkb; }
+  }
   const int bn = (splits > 1) ? 256 : pick_pair_bn(M, N);
   if (splits > 1) {
     const uint64_t tiles = (uint64_t)((M + 255) / 256) * ((N + 255) / 256);

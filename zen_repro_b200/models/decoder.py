@@ -187,6 +187,13 @@ class DecoderLM(nn.Module):
             self.tp_ws = ws
         return self
 
+    def disable_fused_tp(self):
+        """Back to GEMM + NCCL all-reduce for the tensor-parallel layers (the workspace stays allocated)."""
+        for b in self.blocks:
+            b.tp_ws = None
+        self._tp_ws_off, self.tp_ws = getattr(self, "tp_ws", None), None
+        return self
+
     def enable_sequence_parallel(self, on: bool = True):
         """Shard the residual stream over the tokens of the TP group (tokens per step must divide by the group size).
         Norm parameters and the biases of row-parallel layers then see only this rank's tokens; their gradients are

@@ -18,6 +18,19 @@ _FORCE_TORCH = os.environ.get("ZEN_GEMM", "") == "torch"
 _PAIR_MODE = os.environ.get("ZEN_GEMM_2CTA", "auto")      # auto | 0 | 1
 
 
+_clusters_cached = [0]
+
+
+def _clusters() -> int:
+    """CTA pairs the device runs at once (one per two SMs; 74 on a B200)."""
+    if not _clusters_cached[0]:
+        n = 148
+        if torch.cuda.is_available():
+            n = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        _clusters_cached[0] = max(1, n // 2)
+    return _clusters_cached[0]
+
+
 def use_pair_kernel(M: int, N: int, K: int) -> bool:
     """CTA-pair (256 x 256 tile) kernel when the problem fills the 74 clusters reasonably well."""
     if _PAIR_MODE == "0":
@@ -27,8 +40,8 @@ def use_pair_kernel(M: int, N: int, K: int) -> bool:
     if M < 512 or N < 256:
         return False
     tiles = ((M + 255) // 256) * ((N + 255) // 256)
-    waves = -(-tiles // 74)
-    eff = tiles / (waves * 74.0)
+    waves = -(-tiles // _clusters())
+    eff = tiles / float(waves * _clusters())
     pad = (N / (((N + 255) // 256) * 256.0)) * (M / (((M + 255) // 256) * 256.0))
     score = eff * pad
     return score >= 0.6
@@ -49,9 +62,10 @@ def split_k_choice(M: int, N: int, K: int) -> int:
         return 1
     tm, tn = (M + 255) // 256, (N + 255) // 256
     tiles = tm * tn
-    if (M * N) / (tiles * 65536.0) < 0.75 or tiles > 37:
+    # both slices of every tile must be resident in the launch's single wave of clusters (they wait for each other)
+    if (M * N) / (tiles * 65536.0) < 0.75 or tiles * 2 > _clusters():
         return 1
-    splits = min(74 // tiles, (K // 64) // 8, 2)          # two slices: the fast store path of the kernel
+    splits = min(_clusters() // tiles, (K // 64) // 8, 2)  # two slices: the fast store path of the kernel
     return splits if splits >= 2 and tiles * splits * 2 * 128 * 256 <= _WS_FLOATS and tiles * 16 <= _N_COUNTERS else 1
 
 

@@ -115,9 +115,17 @@ class FusedAdamW(torch.optim.Optimizer):
                     p.data.copy_(w.to(p.dtype))
         return None
 
+    @property
+    def steps_done(self) -> int:
+        """Optimizer steps taken so far.  With the device counter enabled that counter is the truth: a replayed CUDA
+        graph advances it without running the host side of ``step`` (reading it synchronises the device)."""
+        if self._step_dev is not None:
+            self._step = int(self._step_dev.item())
+        return self._step
+
     def state_dict(self):
         sd = super().state_dict()
-        sd["zen_step"] = self._step
+        sd["zen_step"] = self.steps_done
         return sd
 
     def load_state_dict(self, sd):
@@ -125,3 +133,5 @@ class FusedAdamW(torch.optim.Optimizer):
         self._step = sd.pop("zen_step", 0)
         super().load_state_dict(sd)
         self._tables.clear()
+        if self._step_dev is not None:           # the bias corrections of a captured step read the device counter
+            self._step_dev.fill_(self._step)

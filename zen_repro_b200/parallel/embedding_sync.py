@@ -28,6 +28,7 @@ class EmbeddingRowSync:
         self._pending = None
         self.deterministic = deterministic
         self.last_count = None
+        self.force_library = False     # set after a reported failure of the peer-memory engine: all-gather the rows instead
 
     # ---- called from EmbeddingFn.backward -----------------------------------------------------
     def scratch_for(self, tokens: int, dy: torch.Tensor):
@@ -65,7 +66,7 @@ class EmbeddingRowSync:
         if self.P == 1:
             E.rows_add_(grad, rows, count, vals)
             return grad
-        if grad.is_cuda:
+        if grad.is_cuda and not self.force_library:
             self.prepare(grad.device)
             self._engine(rows, count, vals, grad, scale=self.scale)
         else:

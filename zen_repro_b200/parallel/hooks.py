@@ -161,7 +161,7 @@ def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, e
             if thr is not None:
                 buf.copy_(torch.where(buf.abs() >= thr.to(buf.dtype), buf, torch.zeros((), device=buf.device, dtype=buf.dtype)))
             return _future(buf, torch_future)
-        if buf.device.type == "cuda" and buf.numel() > SMALL_BUCKET:
+        if buf.device.type == "cuda" and buf.numel() > SMALL_BUCKET and not state.get("force_dense"):
             eng = engine_for(buf.numel(), buf.device)
             out = eng(buf, method=method, threshold=thr)
             if verify:
@@ -169,7 +169,7 @@ def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, e
                 out = verified_or_dense(out, eng.check(), masked, dp_group, state)
         else:
             masked = buf if thr is None else torch.where(buf.abs() >= thr.to(buf.dtype), buf, torch.zeros_like(buf))
-            if buf.numel() <= SMALL_BUCKET:
+            if buf.numel() <= SMALL_BUCKET or state.get("force_dense"):
                 out = masked.clone()
                 dist.all_reduce(out, group=dp_group)
             else:

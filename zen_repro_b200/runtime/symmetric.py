@@ -110,6 +110,10 @@ class IpcSymmetric(SymmetricRegion):
         for p in self._opened:
             lib.zen_ipc_close(ctypes.c_void_p(p))
         self._opened = []
+        if self._own and self.nranks > 1 and dist.is_initialized():
+            # every peer has unmapped this rank's region before it is freed
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
         if self._own:
             lib.zen_sym_free(ctypes.c_void_p(self._own))
             self._own = 0

@@ -47,6 +47,9 @@ class TrainConfig:
     heartbeat_s: float = 0.0          # > 0: host heartbeat between ranks, checked before every step (PeerLost is raised)
     cuda_graph: bool = False          # capture forward + backward + sync + optimizer once, then replay it every step
     graph_warmup: int = 2             # real steps launched from the host before the capture
+    status_mirror: bool = True        # mirror the kernels' status words to the host every step (read one step late)
+    on_sync_error: str = "recover"    # "recover": resync the replicas and switch the failing path to its library form;
+                                      # "raise": stop with SyncStatusError
 
     def to_dict(self):
         return dataclasses.asdict(self)
@@ -89,12 +92,28 @@ class Trainer:
                         hook.engine_for(b.buffer.numel(), self.device)
             self.model.module.register_comm_hook(None, hook)
             self._hook = hook
-        self.step_count = 0
+        self.step_count = 0                  # optimizer steps since the start of training (restored by a resume)
+        self._steps_here = 0                 # steps run by this process; the graph capture waits for graph_warmup of them
         self.heartbeat = None
         if cfg.heartbeat_s > 0 and dist.is_initialized() and dist.get_world_size() > 1:
             from .parallel.failure import Heartbeat
 
             self.heartbeat = Heartbeat(interval=cfg.heartbeat_s / 4, timeout=cfg.heartbeat_s)
+        self.health = None
+        self.recoveries: list = []
+        if cfg.status_mirror:
+            from .parallel.health import StatusMirror
+
+            self.health = StatusMirror(self.device, self.plugin.dp_group if dist.is_initialized() else None)
+            emb = self.model.module.embedding_sync
+            if emb is not None and emb._engine is not None:
+                self.health.add("embedding_rows", emb._engine.state.status_t)
+            if getattr(self, "_hook", None) is not None:
+                for numel, eng in self._hook.state["engines"].items():
+                    self.health.add(f"sparse_{numel}", eng.rank_state.status_t)
+            ws = getattr(self.model.unwrap(), "tp_ws", None)
+            if ws is not None:
+                self.health.add("tp_fused", ws.status)
         self._graph = None
         self.graph_launches_per_step = 0
         self._static_ids = self._static_loss = None
@@ -134,16 +153,55 @@ class Trainer:
         self.graph_launches_per_step = _native.launch_count() - before      # this library's kernels inside the graph
         self._graph = g
 
+    def _recover(self, bad: dict) -> None:
+        """A communication kernel reported overflow or an expired wait in an earlier step (same step and same value on
+        every rank).  That step used incomplete gradients on some rank, so the replicas may differ: re-broadcast
+        parameters and optimizer state from data-parallel rank 0, switch the failing path to its library form (dense
+        all-reduce of the thresholded bucket, all-gather of the embedding rows, NCCL all-reduce after the TP GEMMs) and
+        go on.  The step is no longer replayed from a graph afterwards."""
+        from .parallel.health import SyncStatusError, decode
+
+        msg = ", ".join(f"{k}: {decode(v)}" for k, v in bad.items())
+        if self.cfg.on_sync_error == "raise":
+            raise SyncStatusError(f"gradient synchronisation reported errors: {msg}")
+        self.coordinator.print_on_master(f"[zen] step {self.step_count}: {msg}; resynchronising replicas and falling back")
+        self._graph = None
+        self.graph_ok = False
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        if dist.is_initialized() and self.plugin.dp_size > 1:
+            src = dist.get_global_rank(self.plugin.dp_group, 0) if self.plugin.dp_group is not None else 0
+            for p in self.model.parameters():
+                dist.broadcast(p.data, src, group=self.plugin.dp_group)
+                for v in self.optimizer.state.get(p, {}).values():
+                    if torch.is_tensor(v):
+                        dist.broadcast(v, src, group=self.plugin.dp_group)
+        for name in bad:
+            if name == "embedding_rows":
+                self.model.module.embedding_sync.force_library = True
+            elif name == "tp_fused":
+                self.model.unwrap().disable_fused_tp()
+            elif getattr(self, "_hook", None) is not None:
+                self._hook.state["force_dense"] = True
+        self.health.clear()
+        self.recoveries.append({"step": self.step_count, "status": dict(bad)})
+
     def step_device(self, ids: torch.Tensor, labels: torch.Tensor, read_loss: bool = False):
-        if self.graph_ok and labels is ids and self.step_count >= self.cfg.graph_warmup:
+        if self.health is not None and self.health.sources:
+            bad = self.health.poll()
+            if bad:
+                self._recover(bad)
+        if self.graph_ok and labels is ids and self._steps_here >= self.cfg.graph_warmup:
             if self._graph is None:        # the first steps ran eagerly (tables, scratch and peers are set up): record now
                 self._capture(ids)
             self._static_ids.copy_(ids, non_blocking=True)
             self._graph.replay()
             self.step_count += 1
+            self._steps_here += 1
             return float(self._static_loss.item()) if read_loss else self._static_loss
         loss = self._eager_step(ids, labels)
         self.step_count += 1
+        self._steps_here += 1
         return float(loss.item()) if read_loss else loss
 
     def _eager_step(self, ids: torch.Tensor, labels: torch.Tensor):
@@ -151,6 +209,8 @@ class Trainer:
             loss = self.model(ids, labels)
         with trace_range("backward"):
             self.booster.backward(loss, self.optimizer)
+        if self.health is not None and self.health.sources:
+            self.health.publish()
         with trace_range("optimizer_step"):
             self.optimizer.step()
             self.model.module.zero_grad()
@@ -185,6 +245,28 @@ class Trainer:
             raise RuntimeError(f"kernel status words report errors: {bad} (1 = record overflow, 2 = gather overflow, "
                                f"4 = wait expired, 8 = overflow at a peer, 16 = bad argument)")
         return out
+
+    def close(self) -> None:
+        """Drop the captured graph and release the peer-visible regions (sparse engines, fused TP workspace).  A
+        collective over the groups that own those regions: every rank calls it, between steps."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        self._graph = None
+        self._static_ids = self._static_loss = None
+        if self.heartbeat is not None and hasattr(self.heartbeat, "stop"):
+            self.heartbeat.stop()
+        emb = getattr(self.model.module, "embedding_sync", None)
+        if emb is not None and emb._engine is not None:
+            emb._engine.close()
+            emb._engine = None
+        hook = getattr(self, "_hook", None)
+        if hook is not None:
+            for eng in hook.state["engines"].values():
+                eng.close()
+            hook.state["engines"].clear()
+        ws = getattr(self.model.unwrap(), "tp_ws", None) or getattr(self.model.unwrap(), "_tp_ws_off", None)
+        if ws is not None:
+            ws.close()
 
     def bytes_per_step(self, batch: dict) -> tuple[int, int]:
         h2d = batch["input_ids"].numel() * batch["input_ids"].element_size()
