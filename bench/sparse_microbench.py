@@ -69,6 +69,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--transport", default="p2p", choices=["p2p", "nvls"],
+                    help="gather push: one store per peer, or one multimem store replicated by the NVSwitch")
     ap.add_argument("--with_reference", action="store_true",
                     help="also time the reference's own zen_sparse_comm (NCCL + its kernels, bf16 only) from baseline/_ref")
     args = ap.parse_args()
@@ -103,7 +105,13 @@ def main():
                 out = torch.empty_like(xs[0])
                 stage("densify_one", lambda: r0[0].densify(out, e))
                 eng.status()
-                row = dict(mode="virtual", P=P, log2n=ln, density=d, dtype=args.dtype, dist=args.dist,
+                outs = eng(xs, method=method)
+                want = torch.zeros(n, dtype=torch.float32, device=dev)
+                for x in xs:
+                    want += x.float()
+                err = max(float((o.float() - want).abs().max()) for o in outs)
+                st = [a | b for a, b in zip(st, eng.status())]
+                row = dict(mode="virtual", max_err=err, P=P, log2n=ln, density=d, dtype=args.dtype, dist=args.dist,
                            overlap=args.overlap, method=str(method), ms_all_ranks=ms, ms_per_rank=ms / P,
                            dense_bytes=n * xs[0].element_size(), status=st, stages_ms=stages)
                 rows.append(row)
@@ -136,7 +144,7 @@ def main():
         for ln in args.log2n:
             n = 1 << ln
             for d in args.density:
-                eng = E.SparseAllReduce(n, None, max_density=max(0.02, d * 1.5), methods=(1, 2, 3))
+                eng = E.SparseAllReduce(n, None, max_density=max(0.02, d * 1.5), methods=(1, 2, 3), transport=args.transport)
                 x = make_inputs(n, d, P, dtype, dev, args.dist, args.overlap)[rank]
                 out = torch.empty_like(x)
                 def sparse():
@@ -169,7 +177,7 @@ def main():
                             ref_ms[f"reference_m{mth}_ms"] = float(tt.item())
                         except Exception as ex:
                             ref_ms[f"reference_m{mth}_ms"] = f"failed: {type(ex).__name__}"
-                row = dict(mode="nvlink", P=P, log2n=ln, density=d, dtype=args.dtype, dist=args.dist, overlap=args.overlap,
+                row = dict(mode="nvlink", transport=eng.transport, P=P, log2n=ln, density=d, dtype=args.dtype, dist=args.dist, overlap=args.overlap,
                            method=str(method), sparse_ms=ms_s, dense_nccl_ms=ms_d, speedup=ms_d / ms_s, **ref_ms,
                            eff_GBps=n * x.element_size() / ms_s / 1e6, max_err=err, status=int(stm),
                            push_bytes_per_rank=rec_bytes_out)

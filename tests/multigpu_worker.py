@@ -212,7 +212,125 @@ def check_sp_trainer(rank, world, dev):
     print(f"OK sp_trainer rank{rank} {out[True]}", flush=True)
 
 
-CHECKS = {"gemm_ar": check_gemm_allreduce, "sp_trainer": check_sp_trainer, "gemm_rs_ag": check_gemm_rs_ag, "tp_trainer": check_tp_trainer,"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
+def check_sparse_back_to_back(rank, world, dev):
+    """Eight calls on ONE engine with no host synchronisation or collective in between, method 1 and the balanced
+    methods mixed, while the last rank is held back by a finite sleep before each of its consumers: a fast rank is then
+    a whole call ahead of the slow one, which is safe only because record slots and their mails alternate with the
+    call parity.  Guard words around the sub-regions must survive."""
+    from zen_repro_b200.sparse.engine import SparseAllReduce
+
+    n = 1 << 20
+    eng = SparseAllReduce(n, None, max_density=0.1, methods=(1, 2, 3), deterministic=True, wait_ms=5000.0)
+    xs = [make_sparse(n, 0.01 + 0.004 * i, 1000 * i + rank, torch.float32, dev) for i in range(8)]
+    methods = [1, 1, 3, 1, 2, 1, 1, "auto"]
+    outs = []
+    rs = eng.rank_state
+    torch.cuda.synchronize(); dist.barrier()
+    for i, (x, m) in enumerate(zip(xs, methods)):
+        out = torch.empty_like(x)
+        eng.epoch += 1
+        e = eng.epoch
+        if m == 1:
+            rs.partition_push(x, e, None, broadcast=True)
+            if rank == world - 1:
+                torch.cuda._sleep(20_000_000)                 # about 10 ms: the peers finish this call and push the next
+            rs.scatter_sources(out, e)
+        else:
+            from zen_repro_b200.sparse.engine import _fmt_for
+
+            rs.partition_push(x, e, None)
+            if rank == world - 1:
+                torch.cuda._sleep(20_000_000)
+            rs.owner_reduce(e, x.dtype, True)
+            rs.gather_push(e, x.dtype, _fmt_for(m))
+            rs.densify(out, e, _fmt_for(m))
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert eng.check() == 0
+    for x, out in zip(xs, outs):
+        want = x.clone()
+        dist.all_reduce(want)
+        assert torch.equal(out, want) or (out - want).abs().max().item() <= 1e-5, (out - want).abs().max().item()
+    assert rs.damaged_canaries() == []
+    dist.barrier()
+    eng.close()
+    print(f"OK sparse_back_to_back rank{rank}", flush=True)
+
+
+def check_sparse_nvls(rank, world, dev):
+    """Gather push through the multicast alias (one multimem store, replicated by the NVSwitch) against the dense sum."""
+    from zen_repro_b200.sparse.engine import SparseAllReduce
+
+    n = 1 << 22
+    eng = SparseAllReduce(n, None, max_density=0.2, methods=(2, 3), transport="nvls")
+    if eng.transport != "nvls":
+        print(f"OK sparse_nvls rank{rank} (no multicast on this fabric: plain peer stores were used)", flush=True)
+    for rep in range(2):
+        x = make_sparse(n, 0.03 * (rep + 1), 7 * rep + rank, torch.float32, dev)
+        want = x.clone().float()
+        dist.all_reduce(want)
+        for method in (3, 2, "auto"):
+            out = eng(x, method=method)
+            assert eng.check() == 0
+            assert (out.float() - want).abs().max().item() <= 1e-5
+    assert eng.rank_state.damaged_canaries() == []
+    dist.barrier()
+    eng.close()
+    print(f"OK sparse_nvls rank{rank} transport={eng.transport}", flush=True)
+
+
+def check_verify_fallback(rank, world, dev):
+    """``verify=True`` of the hook with a failure made on the host: the last rank does not launch its push for one
+    bucket.  Every rank must see the expired wait (its own or a peer's, through the agreed status), fall back, and
+    return the exact dense sum of the thresholded buckets."""
+    from zen_repro_b200.parallel.hooks import make_zen_comm_hook
+    from zen_repro_b200.parallel.reducer import GradBucket
+    from zen_repro_b200.sparse.engine import SparseAllReduce
+
+    n = 200000
+    eng = SparseAllReduce(n, None, max_density=0.3, methods=(1, 2, 3), wait_ms=300.0)
+    hook = make_zen_comm_hook(None, None, top_k=100, method=3, engines={n: eng}, torch_future=False, verify=True)
+    x = make_sparse(n, 0.05, rank, torch.float32, dev)
+    want = x.clone()
+    dist.all_reduce(want)
+    out = hook(None, GradBucket(0, x.clone(), [], True)).wait()
+    assert hook.state.get("fallbacks", 0) == 0 and (out - want).abs().max().item() <= 1e-5
+    # the failure: this rank's kernels of the next call are not launched (the engine call is replaced by a no-op)
+    if rank == world - 1:
+        eng.rank_state.allreduce = lambda x_, out_, *a, **k: out_.zero_()
+    out = hook(None, GradBucket(0, x.clone(), [], True)).wait()
+    assert hook.state["fallbacks"] == 1 and hook.state["last_status"] != 0
+    assert (out - want).abs().max().item() <= 1e-5, (out - want).abs().max().item()
+    assert float(torch.ones(8, device=dev).sum()) == 8.0      # the context is alive
+    torch.cuda.synchronize()
+    dist.barrier()
+    eng.close()
+    print(f"OK verify_fallback rank{rank} status={hook.state['last_status']}", flush=True)
+
+
+def check_tp2dp2_sparse_embedding(rank, world, dev):
+    """TP 2 x DP 2: the vocabulary-sharded embedding gradient synchronised as sparse rows over the DP group tracks
+    the dense synchronisation of the same run."""
+    from zen_repro_b200.trainer import TrainConfig, Trainer
+
+    assert world % 4 == 0 or world == 4, "needs four ranks"
+    out = {}
+    for sparse in (True, False):
+        t = Trainer(TrainConfig(model="meta-llama/Llama-3.2-3B", num_layers=2, micro_batch=1, seq_len=256, tp=2, lr=1e-4,
+                                data_pool=0, sparse_embedding_under_tp=sparse), init_dist=False)
+        assert (t.model.module.embedding_sync is not None) == sparse
+        out[sparse] = [t.step(next(t.data)) for _ in range(4)]
+        assert not t.check_health(raise_on_error=False) or not any(t.check_health(raise_on_error=False).values())
+        w = t.model.unwrap().wte.detach().float()
+        out[("w", sparse)] = w
+        t.close()
+    assert all(abs(a - b) < 0.02 for a, b in zip(out[True], out[False])), out
+    assert (out[("w", True)] - out[("w", False)]).abs().max().item() < 2e-3
+    print(f"OK tp2dp2_sparse_embedding rank{rank} {out[True]}", flush=True)
+
+
+CHECKS = {"b2b": check_sparse_back_to_back, "nvls": check_sparse_nvls, "verify": check_verify_fallback,
+          "tp2dp2": check_tp2dp2_sparse_embedding, "gemm_ar": check_gemm_allreduce, "sp_trainer": check_sp_trainer, "gemm_rs_ag": check_gemm_rs_ag, "tp_trainer": check_tp_trainer,"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
           "hook": check_zen_hook, "departed": check_departed_rank}
 
 if __name__ == "__main__":

@@ -50,8 +50,12 @@ def build_parser():
     p.add_argument("--sequence_parallel", action="store_true", help="TP with the residual stream sharded over tokens")
     p.add_argument("--save", type=str, default=None, help="checkpoint directory written at the end")
     p.add_argument("--resume", type=str, default=None, help="checkpoint directory to resume from")
-    p.add_argument("--metrics_out", type=str, default=None)
+    p.add_argument("--metrics_out", type=str, default=None, help="JSON-lines file: per-step records and the final summary")
+    p.add_argument("--metrics_every", type=int, default=0,
+                   help="> 0: every N-th step also collect the counters of the sparse paths (one device synchronisation)")
+    p.add_argument("--trace", action="store_true", help="NVTX ranges with the reference's names around every stage")
     p.add_argument("--log_dir", type=str, default=".")
+    p.add_argument("--time_file", type=str, default="time.txt", help="the reference's result sink (appended to)")
     p.add_argument("--time_from", type=int, default=80)
     p.add_argument("--time_to", type=int, default=95)
     return p
@@ -60,6 +64,10 @@ def build_parser():
 def main(argv=None):
     args = build_parser().parse_args(argv)
     set_seed(args.seed)
+    if args.trace:
+        from zen_repro_b200.utils import enable_tracing
+
+        enable_tracing(True)
     rank, world, device = launch_from_torch()
     logger = setup_logger(args.log_dir)
     tp = args.tp if world % args.tp == 0 and args.tp <= world else 1
@@ -91,8 +99,17 @@ def main(argv=None):
             if device.type == "cuda":
                 ev1 = torch.cuda.Event(enable_timing=True); ev1.record()
         batch = next(trainer.data)
+        t_step = time.perf_counter()
         loss = trainer.step(batch, read_loss=True)
+        step_ms = (time.perf_counter() - t_step) * 1e3
         coord.print_on_master(f"Step {step} loss: {loss}")
+        if args.metrics_out:
+            rec = {"kind": "step", "step": step, "loss": loss, "step_ms": step_ms}
+            if args.metrics_every > 0 and step % args.metrics_every == 0:
+                rec.update(trainer.collect_metrics())
+            if coord.is_master():
+                with open(args.metrics_out, "a") as f:
+                    f.write(json.dumps(rec) + "\n")
         if step >= args.num_steps:
             break
     mem = torch.cuda.max_memory_allocated() / 1024 ** 2 if torch.cuda.is_available() else 0.0
@@ -115,16 +132,18 @@ def main(argv=None):
     coord.print_on_master(header + "\n")
     coord.print_on_master(f"{sec_per_it}\n")
     if coord.is_master():
-        with open("time.txt", "a") as f:
+        with open(args.time_file, "a") as f:
             f.write(header + "\n")
             f.write(f"{sec_per_it}\n")
         if args.metrics_out and sec_per_it:
             with open(args.metrics_out, "a") as f:
-                f.write(json.dumps({"model": args.model_name, "method": args.method, "top_k": args.top_k, "dp": dp, "tp": tp,
+                f.write(json.dumps({"kind": "summary", "model": args.model_name, "method": args.method, "top_k": args.top_k, "dp": dp, "tp": tp,
                                     "sec_per_iter": sec_per_it, "tokens_per_s": trainer.tokens_per_step / sec_per_it,
-                                    "max_mem_mb": mem, "config": cfg.to_dict()}) + "\n")
+                                    "max_mem_mb": mem, "recoveries": trainer.recoveries, "kernel_status": health,
+                                    "config": cfg.to_dict()}) + "\n")
     if args.save:
         save_checkpoint(args.save, trainer)
+    trainer.close()
     if dist.is_initialized():
         dist.destroy_process_group()
 

@@ -1,23 +1,29 @@
 // Sparse all-reduce kernels (element granule) for sm_100a.
 //
 // Pipeline per bucket, one launch each, all on one stream, no host sync:
-//   zen_partition_push  : scan the flat bucket once, hash 64-element blocks to
-//                         owners, stage (slot, value) records per owner in shared
-//                         memory and push them in large contiguous runs straight
-//                         into the owner's receive region over NVLink (P2P stores).
-//   zen_owner_reduce    : bounded wait on each source's mailbox, red.add the
-//                         records into this owner's fp32 slots, red.or the
-//                         occupancy bitmap.
-//   zen_gather_push     : count / scan the bitmap, compact the touched slots in
-//                         slot order and push bitmap|COO + values to every peer.
-//   zen_densify         : bounded wait on each owner's mailbox, one pass over
-//                         the output that writes zeros and values together.
+//   zen_partition_push  : stream the flat bucket through a shared-memory ring filled by bulk
+//                         asynchronous copies (cp.async.bulk + mbarrier), hash 64-element blocks to
+//                         owners, stage (slot, value) records per owner in shared memory and push
+//                         them in large contiguous runs straight into the owner's receive region
+//                         over NVLink (P2P stores).
+//   zen_owner_reduce    : bounded wait on every source's mailbox at once, red.add the records
+//                         into this owner's fp32 slots, red.or the occupancy bitmap.
+//   zen_gather_push     : walk the occupancy bitmap, compact the touched slots chunk by chunk,
+//                         reserve room in the payload with one atomic per CTA step and push
+//                         bitmap|COO + values to every peer (P2P stores, or one multimem store
+//                         through the NVSwitch when a multicast alias of the region exists).
+//   zen_densify         : bounded wait on each owner's mailbox, one pass over the output that
+//                         writes zeros and values together.
+//
+// Record slots and their mailboxes exist twice and alternate with the parity of the call number, so a
+// rank that is one call ahead never writes into records that a slower peer is still reading.
 //
 // Replaces, in the reference: the three sparse_balance kernels and the
 // boolean-mask compaction after them (functions_cuda_kernel.cu:97-167,
 // tensor_load_balance.py:24-51), both all_to_all calls and the scatter_add /
 // nonzero between them (comm.py:117-127), encode_bitmap / decode_bitmap and the
 // padded all_gathers (comm.py:59-99, 128-145).
+#include "tc_common.cuh"
 #include "zen_common.cuh"
 
 struct ZenSparseCtx {
@@ -27,9 +33,9 @@ struct ZenSparseCtx {
   uint32_t fmt_mode;        // 0 auto, ZEN_FMT_COO, ZEN_FMT_BITMAP
   uint64_t wait_ns;
   char* sym[ZEN_MAX_RANKS]; // base of every rank's symmetric region
-  uint64_t off_rec_mail;    // ZenMail[P], indexed by source
-  uint64_t off_g_mail;      // ZenMail[P], indexed by owner
-  uint64_t off_rec;         // uint2[P][cap_rec], indexed by source
+  uint64_t off_rec_mail;    // ZenMail[2][ZEN_MAX_RANKS], indexed by call parity and source
+  uint64_t off_g_mail;      // ZenMail[ZEN_MAX_RANKS], indexed by owner
+  uint64_t off_rec;         // uint2[2][P][cap_rec], indexed by call parity and source
   uint64_t off_g_idx;       // uint32[P][g_idx_words]: bitmap words or COO slots
   uint64_t off_g_off;       // uint32[P][nchunks + 1]: value offset of every 1024-slot chunk
   uint64_t off_g_val;       // T[P][cap_g] (stride in bytes: cap_g * 4)
@@ -39,20 +45,33 @@ struct ZenSparseCtx {
   uint32_t nchunks;
   float* acc;               // [S] local
   uint32_t* bitmap;         // [nwords] local
-  uint32_t* chunk_off;      // [nchunks + 1] local: counts, then exclusive offsets
-  uint32_t* cursors;        // [P] record cursors, [P] = done counter K1, [P+1] = done counter K3
+  uint32_t* chunk_off;      // unused by the kernels (kept for layout stability of the binding)
+  uint32_t* cursors;        // [P] record cursors, [MAX] done counter K1, [MAX+1] done counter K3, [MAX+2] payload cursor
   uint32_t* status;         // status word
   uint64_t numel;           // N
   uint32_t nslots;          // S = sb * G
   uint32_t nwords;          // ceil(S / 32)
   ZenPerm perm;
+  const uint32_t* epoch_dev;  // optional: call counter on the device (zen_sparse_epoch_bump); overrides `epoch`
+  char* mc;                   // optional: multicast alias of the symmetric region (stores reach every rank)
+  uint32_t k1_density_ppm;    // nonzeros per million elements that the plan was sized for (0 = unknown)
+  uint32_t pad0;
 };
 
-#define K1_THREADS 256
+__device__ __forceinline__ uint32_t zen_epoch(const ZenSparseCtx& c) { return c.epoch_dev ? *c.epoch_dev : c.epoch; }
+__device__ __forceinline__ uint2* zen_rec_slots(const ZenSparseCtx& c, int at_rank, int src, uint32_t epoch) {
+  return reinterpret_cast<uint2*>(c.sym[at_rank] + c.off_rec) + ((uint64_t)(epoch & 1u) * c.nranks + src) * c.cap_rec;
+}
+__device__ __forceinline__ ZenMail* zen_rec_mail(const ZenSparseCtx& c, int at_rank, int src, uint32_t epoch) {
+  return reinterpret_cast<ZenMail*>(c.sym[at_rank] + c.off_rec_mail) + (epoch & 1u) * ZEN_MAX_RANKS + src;
+}
+
+#define K1_THREADS 288                                  // eight consumer warps and the producer warp
 #define K1_WARPS 8
-#define K1_U 4
-#define K1_QCAP 1024
-#define K1_FLUSH_MIN 256
+#define K1_QCAP 512
+#define K1_FLUSH_MIN 192
+#define K1_STAGE_BYTES 8192
+#define K1_NS 4
 
 // Eight consecutive elements as raw bits: one 16-byte vector for 16-bit types, two for fp32.
 template <typename T> struct Raw8;
@@ -112,175 +131,264 @@ template <> struct Raw8<__half> : Raw8Half<__half> {
 };
 
 // ---------------------------------------------------------------------------------------------
-// K1: partition + compact + push.  Every lane owns 8 consecutive elements (all in one 64-element
-// block, hence one owner); a lane with nonzeros reserves room in its owner's shared-memory queue
-// with one atomic and writes its records there.  Warp w drains queue w to the owner's receive
-// region in runs of at least K1_FLUSH_MIN records.  kBroadcast = true is the method-1 variant: one
-// queue of (global index, value) records pushed to every peer.
-template <typename T, bool kBroadcast>
-__global__ void __launch_bounds__(K1_THREADS, 2)
-zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const float* __restrict__ thr_ptr,
-                          int aligned) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+// K1: partition + compact + push.  The bucket streams through a ring of K1_NS shared-memory stages:
+// a producer warp keeps them filled with bulk asynchronous copies (full / empty mbarriers per stage),
+// eight consumer warps scan them.  Every lane owns 8 consecutive elements at a time (all in one
+// 64-element block, hence one owner); vectors that hold a nonzero are first compacted into a per-warp
+// list, and the expensive part -- owner lookup, queue reservation, record writes -- runs on 32 listed
+// vectors at a time with every lane busy.  Records go to per-owner queues in shared memory; every
+// `batch` stages the consumer warps meet at a named barrier and warp w drains queue w to the owner's
+// receive region in runs of at least K1_FLUSH_MIN records (a queue that fills up earlier spills
+// straight to the destination).  kBroadcast = true is the method-1 variant: one queue of
+// (global index, value) records pushed to every peer.  kRing = false reads the bucket with plain
+// loads instead (a base pointer that is not 16-byte aligned).
+#define K1_CONSUMERS 256
+__device__ __forceinline__ void k1_consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+template <typename T> struct K1Entry { uint32_t w[sizeof(Raw8<T>) / 4]; };
+
+template <typename T, bool kBroadcast, bool kRing>
+__global__ void __launch_bounds__(K1_THREADS, 3)
+zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const float* __restrict__ thr_ptr, int batch) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  constexpr uint32_t VB = 8 * sizeof(T);                              // bytes of one 8-element vector
+  constexpr uint32_t EPS = K1_STAGE_BYTES / sizeof(T);                // elements per stage
+  constexpr int VPL = K1_STAGE_BYTES / VB / K1_CONSUMERS;             // vectors per lane per stage
+  static_assert(VPL >= 1, "stage too small");
+  constexpr int RAWW = sizeof(Raw8<T>) / 4;                           // words per vector (4 or 8)
   const int nq = kBroadcast ? 1 : c.nranks;
-  uint2* q = reinterpret_cast<uint2*>(smem_raw);                    // [nq][K1_QCAP]
+  unsigned char* ring = smem_raw;                                     // [K1_NS][K1_STAGE_BYTES] (kRing)
+  uint2* q = reinterpret_cast<uint2*>(smem_raw + (kRing ? K1_NS * K1_STAGE_BYTES : 0));   // [nq][K1_QCAP]
+  __shared__ uint64_t full[K1_NS], empty[K1_NS];
   __shared__ uint32_t qn[ZEN_MAX_RANKS];
   __shared__ uint32_t qvalid[ZEN_MAX_RANKS];
   __shared__ uint32_t s_last;
+  __shared__ int s_abort;
+  __shared__ __align__(16) K1Entry<T> wdat[K1_WARPS][64];             // per-warp list of vectors with a nonzero (a ring)
+  __shared__ uint32_t wel[K1_WARPS][64];                              // ... and their first element index
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool use_thr = thr_ptr != nullptr;
   const float thr = use_thr ? *thr_ptr : 0.f;
   const uint64_t N = c.numel;
-  const uint64_t nwi = (N + 255) / 256;                               // warp-iterations of 256 elements
-  const uint64_t ncta_it = (nwi + K1_WARPS * K1_U - 1) / (K1_WARPS * K1_U);
+  const uint64_t nst = (N + EPS - 1) / EPS;                           // stages of the whole bucket
+  const uint64_t copy_end = (N * sizeof(T)) & ~15ull;                 // bytes that bulk copies may fetch
+  const uint32_t epoch = zen_epoch(c);
+  const uint64_t rec_base = ((uint64_t)(epoch & 1u) * c.nranks + c.rank) * c.cap_rec;
   uint32_t local_status = 0;
+  if (batch < 1) batch = 1;
 
   if (tid < ZEN_MAX_RANKS) { qn[tid] = 0; qvalid[tid] = 0; }
+  if (tid == 0) {
+    s_abort = 0;
+    if (kRing) {
+      for (int s = 0; s < K1_NS; ++s) { tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], K1_WARPS); }
+      tc::fence_barrier_init();
+    }
+  }
   __syncthreads();
 
-  constexpr int RAWW = sizeof(Raw8<T>) / 4;                           // words per staged vector (4 or 8)
-  __shared__ uint32_t wbuf[K1_WARPS][64][RAWW + 1];                   // per-warp staging: {first element, raw vector}
-  uint32_t wcnt = 0;                                                  // staged vectors of this warp (warp-uniform)
-
-  // Records of one 8-element vector starting at element e32: choose the owner, reserve queue space, write them.
-  auto emit = [&](uint32_t e32, const Raw8<T>& vec) {
-    uint32_t m = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      bool keep = vec.nonzero(i);
-      if (use_thr) keep = keep && (fabsf(vec.value(i)) >= thr);
-      m |= keep ? (1u << i) : 0u;
-    }
-    if (!m) return;
-    uint32_t owner = 0, slot0 = e32;
-    if (!kBroadcast) {
-      const uint32_t pb = zen_perm_fwd(c.perm, e32 >> c.perm.lg);
-      owner = zen_owner_of(c.perm, pb, c.nranks);
-      slot0 = ((pb - owner * c.perm.sb) << c.perm.lg) + (e32 & (c.perm.block - 1u));
-    }
-    const uint32_t cnt = __popc(m);
-    uint32_t k = atomicAdd(&qn[owner], cnt);
-    bool direct = false;
-    if (k + cnt > K1_QCAP) {
-      if (k <= K1_QCAP) qvalid[owner] = k;                            // exactly one lane per overflow sees this
-      direct = true;
-      k = atomicAdd(&c.cursors[owner], cnt);                          // reserve directly in the destination
-    }
-    while (m) {
-      const int i = __ffs(m) - 1;
-      m &= m - 1;
-      const uint2 rec = make_uint2(slot0 + i, vec.bits(i));
-      if (!direct) {
-        q[owner * K1_QCAP + k] = rec;
-      } else if (k < c.cap_rec) {
-        if (kBroadcast) {
-          for (int p = 0; p < c.nranks; ++p)
-            reinterpret_cast<uint2*>(c.sym[p] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
-        } else {
-          reinterpret_cast<uint2*>(c.sym[owner] + c.off_rec)[(uint64_t)c.rank * c.cap_rec + k] = rec;
-        }
-      } else {
-        local_status |= ZEN_REC_OVERFLOW;
-      }
-      ++k;
+  auto stage_bytes = [&](uint64_t it) -> uint32_t {
+    const uint64_t b0 = it * K1_STAGE_BYTES;
+    return b0 >= copy_end ? 0u : (uint32_t)min((uint64_t)K1_STAGE_BYTES, copy_end - b0);
+  };
+  // bounded wait on an mbarrier phase; gives up at once when the CTA has already aborted
+  auto wait_phase = [&](uint64_t* bar, uint32_t parity) -> bool {
+    if (tc::mbar_test(bar, parity)) return true;
+    const uint64_t t0 = zen_globaltimer();
+    for (;;) {
+      for (int i = 0; i < 128; ++i)
+        if (tc::mbar_test(bar, parity)) return true;
+      if (*(volatile int*)&s_abort || zen_globaltimer() - t0 > c.wait_ns) { s_abort = 1; return false; }
     }
   };
 
-  for (uint64_t it = blockIdx.x; it < ncta_it; it += gridDim.x) {
-    Raw8<T> v[K1_U];
-#pragma unroll
-    for (int u = 0; u < K1_U; ++u) {
-      const uint64_t e0 = (it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp) * 256 + (uint64_t)lane * 8;
-      if (e0 < N) v[u].load(g, e0, N, aligned != 0); else v[u].zero();
-    }
-    const bool last_it = (it + gridDim.x >= ncta_it);
-    // Vectors that hold a nonzero are first compacted into this warp's staging list (a ballot and one shared-memory
-    // store), and the expensive part -- owner lookup, queue reservation, record writes -- runs on 32 staged vectors
-    // at a time with every lane busy, instead of once per warp-load for the two or three lanes that have work.
-#pragma unroll
-    for (int u = 0; u < K1_U; ++u) {
-      const bool has = v[u].any();
-      const uint32_t bal = __ballot_sync(0xffffffffu, has);
-      if (!bal) continue;
-      if (has) {
-        uint32_t* ent = wbuf[warp][wcnt + __popc(bal & ((1u << lane) - 1u))];
-        ent[0] = (uint32_t)((it * (K1_WARPS * K1_U) + (uint64_t)u * K1_WARPS + warp) * 256) + lane * 8;
-#pragma unroll
-        for (int k = 0; k < RAWW; ++k) ent[1 + k] = v[u].w[k];
+  if (warp == K1_WARPS) {
+    // ---- producer warp: one lane keeps the ring full
+    if (kRing && lane == 0) {
+      uint32_t issued[K1_NS] = {};
+      uint32_t k = 0;
+      for (uint64_t it = blockIdx.x; it < nst; it += gridDim.x, ++k) {
+        const int s = k % K1_NS;
+        if (k >= K1_NS && !wait_phase(&empty[s], ((k / K1_NS) - 1u) & 1u)) break;
+        const uint32_t b = stage_bytes(it);
+        tc::mbar_expect_tx(&full[s], b);
+        if (b) tc::bulk_load_1d(ring + s * K1_STAGE_BYTES, reinterpret_cast<const unsigned char*>(g) + it * K1_STAGE_BYTES, b, &full[s]);
+        ++issued[s];
       }
-      wcnt += __popc(bal);
-      if (wcnt >= 32) {
-        __syncwarp();
-        {
-          Raw8<T> r;
-          const uint32_t* ent = wbuf[warp][lane];
-#pragma unroll
-          for (int k = 0; k < RAWW; ++k) r.w[k] = ent[1 + k];
-          emit(ent[0], r);
+      if (*(volatile int*)&s_abort) {
+        // give the copies that are still in flight a bounded chance to land before the CTA (and its shared memory) goes
+        const uint64_t t0 = zen_globaltimer();
+        for (int s = 0; s < K1_NS; ++s) {
+          if (!issued[s]) continue;
+          while (!tc::mbar_test(&full[s], (issued[s] - 1u) & 1u) && zen_globaltimer() - t0 < c.wait_ns) {}
         }
-        const uint32_t rest = wcnt - 32;
-        uint32_t tmp[RAWW + 1];
-        if (lane < rest) {
-#pragma unroll
-          for (int k = 0; k <= RAWW; ++k) tmp[k] = wbuf[warp][32 + lane][k];
-        }
-        __syncwarp();
-        if (lane < rest) {
-#pragma unroll
-          for (int k = 0; k <= RAWW; ++k) wbuf[warp][lane][k] = tmp[k];
-        }
-        __syncwarp();
-        wcnt = rest;
       }
     }
-    if (last_it && wcnt) {                               // leftovers of this warp: drain with the lanes that have one
-      __syncwarp();
-      if (lane < wcnt) {
-        Raw8<T> r;
-        const uint32_t* ent = wbuf[warp][lane];
+  } else {
+    // ---- consumer warps
+    uint32_t wtail = 0, whead = 0;                                    // list entries appended / consumed (warp-uniform)
+
+    // Records of one 8-element vector starting at element e32: choose the owner, reserve queue space, write them.
+    auto emit = [&](uint32_t e32, const Raw8<T>& vec) {
+      uint32_t m = 0;
 #pragma unroll
-        for (int k = 0; k < RAWW; ++k) r.w[k] = ent[1 + k];
-        emit(ent[0], r);
+      for (int i = 0; i < 8; ++i) {
+        bool keep = vec.nonzero(i);
+        if (use_thr) keep = keep && (fabsf(vec.value(i)) >= thr);
+        m |= keep ? (1u << i) : 0u;
       }
-      wcnt = 0;
-    }
-    __syncthreads();
-    // flush phase: warp w drains queue w when it holds a worthwhile run (or on the last iteration)
-    if (warp < nq) {
-      uint32_t n = qn[warp];
-      const bool overflowed = n > K1_QCAP;
-      if (overflowed) n = qvalid[warp];
-      if (n > 0 && (n >= K1_FLUSH_MIN || last_it || overflowed)) {
-        uint32_t gbase = 0;
-        if (lane == 0) gbase = atomicAdd(&c.cursors[warp], n);
-        gbase = __shfl_sync(0xffffffffu, gbase, 0);
-        const uint32_t fit = (gbase >= c.cap_rec) ? 0u : min(n, c.cap_rec - gbase);
-        if (fit < n) local_status |= ZEN_REC_OVERFLOW;
-        const uint2* src = q + warp * K1_QCAP;
-        if (kBroadcast) {
-          for (int p = 0; p < c.nranks; ++p) {
-            uint2* dst = reinterpret_cast<uint2*>(c.sym[p] + c.off_rec) + (uint64_t)c.rank * c.cap_rec + gbase;
-            for (uint32_t i = lane; i < fit; i += 32) dst[i] = src[i];
+      if (!m) return;
+      uint32_t owner = 0, slot0 = e32;
+      if (!kBroadcast) {
+        const uint32_t pb = zen_perm_fwd(c.perm, e32 >> c.perm.lg);
+        owner = zen_owner_of(c.perm, pb, c.nranks);
+        slot0 = ((pb - owner * c.perm.sb) << c.perm.lg) + (e32 & (c.perm.block - 1u));
+      }
+      const uint32_t cnt = __popc(m);
+      uint32_t k = atomicAdd(&qn[owner], cnt);
+      bool direct = false;
+      if (k + cnt > K1_QCAP) {
+        if (k <= K1_QCAP) qvalid[owner] = k;                          // exactly one lane per overflow sees this
+        direct = true;
+        k = atomicAdd(&c.cursors[owner], cnt);                        // reserve directly in the destination
+      }
+      while (m) {
+        const int i = __ffs(m) - 1;
+        m &= m - 1;
+        const uint2 rec = make_uint2(slot0 + i, vec.bits(i));
+        if (!direct) {
+          q[owner * K1_QCAP + k] = rec;
+        } else if (k < c.cap_rec) {
+          if (kBroadcast) {
+            for (int p = 0; p < c.nranks; ++p)
+              (reinterpret_cast<uint2*>(c.sym[p] + c.off_rec) + rec_base)[k] = rec;
+          } else {
+            (reinterpret_cast<uint2*>(c.sym[owner] + c.off_rec) + rec_base)[k] = rec;
           }
         } else {
-          uint2* dst = reinterpret_cast<uint2*>(c.sym[warp] + c.off_rec) + (uint64_t)c.rank * c.cap_rec + gbase;
-          for (uint32_t i = lane; i < fit; i += 32) dst[i] = src[i];
+          local_status |= ZEN_REC_OVERFLOW;
+        }
+        ++k;
+      }
+    };
+    auto emit_entry = [&](uint32_t idx) {
+      Raw8<T> r;
+      const uint4* p4 = reinterpret_cast<const uint4*>(&wdat[warp][idx & 63u]);
+#pragma unroll
+      for (int k = 0; k < RAWW / 4; ++k) {
+        const uint4 a = p4[k];
+        r.w[4 * k] = a.x; r.w[4 * k + 1] = a.y; r.w[4 * k + 2] = a.z; r.w[4 * k + 3] = a.w;
+      }
+      emit(wel[warp][idx & 63u], r);
+    };
+    // warp w drains queue w when it holds a worthwhile run (or at the end)
+    auto flush = [&](bool final_flush) {
+      if (warp < nq) {
+        uint32_t n = qn[warp];
+        const bool overflowed = n > K1_QCAP;
+        if (overflowed) n = qvalid[warp];
+        if (n > 0 && (n >= K1_FLUSH_MIN || final_flush || overflowed)) {
+          uint32_t gbase = 0;
+          if (lane == 0) gbase = atomicAdd(&c.cursors[warp], n);
+          gbase = __shfl_sync(0xffffffffu, gbase, 0);
+          const uint32_t fit = (gbase >= c.cap_rec) ? 0u : min(n, c.cap_rec - gbase);
+          if (fit < n) local_status |= ZEN_REC_OVERFLOW;
+          const uint2* src = q + warp * K1_QCAP;
+          if (kBroadcast) {
+            for (int p = 0; p < c.nranks; ++p) {
+              uint2* dst = reinterpret_cast<uint2*>(c.sym[p] + c.off_rec) + rec_base + gbase;
+              for (uint32_t i = lane; i < fit; i += 32) dst[i] = src[i];
+            }
+          } else {
+            uint2* dst = reinterpret_cast<uint2*>(c.sym[warp] + c.off_rec) + rec_base + gbase;
+            for (uint32_t i = lane; i < fit; i += 32) dst[i] = src[i];
+          }
+          __syncwarp();
+          if (lane == 0) { qn[warp] = 0; qvalid[warp] = 0; }
+        } else if (overflowed && lane == 0) {
+          qn[warp] = 0; qvalid[warp] = 0;
+        }
+      }
+    };
+
+    uint32_t kk = 0;
+    int since = 0;
+    for (uint64_t it = blockIdx.x; it < nst; it += gridDim.x, ++kk) {
+      const int s = kk % K1_NS;
+      Raw8<T> v[VPL];
+      if (kRing) {
+        const bool ok = wait_phase(&full[s], (kk / K1_NS) & 1u);
+        const uint32_t sb = ok ? stage_bytes(it) : 0u;
+        const unsigned char* st = ring + s * K1_STAGE_BYTES;
+#pragma unroll
+        for (int u = 0; u < VPL; ++u) {
+          const uint32_t vi = u * K1_CONSUMERS + tid;
+          const uint64_t e0 = it * EPS + (uint64_t)vi * 8;
+          if ((vi + 1) * VB <= sb) {
+            const uint4* p4 = reinterpret_cast<const uint4*>(st + vi * VB);
+#pragma unroll
+            for (int k = 0; k < RAWW / 4; ++k) {
+              const uint4 a = p4[k];
+              v[u].w[4 * k] = a.x; v[u].w[4 * k + 1] = a.y; v[u].w[4 * k + 2] = a.z; v[u].w[4 * k + 3] = a.w;
+            }
+          } else if (ok && e0 < N) {
+            v[u].load(g, e0, N, false);                                // ragged end of the bucket: guarded plain loads
+          } else {
+            v[u].zero();
+          }
         }
         __syncwarp();
-        if (lane == 0) { qn[warp] = 0; qvalid[warp] = 0; }
-      } else if (overflowed && lane == 0) {
-        qn[warp] = 0; qvalid[warp] = 0;
+        if (lane == 0) tc::mbar_arrive(&empty[s]);                     // this warp is done with the stage
+      } else {
+#pragma unroll
+        for (int u = 0; u < VPL; ++u) {
+          const uint64_t e0 = it * EPS + (uint64_t)(u * K1_CONSUMERS + tid) * 8;
+          if (e0 < N) v[u].load(g, e0, N, false); else v[u].zero();
+        }
+      }
+      const bool last_it = (it + gridDim.x >= nst);
+#pragma unroll
+      for (int u = 0; u < VPL; ++u) {
+        const bool has = v[u].any();
+        const uint32_t bal = __ballot_sync(0xffffffffu, has);
+        if (!bal) continue;
+        if (has) {
+          const uint32_t idx = (wtail + __popc(bal & ((1u << lane) - 1u))) & 63u;
+          wel[warp][idx] = (uint32_t)(it * EPS) + (uint32_t)(u * K1_CONSUMERS + tid) * 8u;
+          uint4* p4 = reinterpret_cast<uint4*>(&wdat[warp][idx]);
+#pragma unroll
+          for (int k = 0; k < RAWW / 4; ++k) p4[k] = make_uint4(v[u].w[4 * k], v[u].w[4 * k + 1], v[u].w[4 * k + 2], v[u].w[4 * k + 3]);
+        }
+        wtail += __popc(bal);
+        if (wtail - whead >= 32) {
+          __syncwarp();
+          emit_entry(whead + lane);
+          whead += 32;
+          __syncwarp();
+        }
+      }
+      if (last_it && wtail != whead) {                     // leftovers of this warp: drain with the lanes that have one
+        __syncwarp();
+        if ((uint32_t)lane < wtail - whead) emit_entry(whead + lane);
+        whead = wtail;
+      }
+      if (++since >= batch || last_it) {
+        since = 0;
+        k1_consumer_sync();                                // every consumer's records are in the queues
+        flush(last_it);
+        k1_consumer_sync();                                // queues drained before the next records arrive
       }
     }
-    __syncthreads();
   }
 
+  if (s_abort) local_status |= ZEN_TIMEOUT;
   if (local_status) atomicOr(c.status, local_status);
-  // completion: the last CTA to arrive publishes counts and epochs to the consumers
-  __threadfence_system();
+  // completion: the last CTA to arrive publishes counts and epochs to the consumers.  Every thread's stores are
+  // ordered before thread 0's system-scope fence by the barrier (the fence is cumulative).
   __syncthreads();
   if (tid == 0) {
+    __threadfence_system();
     const uint32_t prev = atomicAdd(&c.cursors[ZEN_MAX_RANKS], 1u);
     s_last = (prev == gridDim.x - 1) ? 1u : 0u;
   }
@@ -291,12 +399,12 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
       const int p = tid;
       const uint32_t raw = atomicAdd(&c.cursors[kBroadcast ? 0 : p], 0u);
       const uint32_t st = atomicOr(c.status, 0u);
-      ZenMail* mail = reinterpret_cast<ZenMail*>(c.sym[p] + c.off_rec_mail) + c.rank;
+      ZenMail* mail = zen_rec_mail(c, p, c.rank, epoch);
       mail->count = min(raw, c.cap_rec);
       mail->info = ((raw > c.cap_rec) || (st & ZEN_REC_OVERFLOW)) ? 1u : 0u;
       mail->aux = 0;
       __threadfence_system();
-      zen_st_release_sys(&mail->epoch, c.epoch);
+      zen_st_release_sys(&mail->epoch, epoch);
     }
     __syncthreads();
     if (tid < ZEN_MAX_RANKS + 1) c.cursors[tid] = 0;                  // ready for the next call
@@ -305,212 +413,260 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
 
 // ---------------------------------------------------------------------------------------------
 // K2: owner-side reduce of sources [src_begin, src_end).  One launch over all sources is the fast
-// mode; one launch per source gives a fixed accumulation order.
+// mode; one launch per source gives a fixed accumulation order.  The waits on the sources' mailboxes
+// run side by side (one thread each); records are read two per 16-byte load, four loads in flight.
 template <typename T>
 __global__ void __launch_bounds__(256)
 zen_owner_reduce_kernel(const ZenSparseCtx c, int src_begin, int src_end) {
-  __shared__ uint32_t s_ok;
+  __shared__ uint32_t s_n[ZEN_MAX_RANKS];
+  __shared__ uint32_t s_flag[ZEN_MAX_RANKS];
+  const uint32_t epoch = zen_epoch(c);
+  const int ns = src_end - src_begin;
+  if ((int)threadIdx.x < ns) {
+    const int s = src_begin + threadIdx.x;
+    const ZenMail* mail = zen_rec_mail(c, c.rank, s, epoch);
+    uint32_t n = 0, fl = 0;
+    if (zen_wait_epoch(&mail->epoch, epoch, c.wait_ns)) {
+      n = min(zen_ld_acquire_sys(&mail->count), c.cap_rec);
+      if (zen_ld_acquire_sys(&mail->info) & 1u) fl = ZEN_PEER_OVERFLOW;
+    } else {
+      fl = ZEN_TIMEOUT;
+    }
+    s_n[threadIdx.x] = n;
+    s_flag[threadIdx.x] = fl;
+  }
+  __syncthreads();
   uint32_t local_status = 0;
-  for (int s = src_begin; s < src_end; ++s) {
-    const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_rec_mail) + s;
-    if (threadIdx.x == 0) s_ok = zen_wait_epoch(&mail->epoch, c.epoch, c.wait_ns) ? 1u : 0u;
-    __syncthreads();
-    const bool ok = s_ok != 0;
-    __syncthreads();
-    if (!ok) { local_status |= ZEN_TIMEOUT; continue; }
-    const uint32_t n = min(zen_ld_acquire_sys(&mail->count), c.cap_rec);
-    if (zen_ld_acquire_sys(&mail->info) & 1u) local_status |= ZEN_PEER_OVERFLOW;
-    const uint2* rec = reinterpret_cast<const uint2*>(c.sym[c.rank] + c.off_rec) + (uint64_t)s * c.cap_rec;
-    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-      const uint2 r = rec[i];
-      if (r.x < c.nslots) {
-        atomicAdd(&c.acc[r.x], ZenVal<T>::unbits(r.y));
-        atomicOr(&c.bitmap[r.x >> 5], 1u << (r.x & 31));
-      } else {
-        local_status |= ZEN_BAD_ARG;
+  auto apply = [&](uint32_t slot, uint32_t bits) {
+    if (slot < c.nslots) {
+      atomicAdd(&c.acc[slot], ZenVal<T>::unbits(bits));
+      atomicOr(&c.bitmap[slot >> 5], 1u << (slot & 31));
+    } else {
+      local_status |= ZEN_BAD_ARG;
+    }
+  };
+  const uint32_t gtid = blockIdx.x * blockDim.x + threadIdx.x, gstride = gridDim.x * blockDim.x;
+  for (int k = 0; k < ns; ++k) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) local_status |= s_flag[k];
+    const uint32_t n = s_n[k];
+    const uint2* rec = zen_rec_slots(c, c.rank, src_begin + k, epoch);
+    const uint4* rec4 = reinterpret_cast<const uint4*>(rec);
+    const uint32_t npair = n >> 1;
+    for (uint32_t i = gtid; i < npair; i += 4 * gstride) {
+      uint4 r[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t j = i + u * gstride;
+        r[u] = (j < npair) ? rec4[j] : make_uint4(0xffffffffu, 0u, 0xffffffffu, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i + u * gstride < npair) { apply(r[u].x, r[u].y); apply(r[u].z, r[u].w); }
       }
     }
+    if ((n & 1u) && gtid == 0) { const uint2 r = rec[n - 1]; apply(r.x, r.y); }
   }
   if (local_status) atomicOr(c.status, local_status);
 }
 
 // ---------------------------------------------------------------------------------------------
-// K3a: touched slots per 1024-slot chunk.
-__global__ void __launch_bounds__(256) zen_chunk_count_kernel(const ZenSparseCtx c) {
-  const int lane = threadIdx.x & 31;
-  const uint32_t gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const uint32_t nw = (gridDim.x * blockDim.x) >> 5;
-  for (uint32_t ch = gw; ch < c.nchunks; ch += nw) {
-    const uint32_t wi = ch * 32 + lane;
-    uint32_t n = (wi < c.nwords) ? __popc(c.bitmap[wi]) : 0u;
-#pragma unroll
-    for (int d = 16; d; d >>= 1) n += __shfl_xor_sync(0xffffffffu, n, d);
-    if (lane == 0) c.chunk_off[ch] = n;
-  }
-}
-
-// K3b: exclusive scan of the chunk counts in place; total at [nchunks].  One CTA.
-__global__ void __launch_bounds__(1024) zen_chunk_scan_kernel(const ZenSparseCtx c) {
-  __shared__ uint32_t part[1024];
-  const uint32_t n = c.nchunks;
-  const uint32_t per = (n + 1023) / 1024;
-  const uint32_t b = threadIdx.x * per, e = min(n, b + per);
-  uint32_t s = 0;
-  for (uint32_t i = b; i < e; ++i) s += c.chunk_off[i];
-  part[threadIdx.x] = s;
-  __syncthreads();
-  for (int d = 1; d < 1024; d <<= 1) {
-    uint32_t t = (threadIdx.x >= (unsigned)d) ? part[threadIdx.x - d] : 0u;
-    __syncthreads();
-    part[threadIdx.x] += t;
-    __syncthreads();
-  }
-  uint32_t run = part[threadIdx.x] - s;
-  for (uint32_t i = b; i < e; ++i) {
-    const uint32_t t = c.chunk_off[i];
-    c.chunk_off[i] = run;
-    run += t;
-  }
-  if (threadIdx.x == 1023) c.chunk_off[n] = part[1023];
-}
-
-// K3c: compact the touched slots of 8 consecutive chunks per CTA into shared memory, then push the
-// contiguous run (values, and COO slots or bitmap words + chunk offsets) to every peer.
+// K3: compact the touched slots of K3_WARPS consecutive 1024-slot chunks per CTA step into shared
+// memory, reserve room for the run in this owner's payload with one atomic (runs start on 8-value
+// boundaries, so every push is a 16-byte vector store), then push the run -- values, and COO slots
+// or bitmap words + the chunk's value offset -- to every peer.  Chunks may land in the payload in any
+// order: the consumer finds a chunk's values through its offset (bitmap) or does not care (COO).
 #define K3_WARPS 8
+#define K3_RUN_ALIGN 8u
+
+__device__ __forceinline__ void zen_multimem_st16(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+}
+__device__ __forceinline__ void zen_multimem_st4(void* mc_addr, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
+}
+
 template <typename T>
 __global__ void __launch_bounds__(K3_WARPS * 32)
 zen_gather_push_kernel(const ZenSparseCtx c) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem_raw);                       // [K3_WARPS * 1024 + 16]
   T* s_val = reinterpret_cast<T*>(smem_raw + (K3_WARPS * 1024 + 16) * 4);        // [K3_WARPS * 1024 + 16]
-  __shared__ uint32_t s_last;
+  __shared__ uint32_t s_last, s_fmt, s_gbase, s_wtot[K3_WARPS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const uint32_t total = c.chunk_off[c.nchunks];
-  const bool overflow = total > c.cap_g;
-  uint32_t fmt = c.fmt_mode;
-  if (fmt == 0) fmt = ((uint64_t)total * 32ull > (uint64_t)c.nslots) ? ZEN_FMT_BITMAP : ZEN_FMT_COO;
-  if (fmt == ZEN_FMT_COO && total > c.g_idx_words) fmt = ZEN_FMT_BITMAP;   // COO list would not fit
+  const uint32_t epoch = zen_epoch(c);
+  if (tid == 0) {
+    // index format: bitmap when more than one slot in 32 is expected to be touched.  The estimate is the number of
+    // records received (an upper bound of the union), which every CTA reads from the same mails.
+    uint32_t fmt = c.fmt_mode;
+    uint64_t recs = 0;
+    for (int s = 0; s < c.nranks; ++s) recs += min(zen_rec_mail(c, c.rank, s, epoch)->count, c.cap_rec);
+    if (fmt == 0) fmt = (recs * 32ull > (uint64_t)c.nslots) ? ZEN_FMT_BITMAP : ZEN_FMT_COO;
+    // a COO list (touched slots plus the padding between runs) must fit the index region
+    const uint64_t ngr = (c.nchunks + K3_WARPS - 1) / K3_WARPS;
+    if (fmt == ZEN_FMT_COO && min(recs, (uint64_t)c.nslots) + K3_RUN_ALIGN * ngr > (uint64_t)c.g_idx_words) fmt = ZEN_FMT_BITMAP;
+    s_fmt = fmt;
+  }
+  __syncthreads();
+  const uint32_t fmt = s_fmt;
   const uint32_t ngroups = (c.nchunks + K3_WARPS - 1) / K3_WARPS;
   constexpr uint32_t VPV = 16 / sizeof(T);                               // values per 16-byte vector
+  uint32_t local_status = 0;
+  char* mc = c.mc;
 
   for (uint32_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
-    const uint32_t ch0 = grp * K3_WARPS;
-    const uint32_t ch = ch0 + warp;
-    const uint32_t gbase = c.chunk_off[ch0];                             // first value of this CTA's run
-    const uint32_t gend = c.chunk_off[min(ch0 + K3_WARPS, c.nchunks)];
-    const uint32_t mis_v = gbase % VPV, mis_i = gbase % 4;
-    uint32_t word = 0, coff = 0;
-    if (ch < c.nchunks) {
-      const uint32_t wi = ch * 32 + lane;
-      word = (wi < c.nwords) ? c.bitmap[wi] : 0u;
-      coff = c.chunk_off[ch];
-      if (wi < c.nwords && word) c.bitmap[wi] = 0;                       // leave the bitmap clean for the next call
+    const uint32_t ch = grp * K3_WARPS + warp;
+    uint32_t word = 0;
+    const uint32_t wi = ch * 32 + lane;
+    if (ch < c.nchunks && wi < c.nwords) {
+      word = c.bitmap[wi];
+      if (word) c.bitmap[wi] = 0;                                        // leave the bitmap clean for the next call
     }
-    uint32_t incl = __popc(word);
+    const uint32_t pc = __popc(word);
+    uint32_t incl = pc;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
       if (lane >= d) incl += t;
     }
-    const uint32_t woff = incl - __popc(word);
+    const uint32_t wtot = __shfl_sync(0xffffffffu, incl, 31);
+    if (lane == 0) s_wtot[warp] = wtot;
+    __syncthreads();
+    uint32_t coff = 0, n = 0;                                            // this chunk's offset in the run, run length
+#pragma unroll
+    for (int w = 0; w < K3_WARPS; ++w) { const uint32_t t = s_wtot[w]; if (w < warp) coff += t; n += t; }
+    const uint32_t nres = (n + K3_RUN_ALIGN - 1) & ~(K3_RUN_ALIGN - 1u);
+    if (tid == 0) s_gbase = n ? atomicAdd(&c.cursors[ZEN_MAX_RANKS + 2], nres) : 0u;
     {
-      // Stream the accumulator: a lane whose bitmap word is non-empty loads its 32 slots as eight independent
-      // 16-byte vectors, clears them, and appends the touched ones (in slot order) to the CTA's staging run.
-      uint32_t r = (coff - gbase) + woff;
-      if (word) {
-        float f[32];
-        float4* ap = reinterpret_cast<float4*>(c.acc + (size_t)ch * 1024 + (size_t)lane * 32);
+      // A lane whose bitmap word is non-empty appends its touched slots (in slot order) to the CTA's staging run and
+      // clears them.  Sparse words are walked bit by bit (only the touched 32-byte sectors move); a warp with dense
+      // words streams all 32 slots of the word as eight 16-byte vectors instead.
+      uint32_t r = coff + (incl - pc);
+      float* ap = c.acc + (size_t)ch * 1024 + (size_t)lane * 32;
+      const uint32_t slot0 = ch * 1024 + lane * 32;
+      const bool dense = __any_sync(0xffffffffu, pc > 10);
+      if (dense) {
+        if (word) {
+          float f[32];
+          float4* ap4 = reinterpret_cast<float4*>(ap);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) *reinterpret_cast<float4*>(&f[4 * k]) = ap[k];
+          for (int k = 0; k < 8; ++k) *reinterpret_cast<float4*>(&f[4 * k]) = ap4[k];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) ap[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-        const uint32_t slot0 = ch * 1024 + lane * 32;
+          for (int k = 0; k < 8; ++k) ap4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if ((word >> i) & 1u) {
-            s_val[mis_v + r] = ZenVal<T>::from_f(f[i]);
-            if (fmt == ZEN_FMT_COO) s_idx[mis_i + r] = slot0 + i;
-            ++r;
+          for (int i = 0; i < 32; ++i) {
+            if ((word >> i) & 1u) {
+              s_val[r] = ZenVal<T>::from_f(f[i]);
+              if (fmt == ZEN_FMT_COO) s_idx[r] = slot0 + i;
+              ++r;
+            }
+          }
+        }
+      } else {
+        uint32_t w = word;
+        while (w) {
+          int i[4];
+          float f[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) { i[u] = w ? (__ffs(w) - 1) : -1; w &= w - 1; }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) f[u] = (i[u] >= 0) ? ap[i[u]] : 0.f;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (i[u] >= 0) {
+              ap[i[u]] = 0.f;
+              s_val[r] = ZenVal<T>::from_f(f[u]);
+              if (fmt == ZEN_FMT_COO) s_idx[r] = slot0 + i[u];
+              ++r;
+            }
           }
         }
       }
     }
+    if (fmt == ZEN_FMT_COO && (uint32_t)tid < nres - n) s_idx[n + tid] = 0xffffffffu;   // padding entries are skipped by the consumer
     __syncthreads();
-    if (!overflow) {
-      const uint32_t n = gend - gbase;
-      for (int p = 0; p < c.nranks; ++p) {
-        char* base = c.sym[p];
-        // values: scalar head up to a 16-byte boundary, vector body, scalar tail
-        T* dv = reinterpret_cast<T*>(base + c.off_g_val + (uint64_t)c.rank * c.cap_g * 4ull) + gbase;
-        const uint32_t head = min(n, (VPV - mis_v) % VPV);
-        for (uint32_t i = tid; i < head; i += blockDim.x) dv[i] = s_val[mis_v + i];
-        const uint32_t nvec = (n - head) / VPV;
-        {
-          uint4* d4 = reinterpret_cast<uint4*>(dv + head);
-          const uint4* s4 = reinterpret_cast<const uint4*>(s_val + mis_v + head);
-          for (uint32_t i = tid; i < nvec; i += blockDim.x) d4[i] = s4[i];
-        }
-        for (uint32_t i = head + nvec * VPV + tid; i < n; i += blockDim.x) dv[i] = s_val[mis_v + i];
+    const uint32_t gbase = s_gbase;
+    if (n && (gbase + nres > c.cap_g || (fmt == ZEN_FMT_COO && gbase + nres > c.g_idx_words))) {
+      local_status |= ZEN_GATHER_OVERFLOW;
+    } else {
+      const uint32_t nvec = nres / VPV, nvi = nres / 4;
+      const uint64_t val_off = c.off_g_val + (uint64_t)c.rank * c.cap_g * 4ull + (uint64_t)gbase * sizeof(T);
+      const uint64_t idx_off = c.off_g_idx + ((uint64_t)c.rank * c.g_idx_words + gbase) * 4ull;
+      const uint64_t bm_off = c.off_g_idx + ((uint64_t)c.rank * c.g_idx_words + wi) * 4ull;
+      const uint64_t off_off = c.off_g_off + ((uint64_t)c.rank * (c.nchunks + 1) + ch) * 4ull;
+      const uint4* sv4 = reinterpret_cast<const uint4*>(s_val);
+      const uint4* si4 = reinterpret_cast<const uint4*>(s_idx);
+      if (mc) {                                                          // one store, replicated by the switch
+        for (uint32_t i = tid; i < nvec; i += blockDim.x) zen_multimem_st16(mc + val_off + (uint64_t)i * 16, sv4[i]);
         if (fmt == ZEN_FMT_COO) {
-          uint32_t* di = reinterpret_cast<uint32_t*>(base + c.off_g_idx) + (uint64_t)c.rank * c.g_idx_words + gbase;
-          const uint32_t hi = min(n, (4u - mis_i) % 4u);
-          for (uint32_t i = tid; i < hi; i += blockDim.x) di[i] = s_idx[mis_i + i];
-          const uint32_t nv = (n - hi) / 4;
-          uint4* d4 = reinterpret_cast<uint4*>(di + hi);
-          const uint4* s4 = reinterpret_cast<const uint4*>(s_idx + mis_i + hi);
-          for (uint32_t i = tid; i < nv; i += blockDim.x) d4[i] = s4[i];
-          for (uint32_t i = hi + nv * 4 + tid; i < n; i += blockDim.x) di[i] = s_idx[mis_i + i];
+          for (uint32_t i = tid; i < nvi; i += blockDim.x) zen_multimem_st16(mc + idx_off + (uint64_t)i * 16, si4[i]);
         } else if (ch < c.nchunks) {
-          uint32_t* db = reinterpret_cast<uint32_t*>(base + c.off_g_idx) + (uint64_t)c.rank * c.g_idx_words;
-          const uint32_t wi = ch * 32 + lane;
-          if (wi < c.nwords) db[wi] = word;
-          if (lane == 0)
-            reinterpret_cast<uint32_t*>(base + c.off_g_off)[(uint64_t)c.rank * (c.nchunks + 1) + ch] = coff;
+          if (wi < c.nwords) zen_multimem_st4(mc + bm_off, word);
+          if (lane == 0) zen_multimem_st4(mc + off_off, gbase + coff);
+        }
+      } else {
+        for (int p = 0; p < c.nranks; ++p) {
+          char* base = c.sym[p];
+          uint4* dv = reinterpret_cast<uint4*>(base + val_off);
+          for (uint32_t i = tid; i < nvec; i += blockDim.x) dv[i] = sv4[i];
+          if (fmt == ZEN_FMT_COO) {
+            uint4* di = reinterpret_cast<uint4*>(base + idx_off);
+            for (uint32_t i = tid; i < nvi; i += blockDim.x) di[i] = si4[i];
+          } else if (ch < c.nchunks) {
+            if (wi < c.nwords) *reinterpret_cast<uint32_t*>(base + bm_off) = word;
+            if (lane == 0) *reinterpret_cast<uint32_t*>(base + off_off) = gbase + coff;
+          }
         }
       }
     }
     __syncthreads();
   }
 
-  __threadfence_system();
+  if (local_status) atomicOr(c.status, local_status);
   __syncthreads();
   if (tid == 0) {
+    __threadfence_system();
     const uint32_t prev = atomicAdd(&c.cursors[ZEN_MAX_RANKS + 1], 1u);
     s_last = (prev == gridDim.x - 1) ? 1u : 0u;
   }
   __syncthreads();
   if (s_last) {
     __threadfence_system();
-    if (overflow && tid == 0) atomicOr(c.status, ZEN_GATHER_OVERFLOW);
     if (tid < c.nranks) {
+      const uint32_t total = atomicAdd(&c.cursors[ZEN_MAX_RANKS + 2], 0u);
       const uint32_t st = atomicOr(c.status, 0u);
+      const bool overflow = total > c.cap_g || (st & ZEN_GATHER_OVERFLOW);
       ZenMail* mail = reinterpret_cast<ZenMail*>(c.sym[tid] + c.off_g_mail) + c.rank;
       mail->count = overflow ? 0u : total;
       mail->info = ((overflow || (st & (ZEN_REC_OVERFLOW | ZEN_PEER_OVERFLOW | ZEN_TIMEOUT))) ? 1u : 0u) | (fmt << 8);
       mail->aux = 0;
       __threadfence_system();
-      zen_st_release_sys(&mail->epoch, c.epoch);
+      zen_st_release_sys(&mail->epoch, epoch);
     }
-    if (tid == 0) c.cursors[ZEN_MAX_RANKS + 1] = 0;
+    __syncthreads();
+    if (tid == 0) { c.cursors[ZEN_MAX_RANKS + 1] = 0; c.cursors[ZEN_MAX_RANKS + 2] = 0; }
   }
 }
 
 // ---------------------------------------------------------------------------------------------
 // K4: densify.  Walks every owner's slot space chunk by chunk; every output element is written once
 // (zeros included), so the output needs no memset.  Owners that chose COO get their blocks
-// zero-filled here and their values scattered by zen_densify_coo_kernel afterwards.
+// zero-filled here and their values scattered by zen_densify_coo_kernel afterwards.  The bitmap word
+// and value offset of a warp's next chunk are fetched while it works on the current one.
 template <typename T>
 __global__ void __launch_bounds__(256)
 zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
   __shared__ uint32_t s_fmt[ZEN_MAX_RANKS];
   const int tid = threadIdx.x, lane = tid & 31;
+  const uint32_t epoch = zen_epoch(c);
   uint32_t local_status = 0;
   if (tid < c.nranks) {
     const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_g_mail) + tid;
     uint32_t f = 0;
-    if (zen_wait_epoch(&mail->epoch, c.epoch, c.wait_ns)) {
-      f = (mail->info >> 8) & 0xffu;
-      if (mail->info & 1u) { local_status |= ZEN_PEER_OVERFLOW; f = 0; }
+    if (zen_wait_epoch(&mail->epoch, epoch, c.wait_ns)) {
+      const uint32_t info = zen_ld_acquire_sys(&mail->info);
+      f = (info >> 8) & 0xffu;
+      if (info & 1u) { local_status |= ZEN_PEER_OVERFLOW; f = 0; }
     } else {
       local_status |= ZEN_TIMEOUT;
     }
@@ -522,21 +678,29 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
   const uint32_t gw = (blockIdx.x * blockDim.x + tid) >> 5;
   const uint32_t nw = (gridDim.x * blockDim.x) >> 5;
   const uint64_t nunits = (uint64_t)c.nranks * c.nchunks;
-  for (uint64_t unit = gw; unit < nunits; unit += nw) {
+  const char* base = c.sym[c.rank];
+  auto fetch = [&](uint64_t unit, uint32_t& word, uint32_t& coff) {
+    word = 0; coff = 0;
+    if (unit >= nunits) return;
     const uint32_t o = (uint32_t)(unit / c.nchunks), ch = (uint32_t)(unit % c.nchunks);
-    const bool bm = s_fmt[o] == ZEN_FMT_BITMAP;
-    const char* base = c.sym[c.rank];
-    const uint32_t* gbm = reinterpret_cast<const uint32_t*>(base + c.off_g_idx) + (uint64_t)o * c.g_idx_words;
-    const T* gval = reinterpret_cast<const T*>(base + c.off_g_val + (uint64_t)o * c.cap_g * 4ull);
+    if (s_fmt[o] != ZEN_FMT_BITMAP) return;
     const uint32_t wi = ch * 32 + lane;
-    uint32_t word = (bm && wi < c.nwords) ? gbm[wi] : 0u;
+    if (wi < c.nwords) word = (reinterpret_cast<const uint32_t*>(base + c.off_g_idx) + (uint64_t)o * c.g_idx_words)[wi];
+    coff = reinterpret_cast<const uint32_t*>(base + c.off_g_off)[(uint64_t)o * (c.nchunks + 1) + ch];
+  };
+  uint32_t word, coff;
+  fetch(gw, word, coff);
+  for (uint64_t unit = gw; unit < nunits; unit += nw) {
+    uint32_t nword, ncoff;
+    fetch(unit + nw, nword, ncoff);
+    const uint32_t o = (uint32_t)(unit / c.nchunks), ch = (uint32_t)(unit % c.nchunks);
+    const T* gval = reinterpret_cast<const T*>(base + c.off_g_val + (uint64_t)o * c.cap_g * 4ull);
     uint32_t incl = __popc(word);
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
       if (lane >= d) incl += t;
     }
-    const uint32_t coff = bm ? reinterpret_cast<const uint32_t*>(base + c.off_g_off)[(uint64_t)o * (c.nchunks + 1) + ch] : 0u;
     const uint32_t woff = coff + incl - __popc(word);
     // four passes of 256 slots: every lane produces 8 consecutive output elements (one or two 16-byte stores)
 #pragma unroll
@@ -556,7 +720,10 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         v[i] = ZenVal<T>::from_f(0.f);
-        if ((byte >> i) & 1u) v[i] = gval[off0 + __popc(byte & ((1u << i) - 1u))];
+        if ((byte >> i) & 1u) {
+          const uint32_t at = off0 + __popc(byte & ((1u << i) - 1u));
+          if (at < c.cap_g) v[i] = gval[at];
+        }
       }
       if (e + 8 <= N) {
         if (sizeof(T) == 2) {
@@ -579,6 +746,7 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
           if (e + i < N) out[e + i] = v[i];
       }
     }
+    word = nword; coff = ncoff;
   }
   if (local_status) atomicOr(c.status, local_status);
 }
@@ -588,11 +756,12 @@ __global__ void __launch_bounds__(256)
 zen_densify_coo_kernel(const ZenSparseCtx c, T* __restrict__ out) {
   __shared__ uint32_t s_n[ZEN_MAX_RANKS];
   const uint32_t G = c.perm.block;
+  const uint32_t epoch = zen_epoch(c);
   if (threadIdx.x < c.nranks) {
     const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_g_mail) + threadIdx.x;
     uint32_t n = 0;
     // the bitmap pass of this call already waited for this epoch
-    if (zen_ld_acquire_sys(&mail->epoch) == c.epoch) {
+    if (zen_ld_acquire_sys(&mail->epoch) == epoch) {
       const uint32_t info = zen_ld_acquire_sys(&mail->info);
       if (((info >> 8) & 0xffu) == ZEN_FMT_COO && !(info & 1u))
         n = min(zen_ld_acquire_sys(&mail->count), min(c.cap_g, c.g_idx_words));
@@ -608,7 +777,7 @@ zen_densify_coo_kernel(const ZenSparseCtx c, T* __restrict__ out) {
     const T* gv = reinterpret_cast<const T*>(base + c.off_g_val + (uint64_t)o * c.cap_g * 4ull);
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
       const uint32_t slot = gi[i];
-      if (slot >= c.nslots) continue;
+      if (slot >= c.nslots) continue;                                  // padding between runs
       const uint32_t blk = zen_perm_inv(c.perm, o * c.perm.sb + (slot >> c.perm.lg));
       const uint64_t e = ((uint64_t)blk << c.perm.lg) + (slot & (G - 1u));
       if (e < c.numel) out[e] = gv[i];
@@ -622,18 +791,21 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 zen_scatter_source_kernel(const ZenSparseCtx c, T* __restrict__ out, int src) {
   __shared__ uint32_t s_ok;
-  const ZenMail* mail = reinterpret_cast<const ZenMail*>(c.sym[c.rank] + c.off_rec_mail) + src;
-  if (threadIdx.x == 0) s_ok = zen_wait_epoch(&mail->epoch, c.epoch, c.wait_ns) ? 1u : 0u;
+  const uint32_t epoch = zen_epoch(c);
+  const ZenMail* mail = zen_rec_mail(c, c.rank, src, epoch);
+  if (threadIdx.x == 0) s_ok = zen_wait_epoch(&mail->epoch, epoch, c.wait_ns) ? 1u : 0u;
   __syncthreads();
   if (!s_ok) { if (threadIdx.x == 0) atomicOr(c.status, ZEN_TIMEOUT); return; }
   if ((mail->info & 1u) && threadIdx.x == 0) atomicOr(c.status, ZEN_PEER_OVERFLOW);
   const uint32_t n = min(mail->count, c.cap_rec);
-  const uint2* rec = reinterpret_cast<const uint2*>(c.sym[c.rank] + c.off_rec) + (uint64_t)src * c.cap_rec;
+  const uint2* rec = zen_rec_slots(c, c.rank, src, epoch);
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const uint2 r = rec[i];
     if (r.x < c.numel) out[r.x] = ZenVal<T>::from_f(ZenVal<T>::to_f(out[r.x]) + ZenVal<T>::unbits(r.y));
   }
 }
+
+__global__ void zen_sparse_epoch_bump_kernel(uint32_t* e) { *e += 1u; }
 
 // ---------------------------------------------------------------------------------------------
 // Owner map (API parity with hash_index, functions_cuda_kernel.cu:169-177): out[i] = owner(i).
@@ -702,24 +874,38 @@ static int sm_count() {
   return g_sm_count;
 }
 
+template <typename T, bool kBroadcast, bool kRing>
+static int launch_partition_as(const ZenSparseCtx& c, const void* g, const float* thr, cudaStream_t st) {
+  constexpr uint32_t EPS = K1_STAGE_BYTES / sizeof(T);
+  const uint64_t nst = (c.numel + EPS - 1) / EPS;
+  const int nq = kBroadcast ? 1 : c.nranks;
+  const size_t smem = (size_t)nq * K1_QCAP * sizeof(uint2) + (kRing ? (size_t)K1_NS * K1_STAGE_BYTES : 0);
+  ZEN_CUDA_CHECK_RET(cudaFuncSetAttribute(zen_partition_push_kernel<T, kBroadcast, kRing>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  // every CTA takes a fixed share of the stages, so the grid is exactly what is resident at once
+  int per_sm = 0;
+  ZEN_CUDA_CHECK_RET(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, zen_partition_push_kernel<T, kBroadcast, kRing>,
+                                                                   K1_THREADS, smem));
+  if (per_sm < 1) per_sm = 1;
+  const int grid = grid_for(nst, 1, sm_count() * per_sm);
+  // stages between two drains of the queues: as many as keep a queue below half of its capacity at the density the
+  // plan was sized for (c.k1_density_ppm nonzeros per million elements; 0 = unknown)
+  int batch = 4;
+  if (c.k1_density_ppm) {
+    const double per_stage = (double)EPS * c.k1_density_ppm * 1e-6 / nq;
+    batch = per_stage > 0 ? (int)((K1_QCAP / 2) / per_stage) : 8;
+    if (batch < 1) batch = 1;
+    if (batch > 8) batch = 8;
+  }
+  zen_partition_push_kernel<T, kBroadcast, kRing><<<grid, K1_THREADS, smem, st>>>(c, (const T*)g, thr, batch);
+  return (int)cudaGetLastError();
+}
+
 template <typename T>
 static int launch_partition(const ZenSparseCtx& c, const void* g, const float* thr, int broadcast, cudaStream_t st) {
-  const uint64_t nwi = (c.numel + 255) / 256;
-  const uint64_t nit = (nwi + K1_WARPS * K1_U - 1) / (K1_WARPS * K1_U);
-  const int grid = grid_for(nit, 1, sm_count() * 3);
-  const int nq = broadcast ? 1 : c.nranks;
-  const size_t smem = (size_t)nq * K1_QCAP * sizeof(uint2);
-  const int aligned = (reinterpret_cast<uintptr_t>(g) % 16 == 0) ? 1 : 0;
-  if (broadcast) {
-    ZEN_CUDA_CHECK_RET(cudaFuncSetAttribute(zen_partition_push_kernel<T, true>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    zen_partition_push_kernel<T, true><<<grid, K1_THREADS, smem, st>>>(c, (const T*)g, thr, aligned);
-  } else {
-    ZEN_CUDA_CHECK_RET(cudaFuncSetAttribute(zen_partition_push_kernel<T, false>,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    zen_partition_push_kernel<T, false><<<grid, K1_THREADS, smem, st>>>(c, (const T*)g, thr, aligned);
-  }
-  return (int)cudaGetLastError();
+  const bool ring = reinterpret_cast<uintptr_t>(g) % 16 == 0;       // bulk copies need a 16-byte aligned source
+  if (broadcast) return ring ? launch_partition_as<T, true, true>(c, g, thr, st) : launch_partition_as<T, true, false>(c, g, thr, st);
+  return ring ? launch_partition_as<T, false, true>(c, g, thr, st) : launch_partition_as<T, false, false>(c, g, thr, st);
 }
 
 #define DISPATCH_DTYPE(dtype, ...)                                       \
@@ -733,6 +919,12 @@ static int launch_partition(const ZenSparseCtx& c, const void* g, const float* t
 extern "C" {
 
 int zen_sparse_ctx_size() { return (int)sizeof(ZenSparseCtx); }
+
+// Advance a device-resident call counter by one (first launch of a call whose kernels read `epoch_dev`).
+int zen_sparse_epoch_bump(uint32_t* epoch_dev, void* stream) {
+  zen_sparse_epoch_bump_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(epoch_dev);
+  return (int)cudaGetLastError();
+}
 
 // K1.  `thr` may be null (keep every nonzero) or point at a device float threshold on |g|.
 int zen_partition_push(const ZenSparseCtx* c, const void* g, const float* thr, int dtype, int broadcast, void* stream) {
@@ -755,12 +947,9 @@ int zen_owner_reduce(const ZenSparseCtx* c, int dtype, int deterministic, void* 
   return (int)cudaGetLastError();
 }
 
-// K3 (count, scan, compact + push).
+// K3 (compact + push in one launch).
 int zen_gather_push(const ZenSparseCtx* c, int dtype, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
-  const int g1 = grid_for(c->nchunks, 8, sm_count() * 8);
-  zen_chunk_count_kernel<<<g1, 256, 0, st>>>(*c);
-  zen_chunk_scan_kernel<<<1, 1024, 0, st>>>(*c);
   const int g3 = grid_for(c->nchunks, K3_WARPS, sm_count() * 3);
   DISPATCH_DTYPE(dtype, {
     const size_t smem = (K3_WARPS * 1024 + 16) * (4 + sizeof(T));
@@ -791,6 +980,20 @@ int zen_scatter_sources(const ZenSparseCtx* c, void* out, int dtype, void* strea
     DISPATCH_DTYPE(dtype, zen_scatter_source_kernel<T><<<sm_count() * 4, 256, 0, st>>>(*c, (T*)out, s));
   }
   return (int)cudaGetLastError();
+}
+
+// One whole call from a single entry (one crossing from the host language instead of five): optional bump of the
+// device call counter, partition + push, then scatter (method 1) or reduce + gather + densify (methods 2 / 3 / auto;
+// `c->fmt_mode` carries the format).  `out` may be `x`: the scan of `x` ends before the first write.
+int zen_sparse_allreduce(const ZenSparseCtx* c, const void* x, const float* thr, void* out, int dtype, int method1,
+                         int deterministic, void* stream) {
+  int rc = 0;
+  if (c->epoch_dev && (rc = zen_sparse_epoch_bump(const_cast<uint32_t*>(c->epoch_dev), stream))) return rc;
+  if ((rc = zen_partition_push(c, x, thr, dtype, method1 ? 1 : 0, stream))) return rc;
+  if (method1) return zen_scatter_sources(c, out, dtype, stream);
+  if ((rc = zen_owner_reduce(c, dtype, deterministic, stream))) return rc;
+  if ((rc = zen_gather_push(c, dtype, stream))) return rc;
+  return zen_densify(c, out, dtype, stream);
 }
 
 int zen_owner_map(int32_t* out, uint64_t n, const ZenPerm* perm, int mode, uint32_t table, int parts, void* stream) {

@@ -28,9 +28,10 @@ def _claim(p, needed: bool) -> bool:
 
 
 def _take_fresh(p) -> bool:
-    """True once per step for a parameter whose bucket view is known to hold zeros (the reducer marks it at
-    ``zero_grad``): the first direct writer may then overwrite instead of accumulate, which lets the GEMM skip
-    reading the old values."""
+    """True once per step for a parameter whose bucket view has not been written yet in this step (the reducer marks
+    it at ``zero_grad``).  The first direct writer then OVERWRITES instead of accumulating: the GEMM skips reading the
+    old values, and the reducer does not have to zero the view between steps (it may still hold the last step's
+    gradient)."""
     fresh = getattr(p, "zen_fresh", False)
     p.zen_fresh = False
     return fresh
@@ -41,6 +42,9 @@ def _declare_autograd_use(p, needed: bool) -> None:
     theirs directly: the reducer then also waits for the accumulate-grad hook of ``p``."""
     if p is not None and needed and getattr(p, "zen_direct_grad", False):
         p.zen_autograd_use = True
+        if getattr(p, "zen_fresh", False) and getattr(p, "zen_stale", False):
+            p.grad.zero_()               # autograd accumulates: the view must not still hold the last step's gradient
+            p.zen_stale = False
 
 
 class LinearFn(torch.autograd.Function):
@@ -93,7 +97,7 @@ class LinearFn(torch.autograd.Function):
                 dw = G.gemm_tn(a, b)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             if ctx.direct[1]:
-                E.colsum(dy2, out=bp.grad)
+                E.colsum(dy2, out=bp.grad, accumulate=not _take_fresh(bp))
                 bp.zen_ready(bp)
             else:
                 db = E.colsum(dy2)
@@ -124,9 +128,17 @@ class NormFn(torch.autograd.Function):
         layer, unit_offset, has_bias, has_res = ctx.cfg
         wp, bp = ctx.params
         direct = ctx.direct
+        acc = True
+        if direct:
+            fw, fb = _take_fresh(wp), (_take_fresh(bp) if bp is not None else None)
+            acc = not fw
+            if fb is not None and fb != fw:          # one of the pair was written before: zero the fresh one, then add
+                (wp if fw else bp).grad.zero_()
+                acc = True
         dh, dw, db = E.norm_bwd(dy.contiguous(), h, weight, rstd, mean if layer else None, dh_in,
                                 layer=layer, unit_offset=unit_offset, has_bias=has_bias,
-                                dw_out=wp.grad if direct else None, db_out=bp.grad if (direct and bp is not None) else None)
+                                dw_out=wp.grad if direct else None, db_out=bp.grad if (direct and bp is not None) else None,
+                                accumulate=acc)
         if direct:
             wp.zen_ready(wp)
             if bp is not None:
@@ -549,7 +561,7 @@ class SPLinearFn(torch.autograd.Function):
                 dw = G.gemm_tn(a, b)
         if has_bias and ctx.needs_input_grad[2]:
             if ctx.direct[1]:
-                E.colsum(db_src, out=bp.grad)
+                E.colsum(db_src, out=bp.grad, accumulate=not _take_fresh(bp))
                 bp.zen_ready(bp)
             else:
                 db = E.colsum(db_src)

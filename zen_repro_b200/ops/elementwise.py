@@ -73,9 +73,10 @@ def norm_fwd(x, weight, bias=None, residual=None, *, eps=1e-5, layer=False, unit
 
 
 def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_offset=False, has_bias=False,
-             dw_out=None, db_out=None):
+             dw_out=None, db_out=None, accumulate=True):
     """Returns (dh, dweight, dbias): dh includes ``dres`` (gradient on the residual stream) when given.
-    With ``dw_out`` / ``db_out`` the parameter gradients are ADDED into those tensors instead."""
+    With ``dw_out`` / ``db_out`` the parameter gradients are added into those tensors instead (``accumulate``) or
+    overwrite them."""
     cols = h.shape[-1]
     dy2, h2 = _c(dy).view(-1, cols), _c(h).view(-1, cols)
     rows = h2.shape[0]
@@ -95,10 +96,10 @@ def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_off
         if dres is not None:
             dh = dh + dres.reshape(-1, cols).float()
         if dw_out is not None:
-            dw_out.add_(dw)
+            dw_out.add_(dw) if accumulate else dw_out.copy_(dw)
             dw = dw_out
         if db_out is not None and db is not None:
-            db_out.add_(db)
+            db_out.add_(db) if accumulate else db_out.copy_(db)
             db = db_out
         return dh.to(h.dtype).view(h.shape), dw, db
     lib = _native.lib()
@@ -106,9 +107,9 @@ def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_off
     part_dw = _scratch_buf("norm_dw", parts * cols, torch.float32, h.device)
     part_db = _scratch_buf("norm_db", parts * cols, torch.float32, h.device) if layer else None
     dh = torch.empty_like(h2)
-    acc = dw_out is not None
-    dw = dw_out if acc else torch.empty_like(weight)
-    db = (db_out if acc else torch.empty_like(weight)) if (layer and has_bias) else None
+    acc = dw_out is not None and accumulate
+    dw = dw_out if dw_out is not None else torch.empty_like(weight)
+    db = (db_out if db_out is not None else torch.empty_like(weight)) if (layer and has_bias) else None
     dres2 = _c(dres).view(-1, cols) if dres is not None else None
     rc = lib.zen_norm_bwd(_native.ptr(dy2), _native.ptr(h2), _native.ptr(weight), _native.ptr(rstd), _native.ptr(mean),
                           _native.ptr(dres2), _native.ptr(dh), _native.ptr(part_dw), _native.ptr(part_db),
@@ -118,17 +119,18 @@ def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_off
     return dh.view(h.shape), dw, db
 
 
-def colsum(a: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Column sums of a [rows, cols] matrix (bias gradients); added into ``out`` when given."""
+def colsum(a: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = True) -> torch.Tensor:
+    """Column sums of a [rows, cols] matrix (bias gradients); added into ``out`` when given (``accumulate``) or written
+    over it."""
     cols = a.shape[-1]
     a2 = _c(a).view(-1, cols)
     if not a.is_cuda:
         r = a2.float().sum(0).to(a.dtype)
-        return r if out is None else out.add_(r)
+        return r if out is None else (out.add_(r) if accumulate else out.copy_(r))
     lib = _native.lib()
     rows = a2.shape[0]
     part = _scratch_buf("colsum", lib.zen_colsum_parts(rows) * cols, torch.float32, a.device)
-    acc = out is not None
+    acc = out is not None and accumulate
     if out is None:
         out = torch.empty(cols, dtype=a.dtype, device=a.device)
     _native.check(lib.zen_colsum(_native.ptr(a2), _native.ptr(part), _native.ptr(out), rows, cols, int(acc), _code(a2),

@@ -28,6 +28,9 @@ class EmbeddingRowSync:
         self._pending = None
         self.deterministic = deterministic
         self.last_count = None
+        self.early = True              # start the row exchange from ``put`` (on a side stream) instead of from ``sync_into``
+        self._stream = None
+        self._started = False
         self.force_library = False     # set after a reported failure of the peer-memory engine: all-gather the rows instead
 
     # ---- called from EmbeddingFn.backward -----------------------------------------------------
@@ -43,6 +46,15 @@ class EmbeddingRowSync:
             raise RuntimeError("a row-sparse gradient is already pending (gradient accumulation over several "
                                "micro-batches must call sync between them)")
         self._pending = (rows, count, vals)
+        if self.early and self._engine is not None and not self.force_library and vals.is_cuda:
+            # the rows exist as soon as the embedding backward has run: exchange them on a side stream now, while the
+            # last dense buckets are still in flight; only the final add into the gradient waits for the dense sync
+            if self._stream is None:
+                self._stream = torch.cuda.Stream()
+            self._stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._stream):
+                self._engine.start(rows, count, vals)
+            self._started = True
 
     # ---- called by the reducer after backward ---------------------------------------------------
     def prepare(self, device):
@@ -66,7 +78,11 @@ class EmbeddingRowSync:
         if self.P == 1:
             E.rows_add_(grad, rows, count, vals)
             return grad
-        if grad.is_cuda and not self.force_library:
+        if self._started:
+            self._started = False
+            torch.cuda.current_stream().wait_stream(self._stream)
+            self._engine.finish(grad, scale=self.scale)
+        elif grad.is_cuda and not self.force_library:
             self.prepare(grad.device)
             self._engine(rows, count, vals, grad, scale=self.scale)
         else:

@@ -163,7 +163,8 @@ def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, e
             return _future(buf, torch_future)
         if buf.device.type == "cuda" and buf.numel() > SMALL_BUCKET and not state.get("force_dense"):
             eng = engine_for(buf.numel(), buf.device)
-            out = eng(buf, method=method, threshold=thr)
+            # in place unless the bucket is still needed for a dense fallback: no second buffer, no copy back
+            out = eng(buf, method=method, threshold=thr, out=None if verify else buf)
             if verify:
                 masked = buf if thr is None else torch.where(buf.abs() >= thr.to(buf.dtype), buf, torch.zeros_like(buf))
                 out = verified_or_dense(out, eng.check(), masked, dp_group, state)

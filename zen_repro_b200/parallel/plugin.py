@@ -82,6 +82,8 @@ class Booster:
             model.sparse_sink = emb_sync
             if getattr(model, "lm_head", None) is not None:
                 wte.zen_sparse_only = True
+            else:
+                wte.zen_early = True         # tied: only the LM-head product is left in the dense gradient
         ddp = ZenDDP(model, pl.dp_group, pl.ddp_bucket_cap_mb, emb_sync, overlap=pl.overlap)
         if emb_sync is not None:
             emb_sync.prepare(pl.device)

@@ -73,8 +73,17 @@ class ZenDDP(nn.Module):
         dense = [p for p in params if not getattr(p, "zen_sparse_only", False)]
         cap = int(bucket_cap_mb * 1024 * 1024)
         self.buckets: list[_Bucket] = []
+        # A parameter flagged ``zen_early`` gets its whole gradient at the very start of backward (the tied token
+        # embedding when its lookup rows travel through the row-sparse path: what is left is the LM-head product).  It
+        # leads the bucket order in a bucket of its own, so its all-reduce overlaps the rest of backward instead of
+        # waiting at the end with the first layers' parameters.
+        early = [p for p in dense if getattr(p, "zen_early", False)]
+        for p in early:
+            self.buckets.append(_Bucket(len(self.buckets), [p], p.dtype, self.device))
         cur, cur_bytes, cur_dtype = [], 0, None
         for p in reversed(dense):
+            if getattr(p, "zen_early", False):
+                continue
             nbytes = p.numel() * p.element_size()
             if cur and (cur_bytes + nbytes > cap or p.dtype != cur_dtype):
                 self.buckets.append(_Bucket(len(self.buckets), cur, cur_dtype, self.device))
@@ -176,6 +185,10 @@ class ZenDDP(nn.Module):
         if self.require_sync:
             for b in self.buckets:
                 if not b.launched:           # parameters without a gradient this step, or undeclared uses
+                    for p, v in zip(b.params, b.views):
+                        if getattr(p, "zen_fresh", False) and getattr(p, "zen_stale", False):
+                            v.zero_()        # nobody wrote it: do not send (or apply) the last step's gradient again
+                            p.zen_stale = False
                     self._launch(b)
             used = self.comm_stream is not None and getattr(self, "_comm_used", False)
             ctx = torch.cuda.stream(self.comm_stream) if used else _null()
@@ -201,6 +214,8 @@ class ZenDDP(nn.Module):
             b.pending = len(b.params)
             b.launched = False
             for p in b.params:
+                p.zen_direct_only = (getattr(p, "zen_expected", 0) > 0 and not getattr(p, "zen_autograd_use", False)
+                                     and not getattr(p, "zen_autograd_done", False) and getattr(p, "zen_complete", False))
                 p.zen_signals = 0
                 p.zen_expected = 0
                 p.zen_autograd_use = False
@@ -208,10 +223,20 @@ class ZenDDP(nn.Module):
                 p.zen_complete = False
 
     def zero_grad(self, set_to_none: bool = False) -> None:
+        """Arm the next step.  A parameter whose gradient came only from direct writers in the step that just ended
+        is not zeroed: its first writer of the next step overwrites the view (``zen_fresh``).  The others (gradients
+        that autograd accumulates) are zeroed."""
         for b in self.buckets:
-            b.buffer.zero_()
-            for p in b.params:
-                p.zen_fresh = True              # the view holds zeros: the first direct writer may overwrite
+            lazy = [bool(getattr(p, "zen_direct_only", False)) for p in b.params]
+            if not any(lazy):
+                b.buffer.zero_()
+            elif not all(lazy):
+                for p, v, l in zip(b.params, b.views, lazy):
+                    if not l:
+                        v.zero_()
+            for p, l in zip(b.params, lazy):
+                p.zen_fresh = True              # nothing written yet in the coming step: the first direct writer overwrites
+                p.zen_stale = l                 # ... and the view still holds the old gradient
         # gradients of row-sparse-only parameters are rebuilt from zero by the embedding sync of the next step
 
 

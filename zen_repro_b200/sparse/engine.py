@@ -21,12 +21,14 @@ from dataclasses import dataclass, field
 import torch
 
 from .. import _native
+from ..utils import trace
 from ..runtime.symmetric import LocalSymmetric, SymmetricRegion, make_symmetric
 from .hashing import BlockPermutation
 
 MAX_RANKS = 8
 ST_REC_OVERFLOW, ST_GATHER_OVERFLOW, ST_TIMEOUT, ST_PEER_OVERFLOW, ST_BAD_ARG = 1, 2, 4, 8, 16
 FMT_AUTO, FMT_COO, FMT_BITMAP = 0, 1, 2
+CANARY_BYTES, CANARY_WORD = 256, 0x5AFEC0DE
 
 
 class _Perm(ctypes.Structure):
@@ -48,6 +50,8 @@ class _Ctx(ctypes.Structure):
         ("cursors", ctypes.c_void_p), ("status", ctypes.c_void_p),
         ("numel", ctypes.c_uint64), ("nslots", ctypes.c_uint32), ("nwords", ctypes.c_uint32),
         ("perm", _Perm),
+        ("epoch_dev", ctypes.c_void_p), ("mc", ctypes.c_void_p),
+        ("k1_density_ppm", ctypes.c_uint32), ("pad0", ctypes.c_uint32),
     ]
 
 
@@ -86,17 +90,31 @@ class SparsePlan:
         per_pair = nnz if self.method1 else math.ceil(nnz / P * self.slack)
         self.cap_rec = _up(min(per_pair + 1024, self.numel + 64), 8)
         union = min(S, math.ceil(S * min(1.0, self.max_density * P) * self.slack))
-        self.cap_g = _up(max(union, 64), 8)
         self.nwords = (S + 31) // 32
         self.nchunks = (S + 1023) // 1024
-        self.g_idx_words = _up(max(self.nwords, self.cap_g if self.forced_coo else 0), 4)
-        off = 0
-        self.off_rec_mail = off; off += _up(16 * MAX_RANKS, 256)
-        self.off_g_mail = off; off += _up(16 * MAX_RANKS, 256)
-        self.off_rec = off; off += _up(P * self.cap_rec * 8, 256)
-        self.off_g_idx = off; off += _up(P * self.g_idx_words * 4, 256)
-        self.off_g_off = off; off += _up(P * (self.nchunks + 1) * 4, 256)
-        self.off_g_val = off; off += _up(P * self.cap_g * 4, 256)
+        ngroups = (self.nchunks + 7) // 8
+        # the gather payload is filled in runs that start on 8-value boundaries: up to 8 padding values per run
+        self.cap_g = _up(max(union, 64) + 8 * ngroups, 8)
+        # bitmap words, or a COO list: the whole payload when format 2 is forced, else as many entries as the
+        # automatic choice can pick COO for (at most one touched slot in 32) plus the padding between runs
+        self.g_idx_words = _up(max(self.nwords, self.cap_g) if self.forced_coo else self.nwords + 8 * ngroups + 64, 4)
+        # sub-regions of the symmetric region, each followed by a guard of CANARY_BYTES that nothing may write
+        off, self.canaries = 0, []
+
+        def take(nbytes):
+            nonlocal off
+            at = off
+            off += _up(nbytes, 256)
+            self.canaries.append(off)
+            off += CANARY_BYTES
+            return at
+
+        self.off_rec_mail = take(2 * 16 * MAX_RANKS)                      # two parities
+        self.off_g_mail = take(16 * MAX_RANKS)
+        self.off_rec = take(2 * P * self.cap_rec * 8)                     # two parities
+        self.off_g_idx = take(P * self.g_idx_words * 4)
+        self.off_g_off = take(P * (self.nchunks + 1) * 4)
+        self.off_g_val = take(P * self.cap_g * 4)
         self.sym_bytes = off
 
     @property
@@ -115,7 +133,7 @@ class SparseRank:
         self.acc = torch.zeros(plan.nslots, dtype=torch.float32, device=dev)
         self.bitmap = torch.zeros(plan.nwords, dtype=torch.int32, device=dev)
         self.chunk_off = torch.zeros(plan.nchunks + 1, dtype=torch.int32, device=dev)
-        self.cursors = torch.zeros(MAX_RANKS + 2, dtype=torch.int32, device=dev)
+        self.cursors = torch.zeros(MAX_RANKS + 4, dtype=torch.int32, device=dev)
         self.status_t = torch.zeros(1, dtype=torch.int32, device=dev)
         c = _Ctx()
         c.rank, c.nranks = region.rank, region.nranks
@@ -129,7 +147,51 @@ class SparseRank:
         c.chunk_off, c.cursors, c.status = self.chunk_off.data_ptr(), self.cursors.data_ptr(), self.status_t.data_ptr()
         c.numel, c.nslots = plan.numel, plan.nslots
         c.perm = perm_struct(plan.perm)
+        c.k1_density_ppm = max(1, min(1_000_000, int(plan.max_density * 1e6)))
+        c.mc = getattr(region, "multicast_ptr", 0) if getattr(region, "use_multicast", False) else 0
         self.ctx = c
+        self.epoch_dev = None
+        for at in plan.canaries:                                      # guard words after every sub-region of OUR region
+            region.view(region.rank, at, CANARY_BYTES, torch.int32).fill_(CANARY_WORD)
+
+    def damaged_canaries(self) -> list[int]:
+        """Offsets of guard zones in this rank's region whose pattern was overwritten (by a peer's or an own store that
+        ran past its sub-region).  Synchronises; for tests and health checks."""
+        bad = []
+        for at in self.plan.canaries:
+            if not bool((self.region.view(self.region.rank, at, CANARY_BYTES, torch.int32) == CANARY_WORD).all()):
+                bad.append(at)
+        return bad
+
+    def enable_device_epoch(self, start: int = 0):
+        """Keep the call counter on the device: every kernel reads it there and ``allreduce`` bumps it first, so a
+        captured sequence of calls stays in step with the peers when the graph is replayed."""
+        self.epoch_dev = torch.full((1,), start, dtype=torch.int32, device=self.acc.device)
+        self.ctx.epoch_dev = self.epoch_dev.data_ptr()
+
+    def allreduce(self, x: torch.Tensor, out: torch.Tensor, epoch: int, thr: torch.Tensor | None = None,
+                  method1: bool = False, fmt: int = FMT_AUTO, deterministic: bool = False):
+        """All kernels of one call from a single native entry."""
+        assert x.is_cuda and x.is_contiguous() and x.numel() == self.plan.numel
+        assert out.is_contiguous() and out.numel() == self.plan.numel and out.data_ptr() % 16 == 0
+        # ``out`` may be ``x`` itself: this rank's scan of ``x`` has finished (stream order) before anything is written
+        rc = self.lib.zen_sparse_allreduce(self._prep(epoch, fmt), _native.ptr(x), _native.ptr(thr), _native.ptr(out),
+                                           _native.DTYPE_CODE[x.dtype], int(method1), int(deterministic),
+                                           _native.stream_ptr())
+        _native.check(rc, "zen_sparse_allreduce")
+
+    def metrics(self, epoch: int) -> dict:
+        """What the mails of call ``epoch`` say (synchronises): records this owner received from every source, touched
+        slots per owner as gathered here (padding between runs included), index format per owner."""
+        P = self.region.nranks
+        rm = self.region.view(self.region.rank, self.plan.off_rec_mail, 2 * 16 * MAX_RANKS, torch.int32).view(2, MAX_RANKS, 4)
+        gm = self.region.view(self.region.rank, self.plan.off_g_mail, 16 * MAX_RANKS, torch.int32).view(MAX_RANKS, 4)
+        rm, gm = rm[epoch & 1, :P].cpu(), gm[:P].cpu()
+        ok_r = [int(e) == epoch for e in rm[:, 3]]
+        ok_g = [int(e) == epoch for e in gm[:, 3]]
+        return {"recv_records": [int(c) if ok else None for c, ok in zip(rm[:, 0], ok_r)],
+                "gathered": [int(c) if ok else None for c, ok in zip(gm[:, 0], ok_g)],
+                "format": [{FMT_COO: "coo", FMT_BITMAP: "bitmap"}.get((int(i) >> 8) & 0xff, "none") for i in gm[:, 1]]}
 
     def _prep(self, epoch: int, fmt: int = FMT_AUTO):
         self.ctx.epoch = epoch
@@ -191,16 +253,44 @@ class SparseAllReduce:
     """
 
     def __init__(self, numel: int, group=None, *, block: int = 64, max_density: float = 0.12,
-                 methods=(3,), deterministic: bool = False, wait_ms: float = 2000.0, backend: str | None = None):
+                 methods=(3,), deterministic: bool = False, wait_ms: float = 2000.0, backend: str | None = None,
+                 transport: str = "p2p"):
+        """``transport``: "p2p" pushes the gathered payload to every peer with its own stores; "nvls" writes it once
+        to the multicast alias of the region and lets the NVSwitch replicate it (needs the torch symmetric-memory
+        backend and a fabric that offers multicast; falls back to "p2p" otherwise)."""
         import torch.distributed as dist
 
         self.group = group
         P = dist.get_world_size(group)
         self.plan = SparsePlan(numel, P, block, max_density, method1=1 in methods, forced_coo=2 in methods)
-        self.region = make_symmetric(self.plan.sym_bytes, group, backend)
+        self.transport = transport
+        if transport == "nvls":
+            self.region = make_symmetric(self.plan.sym_bytes, group, "torch")
+            self.region.use_multicast = bool(getattr(self.region, "multicast_ptr", 0))
+            if not self.region.use_multicast:
+                self.transport = "p2p"
+        else:
+            self.region = make_symmetric(self.plan.sym_bytes, group, backend)
         self.rank_state = SparseRank(self.plan, self.region, wait_ms)
         self.deterministic = deterministic
         self.epoch = 0
+        self.calls = 0
+        self.timer = None              # a utils.trace.StageTimer: per-stage CUDA-event times (stage-by-stage launches)
+
+    def metrics(self) -> dict:
+        """Counters of the last call (synchronises the device): density of what this owner received, touched slots
+        over all owners, bytes this rank pushed over the links, index formats."""
+        torch.cuda.synchronize()
+        P, plan = self.plan.nranks, self.plan
+        m = self.rank_state.metrics(self.epoch)
+        recv = [c for c in m["recv_records"] if c is not None]
+        gath = [c for c in m["gathered"] if c is not None]
+        es = 4
+        out = {"numel": plan.numel, "ranks": P, "owner_recv_records": sum(recv), "owner_recv_density": sum(recv) / max(1, plan.nslots * P),
+               "union_slots": sum(gath), "union_density": sum(gath) / max(1, plan.numel), "format": m["format"],
+               "gather_bytes_pushed": (P - 1) * ((gath[self.region.rank] if len(gath) == P else 0) * es + plan.nwords * 4),
+               "calls": self.calls}
+        return out
 
     def __call__(self, x: torch.Tensor, method=3, out: torch.Tensor | None = None,
                  threshold: torch.Tensor | None = None) -> torch.Tensor:
@@ -208,17 +298,34 @@ class SparseAllReduce:
         if out is None:
             out = torch.empty_like(flat)
         self.epoch += 1
-        e, rs = self.epoch, self.rank_state
-        if method == 1:
-            rs.partition_push(flat, e, threshold, broadcast=True)
-            rs.scatter_sources(out.reshape(-1), e)
+        e, rs, fmt = self.epoch, self.rank_state, _fmt_for(method)
+        self.calls += 1
+        if not trace.tracing_enabled() and self.timer is None:
+            rs.allreduce(flat, out.reshape(-1), e, threshold, method1=(method == 1), fmt=fmt, deterministic=self.deterministic)
         else:
-            fmt = _fmt_for(method)
-            rs.partition_push(flat, e, threshold)
-            rs.owner_reduce(e, flat.dtype, self.deterministic)
-            rs.gather_push(e, flat.dtype, fmt)
-            rs.densify(out.reshape(-1), e, fmt)
+            # stage by stage, under the range names that the reference gives the corresponding steps (comm.py:104-146,
+            # tensor_load_balance.py:25-44); with ``timer`` set every stage is also bracketed by CUDA events
+            stage = self.timer.stage if self.timer is not None else trace.trace_range
+            if rs.epoch_dev is not None:
+                _native.check(rs.lib.zen_sparse_epoch_bump(_native.ptr(rs.epoch_dev), _native.stream_ptr()), "zen_sparse_epoch_bump")
+            if method == 1:
+                with stage("encode_sparse_tensor"):
+                    rs.partition_push(flat, e, threshold, broadcast=True)
+                with stage("decode_sparse_tensors"):
+                    rs.scatter_sources(out.reshape(-1), e)
+            else:
+                with stage("load_balance"):                    # + "alltoallv indices" / "alltoallv values": pushed in the scan
+                    rs.partition_push(flat, e, threshold)
+                with stage("decode_sparse_tensors"):           # owner-side scatter-add
+                    rs.owner_reduce(e, flat.dtype, self.deterministic)
+                with stage("encode_bitmap" if fmt == FMT_BITMAP else "encode_sparse_tensor"):   # + "allgatherv"
+                    rs.gather_push(e, flat.dtype, fmt)
+                with stage("decode_bitmap" if fmt == FMT_BITMAP else "decode_sparse_tensors"):
+                    rs.densify(out.reshape(-1), e, fmt)
         return out.reshape(x.shape)
+
+    def enable_device_epoch(self):
+        self.rank_state.enable_device_epoch(self.epoch)
 
     def check(self) -> int:
         return self.rank_state.read_status()

@@ -126,7 +126,9 @@ class RowSparseAllReduce:
         self._epoch_dev = torch.full((1,), self.epoch, dtype=torch.int32, device=dev)
         self.state.ctx.epoch_dev = self._epoch_dev.data_ptr()
 
-    def __call__(self, rows, count, vals, grad, scale=1.0, overwrite=False):
+    def start(self, rows, count, vals):
+        """First three stages (push to the owners, owner reduce, push of the reduced rows to every rank): needs only this
+        rank's rows, so it can run on a side stream while the dense gradient is still being reduced."""
         self.epoch += 1
         if self._epoch_dev is not None:
             _native.check(self.state.lib.zen_row_epoch_bump(_native.ptr(self._epoch_dev), _native.stream_ptr()),
@@ -135,8 +137,15 @@ class RowSparseAllReduce:
         s.push(rows, count, vals, e)
         s.reduce(vals.dtype, e, self.deterministic)
         s.gather_push(vals.dtype, e)
-        s.apply(grad, e, scale, overwrite)
+
+    def finish(self, grad, scale=1.0, overwrite=False):
+        """Last stage: add (or write) the gathered rows into the dense gradient."""
+        self.state.apply(grad, self.epoch, scale, overwrite)
         return grad
+
+    def __call__(self, rows, count, vals, grad, scale=1.0, overwrite=False):
+        self.start(rows, count, vals)
+        return self.finish(grad, scale, overwrite)
 
     def check(self) -> int:
         return self.state.read_status()

@@ -29,7 +29,7 @@ class TrainConfig:
     tp: int = 1
     method: int = 0                   # 0 dense buckets (+ sparse embedding rows); 1/2/3 ZEN top-k hook on all buckets
     top_k: float = 1.0
-    bucket_cap_mb: float = 128.0
+    bucket_cap_mb: float = 32.0
     sparse_embedding: bool = True
     grad_checkpoint: bool = False
     lr: float = 1e-3
@@ -117,12 +117,17 @@ class Trainer:
         self._graph = None
         self.graph_launches_per_step = 0
         self._static_ids = self._static_loss = None
-        self.graph_ok = (cfg.cuda_graph and self.device.type == "cuda" and cfg.method == 0 and cfg.tp == 1)
+        self.graph_ok = (cfg.cuda_graph and self.device.type == "cuda" and cfg.tp == 1)
         if self.graph_ok:
+            # everything a replayed step must see change lives on the device: AdamW's step count and the call counters
+            # of the sparse engines (row granule for the embedding, element granule for the top-k hook)
             self.optimizer.enable_device_step(self.device)
             emb = self.model.module.embedding_sync
             if emb is not None and emb._engine is not None:
                 emb._engine.enable_device_epoch()
+            if getattr(self, "_hook", None) is not None:
+                for eng in self._hook.state["engines"].values():
+                    eng.enable_device_epoch()
 
     @property
     def tokens_per_step(self) -> int:
@@ -244,6 +249,39 @@ class Trainer:
         if bad and raise_on_error:
             raise RuntimeError(f"kernel status words report errors: {bad} (1 = record overflow, 2 = gather overflow, "
                                f"4 = wait expired, 8 = overflow at a peer, 16 = bad argument)")
+        return out
+
+    def collect_metrics(self) -> dict:
+        """Counters of the sparse synchronisation paths after the last step: density of what was sent, density of the
+        union, load balance across owners (max / mean of the records each owner received), bytes pushed over the links,
+        index formats, reported overflow / timeout bits and the number of fallbacks so far.  Synchronises the device
+        and runs one small all-gather: every rank calls it at the same step (every N-th step, not in the hot loop)."""
+        out: dict = {"optimizer_steps": self.step_count, "recoveries": len(self.recoveries)}
+        if self.health is not None:
+            out["status_bits"] = dict(self.health.last)
+        world = self.plugin.dp_size
+        emb = getattr(self.model.module, "embedding_sync", None)
+        if emb is not None and emb.last_count is not None:
+            rows = int(emb.last_count.item())
+            out["embedding_rows_sent"] = rows
+            out["embedding_row_density"] = rows / emb.vocab
+            out["embedding_bytes_pushed"] = rows * (emb.d * 2 + 4)
+        hook = getattr(self, "_hook", None)
+        if hook is not None:
+            out["fallbacks"] = hook.state.get("fallbacks", 0)
+            per_bucket = {}
+            for numel, eng in hook.state["engines"].items():
+                m = eng.metrics()
+                loads = torch.tensor([float(m["owner_recv_records"])], device=self.device)
+                if world > 1:
+                    every = [torch.zeros_like(loads) for _ in range(world)]
+                    dist.all_gather(every, loads, group=self.plugin.dp_group)
+                    loads = torch.cat(every)
+                mean = float(loads.mean())
+                m["partition_max_over_mean"] = float(loads.max()) / mean if mean > 0 else 1.0
+                m["density_sent"] = float(loads.sum()) / (numel * max(1, world))
+                per_bucket[str(numel)] = m
+            out["buckets"] = per_bucket
         return out
 
     def close(self) -> None:

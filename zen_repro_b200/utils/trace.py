@@ -21,6 +21,10 @@ def enable_tracing(on: bool = True) -> None:
     _ENABLED = on
 
 
+def tracing_enabled() -> bool:
+    return _ENABLED
+
+
 @contextlib.contextmanager
 def trace_range(name: str):
     if _ENABLED and torch.cuda.is_available():
