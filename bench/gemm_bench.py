@@ -1,6 +1,8 @@
 """GEMM microbenchmark: tcgen05 kernel vs torch.matmul (cuBLAS) on the shapes of the benchmark models.
 
     python bench/gemm_bench.py [--shapes gpt2|llama|square] [--iters 20]
+    python bench/gemm_bench.py --one 8192 2304 768 --modes nt --iters 3      # one shape, own kernel only, a few launches
+                                                                             # (the small case for a profiler capture)
 """
 import argparse
 import json
@@ -39,7 +41,27 @@ def main():
     ap.add_argument("--shapes", default="gpt2")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--modes", nargs="+", default=["nt", "nn", "tn"])
+    ap.add_argument("--one", type=int, nargs=3, metavar=("M", "N", "K"), default=None)
+    ap.add_argument("--bn", type=int, default=0, help="with --one: force the N tile (0 = chosen per call)")
     args = ap.parse_args()
+    if args.one:
+        M, N, K = args.one
+        torch.manual_seed(0)
+        mode = args.modes[0]
+        if mode == "nt":
+            x, w = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(N, K, device="cuda").bfloat16()
+            f = lambda: G.gemm_nt(x, w, bn=args.bn)
+        elif mode == "nn":
+            x, w = torch.randn(M, K, device="cuda").bfloat16(), torch.randn(K, N, device="cuda").bfloat16()
+            f = lambda: G.gemm_nn(x, w, bn=args.bn)
+        else:
+            x, w = torch.randn(K, M, device="cuda").bfloat16(), torch.randn(K, N, device="cuda").bfloat16()
+            f = lambda: G.gemm_tn(x, w, bn=args.bn)
+        for _ in range(args.iters):
+            out = f()
+        torch.cuda.synchronize()
+        print("ok", float(out.float().abs().mean()), G.gemm_error())
+        return
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     for (M, N, K) in SHAPES[args.shapes]:
         for mode in args.modes:

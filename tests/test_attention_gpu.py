@@ -99,3 +99,30 @@ def test_autograd_path_uses_the_kernels():
     want.square().mean().backward()
     rel = (qkv.grad.float() - x.grad).norm() / x.grad.norm()
     assert rel < 0.03, float(rel)
+
+
+@pytest.mark.parametrize("B,S,hq,hkv,hd", [(2, 200, 4, 4, 80), (1, 200, 8, 2, 64), (2, 256, 32, 32, 80), (1, 130, 4, 1, 96)])
+def test_padded_shapes_stay_on_the_kernels(B, S, hq, hkv, hd, monkeypatch):
+    """Head sizes and sequence lengths that the kernels do not take directly (OPT-2.7b has head_dim 80) are zero-padded
+    to the next covered shape; forward and gradient against the fp32 restatement, and no library attention call."""
+    import torch.nn.functional as F
+
+    from zen_repro_b200.ops import autograd as O
+
+    def _no_sdpa(*a, **k):
+        raise AssertionError("library attention was called")
+
+    monkeypatch.setattr(F, "scaled_dot_product_attention", _no_sdpa)
+    torch.manual_seed(4)
+    qkv = (torch.randn(B * S, (hq + 2 * hkv) * hd, device="cuda") * 0.7).bfloat16().requires_grad_(True)
+    out = O.attention(qkv, B, S, hq, hkv, hd)
+    dout = (torch.randn(B * S, hq * hd, device="cuda") * 0.5).bfloat16()
+    out.backward(dout)
+    torch.cuda.synchronize()
+    assert A.attention_error() == 0
+    x = qkv.detach().float().requires_grad_(True)
+    want, _ = _ref(x, B, S, hq, hkv, hd, 1.0 / math.sqrt(hd))
+    torch.testing.assert_close(out.float(), want, atol=2e-2, rtol=2e-2)
+    (g,) = torch.autograd.grad(want, x, dout.float())
+    rel = (qkv.grad.float() - g).norm() / g.norm()
+    assert rel < 0.02, float(rel)

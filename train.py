@@ -53,12 +53,34 @@ def build_parser():
     p.add_argument("--metrics_out", type=str, default=None, help="JSON-lines file: per-step records and the final summary")
     p.add_argument("--metrics_every", type=int, default=0,
                    help="> 0: every N-th step also collect the counters of the sparse paths (one device synchronisation)")
+    p.add_argument("--profile_steps", type=int, default=0,
+                   help="> 0: after the run, record this many more steps with the torch profiler and print the kernels that "
+                        "the step spends its device time in (launches come from the host for these steps)")
     p.add_argument("--trace", action="store_true", help="NVTX ranges with the reference's names around every stage")
     p.add_argument("--log_dir", type=str, default=".")
     p.add_argument("--time_file", type=str, default="time.txt", help="the reference's result sink (appended to)")
     p.add_argument("--time_from", type=int, default=80)
     p.add_argument("--time_to", type=int, default=95)
     return p
+
+
+def kernel_shares(trainer, steps: int, coord, top: int = 24) -> None:
+    """Kernel time inside real training steps (torch profiler, CUPTI kernel records: no replay, warm caches)."""
+    from torch.profiler import ProfilerActivity, profile
+
+    trainer._graph, trainer.graph_ok = None, False
+    ids = next(trainer.data)["input_ids"].to(trainer.device)
+    trainer.step_device(ids, ids)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            trainer.step_device(ids, ids)
+        torch.cuda.synchronize()
+    rows = sorted(prof.key_averages(), key=lambda r: -r.device_time_total)
+    total = sum(r.device_time_total for r in rows) / steps
+    coord.print_on_master(f"== {trainer.cfg.model}: {total:.0f} us of kernel time per step")
+    for r in rows[:top]:
+        coord.print_on_master(f"{r.device_time_total / steps:9.1f} us/step  n={r.count // steps:4d}  {r.key[:110]}")
 
 
 def main(argv=None):
@@ -141,6 +163,8 @@ def main(argv=None):
                                     "sec_per_iter": sec_per_it, "tokens_per_s": trainer.tokens_per_step / sec_per_it,
                                     "max_mem_mb": mem, "recoveries": trainer.recoveries, "kernel_status": health,
                                     "config": cfg.to_dict()}) + "\n")
+    if args.profile_steps > 0 and device.type == "cuda":
+        kernel_shares(trainer, args.profile_steps, coord)
     if args.save:
         save_checkpoint(args.save, trainer)
     trainer.close()

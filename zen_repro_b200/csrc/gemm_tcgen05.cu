@@ -48,6 +48,8 @@ struct GemmParams {
   int rank;                   // this rank's index in the group
   uint32_t epoch;             // call counter, same on every rank; parity selects the exchange buffer
   uint32_t max_tiles;         // capacity of one flag row
+  const uint32_t* epoch_dev;  // optional step counter on the device: the call counter is *epoch_dev * epoch_stride + epoch
+  uint32_t epoch_stride;      // (same parity as the number of calls per step, so that consecutive calls alternate buffers)
   uint64_t wait_ns;
   __nv_bfloat16* my_recv;     // this rank's exchange region: [2 parities][npeers slots][M * recv_ld] bf16
   uint32_t* my_flags;         // this rank's flags: [2 parities][npeers slots][max_tiles] epochs
@@ -72,6 +74,12 @@ struct GemmParams {
   const __nv_bfloat16* a_local;
   int lda_local;
 };
+
+// The call counter as the kernels compare it: by value, or derived from a device-resident step counter so that a
+// captured launch sees a new value at every replay.
+__device__ __forceinline__ uint32_t cur_epoch(const GemmParams& p) {
+  return p.epoch_dev ? (*p.epoch_dev) * p.epoch_stride + p.epoch : p.epoch;
+}
 
 constexpr int COLL_AR = 0, COLL_RS = 1, COLL_AG = 2;
 
@@ -235,9 +243,9 @@ __device__ __forceinline__ bool finish_tile(const GemmParams& p, int tile, uint3
   if (et < p.npeers) {
     const uint32_t* f = p.my_flags + ((size_t)par * p.npeers + et) * p.max_tiles + tc.fidx;
     const uint64_t t0 = gtimer();
-    bool got = ld_acquire_sys_u32(f) == p.epoch;
+    bool got = ld_acquire_sys_u32(f) == cur_epoch(p);
     while (!got) {
-      for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f) == p.epoch;
+      for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f) == cur_epoch(p);
       if (!got && (gtimer() - t0 > p.wait_ns || *abort_flag)) break;
     }
     if (!got) { atomicOr(p.status, 4u); *abort_flag = 5; atomicCAS(&g_gemm_error, 0, 5); }
@@ -398,13 +406,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             // rows of a peer: its epilogue warps push them into this rank's gather region; wait for the chunk
             amap = &tma_g;
             const int nslices = ag_slices(gridDim.x, p.rows_per_rank / BM, p.max_tiles);
-            const uint32_t* f = p.my_flags + (size_t)(p.epoch & 1u) * p.npeers * p.max_tiles + (tc.mloc / BM) * nslices;
+            const uint32_t* f = p.my_flags + (size_t)(cur_epoch(p) & 1u) * p.npeers * p.max_tiles + (tc.mloc / BM) * nslices;
             const uint64_t t0 = gtimer();
             bool got = true;
             for (int sl = 0; sl < nslices && got; ++sl) {               // every column slice of the chunk
-              got = ld_acquire_sys_u32(f + sl) == p.epoch;
+              got = ld_acquire_sys_u32(f + sl) == cur_epoch(p);
               while (!got) {
-                for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f + sl) == p.epoch;
+                for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f + sl) == cur_epoch(p);
                 if (!got && (gtimer() - t0 > p.wait_ns || *abort_flag)) break;
               }
             }
@@ -470,7 +478,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int grp = warp & 3;                   // TMEM lane quarter this warp may read
     uint32_t tcount = 0;
     bool ok = true;
-    const uint32_t par = p.epoch & 1u;
+    const uint32_t par = cur_epoch(p) & 1u;
     const bool rs = p.npeers > 0 && p.coll_mode == COLL_RS, ag = p.npeers > 0 && p.coll_mode == COLL_AG;
     if (ag) {
       // ---- all-gather: push this rank's rows to the peer, one 128-row chunk per CTA, while the first tiles
@@ -503,7 +511,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         __threadfence_system();
         epilogue_barrier();
         if (et < p.npeers)
-          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + c * nslices + sl, p.epoch);
+          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + c * nslices + sl, cur_epoch(p));
       }
     }
     // Deferred reduction (bf16 output, no accumulation): a tile's epilogue pushes the partial to the peers, stores
@@ -613,7 +621,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         epilogue_barrier();
         const int et = threadIdx.x - 64;                                   // 0..127 among the epilogue threads
         if (et < p.npeers && !(rs && (mine || p.peer_rank[et] != tc.owner)))
-          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + ftile, p.epoch);
+          st_release_sys_u32(p.peer_flags[et] + ((size_t)par * p.npeers + p.peer_slot_of_me[et]) * p.max_tiles + ftile, cur_epoch(p));
         if (deferred) {
           tc_fence_before();
           __syncwarp();
@@ -632,9 +640,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (et < p.npeers) {
           const uint32_t* f = p.my_flags + ((size_t)par * p.npeers + et) * p.max_tiles + ftile;
           const uint64_t t0 = gtimer();
-          bool got = ld_acquire_sys_u32(f) == p.epoch;
+          bool got = ld_acquire_sys_u32(f) == cur_epoch(p);
           while (!got) {
-            for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f) == p.epoch;
+            for (int i = 0; i < 64 && !got; ++i) got = ld_acquire_sys_u32(f) == cur_epoch(p);
             if (!got && (gtimer() - t0 > p.wait_ns || *abort_flag)) break;
           }
           if (!got) { atomicOr(p.status, 4u); *abort_flag = 5; atomicCAS(&g_gemm_error, 0, 5); }
@@ -854,6 +862,9 @@ struct ZenGemmArCtx {
   void* recv[8];              // exchange region of every rank (this rank's own address included)
   void* flags[8];             // flag region of every rank
   uint32_t* status;
+  const uint32_t* epoch_dev;  // optional device step counter (see GemmParams::epoch_dev); `epoch` is then the call's index in the step
+  uint32_t epoch_stride;
+  uint32_t pad;
 };
 namespace {
 thread_local const ZenGemmArCtx* g_ar_next = nullptr;
@@ -862,6 +873,8 @@ void fill_ar(GemmParams& p, const ZenGemmArCtx& c) {
   p.npeers = c.nranks - 1;
   p.rank = c.rank;
   p.epoch = c.epoch;
+  p.epoch_dev = c.epoch_dev;
+  p.epoch_stride = c.epoch_stride;
   p.max_tiles = c.max_tiles;
   p.wait_ns = c.wait_ns;
   p.slot_elems = c.slot_elems;
@@ -914,6 +927,9 @@ int zen_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M
     if (rs) p.recv_ld = (N + 7) / 8 * 8;
     if (ag) {
       // A is this rank's row block; the peer's block arrives in this rank's own region
+      // the gathered rows are read through a tensor map that is chosen here, on the host, by the parity of `epoch`:
+      // with a device step counter that equals the parity of the full counter only for an even stride
+      if (p.epoch_dev && (p.epoch_stride & 1u)) return -8;
       if (a_mn || nranks != 2 || (K % 8) || (uint64_t)p.rows_per_rank * K > p.slot_elems ||
           (uint32_t)(p.rows_per_rank / BM) > p.max_tiles) return -7;
       p.a_local = reinterpret_cast<const __nv_bfloat16*>(A);

@@ -27,13 +27,15 @@ inline EncodeTiledFn get_encode() {
 }
 
 struct Key {
-  const void* ptr; uint64_t d0, d1, ld; uint32_t b0, b1;
-  bool operator==(const Key& o) const { return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1; }
+  const void* ptr; uint64_t d0, d1, ld; uint32_t b0, b1; int dev;
+  bool operator==(const Key& o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && ld == o.ld && b0 == o.b0 && b1 == o.b1 && dev == o.dev;
+  }
 };
 struct KeyHash {
   size_t operator()(const Key& k) const {
     size_t h = reinterpret_cast<size_t>(k.ptr);
-    for (uint64_t v : {k.d0, k.d1, k.ld, (uint64_t)k.b0, (uint64_t)k.b1}) h = h * 1000003u ^ v;
+    for (uint64_t v : {k.d0, k.d1, k.ld, (uint64_t)k.b0, (uint64_t)k.b1, (uint64_t)k.dev}) h = h * 1000003u ^ v;
     return h;
   }
 };
@@ -42,7 +44,9 @@ struct KeyHash {
 inline int get(const void* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t b0, uint32_t b1, CUtensorMap* out) {
   static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
   static std::mutex mu;
-  Key key{ptr, d0, d1, ld, b0, b1};
+  int dev = 0;
+  cudaGetDevice(&dev);                                      // the same address can name different memory on another device
+  Key key{ptr, d0, d1, ld, b0, b1, dev};
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
@@ -59,7 +63,14 @@ inline int get(const void* ptr, uint64_t d0, uint64_t d1, uint64_t ld, uint32_t 
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return -11;
   std::lock_guard<std::mutex> g(mu);
-  if (cache.size() > 4096) cache.clear();
+  if (cache.size() >= 4096) {
+    // drop about half of the entries (every other one in iteration order) instead of all: the maps of the running
+    // step mostly survive, and the table stays bounded
+    bool drop = false;
+    for (auto it = cache.begin(); it != cache.end();) {
+      if ((drop = !drop)) it = cache.erase(it); else ++it;
+    }
+  }
   cache[key] = *out;
   return 0;
 }

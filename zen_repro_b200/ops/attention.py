@@ -1,10 +1,13 @@
 """Causal self-attention (MHA / GQA / MQA) over a fused qkv buffer.
 
 The raw entry points take the fused projection ``qkv[B*S, (Hq + 2*Hkv)*hd]`` and return
-``out[B*S, Hq*hd]``.  On CUDA the forward and backward run through
-``torch.nn.functional.scaled_dot_product_attention`` (library flash kernels) until the tcgen05
-attention kernels in ``csrc/`` cover the shape; on CPU a plain softmax(QK^T)V restatement is used,
-which is also the oracle for tests.
+``out[B*S, Hq*hd]``.  On CUDA, bf16 forward and backward run on the tcgen05 flash kernels of
+``csrc/attention_tcgen05.cu`` (head_dim 64 / 128 / 256, sequence a multiple of 128); other head sizes up
+to 256 and other sequence lengths are zero-padded to the next covered shape (``padded_shape``): padded
+head columns add nothing to any dot product, and padded positions sit at the end, where the causal mask
+hides them from every real query and their zero output gradient adds nothing to dK / dV.  On CPU a plain
+softmax(QK^T)V restatement is used, which is also the oracle for tests.  The library attention is reached
+only for other dtypes or when forced with ``ZEN_ATTN=lib``.
 """
 from __future__ import annotations
 
@@ -35,6 +38,24 @@ def have_kernel(seq, hq, hkv, hd, dtype) -> bool:
 
 
 HAVE_BWD = True
+
+
+def padded_shape(seq, hq, hkv, hd, dtype):
+    """(seq', hd') of the covered shape that (seq, hd) is zero-padded to, or None when padding cannot help."""
+    if _MODE == "lib" or dtype != torch.bfloat16 or hq % hkv or hd > 256 or not HAVE_BWD:
+        return None
+    return (seq + 127) // 128 * 128, next(h for h in (64, 128, 256) if h >= hd)
+
+
+def pad_qkv(qkv, bsz, seq, nheads, hd, seq_p, hd_p):
+    """[B*S, nheads*hd] -> zero-padded [B*S', nheads*hd'] (contiguous)."""
+    out = qkv.new_zeros(bsz, seq_p, nheads, hd_p)
+    out[:, :seq, :, :hd] = qkv.view(bsz, seq, nheads, hd)
+    return out.view(bsz * seq_p, nheads * hd_p)
+
+
+def unpad(t, bsz, seq, nheads, hd, seq_p, hd_p):
+    return t.view(bsz, seq_p, nheads, hd_p)[:, :seq, :, :hd].reshape(bsz * seq, nheads * hd)
 
 
 def attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale):

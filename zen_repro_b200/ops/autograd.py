@@ -387,9 +387,33 @@ class AttentionFn(torch.autograd.Function):
         return dqkv, None, None, None, None, None, None
 
 
+class PaddedAttentionFn(torch.autograd.Function):
+    """The same attention for a head size or sequence length that the kernels do not take directly: zero-pad to the
+    next covered shape, run the kernels there, cut the result back."""
+
+    @staticmethod
+    def forward(ctx, qkv, bsz, seq, hq, hkv, hd, scale, seq_p, hd_p):
+        qp = A.pad_qkv(qkv, bsz, seq, hq + 2 * hkv, hd, seq_p, hd_p)
+        out_p, lse2 = A.attention_fwd_kernel(qp, bsz, seq_p, hq, hkv, hd_p, scale)
+        ctx.save_for_backward(qp, out_p, lse2)
+        ctx.cfg = (bsz, seq, hq, hkv, hd, scale, seq_p, hd_p)
+        return A.unpad(out_p, bsz, seq, hq, hd, seq_p, hd_p)
+
+    @staticmethod
+    def backward(ctx, dout):
+        qp, out_p, lse2 = ctx.saved_tensors
+        bsz, seq, hq, hkv, hd, scale, seq_p, hd_p = ctx.cfg
+        dp = A.pad_qkv(dout.contiguous(), bsz, seq, hq, hd, seq_p, hd_p)
+        dqkv_p = A.attention_bwd_kernel(dp, qp, out_p, lse2, bsz, seq_p, hq, hkv, hd_p, scale)
+        return (A.unpad(dqkv_p, bsz, seq, hq + 2 * hkv, hd, seq_p, hd_p),) + (None,) * 8
+
+
 def attention(qkv, bsz, seq, hq, hkv, hd, scale=None):
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
     if qkv.is_cuda and not A.have_kernel(seq, hq, hkv, hd, qkv.dtype):
+        pad = A.padded_shape(seq, hq, hkv, hd, qkv.dtype)
+        if pad is not None:
+            return PaddedAttentionFn.apply(qkv, bsz, seq, hq, hkv, hd, scale, *pad)
         # library fallback under plain autograd (keeps the forward's softmax statistics, no recompute)
         q, k, v = A._split(qkv, bsz, seq, hq, hkv, hd)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale, enable_gqa=(hq != hkv))

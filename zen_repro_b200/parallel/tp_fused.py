@@ -22,7 +22,8 @@ from ..runtime.symmetric import make_symmetric
 class _ArCtx(ctypes.Structure):
     _fields_ = [("nranks", ctypes.c_int32), ("rank", ctypes.c_int32), ("epoch", ctypes.c_uint32),
                 ("max_tiles", ctypes.c_uint32), ("wait_ns", ctypes.c_uint64), ("slot_elems", ctypes.c_uint64),
-                ("recv", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8), ("status", ctypes.c_void_p)]
+                ("recv", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8), ("status", ctypes.c_void_p),
+                ("epoch_dev", ctypes.c_void_p), ("epoch_stride", ctypes.c_uint32), ("pad", ctypes.c_uint32)]
 
 
 class FusedTPWorkspace:
@@ -47,6 +48,29 @@ class FusedTPWorkspace:
         c.status = self.status.data_ptr()
         self.ctx = c
         self.epoch = 0
+        self.calls_in_step = 0             # calls since the last begin_step()
+        self.calls_last_step = 0
+        self._step_dev = None              # device step counter (CUDA-graph mode)
+
+    def begin_step(self):
+        """Mark the start of a training step.  In device-counter mode this launches the one-thread kernel that advances
+        the step counter; every call of the step then carries only its index within the step by value."""
+        self.calls_last_step, self.calls_in_step = self.calls_in_step, 0
+        if self._step_dev is not None:
+            _native.check(_native.lib().zen_sparse_epoch_bump(_native.ptr(self._step_dev), _native.stream_ptr()),
+                          "zen_sparse_epoch_bump")
+
+    def enable_device_epoch(self, calls_per_step: int) -> bool:
+        """Derive the call counter from a step counter on the device (counter = step * stride + index in the step), so
+        that a captured step sees fresh counter values at every replay.  The stride has the parity of the number of
+        calls per step: consecutive calls then keep alternating between the two exchange buffers across the step
+        boundary.  Every rank of the group must pass the same ``calls_per_step``."""
+        stride = calls_per_step + 2
+        self._step_dev = torch.full((1,), self.epoch // stride + 1, dtype=torch.int32, device=self.status.device)
+        self.ctx.epoch_dev = self._step_dev.data_ptr()
+        self.ctx.epoch_stride = stride
+        self.calls_in_step = 0
+        return stride % 2 == 0             # the all-gather form needs an even stride (its buffer is chosen on the host)
 
     def fits(self, M: int, N: int) -> bool:
         return M * ((N + 7) // 8 * 8) <= self.slot_elems and ((M + 127) // 128) * ((N + 127) // 128) <= self.max_tiles
@@ -59,8 +83,12 @@ class FusedTPWorkspace:
         a2, b2 = _rowmajor(a), _rowmajor(b)
         if out is None:
             out = torch.empty(M // self.P if mode == 1 else M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
-        self.epoch += 1
-        self.ctx.epoch = self.epoch
+        self.calls_in_step += 1
+        if self._step_dev is not None:
+            self.ctx.epoch = self.calls_in_step
+        else:
+            self.epoch += 1
+            self.ctx.epoch = self.epoch
         rc = _native.lib().zen_gemm_bf16_coll(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
                                               a2.stride(0), b2.stride(0), out.stride(0), int(a_mn), int(b_mn),
                                               int(out.dtype == torch.float32), 0, 0, ctypes.byref(self.ctx), mode,

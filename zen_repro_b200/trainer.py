@@ -117,7 +117,7 @@ class Trainer:
         self._graph = None
         self.graph_launches_per_step = 0
         self._static_ids = self._static_loss = None
-        self.graph_ok = (cfg.cuda_graph and self.device.type == "cuda" and cfg.tp == 1)
+        self.graph_ok = cfg.cuda_graph and self.device.type == "cuda"
         if self.graph_ok:
             # everything a replayed step must see change lives on the device: AdamW's step count and the call counters
             # of the sparse engines (row granule for the embedding, element granule for the top-k hook)
@@ -148,6 +148,14 @@ class Trainer:
         graph.  Everything the step reads at run time lives on the device: the token buffer, the optimizer's step
         count and the sparse engine's call counter."""
         self._static_ids = ids.clone()
+        ws = getattr(self.model.unwrap(), "tp_ws", None)
+        if ws is not None and ws._step_dev is None:
+            # the fused TP GEMMs counted their calls during the eager steps; from here on the counter lives on the device
+            even = ws.enable_device_epoch(ws.calls_in_step or ws.calls_last_step)
+            if self.cfg.sequence_parallel and not even:
+                self.graph_ok = False
+                ws._step_dev, ws.ctx.epoch_dev = None, None
+                return False
         torch.cuda.synchronize()
         from . import _native
 
@@ -157,6 +165,7 @@ class Trainer:
             self._static_loss = self._eager_step(self._static_ids, self._static_ids)
         self.graph_launches_per_step = _native.launch_count() - before      # this library's kernels inside the graph
         self._graph = g
+        return True
 
     def _recover(self, bad: dict) -> None:
         """A communication kernel reported overflow or an expired wait in an earlier step (same step and same value on
@@ -197,8 +206,8 @@ class Trainer:
             if bad:
                 self._recover(bad)
         if self.graph_ok and labels is ids and self._steps_here >= self.cfg.graph_warmup:
-            if self._graph is None:        # the first steps ran eagerly (tables, scratch and peers are set up): record now
-                self._capture(ids)
+            if self._graph is None and not self._capture(ids):   # the first steps ran eagerly (tables, scratch, peers): record now
+                return self.step_device(ids, labels, read_loss)
             self._static_ids.copy_(ids, non_blocking=True)
             self._graph.replay()
             self.step_count += 1
@@ -210,6 +219,9 @@ class Trainer:
         return float(loss.item()) if read_loss else loss
 
     def _eager_step(self, ids: torch.Tensor, labels: torch.Tensor):
+        ws = getattr(self.model.unwrap(), "tp_ws", None)
+        if ws is not None:
+            ws.begin_step()
         with trace_range("forward"):
             loss = self.model(ids, labels)
         with trace_range("backward"):
