@@ -69,6 +69,8 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--plan_methods", type=int, nargs="+", default=[3],
+                    help="methods the buffers are sized for (1 needs record slots for a full sparse all-gather)")
     ap.add_argument("--transport", default="p2p", choices=["p2p", "nvls"],
                     help="gather push: one store per peer, or one multimem store replicated by the NVSwitch")
     ap.add_argument("--with_reference", action="store_true",
@@ -88,7 +90,7 @@ def main():
         for ln in args.log2n:
             n = 1 << ln
             for d in args.density:
-                eng = E.VirtualSparseAllReduce(n, P, max_density=max(0.02, d * 1.5), methods=(1, 2, 3))
+                eng = E.VirtualSparseAllReduce(n, P, max_density=max(0.02, d * 1.5), methods=tuple(args.plan_methods))
                 xs = make_inputs(n, d, P, dtype, dev, args.dist, args.overlap)
                 ms = time_fn(lambda: eng(xs, method=method), args.iters, args.warmup, flush)
                 st = eng.status()
@@ -144,7 +146,8 @@ def main():
         for ln in args.log2n:
             n = 1 << ln
             for d in args.density:
-                eng = E.SparseAllReduce(n, None, max_density=max(0.02, d * 1.5), methods=(1, 2, 3), transport=args.transport)
+                eng = E.SparseAllReduce(n, None, max_density=max(0.02, d * 1.5), methods=tuple(args.plan_methods),
+                                        transport=args.transport)
                 x = make_inputs(n, d, P, dtype, dev, args.dist, args.overlap)[rank]
                 out = torch.empty_like(x)
                 def sparse():
@@ -164,6 +167,10 @@ def main():
                 ms_s, ms_d, stm, err = t.tolist()
                 nnz = int((x != 0).sum())
                 rec_bytes_out = nnz * 8 * (P - 1) / P
+                em = eng.metrics()
+                u = torch.tensor([float(em["union_slots"])], device=dev, dtype=torch.float64)
+                dist.all_reduce(u)
+                union_density = float(u.item()) / P / n                    # every rank gathers every owner's run
                 ref_ms = {}
                 if ref_lba is not None:
                     xr = x.clone()
@@ -180,7 +187,8 @@ def main():
                 row = dict(mode="nvlink", transport=eng.transport, P=P, log2n=ln, density=d, dtype=args.dtype, dist=args.dist, overlap=args.overlap,
                            method=str(method), sparse_ms=ms_s, dense_nccl_ms=ms_d, speedup=ms_d / ms_s, **ref_ms,
                            eff_GBps=n * x.element_size() / ms_s / 1e6, max_err=err, status=int(stm),
-                           push_bytes_per_rank=rec_bytes_out)
+                           push_bytes_per_rank=rec_bytes_out, union_density=union_density, format=em["format"][0],
+                           gather_bytes_pushed=em["gather_bytes_pushed"])
                 if rank == 0:
                     rows.append(row)
                     print(json.dumps(row), flush=True)

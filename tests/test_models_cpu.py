@@ -26,6 +26,15 @@ def _hf_model(cfg):
                                      rope_theta=cfg.rope_theta, tie_word_embeddings=cfg.tie_embeddings,
                                      attention_dropout=0.0, **common)
         return transformers.LlamaForCausalLM(c)
+    if cfg.post_norms:                   # Gemma-2: post norms, soft-capped scores and logits, sliding-window layers
+        c = transformers.Gemma2Config(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+                                      num_key_value_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
+                                      max_position_embeddings=cfg.max_position, rms_norm_eps=cfg.norm_eps,
+                                      rope_theta=cfg.rope_theta, hidden_activation="gelu_pytorch_tanh",
+                                      attn_logit_softcapping=cfg.attn_softcap, final_logit_softcapping=cfg.final_softcap,
+                                      sliding_window=cfg.sliding_window, query_pre_attn_scalar=cfg.head_dim,
+                                      attention_dropout=0.0, attn_implementation="eager", **common)
+        return transformers.Gemma2ForCausalLM(c)
     c = transformers.GemmaConfig(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
                                  num_key_value_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
                                  max_position_embeddings=cfg.max_position, rms_norm_eps=cfg.norm_eps,
@@ -33,16 +42,23 @@ def _hf_model(cfg):
     return transformers.GemmaForCausalLM(c)
 
 
-@pytest.mark.parametrize("name", ["tiny-gpt2", "tiny-opt", "tiny-llama", "tiny-gemma"])
+@pytest.mark.parametrize("name", ["tiny-gpt2", "tiny-opt", "tiny-llama", "tiny-gemma", "tiny-gemma2"])
 def test_loss_and_grads_match_huggingface(name):
     torch.manual_seed(0)
     cfg = get_config(name)
     ours = build_model(cfg, dtype=torch.float32)
+    if cfg.post_norms:
+        with torch.no_grad():            # norms away from their initial value, large scores and logits: the caps must bite
+            for n, p in ours.named_parameters():
+                if "norm" in n:
+                    p.normal_(0.0, 0.3)
+                elif "qkv_w" in n or n == "wte":
+                    p.mul_(25.0)
     hf = _hf_model(cfg).float().train()
     missing, unexpected = hf.load_state_dict(ours.hf_state_dict(), strict=False)
     assert not unexpected, unexpected
     assert all("inv_freq" in m or "bias" in m.split(".")[-1] and "attn" in m for m in missing) or not missing, missing
-    ids = torch.randint(0, cfg.vocab_size, (3, 24))
+    ids = torch.randint(1, cfg.vocab_size, (3, 24))      # not id 0: HF treats it as padding and drops its lookup gradient
     loss_o = ours(ids, ids)
     loss_h = hf(input_ids=ids, labels=ids).loss
     torch.testing.assert_close(loss_o, loss_h, atol=2e-5, rtol=2e-5)
@@ -60,7 +76,7 @@ def test_loss_and_grads_match_huggingface(name):
     assert len(got) > 10
 
 
-@pytest.mark.parametrize("name", ["tiny-gpt2", "tiny-opt", "tiny-llama", "tiny-gemma"])
+@pytest.mark.parametrize("name", ["tiny-gpt2", "tiny-opt", "tiny-llama", "tiny-gemma", "tiny-gemma2"])
 def test_hf_state_dict_round_trip(name):
     torch.manual_seed(1)
     a = build_model(name, dtype=torch.float32)

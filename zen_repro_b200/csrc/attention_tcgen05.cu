@@ -30,7 +30,19 @@ struct AttnParams {
   int B, S, Hq, Hkv;
   int ld_out;
   float scale_log2;       // softmax scale * log2(e)
+  float cap_a;            // soft-capping of the scaled scores, cap * tanh(s * scale / cap): scale / cap, or 0 for none
 };
+
+// Soft-capped raw score: the value x' with x' * scale = cap * tanh(x * scale / cap), so that everything after it
+// (maximum, exponentials, the saved log-sum-exp) goes on as for plain scores.  a = scale / cap.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t softcap_bits(uint32_t raw, float a, float inv_a) {
+  return __float_as_uint(tanh_fast(__uint_as_float(raw) * a) * inv_a);
+}
 
 template <int HD>
 struct FwdCfg {
@@ -161,6 +173,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
       tmem_ld32_nowait(tS + lane_addr + 64, r2);
       tmem_ld32_nowait(tS + lane_addr + 96, r3);
       tmem_wait_ld();
+      if (p.cap_a != 0.f) {
+        const float a = p.cap_a, ia = 1.f / p.cap_a;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          r0[i] = softcap_bits(r0[i], a, ia); r1[i] = softcap_bits(r1[i], a, ia);
+          r2[i] = softcap_bits(r2[i], a, ia); r3[i] = softcap_bits(r3[i], a, ia);
+        }
+      }
       if (diag) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -298,6 +318,7 @@ struct AttnBwdParams {
   float scale;
   float* part;            // hd 256, hsplit > 1: fp32 partial dK | dV, each [hsplit][B*S][Hkv * 256]
   int hsplit;             // CTAs that share one KV head (each takes Hq / Hkv / hsplit query heads)
+  float cap_a;            // soft-capping (head_dim 256 kernels): scale / cap, or 0 for none
 };
 
 // ---- dQ: one CTA per (query tile, head, batch).  Per key tile: S = Q K^T and dP = dO V^T into tensor memory,
@@ -896,6 +917,12 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
       tmem_ld32_nowait(tS + lane_addr + hf * 32, sa);
       if (MODE != BWD_DV) tmem_ld32_nowait(tDP + lane_addr + hf * 32, da);
       tmem_wait_ld();
+      const bool capped = p.cap_a != 0.f;
+      if (capped) {
+        const float a = p.cap_a, ia = 1.f / p.cap_a;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sa[i] = softcap_bits(sa[i], a, ia);
+      }
       // causal mask: key index against query index (resident row is the query in dQ, the key otherwise)
       const int res_idx = ri * 128 + row, str0 = t * 64 + hf * 32;
       const bool need_mask = (MODE == BWD_DQ) ? (str0 + 31 > ri * 128) : (str0 < ri * 128 + 128);
@@ -931,6 +958,12 @@ attn_bwd256_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid
             w0 = p0;
             w1 = p1;
           }
+        }
+        if (capped && MODE != BWD_DV) {
+          // chain rule through cap * tanh(.): 1 - tanh^2, with tanh = capped score * a (masked entries: factor 0)
+          const float t0 = fminf(fabsf(__uint_as_float(sa[i]) * p.cap_a), 1.f), t1 = fminf(fabsf(__uint_as_float(sa[i + 1]) * p.cap_a), 1.f);
+          w0 *= 1.f - t0 * t0;
+          w1 *= 1.f - t1 * t1;
         }
         pk[i >> 1] = pack_bf16(w0, w1);
       }
@@ -1339,14 +1372,15 @@ int zen_attn_bwd64_variant(int v) {
 // Causal attention forward.  qkv: bf16 [B*S, (Hq + 2*Hkv) * hd] with row stride ld_qkv (elements, multiple of 8,
 // base 16-byte aligned); out: bf16 [B*S, Hq*hd] (row stride ld_out); lse2: fp32 [B, Hq, S].
 // Supported: hd in {64, 128, 256}, S a multiple of 128, Hq a multiple of Hkv.
+// softcap > 0: scores are soft-capped, cap * tanh(s * scale / cap), before the softmax (0 = none).
 int zen_attn_fwd(const void* qkv, void* out, float* lse2, int B, int S, int Hq, int Hkv, int hd, int ld_qkv, int ld_out,
-                 float scale, void* stream) {
+                 float scale, float softcap, void* stream) {
   if (S % 128 || Hq % Hkv || (hd != 64 && hd != 128 && hd != 256)) return -2;
   if ((ld_qkv % 8) || (ld_out % 8) || (reinterpret_cast<uintptr_t>(qkv) % 16) || (reinterpret_cast<uintptr_t>(out) % 16)) return -3;
   CUtensorMap tm;
   int rc = attn_make_map(qkv, (uint64_t)(Hq + 2 * Hkv) * hd, (uint64_t)B * S, (uint64_t)ld_qkv, &tm);
   if (rc) return rc;
-  AttnParams p{(__nv_bfloat16*)out, lse2, B, S, Hq, Hkv, ld_out, scale * 1.4426950408889634f};
+  AttnParams p{(__nv_bfloat16*)out, lse2, B, S, Hq, Hkv, ld_out, scale * 1.4426950408889634f, softcap > 0.f ? scale / softcap : 0.f};
   cudaStream_t st = (cudaStream_t)stream;
   if (hd == 64) return launch_fwd<64>(tm, p, st);
   if (hd == 128) return launch_fwd<128>(tm, p, st);
@@ -1358,9 +1392,12 @@ int zen_attn_fwd(const void* qkv, void* out, float* lse2, int B, int S, int Hq, 
 // part / hsplit (hd 256 only): with hsplit > 1 the query heads of a KV head are spread over hsplit CTAs whose fp32
 // partial dK / dV go to `part` (2 * hsplit * B*S * Hkv*256 floats) and are summed by a last kernel; hsplit divides
 // Hq / Hkv.  Pass hsplit <= 1 (part unused) to let one CTA walk all heads of its group.
+// softcap > 0 (as in the forward) is taken by the head_dim 256 kernels only.
 int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse2, float* Dbuf, void* dqkv, int B,
-                 int S, int Hq, int Hkv, int hd, int ld_qkv, int ld_o, float scale, float* part, int hsplit, void* stream) {
+                 int S, int Hq, int Hkv, int hd, int ld_qkv, int ld_o, float scale, float softcap, float* part, int hsplit,
+                 void* stream) {
   if (S % 128 || Hq % Hkv || (hd != 64 && hd != 128 && hd != 256)) return -2;
+  if (softcap > 0.f && hd != 256) return -9;
   if ((ld_qkv % 8) || (ld_o % 8) || (reinterpret_cast<uintptr_t>(qkv) % 16) || (reinterpret_cast<uintptr_t>(dout) % 16) ||
       (reinterpret_cast<uintptr_t>(dqkv) % 16) || (reinterpret_cast<uintptr_t>(out) % 16)) return -3;
   cudaStream_t st = (cudaStream_t)stream;
@@ -1377,7 +1414,8 @@ int zen_attn_bwd(const void* qkv, const void* out, const void* dout, const float
   }
   if (hsplit < 1 || hd != 256 || !part) hsplit = 1;
   if ((Hq / Hkv) % hsplit) return -2;
-  AttnBwdParams p{(__nv_bfloat16*)dqkv, lse2, Dbuf, B, S, Hq, Hkv, ld_qkv, scale * 1.4426950408889634f, scale, part, hsplit};
+  AttnBwdParams p{(__nv_bfloat16*)dqkv, lse2, Dbuf, B, S, Hq, Hkv, ld_qkv, scale * 1.4426950408889634f, scale, part, hsplit,
+                  softcap > 0.f ? scale / softcap : 0.f};
   dim3 gq(S / 128, Hq, B), gk(S / 128, Hkv, B);
   if (hd == 64 && g_bwd64_variant >= 1) {
     CUtensorMap tq64, tdo64, to128;

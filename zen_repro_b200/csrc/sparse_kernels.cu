@@ -68,10 +68,10 @@ __device__ __forceinline__ ZenMail* zen_rec_mail(const ZenSparseCtx& c, int at_r
 
 #define K1_THREADS 288                                  // eight consumer warps and the producer warp
 #define K1_WARPS 8
-#define K1_QCAP 512
-#define K1_FLUSH_MIN 192
+#define K1_QCAP 256
+#define K1_FLUSH_MIN 128
 #define K1_STAGE_BYTES 8192
-#define K1_NS 4
+#define K1_NS 3
 
 // Eight consecutive elements as raw bits: one 16-byte vector for 16-bit types, two for fp32.
 template <typename T> struct Raw8;
@@ -99,6 +99,17 @@ template <> struct Raw8<float> {
   }
   __device__ __forceinline__ float value(int i) const { return __uint_as_float(bits(i)); }
   __device__ __forceinline__ bool nonzero(int i) const { return (bits(i) & 0x7fffffffu) != 0u; }
+  // bit i set when element i is kept: |x| >= threshold, as an integer compare of the magnitude bits (monotonic for
+  // non-negative floats); tbits = 1 keeps every nonzero; NaNs are dropped when a real threshold is in force
+  __device__ __forceinline__ uint32_t keep_mask(uint32_t tbits, bool use_thr, float) const {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t a = w[i] & 0x7fffffffu;
+      m |= (a >= tbits && (!use_thr || a <= 0x7f800000u)) ? (1u << i) : 0u;
+    }
+    return m;
+  }
 };
 template <typename T16> struct Raw8Half {
   uint32_t w[4];
@@ -125,9 +136,29 @@ template <typename T16> struct Raw8Half {
 };
 template <> struct Raw8<__nv_bfloat16> : Raw8Half<__nv_bfloat16> {
   __device__ __forceinline__ float value(int i) const { return __uint_as_float(bits(i) << 16); }
+  __device__ __forceinline__ uint32_t keep_mask(uint32_t tbits, bool use_thr, float) const {
+    uint32_t m = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t lo = (w[k] & 0x7fffu) << 16, hi = w[k] & 0x7fff0000u;     // magnitudes as fp32 bit patterns
+      m |= (lo >= tbits && (!use_thr || lo <= 0x7f800000u)) ? (1u << (2 * k)) : 0u;
+      m |= (hi >= tbits && (!use_thr || hi <= 0x7f800000u)) ? (2u << (2 * k)) : 0u;
+    }
+    return m;
+  }
 };
 template <> struct Raw8<__half> : Raw8Half<__half> {
   __device__ __forceinline__ float value(int i) const { return __half2float(__ushort_as_half((unsigned short)bits(i))); }
+  __device__ __forceinline__ uint32_t keep_mask(uint32_t, bool use_thr, float thr) const {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      bool keep = nonzero(i);
+      if (use_thr) keep = keep && (fabsf(value(i)) >= thr);
+      m |= keep ? (1u << i) : 0u;
+    }
+    return m;
+  }
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -148,7 +179,7 @@ __device__ __forceinline__ void k1_consumer_sync() { asm volatile("bar.sync 1, 2
 template <typename T> struct K1Entry { uint32_t w[sizeof(Raw8<T>) / 4]; };
 
 template <typename T, bool kBroadcast, bool kRing>
-__global__ void __launch_bounds__(K1_THREADS, 3)
+__global__ void __launch_bounds__(K1_THREADS, 4)
 zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const float* __restrict__ thr_ptr, int batch) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   constexpr uint32_t VB = 8 * sizeof(T);                              // bytes of one 8-element vector
@@ -169,10 +200,12 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool use_thr = thr_ptr != nullptr;
-  const float thr = use_thr ? *thr_ptr : 0.f;
+  const float thr = use_thr ? fmaxf(*thr_ptr, 0.f) : 0.f;
+  const uint32_t tbits = use_thr ? max(__float_as_uint(thr), 1u) : 1u; // magnitude bits an element must reach to be kept
   const uint64_t N = c.numel;
-  const uint64_t nst = (N + EPS - 1) / EPS;                           // stages of the whole bucket
+  const uint32_t nst = (uint32_t)((N + EPS - 1) / EPS);               // stages of the whole bucket
   const uint64_t copy_end = (N * sizeof(T)) & ~15ull;                 // bytes that bulk copies may fetch
+  const uint32_t full_stages = (uint32_t)(copy_end / K1_STAGE_BYTES);
   const uint32_t epoch = zen_epoch(c);
   const uint64_t rec_base = ((uint64_t)(epoch & 1u) * c.nranks + c.rank) * c.cap_rec;
   uint32_t local_status = 0;
@@ -188,9 +221,10 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
   }
   __syncthreads();
 
-  auto stage_bytes = [&](uint64_t it) -> uint32_t {
-    const uint64_t b0 = it * K1_STAGE_BYTES;
-    return b0 >= copy_end ? 0u : (uint32_t)min((uint64_t)K1_STAGE_BYTES, copy_end - b0);
+  auto stage_bytes = [&](uint32_t it) -> uint32_t {
+    if (it < full_stages) return K1_STAGE_BYTES;
+    const uint64_t b0 = (uint64_t)it * K1_STAGE_BYTES;
+    return b0 >= copy_end ? 0u : (uint32_t)(copy_end - b0);
   };
   // bounded wait on an mbarrier phase; gives up at once when the CTA has already aborted
   auto wait_phase = [&](uint64_t* bar, uint32_t parity) -> bool {
@@ -208,12 +242,12 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
     if (kRing && lane == 0) {
       uint32_t issued[K1_NS] = {};
       uint32_t k = 0;
-      for (uint64_t it = blockIdx.x; it < nst; it += gridDim.x, ++k) {
+      for (uint32_t it = blockIdx.x; it < nst; it += gridDim.x, ++k) {
         const int s = k % K1_NS;
         if (k >= K1_NS && !wait_phase(&empty[s], ((k / K1_NS) - 1u) & 1u)) break;
         const uint32_t b = stage_bytes(it);
         tc::mbar_expect_tx(&full[s], b);
-        if (b) tc::bulk_load_1d(ring + s * K1_STAGE_BYTES, reinterpret_cast<const unsigned char*>(g) + it * K1_STAGE_BYTES, b, &full[s]);
+        if (b) tc::bulk_load_1d(ring + s * K1_STAGE_BYTES, reinterpret_cast<const unsigned char*>(g) + (uint64_t)it * K1_STAGE_BYTES, b, &full[s]);
         ++issued[s];
       }
       if (*(volatile int*)&s_abort) {
@@ -231,13 +265,7 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
 
     // Records of one 8-element vector starting at element e32: choose the owner, reserve queue space, write them.
     auto emit = [&](uint32_t e32, const Raw8<T>& vec) {
-      uint32_t m = 0;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        bool keep = vec.nonzero(i);
-        if (use_thr) keep = keep && (fabsf(vec.value(i)) >= thr);
-        m |= keep ? (1u << i) : 0u;
-      }
+      uint32_t m = vec.keep_mask(tbits, use_thr, thr);
       if (!m) return;
       uint32_t owner = 0, slot0 = e32;
       if (!kBroadcast) {
@@ -314,28 +342,42 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
 
     uint32_t kk = 0;
     int since = 0;
-    for (uint64_t it = blockIdx.x; it < nst; it += gridDim.x, ++kk) {
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    for (uint32_t it = blockIdx.x; it < nst; it += gridDim.x, ++kk) {
       const int s = kk % K1_NS;
       Raw8<T> v[VPL];
+      const uint32_t ebase = it * EPS + tid * 8u;                      // first element of this lane's first vector
       if (kRing) {
         const bool ok = wait_phase(&full[s], (kk / K1_NS) & 1u);
-        const uint32_t sb = ok ? stage_bytes(it) : 0u;
-        const unsigned char* st = ring + s * K1_STAGE_BYTES;
+        const unsigned char* st = ring + s * K1_STAGE_BYTES + tid * VB;
+        if (ok && it < full_stages) {                                  // a whole stage: no bounds to look at
 #pragma unroll
-        for (int u = 0; u < VPL; ++u) {
-          const uint32_t vi = u * K1_CONSUMERS + tid;
-          const uint64_t e0 = it * EPS + (uint64_t)vi * 8;
-          if ((vi + 1) * VB <= sb) {
-            const uint4* p4 = reinterpret_cast<const uint4*>(st + vi * VB);
+          for (int u = 0; u < VPL; ++u) {
+            const uint4* p4 = reinterpret_cast<const uint4*>(st + u * K1_CONSUMERS * VB);
 #pragma unroll
             for (int k = 0; k < RAWW / 4; ++k) {
               const uint4 a = p4[k];
               v[u].w[4 * k] = a.x; v[u].w[4 * k + 1] = a.y; v[u].w[4 * k + 2] = a.z; v[u].w[4 * k + 3] = a.w;
             }
-          } else if (ok && e0 < N) {
-            v[u].load(g, e0, N, false);                                // ragged end of the bucket: guarded plain loads
-          } else {
-            v[u].zero();
+          }
+        } else {
+          const uint32_t sb = ok ? stage_bytes(it) : 0u;
+#pragma unroll
+          for (int u = 0; u < VPL; ++u) {
+            const uint32_t vi = u * K1_CONSUMERS + tid;
+            const uint64_t e0 = (uint64_t)it * EPS + (uint64_t)vi * 8;
+            if ((vi + 1) * VB <= sb) {
+              const uint4* p4 = reinterpret_cast<const uint4*>(st + u * K1_CONSUMERS * VB);
+#pragma unroll
+              for (int k = 0; k < RAWW / 4; ++k) {
+                const uint4 a = p4[k];
+                v[u].w[4 * k] = a.x; v[u].w[4 * k + 1] = a.y; v[u].w[4 * k + 2] = a.z; v[u].w[4 * k + 3] = a.w;
+              }
+            } else if (ok && e0 < N) {
+              v[u].load(g, e0, N, false);                              // ragged end of the bucket: guarded plain loads
+            } else {
+              v[u].zero();
+            }
           }
         }
         __syncwarp();
@@ -343,7 +385,7 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
       } else {
 #pragma unroll
         for (int u = 0; u < VPL; ++u) {
-          const uint64_t e0 = it * EPS + (uint64_t)(u * K1_CONSUMERS + tid) * 8;
+          const uint64_t e0 = (uint64_t)it * EPS + (uint64_t)(u * K1_CONSUMERS + tid) * 8;
           if (e0 < N) v[u].load(g, e0, N, false); else v[u].zero();
         }
       }
@@ -354,8 +396,8 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
         const uint32_t bal = __ballot_sync(0xffffffffu, has);
         if (!bal) continue;
         if (has) {
-          const uint32_t idx = (wtail + __popc(bal & ((1u << lane) - 1u))) & 63u;
-          wel[warp][idx] = (uint32_t)(it * EPS) + (uint32_t)(u * K1_CONSUMERS + tid) * 8u;
+          const uint32_t idx = (wtail + __popc(bal & lt_mask)) & 63u;
+          wel[warp][idx] = ebase + (uint32_t)u * (K1_CONSUMERS * 8u);
           uint4* p4 = reinterpret_cast<uint4*>(&wdat[warp][idx]);
 #pragma unroll
           for (int k = 0; k < RAWW / 4; ++k) p4[k] = make_uint4(v[u].w[4 * k], v[u].w[4 * k + 1], v[u].w[4 * k + 2], v[u].w[4 * k + 3]);
@@ -417,7 +459,7 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
 // run side by side (one thread each); records are read two per 16-byte load, four loads in flight.
 template <typename T>
 __global__ void __launch_bounds__(256)
-zen_owner_reduce_kernel(const ZenSparseCtx c, int src_begin, int src_end) {
+zen_owner_reduce_kernel(const ZenSparseCtx c, int src_begin, int src_end, int allow_dense) {
   __shared__ uint32_t s_n[ZEN_MAX_RANKS];
   __shared__ uint32_t s_flag[ZEN_MAX_RANKS];
   const uint32_t epoch = zen_epoch(c);
@@ -437,10 +479,17 @@ zen_owner_reduce_kernel(const ZenSparseCtx c, int src_begin, int src_end) {
   }
   __syncthreads();
   uint32_t local_status = 0;
+  // With many records (more than one per eight slots) the occupancy bitmap is not kept: the gather then reads every
+  // slot anyway and takes "touched" to mean "sum is not zero" (a slot whose sum is exactly zero need not travel), which
+  // halves the number of atomics here.  The choice is published for the gather kernel of this call.
+  uint64_t total = 0;
+  for (int k = 0; k < ns; ++k) total += s_n[k];
+  const bool dense_mode = allow_dense && total * 8ull > (uint64_t)c.nslots;
+  if (blockIdx.x == 0 && threadIdx.x == 0) c.cursors[ZEN_MAX_RANKS + 3] = dense_mode ? 1u : 0u;
   auto apply = [&](uint32_t slot, uint32_t bits) {
     if (slot < c.nslots) {
       atomicAdd(&c.acc[slot], ZenVal<T>::unbits(bits));
-      atomicOr(&c.bitmap[slot >> 5], 1u << (slot & 31));
+      if (!dense_mode) atomicOr(&c.bitmap[slot >> 5], 1u << (slot & 31));
     } else {
       local_status |= ZEN_BAD_ARG;
     }
@@ -470,11 +519,12 @@ zen_owner_reduce_kernel(const ZenSparseCtx c, int src_begin, int src_end) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// K3: compact the touched slots of K3_WARPS consecutive 1024-slot chunks per CTA step into shared
-// memory, reserve room for the run in this owner's payload with one atomic (runs start on 8-value
-// boundaries, so every push is a 16-byte vector store), then push the run -- values, and COO slots
-// or bitmap words + the chunk's value offset -- to every peer.  Chunks may land in the payload in any
-// order: the consumer finds a chunk's values through its offset (bitmap) or does not care (COO).
+// K3: one warp per 1024-slot chunk: compact the chunk's touched slots into the warp's shared-memory
+// staging area and push the run -- values, and COO slots or bitmap words + the chunk's value offset --
+// to every peer.  Room in this owner's payload is reserved per CTA step (16 chunks) with one atomic;
+// runs start on 8-value boundaries, so every push is a 16-byte vector store.  Chunks may land in the
+// payload in any order: the consumer finds a chunk's values through its offset (bitmap) or does not
+// care (COO).
 #define K3_WARPS 8
 #define K3_RUN_ALIGN 8u
 
@@ -486,14 +536,18 @@ __device__ __forceinline__ void zen_multimem_st4(void* mc_addr, uint32_t v) {
   asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
 }
 
+#define K3_CPW 2                                          // chunks per warp and step
+#define K3_CPS (K3_WARPS * K3_CPW)                        // chunks per CTA step: one reservation in the payload for all of them
+
 template <typename T>
 __global__ void __launch_bounds__(K3_WARPS * 32)
 zen_gather_push_kernel(const ZenSparseCtx c) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem_raw);                       // [K3_WARPS * 1024 + 16]
-  T* s_val = reinterpret_cast<T*>(smem_raw + (K3_WARPS * 1024 + 16) * 4);        // [K3_WARPS * 1024 + 16]
-  __shared__ uint32_t s_last, s_fmt, s_gbase, s_wtot[K3_WARPS];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // per-warp staging of one chunk: up to 1024 slot ids and values (plus padding to a whole 16-byte vector)
+  uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem_raw) + warp * 1032;
+  T* s_val = reinterpret_cast<T*>(smem_raw + K3_WARPS * 1032 * 4) + warp * 1032;
+  __shared__ uint32_t s_last, s_fmt, s_gbase, s_tot[K3_CPS];
   const uint32_t epoch = zen_epoch(c);
   if (tid == 0) {
     // index format: bitmap when more than one slot in 32 is expected to be touched.  The estimate is the number of
@@ -503,123 +557,157 @@ zen_gather_push_kernel(const ZenSparseCtx c) {
     for (int s = 0; s < c.nranks; ++s) recs += min(zen_rec_mail(c, c.rank, s, epoch)->count, c.cap_rec);
     if (fmt == 0) fmt = (recs * 32ull > (uint64_t)c.nslots) ? ZEN_FMT_BITMAP : ZEN_FMT_COO;
     // a COO list (touched slots plus the padding between runs) must fit the index region
-    const uint64_t ngr = (c.nchunks + K3_WARPS - 1) / K3_WARPS;
-    if (fmt == ZEN_FMT_COO && min(recs, (uint64_t)c.nslots) + K3_RUN_ALIGN * ngr > (uint64_t)c.g_idx_words) fmt = ZEN_FMT_BITMAP;
+    if (fmt == ZEN_FMT_COO && min(recs, (uint64_t)c.nslots) + K3_RUN_ALIGN * (uint64_t)c.nchunks > (uint64_t)c.g_idx_words) fmt = ZEN_FMT_BITMAP;
     s_fmt = fmt;
   }
   __syncthreads();
   const uint32_t fmt = s_fmt;
-  const uint32_t ngroups = (c.nchunks + K3_WARPS - 1) / K3_WARPS;
   constexpr uint32_t VPV = 16 / sizeof(T);                               // values per 16-byte vector
   uint32_t local_status = 0;
   char* mc = c.mc;
+  const bool no_bitmap = c.cursors[ZEN_MAX_RANKS + 3] != 0u;            // the reduce kept no bitmap: touched = nonzero sum
+  const uint32_t nsteps = (c.nchunks + K3_CPS - 1) / K3_CPS;
 
-  for (uint32_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
-    const uint32_t ch = grp * K3_WARPS + warp;
-    uint32_t word = 0;
-    const uint32_t wi = ch * 32 + lane;
-    if (ch < c.nchunks && wi < c.nwords) {
-      word = c.bitmap[wi];
-      if (word) c.bitmap[wi] = 0;                                        // leave the bitmap clean for the next call
+  // One step = K3_CPS consecutive chunks, K3_CPW per warp.  The warps count their chunks' touched slots, the CTA
+  // reserves room for all of them with ONE atomic on the payload cursor (atomics on one address are served one after
+  // the other, so there must be few), then every warp compacts and pushes its chunks on its own.
+  for (uint32_t step = blockIdx.x; step < nsteps; step += gridDim.x) {
+    const uint32_t ch_first = step * K3_CPS + warp * K3_CPW;
+    uint32_t word[K3_CPW], incl[K3_CPW];
+#pragma unroll
+    for (int j = 0; j < K3_CPW; ++j) {
+      const uint32_t ch = ch_first + j, wi = ch * 32 + lane;
+      word[j] = 0;
+      if (ch < c.nchunks && wi < c.nwords) {
+        if (no_bitmap) {
+          const float4* ap4 = reinterpret_cast<const float4*>(c.acc + (size_t)wi * 32);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float4 v = ap4[k];
+            word[j] |= ((__float_as_uint(v.x) & 0x7fffffffu) ? 1u : 0u) << (4 * k) | ((__float_as_uint(v.y) & 0x7fffffffu) ? 2u : 0u) << (4 * k) |
+                       ((__float_as_uint(v.z) & 0x7fffffffu) ? 4u : 0u) << (4 * k) | ((__float_as_uint(v.w) & 0x7fffffffu) ? 8u : 0u) << (4 * k);
+          }
+        } else {
+          word[j] = c.bitmap[wi];
+          if (word[j]) c.bitmap[wi] = 0;                                 // leave the bitmap clean for the next call
+        }
+      }
     }
-    const uint32_t pc = __popc(word);
-    uint32_t incl = pc;
+#pragma unroll
+    for (int j = 0; j < K3_CPW; ++j) {
+      uint32_t v = __popc(word[j]);
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        uint32_t t = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += t;
+      }
+      incl[j] = v;
+      if (lane == 31) s_tot[warp * K3_CPW + j] = (v + K3_RUN_ALIGN - 1) & ~(K3_RUN_ALIGN - 1u);   // run length, padded
+    }
+    __syncthreads();
+    // offsets of this warp's chunks inside the CTA's reservation: prefix over the padded run lengths (one per lane)
+    uint32_t pre = (lane < K3_CPS) ? s_tot[lane] : 0u;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      uint32_t t = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += t;
+      uint32_t t = __shfl_up_sync(0xffffffffu, pre, d);
+      if (lane >= d) pre += t;
     }
-    const uint32_t wtot = __shfl_sync(0xffffffffu, incl, 31);
-    if (lane == 0) s_wtot[warp] = wtot;
+    const uint32_t cta_total = __shfl_sync(0xffffffffu, pre, 31);
+    pre -= (lane < K3_CPS) ? s_tot[lane] : 0u;                           // exclusive
+    if (tid == 0) s_gbase = cta_total ? atomicAdd(&c.cursors[ZEN_MAX_RANKS + 2], cta_total) : 0u;
     __syncthreads();
-    uint32_t coff = 0, n = 0;                                            // this chunk's offset in the run, run length
+    const uint32_t cta_base = s_gbase;
+    const bool fits = cta_base + cta_total <= c.cap_g && (fmt != ZEN_FMT_COO || cta_base + cta_total <= c.g_idx_words);
+    if (cta_total && !fits) local_status |= ZEN_GATHER_OVERFLOW;
 #pragma unroll
-    for (int w = 0; w < K3_WARPS; ++w) { const uint32_t t = s_wtot[w]; if (w < warp) coff += t; n += t; }
-    const uint32_t nres = (n + K3_RUN_ALIGN - 1) & ~(K3_RUN_ALIGN - 1u);
-    if (tid == 0) s_gbase = n ? atomicAdd(&c.cursors[ZEN_MAX_RANKS + 2], nres) : 0u;
-    {
-      // A lane whose bitmap word is non-empty appends its touched slots (in slot order) to the CTA's staging run and
-      // clears them.  Sparse words are walked bit by bit (only the touched 32-byte sectors move); a warp with dense
-      // words streams all 32 slots of the word as eight 16-byte vectors instead.
-      uint32_t r = coff + (incl - pc);
-      float* ap = c.acc + (size_t)ch * 1024 + (size_t)lane * 32;
-      const uint32_t slot0 = ch * 1024 + lane * 32;
-      const bool dense = __any_sync(0xffffffffu, pc > 10);
-      if (dense) {
-        if (word) {
-          float f[32];
-          float4* ap4 = reinterpret_cast<float4*>(ap);
+    for (int j = 0; j < K3_CPW; ++j) {
+      const uint32_t ch = ch_first + j, wi = ch * 32 + lane;
+      if (ch >= c.nchunks) continue;
+      const uint32_t w0 = word[j], pc = __popc(w0);
+      const uint32_t n = __shfl_sync(0xffffffffu, incl[j], 31);
+      const uint32_t nres = (n + K3_RUN_ALIGN - 1) & ~(K3_RUN_ALIGN - 1u);
+      const uint32_t gbase = cta_base + __shfl_sync(0xffffffffu, pre, warp * K3_CPW + j);
+      {
+        // A lane whose word is non-empty appends its touched slots (in slot order) to the staging run and clears
+        // them.  Sparse words are walked bit by bit (only the touched 32-byte sectors move); a warp with dense words
+        // streams all 32 slots of each word as eight 16-byte vectors instead.
+        uint32_t r = incl[j] - pc;
+        float* ap = c.acc + (size_t)ch * 1024 + (size_t)lane * 32;
+        const uint32_t slot0 = ch * 1024 + lane * 32;
+        const bool dense = no_bitmap || __any_sync(0xffffffffu, pc > 10);
+        if (dense) {
+          if (w0) {
+            float f[32];
+            float4* ap4 = reinterpret_cast<float4*>(ap);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) *reinterpret_cast<float4*>(&f[4 * k]) = ap4[k];
+            for (int k = 0; k < 8; ++k) *reinterpret_cast<float4*>(&f[4 * k]) = ap4[k];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) ap4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < 8; ++k) ap4[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if ((word >> i) & 1u) {
-              s_val[r] = ZenVal<T>::from_f(f[i]);
-              if (fmt == ZEN_FMT_COO) s_idx[r] = slot0 + i;
-              ++r;
+            for (int i = 0; i < 32; ++i) {
+              if ((w0 >> i) & 1u) {
+                s_val[r] = ZenVal<T>::from_f(f[i]);
+                if (fmt == ZEN_FMT_COO) s_idx[r] = slot0 + i;
+                ++r;
+              }
             }
           }
-        }
-      } else {
-        uint32_t w = word;
-        while (w) {
-          int i[4];
-          float f[4];
+        } else {
+          uint32_t w = w0;
+          while (w) {
+            int i[4];
+            float fv[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) { i[u] = w ? (__ffs(w) - 1) : -1; w &= w - 1; }
+            for (int u = 0; u < 4; ++u) { i[u] = w ? (__ffs(w) - 1) : -1; w &= w - 1; }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) f[u] = (i[u] >= 0) ? ap[i[u]] : 0.f;
+            for (int u = 0; u < 4; ++u) fv[u] = (i[u] >= 0) ? ap[i[u]] : 0.f;
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (i[u] >= 0) {
-              ap[i[u]] = 0.f;
-              s_val[r] = ZenVal<T>::from_f(f[u]);
-              if (fmt == ZEN_FMT_COO) s_idx[r] = slot0 + i[u];
-              ++r;
+            for (int u = 0; u < 4; ++u) {
+              if (i[u] >= 0) {
+                ap[i[u]] = 0.f;
+                s_val[r] = ZenVal<T>::from_f(fv[u]);
+                if (fmt == ZEN_FMT_COO) s_idx[r] = slot0 + i[u];
+                ++r;
+              }
             }
           }
         }
       }
-    }
-    if (fmt == ZEN_FMT_COO && (uint32_t)tid < nres - n) s_idx[n + tid] = 0xffffffffu;   // padding entries are skipped by the consumer
-    __syncthreads();
-    const uint32_t gbase = s_gbase;
-    if (n && (gbase + nres > c.cap_g || (fmt == ZEN_FMT_COO && gbase + nres > c.g_idx_words))) {
-      local_status |= ZEN_GATHER_OVERFLOW;
-    } else {
-      const uint32_t nvec = nres / VPV, nvi = nres / 4;
-      const uint64_t val_off = c.off_g_val + (uint64_t)c.rank * c.cap_g * 4ull + (uint64_t)gbase * sizeof(T);
-      const uint64_t idx_off = c.off_g_idx + ((uint64_t)c.rank * c.g_idx_words + gbase) * 4ull;
-      const uint64_t bm_off = c.off_g_idx + ((uint64_t)c.rank * c.g_idx_words + wi) * 4ull;
-      const uint64_t off_off = c.off_g_off + ((uint64_t)c.rank * (c.nchunks + 1) + ch) * 4ull;
-      const uint4* sv4 = reinterpret_cast<const uint4*>(s_val);
-      const uint4* si4 = reinterpret_cast<const uint4*>(s_idx);
-      if (mc) {                                                          // one store, replicated by the switch
-        for (uint32_t i = tid; i < nvec; i += blockDim.x) zen_multimem_st16(mc + val_off + (uint64_t)i * 16, sv4[i]);
-        if (fmt == ZEN_FMT_COO) {
-          for (uint32_t i = tid; i < nvi; i += blockDim.x) zen_multimem_st16(mc + idx_off + (uint64_t)i * 16, si4[i]);
-        } else if (ch < c.nchunks) {
-          if (wi < c.nwords) zen_multimem_st4(mc + bm_off, word);
-          if (lane == 0) zen_multimem_st4(mc + off_off, gbase + coff);
-        }
-      } else {
-        for (int p = 0; p < c.nranks; ++p) {
-          char* base = c.sym[p];
-          uint4* dv = reinterpret_cast<uint4*>(base + val_off);
-          for (uint32_t i = tid; i < nvec; i += blockDim.x) dv[i] = sv4[i];
+      if (fmt == ZEN_FMT_COO && (uint32_t)lane < nres - n) s_idx[n + lane] = 0xffffffffu;   // padding entries are skipped by the consumer
+      __syncwarp();
+      if (fits) {
+        const uint32_t nvec = nres / VPV, nvi = nres / 4;
+        const uint64_t val_off = c.off_g_val + (uint64_t)c.rank * c.cap_g * 4ull + (uint64_t)gbase * sizeof(T);
+        const uint64_t idx_off = c.off_g_idx + ((uint64_t)c.rank * c.g_idx_words + gbase) * 4ull;
+        const uint64_t bm_off = c.off_g_idx + ((uint64_t)c.rank * c.g_idx_words + wi) * 4ull;
+        const uint64_t off_off = c.off_g_off + ((uint64_t)c.rank * (c.nchunks + 1) + ch) * 4ull;
+        const uint4* sv4 = reinterpret_cast<const uint4*>(s_val);
+        const uint4* si4 = reinterpret_cast<const uint4*>(s_idx);
+        if (mc) {                                                        // one store, replicated by the switch
+          for (uint32_t i = lane; i < nvec; i += 32) zen_multimem_st16(mc + val_off + (uint64_t)i * 16, sv4[i]);
           if (fmt == ZEN_FMT_COO) {
-            uint4* di = reinterpret_cast<uint4*>(base + idx_off);
-            for (uint32_t i = tid; i < nvi; i += blockDim.x) di[i] = si4[i];
-          } else if (ch < c.nchunks) {
-            if (wi < c.nwords) *reinterpret_cast<uint32_t*>(base + bm_off) = word;
-            if (lane == 0) *reinterpret_cast<uint32_t*>(base + off_off) = gbase + coff;
+            for (uint32_t i = lane; i < nvi; i += 32) zen_multimem_st16(mc + idx_off + (uint64_t)i * 16, si4[i]);
+          } else {
+            if (wi < c.nwords) zen_multimem_st4(mc + bm_off, w0);
+            if (lane == 0) zen_multimem_st4(mc + off_off, gbase);
+          }
+        } else {
+          for (int p = 0; p < c.nranks; ++p) {
+            char* base = c.sym[p];
+            uint4* dv = reinterpret_cast<uint4*>(base + val_off);
+            for (uint32_t i = lane; i < nvec; i += 32) dv[i] = sv4[i];
+            if (fmt == ZEN_FMT_COO) {
+              uint4* di = reinterpret_cast<uint4*>(base + idx_off);
+              for (uint32_t i = lane; i < nvi; i += 32) di[i] = si4[i];
+            } else {
+              if (wi < c.nwords) *reinterpret_cast<uint32_t*>(base + bm_off) = w0;
+              if (lane == 0) *reinterpret_cast<uint32_t*>(base + off_off) = gbase;
+            }
           }
         }
       }
+      __syncwarp();                                                      // the staging area is free again
     }
-    __syncthreads();
   }
 
   if (local_status) atomicOr(c.status, local_status);
@@ -677,23 +765,30 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
   const uint64_t N = c.numel;
   const uint32_t gw = (blockIdx.x * blockDim.x + tid) >> 5;
   const uint32_t nw = (gridDim.x * blockDim.x) >> 5;
-  const uint64_t nunits = (uint64_t)c.nranks * c.nchunks;
+  const uint32_t nunits = (uint32_t)c.nranks * c.nchunks;
   const char* base = c.sym[c.rank];
-  auto fetch = [&](uint64_t unit, uint32_t& word, uint32_t& coff) {
-    word = 0; coff = 0;
-    if (unit >= nunits) return;
-    const uint32_t o = (uint32_t)(unit / c.nchunks), ch = (uint32_t)(unit % c.nchunks);
-    if (s_fmt[o] != ZEN_FMT_BITMAP) return;
-    const uint32_t wi = ch * 32 + lane;
-    if (wi < c.nwords) word = (reinterpret_cast<const uint32_t*>(base + c.off_g_idx) + (uint64_t)o * c.g_idx_words)[wi];
-    coff = reinterpret_cast<const uint32_t*>(base + c.off_g_off)[(uint64_t)o * (c.nchunks + 1) + ch];
+  const uint32_t* gidx = reinterpret_cast<const uint32_t*>(base + c.off_g_idx);
+  const uint32_t* goff = reinterpret_cast<const uint32_t*>(base + c.off_g_off);
+  // units are (owner, chunk) pairs walked with a fixed stride; the pair is advanced without divisions
+  const uint32_t stride_o = nw / c.nchunks, stride_ch = nw % c.nchunks;
+  auto advance = [&](uint32_t& o, uint32_t& ch) {
+    o += stride_o; ch += stride_ch;
+    if (ch >= c.nchunks) { ch -= c.nchunks; ++o; }
   };
+  auto fetch = [&](uint32_t o, uint32_t ch, uint32_t& word, uint32_t& coff) {
+    word = 0; coff = 0;
+    if (o >= (uint32_t)c.nranks || s_fmt[o] != ZEN_FMT_BITMAP) return;
+    const uint32_t wi = ch * 32 + lane;
+    if (wi < c.nwords) word = gidx[(size_t)o * c.g_idx_words + wi];
+    coff = goff[(size_t)o * (c.nchunks + 1) + ch];
+  };
+  uint32_t o = gw / c.nchunks, ch = gw % c.nchunks;
   uint32_t word, coff;
-  fetch(gw, word, coff);
-  for (uint64_t unit = gw; unit < nunits; unit += nw) {
-    uint32_t nword, ncoff;
-    fetch(unit + nw, nword, ncoff);
-    const uint32_t o = (uint32_t)(unit / c.nchunks), ch = (uint32_t)(unit % c.nchunks);
+  fetch(o, ch, word, coff);
+  for (uint32_t unit = gw; unit < nunits; unit += nw) {
+    uint32_t no = o, nch = ch, nword, ncoff;
+    advance(no, nch);
+    fetch(no, nch, nword, ncoff);
     const T* gval = reinterpret_cast<const T*>(base + c.off_g_val + (uint64_t)o * c.cap_g * 4ull);
     uint32_t incl = __popc(word);
 #pragma unroll
@@ -702,6 +797,47 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
       if (lane >= d) incl += t;
     }
     const uint32_t woff = coff + incl - __popc(word);
+    const uint32_t n_chunk = __shfl_sync(0xffffffffu, incl, 31);
+    if (G == 64u && n_chunk <= 160u) {
+      // Sparse chunk (the usual case below ~15 % union density): write the chunk's sixteen 64-element blocks as zeros
+      // with wide stores, then drop the few values in with narrow ones.  Lane j < 16 finds where block j lives.
+      uint64_t eb = ~0ull;
+      {
+        const uint32_t slotb = ch * 1024 + (lane & 15) * 64;
+        if (slotb < c.nslots) {
+          const uint64_t e = (uint64_t)zen_perm_inv(c.perm, o * c.perm.sb + (slotb >> 6)) << 6;
+          if (e < N) eb = e;
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const uint64_t e0 = __shfl_sync(0xffffffffu, eb, it * 4 + (lane >> 3));
+        if (e0 == ~0ull) continue;
+        const uint64_t e = e0 + (lane & 7) * 8;
+        if (e + 8 <= N) {
+          reinterpret_cast<uint4*>(out + e)[0] = make_uint4(0u, 0u, 0u, 0u);
+          if (sizeof(T) == 4) reinterpret_cast<uint4*>(out + e)[1] = make_uint4(0u, 0u, 0u, 0u);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (e + i < N) out[e + i] = ZenVal<T>::from_bits(0u);
+        }
+      }
+      __syncwarp();                                        // the zeros of every lane are ordered before the values below
+      const uint64_t e0 = __shfl_sync(0xffffffffu, eb, lane >> 1);
+      if (e0 != ~0ull) {
+        const uint64_t e = e0 + (lane & 1) * 32;
+        uint32_t w = word, at = woff;
+        while (w) {
+          const int i = __ffs(w) - 1;
+          w &= w - 1;
+          if (at < c.cap_g && e + i < N) out[e + i] = gval[at];
+          ++at;
+        }
+      }
+      word = nword; coff = ncoff; o = no; ch = nch;
+      continue;
+    }
     // four passes of 256 slots: every lane produces 8 consecutive output elements (one or two 16-byte stores)
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
@@ -716,37 +852,42 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
       const uint32_t sh = (lane & 3) * 8;
       const uint32_t byte = (w >> sh) & 0xffu;
       const uint32_t off0 = wo + __popc(w & ((1u << sh) - 1u));
-      T v[8];
+      // walk the set bits of this lane's byte only (most bytes are empty or hold one or two values) and drop each value
+      // into its place in the 16-byte (32-byte for fp32) output vector
+      constexpr int NW = sizeof(T) == 2 ? 4 : 8;
+      uint32_t pk[NW];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        v[i] = ZenVal<T>::from_f(0.f);
-        if ((byte >> i) & 1u) {
-          const uint32_t at = off0 + __popc(byte & ((1u << i) - 1u));
-          if (at < c.cap_g) v[i] = gval[at];
+      for (int k = 0; k < NW; ++k) pk[k] = 0u;
+      uint32_t b = byte, at = off0;
+      while (b) {
+        const int i = __ffs(b) - 1;
+        b &= b - 1;
+        uint32_t bits = 0u;
+        if (at < c.cap_g) bits = ZenVal<T>::bits(gval[at]);
+        ++at;
+        if (sizeof(T) == 2) {
+          const uint32_t v = bits << ((i & 1) * 16);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) pk[k] |= ((i >> 1) == k) ? v : 0u;
+        } else {
+#pragma unroll
+          for (int k = 0; k < NW; ++k) pk[k] |= (i == k) ? bits : 0u;
         }
       }
       if (e + 8 <= N) {
-        if (sizeof(T) == 2) {
-          uint4 pk;
-          pk.x = ZenVal<T>::bits(v[0]) | (ZenVal<T>::bits(v[1]) << 16);
-          pk.y = ZenVal<T>::bits(v[2]) | (ZenVal<T>::bits(v[3]) << 16);
-          pk.z = ZenVal<T>::bits(v[4]) | (ZenVal<T>::bits(v[5]) << 16);
-          pk.w = ZenVal<T>::bits(v[6]) | (ZenVal<T>::bits(v[7]) << 16);
-          *reinterpret_cast<uint4*>(out + e) = pk;
-        } else {
-          uint4 lo, hi;
-          lo.x = ZenVal<T>::bits(v[0]); lo.y = ZenVal<T>::bits(v[1]); lo.z = ZenVal<T>::bits(v[2]); lo.w = ZenVal<T>::bits(v[3]);
-          hi.x = ZenVal<T>::bits(v[4]); hi.y = ZenVal<T>::bits(v[5]); hi.z = ZenVal<T>::bits(v[6]); hi.w = ZenVal<T>::bits(v[7]);
-          reinterpret_cast<uint4*>(out + e)[0] = lo;
-          reinterpret_cast<uint4*>(out + e)[1] = hi;
-        }
+        reinterpret_cast<uint4*>(out + e)[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        if (sizeof(T) == 4) reinterpret_cast<uint4*>(out + e)[1] = make_uint4(pk[NW - 4], pk[NW - 3], pk[NW - 2], pk[NW - 1]);
       } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (e + i < N) out[e + i] = v[i];
+        for (int i = 0; i < 8; ++i) {
+          if (e + i < N) {
+            const uint32_t bits = (sizeof(T) == 2) ? ((pk[(i >> 1) % NW] >> ((i & 1) * 16)) & 0xffffu) : pk[i % NW];
+            out[e + i] = ZenVal<T>::from_bits(bits);
+          }
+        }
       }
     }
-    word = nword; coff = ncoff;
+    word = nword; coff = ncoff; o = no; ch = nch;
   }
   if (local_status) atomicOr(c.status, local_status);
 }
@@ -939,10 +1080,10 @@ int zen_owner_reduce(const ZenSparseCtx* c, int dtype, int deterministic, void* 
   const int grid = sm_count() * 4;
   if (deterministic) {
     for (int s = 0; s < c->nranks; ++s) {
-      DISPATCH_DTYPE(dtype, zen_owner_reduce_kernel<T><<<grid, 256, 0, st>>>(*c, s, s + 1));
+      DISPATCH_DTYPE(dtype, zen_owner_reduce_kernel<T><<<grid, 256, 0, st>>>(*c, s, s + 1, 0));
     }
   } else {
-    DISPATCH_DTYPE(dtype, zen_owner_reduce_kernel<T><<<grid, 256, 0, st>>>(*c, 0, c->nranks));
+    DISPATCH_DTYPE(dtype, zen_owner_reduce_kernel<T><<<grid, 256, 0, st>>>(*c, 0, c->nranks, 1));
   }
   return (int)cudaGetLastError();
 }
@@ -950,9 +1091,9 @@ int zen_owner_reduce(const ZenSparseCtx* c, int dtype, int deterministic, void* 
 // K3 (compact + push in one launch).
 int zen_gather_push(const ZenSparseCtx* c, int dtype, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
-  const int g3 = grid_for(c->nchunks, K3_WARPS, sm_count() * 3);
+  const int g3 = grid_for(c->nchunks, K3_CPS, sm_count() * 3);
   DISPATCH_DTYPE(dtype, {
-    const size_t smem = (K3_WARPS * 1024 + 16) * (4 + sizeof(T));
+    const size_t smem = (size_t)K3_WARPS * 1032 * (4 + sizeof(T));
     ZEN_CUDA_CHECK_RET(cudaFuncSetAttribute(zen_gather_push_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     zen_gather_push_kernel<T><<<g3, K3_WARPS * 32, smem, st>>>(*c);
   });

@@ -98,18 +98,21 @@ template <> struct ZenVal<float> {
   static __device__ __forceinline__ float from_f(float v) { return v; }
   static __device__ __forceinline__ uint32_t bits(float v) { return __float_as_uint(v); }
   static __device__ __forceinline__ float unbits(uint32_t b) { return __uint_as_float(b); }
+  static __device__ __forceinline__ float from_bits(uint32_t b) { return __uint_as_float(b); }
 };
 template <> struct ZenVal<__nv_bfloat16> {
   static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
   static __device__ __forceinline__ uint32_t bits(__nv_bfloat16 v) { return (uint32_t)__bfloat16_as_ushort(v); }
   static __device__ __forceinline__ float unbits(uint32_t b) { return __uint_as_float(b << 16); }
+  static __device__ __forceinline__ __nv_bfloat16 from_bits(uint32_t b) { return __ushort_as_bfloat16((unsigned short)b); }
 };
 template <> struct ZenVal<__half> {
   static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
   static __device__ __forceinline__ uint32_t bits(__half v) { return (uint32_t)__half_as_ushort(v); }
   static __device__ __forceinline__ float unbits(uint32_t b) { return __half2float(__ushort_as_half((unsigned short)b)); }
+  static __device__ __forceinline__ __half from_bits(uint32_t b) { return __ushort_as_half((unsigned short)b); }
 };
 
 #define ZEN_DTYPE_F32 0

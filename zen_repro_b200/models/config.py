@@ -27,6 +27,11 @@ class ModelConfig:
     init_std: float = 0.02
     grad_checkpoint: bool = False
     name: str = "gpt2"
+    # Gemma-2 additions (all off for the other families)
+    post_norms: bool = False          # a second RMSNorm on the output of the attention and of the MLP branch
+    attn_softcap: float = 0.0         # scores -> cap * tanh(scores / cap) before the softmax
+    final_softcap: float = 0.0        # logits -> cap * tanh(logits / cap) before the loss
+    sliding_window: int = 0           # every other layer attends to the last `sliding_window` positions only
 
     # ---- derived behaviour -------------------------------------------------------------
     @property
@@ -108,11 +113,13 @@ PRESETS = {
                                            hidden_size=3072, num_layers=28, num_heads=24, num_kv_heads=8, head_dim=128,
                                            intermediate_size=8192, max_position=8192, norm_eps=1e-5,
                                            rope_theta=500000.0, tie_embeddings=True),
-    # gemma-2-2b shapes on the Gemma-1 block (no soft-capping / sliding window); the reference forces 8 KV heads
-    # for any gemma model (train.py:146-147)
+    # Gemma-2 2B: pre + post norms around both branches, soft-capped attention scores (50) and final logits (30),
+    # sliding-window attention (4096) on every other layer; the reference forces 8 KV heads for any gemma model
+    # (train.py:146-147)
     "google/gemma-2-2b": ModelConfig(family="gemma", name="google/gemma-2-2b", vocab_size=256000, hidden_size=2304,
                                      num_layers=26, num_heads=8, num_kv_heads=8, head_dim=256, intermediate_size=9216,
-                                     max_position=8192, norm_eps=1e-6, tie_embeddings=True),
+                                     max_position=8192, norm_eps=1e-6, tie_embeddings=True, post_norms=True,
+                                     attn_softcap=50.0, final_softcap=30.0, sliding_window=4096),
     # tiny models for tests and smoke runs
     "tiny-gpt2": ModelConfig(family="gpt2", name="tiny-gpt2", vocab_size=1000, hidden_size=64, num_layers=2,
                              num_heads=4, num_kv_heads=4, head_dim=16, intermediate_size=256, max_position=64),
@@ -122,6 +129,9 @@ PRESETS = {
     "tiny-gemma": ModelConfig(family="gemma", name="tiny-gemma", vocab_size=1000, hidden_size=64, num_layers=2,
                               num_heads=4, num_kv_heads=1, head_dim=32, intermediate_size=128, max_position=64,
                               norm_eps=1e-6),
+    "tiny-gemma2": ModelConfig(family="gemma", name="tiny-gemma2", vocab_size=1000, hidden_size=64, num_layers=2,
+                               num_heads=4, num_kv_heads=2, head_dim=32, intermediate_size=128, max_position=64,
+                               norm_eps=1e-6, post_norms=True, attn_softcap=50.0, final_softcap=30.0, sliding_window=4096),
     "tiny-opt": ModelConfig(family="opt", name="tiny-opt", vocab_size=1000, hidden_size=64, num_layers=2, num_heads=4,
                             num_kv_heads=4, head_dim=16, intermediate_size=256, max_position=64),
 }

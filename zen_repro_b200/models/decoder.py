@@ -49,6 +49,9 @@ class Block(nn.Module):
 
         self.norm1_w = nn.Parameter(torch.empty(d, **kw))
         self.norm2_w = nn.Parameter(torch.empty(d, **kw))
+        # Gemma-2: a second norm on the output of each branch, before it joins the residual stream
+        self.postnorm1_w = nn.Parameter(torch.empty(d, **kw)) if cfg.post_norms else None
+        self.postnorm2_w = nn.Parameter(torch.empty(d, **kw)) if cfg.post_norms else None
         self.qkv_w, self.o_w = w(d, qkv_out), w(self.hq * hd, d)
         self.up_w, self.down_w = w(d, up_out), w(self.inner, d)
         if cfg.has_bias:
@@ -60,6 +63,20 @@ class Block(nn.Module):
             self.down_b = nn.Parameter(torch.empty(d, **kw))
         else:
             self.norm1_b = self.norm2_b = self.qkv_b = self.o_b = self.up_b = self.down_b = None
+
+    def _post(self, x, w):
+        """Branch-output norm of Gemma-2 (identity for the other families)."""
+        if w is None:
+            return x
+        cfg = self.cfg
+        return O.fused_norm(x, None, w, None, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)[0]
+
+    def _attend(self, qkv, bsz, seq):
+        cfg = self.cfg
+        if cfg.sliding_window and seq > cfg.sliding_window:
+            raise NotImplementedError(f"sequence length {seq} exceeds the sliding window {cfg.sliding_window}: windowed "
+                                      f"attention layers are only run where the window covers the whole sequence")
+        return O.attention(qkv, bsz, seq, self.hq, self.hkv, cfg.head_dim, softcap=cfg.attn_softcap)
 
     tp_ws = None        # FusedTPWorkspace shared by all blocks of a model (set by DecoderLM.enable_fused_tp)
     sequence_parallel = False   # residual stream sharded over the tokens of the TP group (DecoderLM.enable_sequence_parallel)
@@ -77,12 +94,13 @@ class Block(nn.Module):
         qkv = O.linear(y, self.qkv_w, self.qkv_b, cfg.weight_layout)
         if not cfg.learned_positions:
             qkv = O.rope_qkv(qkv, self.hq, self.hkv, cfg.head_dim, seq, cfg.rope_theta)
-        a = O.attention(qkv, bsz, seq, self.hq, self.hkv, cfg.head_dim)
+        a = self._attend(qkv, bsz, seq)
         # the bias of a row-parallel layer is added once, after the reduction
         o = O.linear(a, self.o_w, self.o_b if tp == 1 else None, cfg.weight_layout)
         o = O.reduce_from_tp(o, g)
         if tp > 1 and self.o_b is not None:
             o = o + self.o_b
+        o = self._post(o, self.postnorm1_w)
         y2, h2 = O.fused_norm(o, h, self.norm2_w, self.norm2_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
         y2 = O.copy_to_tp(y2, g)
         u = O.linear(y2, self.up_w, self.up_b, cfg.weight_layout)
@@ -91,7 +109,7 @@ class Block(nn.Module):
         dn = O.reduce_from_tp(dn, g)
         if tp > 1 and self.down_b is not None:
             dn = dn + self.down_b
-        return dn, h2
+        return self._post(dn, self.postnorm2_w), h2
 
 
 def _block_forward_fused_tp(self, x, res, bsz, seq, ws):
@@ -102,13 +120,13 @@ def _block_forward_fused_tp(self, x, res, bsz, seq, ws):
     qkv = O.linear(y, self.qkv_w, self.qkv_b, cfg.weight_layout, "col", ws)
     if not cfg.learned_positions:
         qkv = O.rope_qkv(qkv, self.hq, self.hkv, cfg.head_dim, seq, cfg.rope_theta)
-    a = O.attention(qkv, bsz, seq, self.hq, self.hkv, cfg.head_dim)
-    o = O.linear(a, self.o_w, self.o_b, cfg.weight_layout, "row", ws)
+    a = self._attend(qkv, bsz, seq)
+    o = self._post(O.linear(a, self.o_w, self.o_b, cfg.weight_layout, "row", ws), self.postnorm1_w)
     y2, h2 = O.fused_norm(o, h, self.norm2_w, self.norm2_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
     u = O.linear(y2, self.up_w, self.up_b, cfg.weight_layout, "col", ws)
     m = O.activation(u, cfg.act)
     dn = O.linear(m, self.down_w, self.down_b, cfg.weight_layout, "row", ws)
-    return dn, h2
+    return self._post(dn, self.postnorm2_w), h2
 
 
 Block._forward_fused_tp = _block_forward_fused_tp
@@ -127,13 +145,13 @@ def _block_forward_sp(self, x, res, bsz, seq):
     qkv = O.sp_linear(y, self.qkv_w, self.qkv_b, lay, "ag", g, ws)
     if not cfg.learned_positions:
         qkv = O.rope_qkv(qkv, self.hq, self.hkv, cfg.head_dim, seq, cfg.rope_theta)
-    a = O.attention(qkv, bsz, seq, self.hq, self.hkv, cfg.head_dim)
-    o = O.sp_linear(a, self.o_w, self.o_b, lay, "rs", g, ws)
+    a = self._attend(qkv, bsz, seq)
+    o = self._post(O.sp_linear(a, self.o_w, self.o_b, lay, "rs", g, ws), self.postnorm1_w)
     y2, h2 = O.fused_norm(o, h, self.norm2_w, self.norm2_b, cfg.norm_eps, cfg.layer_norm, cfg.norm_unit_offset)
     u = O.sp_linear(y2, self.up_w, self.up_b, lay, "ag", g, ws)
     m = O.activation(u, cfg.act)
     dn = O.sp_linear(m, self.down_w, self.down_b, lay, "rs", g, ws)
-    return dn, h2
+    return self._post(dn, self.postnorm2_w), h2
 
 
 Block._forward_sp = _block_forward_sp
@@ -207,7 +225,7 @@ class DecoderLM(nn.Module):
     def _sp_partial_params(self):
         ps = [self.norm_f_w, self.norm_f_b]
         for b in self.blocks:
-            ps += [b.norm1_w, b.norm2_w, b.norm1_b, b.norm2_b, b.o_b, b.down_b]
+            ps += [b.norm1_w, b.norm2_w, b.norm1_b, b.norm2_b, b.o_b, b.down_b, b.postnorm1_w, b.postnorm2_w]
         return [p for p in ps if p is not None]
 
     def head_weight(self):
@@ -236,7 +254,10 @@ class DecoderLM(nn.Module):
         if sp:
             y = O.gather_from_sp(y, self.tp_group)
         if labels is None:
-            return self._logits(y).view(bsz, seq, -1)
+            logits = self._logits(y).view(bsz, seq, -1)
+            if cfg.final_softcap > 0:
+                logits = cfg.final_softcap * torch.tanh(logits.float() / cfg.final_softcap)
+            return logits
         if shift_labels:
             lab = torch.full_like(labels, -100)
             lab[:, :-1] = labels[:, 1:]
@@ -244,7 +265,7 @@ class DecoderLM(nn.Module):
             lab = labels
         if tp > 1:
             return self._vocab_parallel_loss(y, lab.reshape(-1))
-        return O.lm_head_loss(y, self.head_weight(), lab.reshape(-1))
+        return O.lm_head_loss(y, self.head_weight(), lab.reshape(-1), softcap=cfg.final_softcap)
 
     # ---- vocab-parallel pieces (TP > 1) ------------------------------------------------------
     def _vocab_parallel_embed(self, ids, seq):
@@ -275,7 +296,8 @@ class DecoderLM(nn.Module):
         """Cross-entropy over vocabulary shards; the hidden-state gradient is the sum over the group of each shard's
         dlogits @ W_local (the input of this function is replicated, so that sum is its full gradient)."""
         return O.vocab_parallel_lm_head_loss(y, self.head_weight(), labels, self.tp_group, self.vocab_start,
-                                             self.cfg.vocab_size, tp_ws=getattr(self, "tp_ws", None))
+                                             self.cfg.vocab_size, tp_ws=getattr(self, "tp_ws", None),
+                                             softcap=self.cfg.final_softcap)
 
     def sync_replicated_grads(self):
         """Sum over the TP group the gradients of weights that are replicated but see only part of the work: the

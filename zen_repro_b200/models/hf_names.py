@@ -1,7 +1,7 @@
 """HuggingFace parameter names and shapes <-> this framework's fused parameters.
 
 ``to_hf`` splits the fused qkv and gate|up matrices and renames everything so that the result loads
-into ``transformers``' GPT2LMHeadModel / OPTForCausalLM / LlamaForCausalLM / GemmaForCausalLM with
+into ``transformers``' GPT2LMHeadModel / OPTForCausalLM / LlamaForCausalLM / GemmaForCausalLM / Gemma2ForCausalLM with
 ``load_state_dict``; ``from_hf`` is the inverse.  Only full (TP = 1) models are converted; sharded
 models are gathered first by the checkpoint code.
 """
@@ -67,7 +67,13 @@ def to_hf(model) -> dict:
             put(p + "self_attn.v_proj.weight", v); put(p + "self_attn.o_proj.weight", b.o_w)
             put(p + "mlp.gate_proj.weight", gate); put(p + "mlp.up_proj.weight", up)
             put(p + "mlp.down_proj.weight", b.down_w)
-            put(p + "input_layernorm.weight", b.norm1_w); put(p + "post_attention_layernorm.weight", b.norm2_w)
+            put(p + "input_layernorm.weight", b.norm1_w)
+            if cfg.post_norms:       # Gemma-2 names: post_attention = norm on the attention output, pre_feedforward = MLP input
+                put(p + "post_attention_layernorm.weight", b.postnorm1_w)
+                put(p + "pre_feedforward_layernorm.weight", b.norm2_w)
+                put(p + "post_feedforward_layernorm.weight", b.postnorm2_w)
+            else:
+                put(p + "post_attention_layernorm.weight", b.norm2_w)
         put("model.norm.weight", model.norm_f_w)
         put("lm_head.weight", model.head_weight()[:V])
     return sd
@@ -118,8 +124,11 @@ def from_hf(model, sd: dict, strict: bool = True):
             p = f"model.layers.{i}."
             cp(b.qkv_w, torch.cat([get(p + f"self_attn.{n}_proj.weight") for n in "qkv"], 0))
             cp(b.up_w, torch.cat([get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")], 0))
-            for ours, theirs in (("o_w", "self_attn.o_proj.weight"), ("down_w", "mlp.down_proj.weight"),
-                                 ("norm1_w", "input_layernorm.weight"), ("norm2_w", "post_attention_layernorm.weight")):
+            norms = ((("norm1_w", "input_layernorm.weight"), ("postnorm1_w", "post_attention_layernorm.weight"),
+                      ("norm2_w", "pre_feedforward_layernorm.weight"), ("postnorm2_w", "post_feedforward_layernorm.weight"))
+                     if cfg.post_norms else
+                     (("norm1_w", "input_layernorm.weight"), ("norm2_w", "post_attention_layernorm.weight")))
+            for ours, theirs in (("o_w", "self_attn.o_proj.weight"), ("down_w", "mlp.down_proj.weight")) + norms:
                 cp(getattr(b, ours), get(p + theirs))
         cp(model.norm_f_w, get("model.norm.weight"))
     if model.lm_head is not None:

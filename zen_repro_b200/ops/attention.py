@@ -30,9 +30,12 @@ def kernel_covers(seq, hq, hkv, hd, dtype, backward: bool = False) -> bool:
     return hd in (64, 128, 256)
 
 
-def have_kernel(seq, hq, hkv, hd, dtype) -> bool:
-    """True when forward AND backward run on the hand-written kernels for this shape."""
+def have_kernel(seq, hq, hkv, hd, dtype, softcap: float = 0.0) -> bool:
+    """True when forward AND backward run on the hand-written kernels for this shape (soft-capped scores: the
+    head_dim 256 kernels only; other head sizes are padded to 256)."""
     if _MODE == "lib":
+        return False
+    if softcap > 0 and hd != 256:
         return False
     return kernel_covers(seq, hq, hkv, hd, dtype, backward=True) and HAVE_BWD
 
@@ -40,11 +43,11 @@ def have_kernel(seq, hq, hkv, hd, dtype) -> bool:
 HAVE_BWD = True
 
 
-def padded_shape(seq, hq, hkv, hd, dtype):
+def padded_shape(seq, hq, hkv, hd, dtype, softcap: float = 0.0):
     """(seq', hd') of the covered shape that (seq, hd) is zero-padded to, or None when padding cannot help."""
     if _MODE == "lib" or dtype != torch.bfloat16 or hq % hkv or hd > 256 or not HAVE_BWD:
         return None
-    return (seq + 127) // 128 * 128, next(h for h in (64, 128, 256) if h >= hd)
+    return (seq + 127) // 128 * 128, (256 if softcap > 0 else next(h for h in (64, 128, 256) if h >= hd))
 
 
 def pad_qkv(qkv, bsz, seq, nheads, hd, seq_p, hd_p):
@@ -58,13 +61,15 @@ def unpad(t, bsz, seq, nheads, hd, seq_p, hd_p):
     return t.view(bsz, seq_p, nheads, hd_p)[:, :seq, :, :hd].reshape(bsz * seq, nheads * hd)
 
 
-def attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale):
-    """tcgen05 forward: returns (out[B*S, Hq*hd], lse2[B, Hq, S]) with lse2 in base 2 of the scaled scores."""
+def attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale, softcap: float = 0.0):
+    """tcgen05 forward: returns (out[B*S, Hq*hd], lse2[B, Hq, S]) with lse2 in base 2 of the scaled scores.
+    ``softcap`` > 0 soft-caps the scaled scores, cap * tanh(s / cap), before the softmax (Gemma-2)."""
     assert qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
     out = torch.empty(bsz * seq, hq * hd, dtype=qkv.dtype, device=qkv.device)
     lse2 = torch.empty(bsz, hq, seq, dtype=torch.float32, device=qkv.device)
     rc = _native.lib().zen_attn_fwd(_native.ptr(qkv), _native.ptr(out), _native.ptr(lse2), bsz, seq, hq, hkv, hd,
-                                    qkv.stride(0), out.stride(0), ctypes.c_float(scale), _native.stream_ptr())
+                                    qkv.stride(0), out.stride(0), ctypes.c_float(scale), ctypes.c_float(softcap),
+                                    _native.stream_ptr())
     _native.check(rc, "zen_attn_fwd")
     return out, lse2
 
@@ -73,7 +78,7 @@ _BWD64 = os.environ.get("ZEN_ATTN_BWD64", "")      # "", or 0 / 1 / 2: which hea
 _bwd64_applied = False
 
 
-def attention_bwd_kernel(dout, qkv, out, lse2, bsz, seq, hq, hkv, hd, scale):
+def attention_bwd_kernel(dout, qkv, out, lse2, bsz, seq, hq, hkv, hd, scale, softcap: float = 0.0):
     """tcgen05 backward: gradient of the fused qkv buffer (dQ kernel + dK/dV kernel, no atomics)."""
     global _bwd64_applied
     if _BWD64 and not _bwd64_applied:
@@ -92,7 +97,8 @@ def attention_bwd_kernel(dout, qkv, out, lse2, bsz, seq, hq, hkv, hd, scale):
             part = torch.empty(2 * hsplit * bsz * seq * hkv * 256, dtype=torch.float32, device=qkv.device)
     rc = _native.lib().zen_attn_bwd(_native.ptr(qkv), _native.ptr(out), _native.ptr(dout), _native.ptr(lse2), _native.ptr(dbuf),
                                     _native.ptr(dqkv), bsz, seq, hq, hkv, hd, qkv.stride(0), out.stride(0),
-                                    ctypes.c_float(scale), _native.ptr(part), hsplit, _native.stream_ptr())
+                                    ctypes.c_float(scale), ctypes.c_float(softcap), _native.ptr(part), hsplit,
+                                    _native.stream_ptr())
     _native.check(rc, "zen_attn_bwd")
     return dqkv
 
@@ -109,38 +115,42 @@ def _split(qkv, bsz, seq, hq, hkv, hd):
     return q, k, v
 
 
-def reference_attention(qkv, bsz, seq, hq, hkv, hd, scale):
+def reference_attention(qkv, bsz, seq, hq, hkv, hd, scale, softcap: float = 0.0):
     q, k, v = _split(qkv.float(), bsz, seq, hq, hkv, hd)
     rep = hq // hkv
     k = k.repeat_interleave(rep, dim=1)
     v = v.repeat_interleave(rep, dim=1)
     s = (q @ k.transpose(-1, -2)) * scale
+    if softcap > 0:
+        s = softcap * torch.tanh(s / softcap)
     mask = torch.ones(seq, seq, dtype=torch.bool, device=qkv.device).tril()
     s = s.masked_fill(~mask, float("-inf"))
     o = torch.softmax(s, -1) @ v
     return o.transpose(1, 2).reshape(bsz * seq, hq * hd).to(qkv.dtype)
 
 
-def attention_fwd(qkv, bsz, seq, hq, hkv, hd, scale):
+def attention_fwd(qkv, bsz, seq, hq, hkv, hd, scale, softcap: float = 0.0):
     if not qkv.is_cuda:
-        return reference_attention(qkv, bsz, seq, hq, hkv, hd, scale), ()
+        return reference_attention(qkv, bsz, seq, hq, hkv, hd, scale, softcap), ()
     if have_kernel(seq, hq, hkv, hd, qkv.dtype) and qkv.is_contiguous():
-        out, lse2 = attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale)
+        out, lse2 = attention_fwd_kernel(qkv, bsz, seq, hq, hkv, hd, scale, softcap)
         return out, (lse2,)
+    if softcap > 0:
+        return reference_attention(qkv, bsz, seq, hq, hkv, hd, scale, softcap), ()
     q, k, v = _split(qkv, bsz, seq, hq, hkv, hd)
     o = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale, enable_gqa=(hq != hkv))
     return o.transpose(1, 2).reshape(bsz * seq, hq * hd), ()
 
 
-def attention_bwd(dout, qkv, out, saved, bsz, seq, hq, hkv, hd, scale):
+def attention_bwd(dout, qkv, out, saved, bsz, seq, hq, hkv, hd, scale, softcap: float = 0.0):
     """Gradient w.r.t. the fused qkv buffer: the tcgen05 kernels when the forward saved its statistics, else a
     recomputation under autograd."""
     if len(saved) == 1 and qkv.is_cuda:
-        return attention_bwd_kernel(dout, qkv, out, saved[0], bsz, seq, hq, hkv, hd, scale)
+        return attention_bwd_kernel(dout, qkv, out, saved[0], bsz, seq, hq, hkv, hd, scale, softcap)
     with torch.enable_grad():
         x = qkv.detach().requires_grad_(True)
-        if not qkv.is_cuda:
-            o = reference_attention(x, bsz, seq, hq, hkv, hd, scale)
+        if not qkv.is_cuda or softcap > 0:
+            o = reference_attention(x, bsz, seq, hq, hkv, hd, scale, softcap)
         else:
             q, k, v = _split(x, bsz, seq, hq, hkv, hd)
             o = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale, enable_gqa=(hq != hkv))

@@ -250,6 +250,21 @@ def embedding(ids, wte, wpe=None, seq=1, pos_offset=0, scale=1.0, sparse_sink=No
     return EmbeddingFn.apply(ids, wte, wpe, seq, pos_offset, scale, sparse_sink, vocab_start)
 
 
+def _softcap_(logits: torch.Tensor, cap: float):
+    """In place logits <- cap * tanh(logits / cap); returns tanh(logits / cap) for the gradient (None when off)."""
+    if not cap or cap <= 0:
+        return None
+    th = torch.tanh(logits.float() / cap) if logits.dtype != torch.float32 else torch.tanh(logits / cap)
+    logits.copy_(th * cap)
+    return th
+
+
+def _softcap_grad_(dlogits: torch.Tensor, th) -> None:
+    """In place chain rule through the soft-capping: dlogits <- dlogits * (1 - tanh^2)."""
+    if th is not None:
+        dlogits.copy_(dlogits.float() * (1.0 - th * th))
+
+
 class LMHeadLossFn(torch.autograd.Function):
     """mean cross-entropy(h @ W^T, labels).  Logits are computed, turned into dlogits in place by one
     kernel (already scaled by 1 / valid-token-count, read from the device), and immediately consumed
@@ -257,7 +272,7 @@ class LMHeadLossFn(torch.autograd.Function):
     is assumed to be 1 (``unit_grad``); otherwise the saved gradients are rescaled in backward."""
 
     @staticmethod
-    def forward(ctx, h, weight, labels, ignore_index, chunk_tokens, unit_grad):
+    def forward(ctx, h, weight, labels, ignore_index, chunk_tokens, unit_grad, softcap=0.0):
         h2 = h.reshape(-1, h.shape[-1])
         lab = labels.reshape(-1)
         T = h2.shape[0]
@@ -281,7 +296,9 @@ class LMHeadLossFn(torch.autograd.Function):
             buf = torch.empty(e - s, vpad, dtype=h2.dtype, device=h2.device)
             logits = buf[:, :V]
             G.gemm_nt(h2[s:e], weight, out=logits, pad_ok=True)
+            th = _softcap_(logits, softcap)
             loss, dl = E.cross_entropy(logits, lab[s:e], grad_scale=1.0, grad_scale_dev=inv, ignore_index=ignore_index)
+            _softcap_grad_(dl, th)
             loss_sum += loss.sum()
             G.gemm_nn(dl, weight, out=dh[s:e])
             G.gemm_tn(dl, h2[s:e], out=dw, accumulate=not (fresh and s == 0))
@@ -296,14 +313,15 @@ class LMHeadLossFn(torch.autograd.Function):
         hshape, wdtype, direct, unit = ctx.cfg
         if direct:
             ctx.wp.zen_ready(ctx.wp)
-            return dh.view(hshape), None, None, None, None, None
+            return dh.view(hshape), None, None, None, None, None, None
         if unit:
-            return dh.view(hshape), dw.to(wdtype), None, None, None, None
-        return (dh.float() * g).to(dh.dtype).view(hshape), (dw.float() * g).to(wdtype), None, None, None, None
+            return dh.view(hshape), dw.to(wdtype), None, None, None, None, None
+        return (dh.float() * g).to(dh.dtype).view(hshape), (dw.float() * g).to(wdtype), None, None, None, None, None
 
 
-def lm_head_loss(h, weight, labels, ignore_index=-100, chunk_tokens=8192, unit_grad=True):
-    return LMHeadLossFn.apply(h, weight, labels, ignore_index, chunk_tokens, unit_grad)
+def lm_head_loss(h, weight, labels, ignore_index=-100, chunk_tokens=8192, unit_grad=True, softcap: float = 0.0):
+    """``softcap`` > 0: logits -> cap * tanh(logits / cap) before the loss (Gemma-2's final-logit soft-capping)."""
+    return LMHeadLossFn.apply(h, weight, labels, ignore_index, chunk_tokens, unit_grad, softcap)
 
 
 class VocabParallelLMHeadLossFn(torch.autograd.Function):
@@ -313,7 +331,7 @@ class VocabParallelLMHeadLossFn(torch.autograd.Function):
     (fused into the GEMM epilogue when a workspace is given).  Unit incoming gradient assumed, as in LMHeadLossFn."""
 
     @staticmethod
-    def forward(ctx, h, weight, labels, group, vocab_start, vocab_size, ignore_index, chunk_tokens, tp_ws):
+    def forward(ctx, h, weight, labels, group, vocab_start, vocab_size, ignore_index, chunk_tokens, tp_ws, softcap=0.0):
         h2 = h.reshape(-1, h.shape[-1])
         lab = labels.reshape(-1)
         T = h2.shape[0]
@@ -333,6 +351,7 @@ class VocabParallelLMHeadLossFn(torch.autograd.Function):
             buf = torch.empty(e - s, vpad, dtype=h2.dtype, device=h2.device)
             logits = buf[:, :Vl]
             G.gemm_nt(h2[s:e], weight, out=logits, pad_ok=True)
+            th = _softcap_(logits, softcap)
             m, se, tgt = E.xent_partial(logits, lab[s:e], valid_cols, vocab_start, ignore_index)
             gm = m.clone()
             dist.all_reduce(gm, op=dist.ReduceOp.MAX, group=group)
@@ -343,6 +362,7 @@ class VocabParallelLMHeadLossFn(torch.autograd.Function):
             valid = lab[s:e] != ignore_index
             loss_sum += ((lse - packed[1]) * valid).sum()
             E.xent_apply_(logits, lab[s:e], lse, valid_cols, vocab_start, grad_scale_dev=inv, ignore_index=ignore_index)
+            _softcap_grad_(logits, th)
             if tp_ws is not None and tp_ws.fits(e - s, h2.shape[1]):
                 tp_ws.gemm_ar_nn(logits, weight, out=dh[s:e])
             else:
@@ -361,30 +381,31 @@ class VocabParallelLMHeadLossFn(torch.autograd.Function):
         hshape, direct = ctx.cfg
         if direct:
             ctx.wp.zen_ready(ctx.wp)
-            return (dh.view(hshape),) + (None,) * 8
-        return (dh.view(hshape), dw) + (None,) * 7
+            return (dh.view(hshape),) + (None,) * 9
+        return (dh.view(hshape), dw) + (None,) * 8
 
 
 def vocab_parallel_lm_head_loss(h, weight, labels, group, vocab_start, vocab_size, ignore_index=-100, chunk_tokens=8192,
-                                tp_ws=None):
-    return VocabParallelLMHeadLossFn.apply(h, weight, labels, group, vocab_start, vocab_size, ignore_index, chunk_tokens, tp_ws)
+                                tp_ws=None, softcap: float = 0.0):
+    return VocabParallelLMHeadLossFn.apply(h, weight, labels, group, vocab_start, vocab_size, ignore_index, chunk_tokens,
+                                           tp_ws, softcap)
 
 
 class AttentionFn(torch.autograd.Function):
     """Causal self-attention over a fused qkv projection [B*S, (Hq + 2 Hkv) * hd] -> [B*S, Hq * hd]."""
 
     @staticmethod
-    def forward(ctx, qkv, bsz, seq, hq, hkv, hd, scale):
-        out, saved = A.attention_fwd(qkv, bsz, seq, hq, hkv, hd, scale)
+    def forward(ctx, qkv, bsz, seq, hq, hkv, hd, scale, softcap):
+        out, saved = A.attention_fwd(qkv, bsz, seq, hq, hkv, hd, scale, softcap)
         ctx.save_for_backward(qkv, out, *saved)
-        ctx.cfg = (bsz, seq, hq, hkv, hd, scale)
+        ctx.cfg = (bsz, seq, hq, hkv, hd, scale, softcap)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         qkv, out, *saved = ctx.saved_tensors
         dqkv = A.attention_bwd(dout.contiguous(), qkv, out, saved, *ctx.cfg)
-        return dqkv, None, None, None, None, None, None
+        return (dqkv,) + (None,) * 7
 
 
 class PaddedAttentionFn(torch.autograd.Function):
@@ -392,33 +413,36 @@ class PaddedAttentionFn(torch.autograd.Function):
     next covered shape, run the kernels there, cut the result back."""
 
     @staticmethod
-    def forward(ctx, qkv, bsz, seq, hq, hkv, hd, scale, seq_p, hd_p):
+    def forward(ctx, qkv, bsz, seq, hq, hkv, hd, scale, softcap, seq_p, hd_p):
         qp = A.pad_qkv(qkv, bsz, seq, hq + 2 * hkv, hd, seq_p, hd_p)
-        out_p, lse2 = A.attention_fwd_kernel(qp, bsz, seq_p, hq, hkv, hd_p, scale)
+        out_p, lse2 = A.attention_fwd_kernel(qp, bsz, seq_p, hq, hkv, hd_p, scale, softcap)
         ctx.save_for_backward(qp, out_p, lse2)
-        ctx.cfg = (bsz, seq, hq, hkv, hd, scale, seq_p, hd_p)
+        ctx.cfg = (bsz, seq, hq, hkv, hd, scale, softcap, seq_p, hd_p)
         return A.unpad(out_p, bsz, seq, hq, hd, seq_p, hd_p)
 
     @staticmethod
     def backward(ctx, dout):
         qp, out_p, lse2 = ctx.saved_tensors
-        bsz, seq, hq, hkv, hd, scale, seq_p, hd_p = ctx.cfg
+        bsz, seq, hq, hkv, hd, scale, softcap, seq_p, hd_p = ctx.cfg
         dp = A.pad_qkv(dout.contiguous(), bsz, seq, hq, hd, seq_p, hd_p)
-        dqkv_p = A.attention_bwd_kernel(dp, qp, out_p, lse2, bsz, seq_p, hq, hkv, hd_p, scale)
-        return (A.unpad(dqkv_p, bsz, seq, hq + 2 * hkv, hd, seq_p, hd_p),) + (None,) * 8
+        dqkv_p = A.attention_bwd_kernel(dp, qp, out_p, lse2, bsz, seq_p, hq, hkv, hd_p, scale, softcap)
+        return (A.unpad(dqkv_p, bsz, seq, hq + 2 * hkv, hd, seq_p, hd_p),) + (None,) * 9
 
 
-def attention(qkv, bsz, seq, hq, hkv, hd, scale=None):
+def attention(qkv, bsz, seq, hq, hkv, hd, scale=None, softcap: float = 0.0):
+    """``softcap`` > 0: scores are soft-capped, cap * tanh(s * scale / cap), before the softmax (Gemma-2)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
-    if qkv.is_cuda and not A.have_kernel(seq, hq, hkv, hd, qkv.dtype):
-        pad = A.padded_shape(seq, hq, hkv, hd, qkv.dtype)
+    if qkv.is_cuda and not A.have_kernel(seq, hq, hkv, hd, qkv.dtype, softcap):
+        pad = A.padded_shape(seq, hq, hkv, hd, qkv.dtype, softcap)
         if pad is not None:
-            return PaddedAttentionFn.apply(qkv, bsz, seq, hq, hkv, hd, scale, *pad)
+            return PaddedAttentionFn.apply(qkv, bsz, seq, hq, hkv, hd, scale, softcap, *pad)
+        if softcap > 0:
+            return A.reference_attention(qkv, bsz, seq, hq, hkv, hd, scale, softcap)
         # library fallback under plain autograd (keeps the forward's softmax statistics, no recompute)
         q, k, v = A._split(qkv, bsz, seq, hq, hkv, hd)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale, enable_gqa=(hq != hkv))
         return o.transpose(1, 2).reshape(bsz * seq, hq * hd)
-    return AttentionFn.apply(qkv, bsz, seq, hq, hkv, hd, scale)
+    return AttentionFn.apply(qkv, bsz, seq, hq, hkv, hd, scale, softcap)
 
 
 # ------------------------------------------------------------------------------------------ tensor parallel

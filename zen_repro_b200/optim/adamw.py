@@ -131,7 +131,16 @@ class FusedAdamW(torch.optim.Optimizer):
     def load_state_dict(self, sd):
         sd = dict(sd)
         self._step = sd.pop("zen_step", 0)
-        super().load_state_dict(sd)
+        # torch's loader casts floating-point state to the parameter's dtype, which would turn the fp32 moments and
+        # master weights of a bf16 parameter into bf16 (the kernel reads them as fp32): load the groups through torch,
+        # the per-parameter state here, dtype kept
+        saved = sd.get("state", {})
+        super().load_state_dict({"state": {}, "param_groups": sd["param_groups"]})
+        ids = [i for g in sd["param_groups"] for i in g["params"]]
+        params = [p for g in self.param_groups for p in g["params"]]
+        for i, p in zip(ids, params):
+            if i in saved:
+                self.state[p] = {k: (v.detach().clone().to(p.device) if torch.is_tensor(v) else v) for k, v in saved[i].items()}
         self._tables.clear()
         if self._step_dev is not None:           # the bias corrections of a captured step read the device counter
             self._step_dev.fill_(self._step)

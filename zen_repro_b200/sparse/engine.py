@@ -92,7 +92,7 @@ class SparsePlan:
         union = min(S, math.ceil(S * min(1.0, self.max_density * P) * self.slack))
         self.nwords = (S + 31) // 32
         self.nchunks = (S + 1023) // 1024
-        ngroups = (self.nchunks + 7) // 8
+        ngroups = self.nchunks              # one run per 1024-slot chunk
         # the gather payload is filled in runs that start on 8-value boundaries: up to 8 padding values per run
         self.cap_g = _up(max(union, 64) + 8 * ngroups, 8)
         # bitmap words, or a COO list: the whole payload when format 2 is forced, else as many entries as the

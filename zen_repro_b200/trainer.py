@@ -161,8 +161,11 @@ class Trainer:
 
         g = torch.cuda.CUDAGraph()
         before = _native.launch_count()
+        published = self.health.published if self.health is not None else 0
         with torch.cuda.graph(g):
             self._static_loss = self._eager_step(self._static_ids, self._static_ids)
+        if self.health is not None:
+            self.health.published = published      # recorded, not run: the host counts a publish at every replay instead
         self.graph_launches_per_step = _native.launch_count() - before      # this library's kernels inside the graph
         self._graph = g
         return True
@@ -210,6 +213,8 @@ class Trainer:
                 return self.step_device(ids, labels, read_loss)
             self._static_ids.copy_(ids, non_blocking=True)
             self._graph.replay()
+            if self.health is not None and self.health.sources:
+                self.health.published += 1         # the replayed step published its status words
             self.step_count += 1
             self._steps_here += 1
             return float(self._static_loss.item()) if read_loss else self._static_loss
