@@ -46,6 +46,13 @@ def parse():
     ap.add_argument("--no_e2e", action="store_true")
     ap.add_argument("--no_extra", action="store_true", help="skip the extra configurations measured after the GPT-2 headline")
     ap.add_argument("--bucket_cap_mb", type=float, default=None)
+    ap.add_argument("--dense_transport", default=None, choices=["auto", "nccl", "nvls"],
+                    help="dense buckets: library all-reduce or this library's multimem kernel through the NVSwitch")
+    ap.add_argument("--no_sparse_embedding", action="store_true", help="keep the whole embedding gradient in the dense buckets")
+    ap.add_argument("--no_status_mirror", action="store_true", help="do not publish the kernels' status words every step")
+    ap.add_argument("--timeline", action="store_true",
+                    help="after the timed passes, run K eager steps with CUDA events on the compute and communication "
+                         "streams and report the communication that backward did not hide")
     ap.add_argument("--dense_embedding_under_tp", action="store_true",
                     help="TP runs: keep the vocabulary-sharded embedding gradient in the dense buckets")
     ap.add_argument("--sequence_parallel", action="store_true", help="TP layers with the residual stream sharded over tokens")
@@ -75,6 +82,12 @@ def _measure(args, config_name: str, method: int, top_k: float, e2e_pass: bool) 
     extra_cfg = {}
     if args.bucket_cap_mb:
         extra_cfg["bucket_cap_mb"] = args.bucket_cap_mb
+    if args.dense_transport:
+        extra_cfg["dense_transport"] = args.dense_transport
+    if args.no_sparse_embedding:
+        extra_cfg["sparse_embedding"] = False
+    if args.no_status_mirror:
+        extra_cfg["status_mirror"] = False
     cfg = TrainConfig(method=method, top_k=top_k, num_layers=args.num_layers, data_pool=max(4, min(8, args.steps)),
                       cuda_graph=not args.no_graph, sequence_parallel=args.sequence_parallel,
                       sparse_embedding_under_tp=preset["tp"] > 1 and not args.dense_embedding_under_tp, **extra_cfg, **preset)
@@ -124,6 +137,27 @@ def _measure(args, config_name: str, method: int, top_k: float, e2e_pass: bool) 
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
     health = trainer.check_health(raise_on_error=False)
+    graph_on = trainer._graph is not None                     # as the timed passes ran (the timeline below runs eagerly)
+    timeline = None
+    if args.timeline and world > 1:
+        trainer._graph, trainer.graph_ok = None, False
+        ddp_ = trainer.model.module
+        ids = dev_batches[0]
+        trainer.step_device(ids, ids)
+        ddp_.timeline = []
+        s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s2.record()
+        for i in range(args.steps):
+            trainer.step_device(ids, ids)
+        e2.record()
+        rows = ddp_.exposed_comm_us()
+        ddp_.timeline = None
+        n_ = max(1, len(rows))
+        tl = torch.tensor([sum(r["dense_exposed_us"] for r in rows) / n_, sum(r["sync_exposed_us"] for r in rows) / n_,
+                           s2.elapsed_time(e2) * 1e3 / args.steps], device=dev, dtype=torch.float64)
+        dist.all_reduce(tl, op=dist.ReduceOp.MAX)
+        timeline = {"dense_exposed_us": tl[0].item(), "sync_exposed_us": tl[1].item(), "eager_step_us": tl[2].item(),
+                    "note": "eager steps (no graph); max over ranks of the per-rank mean"}
     tokens = trainer.tokens_per_step * args.steps
     if e2e_pass:
         e2e = {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -140,12 +174,14 @@ def _measure(args, config_name: str, method: int, top_k: float, e2e_pass: bool) 
                    "method": cfg.method, "top_k": cfg.top_k,
                    # what was actually built, not what was asked for
                    "embedding_row_sync": ddp.embedding_sync is not None, "bucket_cap_mb": cfg.bucket_cap_mb,
-                   "n_buckets": len(ddp.buckets), "grad_checkpoint": bool(trainer.model_cfg.grad_checkpoint),
-                   "num_layers": trainer.model_cfg.num_layers, "cuda_graph": bool(trainer._graph is not None),
+                   "n_buckets": len(ddp.buckets), "dense_allreduce": "nvls multimem kernel" if getattr(ddp, "arena", None) is not None else "nccl", "grad_checkpoint": bool(trainer.model_cfg.grad_checkpoint),
+                   "num_layers": trainer.model_cfg.num_layers, "cuda_graph": bool(graph_on),
                    "l2": "per-step working set (weights + activations, > 1 GB) exceeds the 126 MB L2"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "gemm_error": gemm.gemm_error(),
         "kernel_status": {k: v for k, v in health.items() if v},
     }
+    if timeline is not None:
+        out["timeline"] = timeline
     trainer.close()
     del trainer, dev_batches
     import gc

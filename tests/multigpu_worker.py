@@ -329,7 +329,52 @@ def check_tp2dp2_sparse_embedding(rank, world, dev):
     print(f"OK tp2dp2_sparse_embedding rank{rank} {out[True]}", flush=True)
 
 
-CHECKS = {"b2b": check_sparse_back_to_back, "nvls": check_sparse_nvls, "verify": check_verify_fallback,
+def check_nvls_dense_allreduce(rank, world, dev):
+    """The multimem all-reduce kernel against the NCCL all-reduce: bf16 and fp32 ranges of one arena, several calls in a
+    row without host synchronisation, the mean folded in; then a trainer whose dense buckets go through it against the
+    same run on NCCL."""
+    from zen_repro_b200.parallel.nvls_allreduce import MulticastArena
+    from zen_repro_b200.trainer import TrainConfig, Trainer
+
+    try:
+        arena = MulticastArena(64 << 20, None, wait_ms=5000.0)
+    except RuntimeError as ex:
+        print(f"OK nvls_dense rank{rank} (skipped: {ex})", flush=True)
+        return
+    g = torch.Generator().manual_seed(50 + rank)
+    cases = [(0, 1 << 20, torch.bfloat16), (4 << 20, 3 * 1000 * 8, torch.float32), (16 << 20, (1 << 22) + 8, torch.bfloat16)]
+    wants, views = [], []
+    for off, n, dt in cases:
+        v = arena.view(off, n, dt)
+        v.copy_(torch.randn(n, generator=g).to(dt))
+        want = v.float().clone()
+        dist.all_reduce(want)
+        wants.append(want / world)
+        views.append(v)
+    torch.cuda.synchronize(); dist.barrier()
+    for (off, n, dt), v in zip(cases, views):
+        arena.allreduce_(off, n * v.element_size(), dt, 1.0 / world)
+    torch.cuda.synchronize()
+    assert arena.check() == 0
+    for v, want, (_, _, dt) in zip(views, wants, cases):
+        tol = 2e-2 if dt == torch.bfloat16 else 1e-5
+        assert (v.float() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item()), dt
+        ref = v.clone()
+        dist.broadcast(ref, 0)
+        assert torch.equal(ref, v)                       # every rank holds the same bits
+    losses = {}
+    for tr in ("nvls", "nccl"):
+        t = Trainer(TrainConfig(model="gpt2", num_layers=2, micro_batch=2, seq_len=128, lr=1e-3, data_pool=4, dense_transport=tr,
+                                cuda_graph=True, graph_warmup=2), init_dist=False)
+        assert (t.model.module.arena is not None) == (tr == "nvls")
+        losses[tr] = [t.step(next(t.data)) for _ in range(6)]
+        assert not any(t.check_health(raise_on_error=False).values())
+        t.close()
+    assert all(abs(a - b) < 0.03 for a, b in zip(losses["nvls"], losses["nccl"])), losses
+    print(f"OK nvls_dense rank{rank} {losses['nvls'][0]:.3f}->{losses['nvls'][-1]:.3f}", flush=True)
+
+
+CHECKS = {"nvls_dense": check_nvls_dense_allreduce, "b2b": check_sparse_back_to_back, "nvls": check_sparse_nvls, "verify": check_verify_fallback,
           "tp2dp2": check_tp2dp2_sparse_embedding, "gemm_ar": check_gemm_allreduce, "sp_trainer": check_sp_trainer, "gemm_rs_ag": check_gemm_rs_ag, "tp_trainer": check_tp_trainer,"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
           "hook": check_zen_hook, "departed": check_departed_rank}
 

@@ -19,7 +19,7 @@ def _run(names, nproc, timeout=600):
     return r.stdout
 
 
-@pytest.mark.parametrize("name", ["sparse", "b2b", "nvls", "verify", "rows", "trainer", "hook", "departed", "gemm_ar", "gemm_rs_ag",
+@pytest.mark.parametrize("name", ["sparse", "b2b", "nvls", "nvls_dense", "verify", "rows", "trainer", "hook", "departed", "gemm_ar", "gemm_rs_ag",
                                   "tp_trainer", "sp_trainer", "tp2dp2"])
 def test_multigpu(name):
     n = torch.cuda.device_count()

@@ -469,8 +469,11 @@ zen_owner_reduce_kernel(const ZenSparseCtx c, int src_begin, int src_end, int al
     const ZenMail* mail = zen_rec_mail(c, c.rank, s, epoch);
     uint32_t n = 0, fl = 0;
     if (zen_wait_epoch(&mail->epoch, epoch, c.wait_ns)) {
-      n = min(zen_ld_acquire_sys(&mail->count), c.cap_rec);
-      if (zen_ld_acquire_sys(&mail->info) & 1u) fl = ZEN_PEER_OVERFLOW;
+      // count and info were written before the epoch's release store: plain loads after the acquire above see them
+      const uint32_t cnt = *reinterpret_cast<const volatile uint32_t*>(&mail->count);
+      const uint32_t info = *reinterpret_cast<const volatile uint32_t*>(&mail->info);
+      n = min(cnt, c.cap_rec);
+      if (info & 1u) fl = ZEN_PEER_OVERFLOW;
     } else {
       fl = ZEN_TIMEOUT;
     }
@@ -521,7 +524,7 @@ zen_owner_reduce_kernel(const ZenSparseCtx c, int src_begin, int src_end, int al
 // ---------------------------------------------------------------------------------------------
 // K3: one warp per 1024-slot chunk: compact the chunk's touched slots into the warp's shared-memory
 // staging area and push the run -- values, and COO slots or bitmap words + the chunk's value offset --
-// to every peer.  Room in this owner's payload is reserved per CTA step (16 chunks) with one atomic;
+// to every peer.  Room in this owner's payload is reserved per CTA step (8 to 32 chunks) with one atomic;
 // runs start on 8-value boundaries, so every push is a 16-byte vector store.  Chunks may land in the
 // payload in any order: the consumer finds a chunk's values through its offset (bitmap) or does not
 // care (COO).
@@ -536,14 +539,15 @@ __device__ __forceinline__ void zen_multimem_st4(void* mc_addr, uint32_t v) {
   asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
 }
 
-#define K3_CPW 2                                          // chunks per warp and step
+#define K3_CPW 4                                          // chunks per warp and step
 #define K3_CPS (K3_WARPS * K3_CPW)                        // chunks per CTA step: one reservation in the payload for all of them
 
 template <typename T>
 __global__ void __launch_bounds__(K3_WARPS * 32)
-zen_gather_push_kernel(const ZenSparseCtx c) {
+zen_gather_push_kernel(const ZenSparseCtx c, int cpw) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // cpw = chunks per warp and step (1 .. K3_CPW), chosen by the launcher so that the steps fill one wave of CTAs
   // per-warp staging of one chunk: up to 1024 slot ids and values (plus padding to a whole 16-byte vector)
   uint32_t* s_idx = reinterpret_cast<uint32_t*>(smem_raw) + warp * 1032;
   T* s_val = reinterpret_cast<T*>(smem_raw + K3_WARPS * 1032 * 4) + warp * 1032;
@@ -566,19 +570,20 @@ zen_gather_push_kernel(const ZenSparseCtx c) {
   uint32_t local_status = 0;
   char* mc = c.mc;
   const bool no_bitmap = c.cursors[ZEN_MAX_RANKS + 3] != 0u;            // the reduce kept no bitmap: touched = nonzero sum
-  const uint32_t nsteps = (c.nchunks + K3_CPS - 1) / K3_CPS;
+  const uint32_t cps = K3_WARPS * (uint32_t)cpw;                        // chunks per CTA step
+  const uint32_t nsteps = (c.nchunks + cps - 1) / cps;
 
   // One step = K3_CPS consecutive chunks, K3_CPW per warp.  The warps count their chunks' touched slots, the CTA
   // reserves room for all of them with ONE atomic on the payload cursor (atomics on one address are served one after
   // the other, so there must be few), then every warp compacts and pushes its chunks on its own.
   for (uint32_t step = blockIdx.x; step < nsteps; step += gridDim.x) {
-    const uint32_t ch_first = step * K3_CPS + warp * K3_CPW;
+    const uint32_t ch_first = step * cps + warp * cpw;
     uint32_t word[K3_CPW], incl[K3_CPW];
 #pragma unroll
     for (int j = 0; j < K3_CPW; ++j) {
       const uint32_t ch = ch_first + j, wi = ch * 32 + lane;
       word[j] = 0;
-      if (ch < c.nchunks && wi < c.nwords) {
+      if (j < cpw && ch < c.nchunks && wi < c.nwords) {
         if (no_bitmap) {
           const float4* ap4 = reinterpret_cast<const float4*>(c.acc + (size_t)wi * 32);
 #pragma unroll
@@ -602,18 +607,18 @@ zen_gather_push_kernel(const ZenSparseCtx c) {
         if (lane >= d) v += t;
       }
       incl[j] = v;
-      if (lane == 31) s_tot[warp * K3_CPW + j] = (v + K3_RUN_ALIGN - 1) & ~(K3_RUN_ALIGN - 1u);   // run length, padded
+      if (lane == 31 && j < cpw) s_tot[warp * cpw + j] = (v + K3_RUN_ALIGN - 1) & ~(K3_RUN_ALIGN - 1u);   // run length, padded
     }
     __syncthreads();
     // offsets of this warp's chunks inside the CTA's reservation: prefix over the padded run lengths (one per lane)
-    uint32_t pre = (lane < K3_CPS) ? s_tot[lane] : 0u;
+    uint32_t pre = ((uint32_t)lane < cps) ? s_tot[lane] : 0u;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       uint32_t t = __shfl_up_sync(0xffffffffu, pre, d);
       if (lane >= d) pre += t;
     }
     const uint32_t cta_total = __shfl_sync(0xffffffffu, pre, 31);
-    pre -= (lane < K3_CPS) ? s_tot[lane] : 0u;                           // exclusive
+    pre -= ((uint32_t)lane < cps) ? s_tot[lane] : 0u;                    // exclusive
     if (tid == 0) s_gbase = cta_total ? atomicAdd(&c.cursors[ZEN_MAX_RANKS + 2], cta_total) : 0u;
     __syncthreads();
     const uint32_t cta_base = s_gbase;
@@ -622,11 +627,11 @@ zen_gather_push_kernel(const ZenSparseCtx c) {
 #pragma unroll
     for (int j = 0; j < K3_CPW; ++j) {
       const uint32_t ch = ch_first + j, wi = ch * 32 + lane;
-      if (ch >= c.nchunks) continue;
+      if (j >= cpw || ch >= c.nchunks) continue;
       const uint32_t w0 = word[j], pc = __popc(w0);
       const uint32_t n = __shfl_sync(0xffffffffu, incl[j], 31);
       const uint32_t nres = (n + K3_RUN_ALIGN - 1) & ~(K3_RUN_ALIGN - 1u);
-      const uint32_t gbase = cta_base + __shfl_sync(0xffffffffu, pre, warp * K3_CPW + j);
+      const uint32_t gbase = cta_base + __shfl_sync(0xffffffffu, pre, warp * cpw + j);
       {
         // A lane whose word is non-empty appends its touched slots (in slot order) to the staging run and clears
         // them.  Sparse words are walked bit by bit (only the touched 32-byte sectors move); a warp with dense words
@@ -744,8 +749,10 @@ zen_gather_push_kernel(const ZenSparseCtx c) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ uint32_t s_fmt[ZEN_MAX_RANKS];
   const int tid = threadIdx.x, lane = tid & 31;
+  T* tile = reinterpret_cast<T*>(smem_raw) + (tid >> 5) * 1024;       // this warp's 1024-element staging tile
   const uint32_t epoch = zen_epoch(c);
   uint32_t local_status = 0;
   if (tid < c.nranks) {
@@ -798,9 +805,14 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
     }
     const uint32_t woff = coff + incl - __popc(word);
     const uint32_t n_chunk = __shfl_sync(0xffffffffu, incl, 31);
-    if (G == 64u && n_chunk <= 160u) {
-      // Sparse chunk (the usual case below ~15 % union density): write the chunk's sixteen 64-element blocks as zeros
-      // with wide stores, then drop the few values in with narrow ones.  Lane j < 16 finds where block j lives.
+    (void)n_chunk;
+    if (G == 64u) {
+      // Assemble the chunk's sixteen 64-element blocks in this warp's shared-memory tile (zeros, then the values at
+      // their slots) and write each block out with full 16-byte vectors: the memory system sees whole lines, however
+      // few or many values the chunk holds.  Lane j < 16 finds where block j lives in the output.
+      constexpr int NV = 1024 * sizeof(T) / 16 / 32;      // 16-byte vectors per lane in the tile (4 or 8)
+      constexpr int VPB = 64 * sizeof(T) / 16;            // vectors per block (8 or 16)
+      constexpr int EPV = 16 / sizeof(T);                 // elements per vector
       uint64_t eb = ~0ull;
       {
         const uint32_t slotb = ch * 1024 + (lane & 15) * 64;
@@ -809,32 +821,36 @@ zen_densify_kernel(const ZenSparseCtx c, T* __restrict__ out) {
           if (e < N) eb = e;
         }
       }
+      uint4* tv = reinterpret_cast<uint4*>(tile);
 #pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const uint64_t e0 = __shfl_sync(0xffffffffu, eb, it * 4 + (lane >> 3));
-        if (e0 == ~0ull) continue;
-        const uint64_t e = e0 + (lane & 7) * 8;
-        if (e + 8 <= N) {
-          reinterpret_cast<uint4*>(out + e)[0] = make_uint4(0u, 0u, 0u, 0u);
-          if (sizeof(T) == 4) reinterpret_cast<uint4*>(out + e)[1] = make_uint4(0u, 0u, 0u, 0u);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (e + i < N) out[e + i] = ZenVal<T>::from_bits(0u);
-        }
-      }
-      __syncwarp();                                        // the zeros of every lane are ordered before the values below
-      const uint64_t e0 = __shfl_sync(0xffffffffu, eb, lane >> 1);
-      if (e0 != ~0ull) {
-        const uint64_t e = e0 + (lane & 1) * 32;
+      for (int k = 0; k < NV; ++k) tv[k * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
+      __syncwarp();
+      {
         uint32_t w = word, at = woff;
+        T* mine = tile + lane * 32;
         while (w) {
           const int i = __ffs(w) - 1;
           w &= w - 1;
-          if (at < c.cap_g && e + i < N) out[e + i] = gval[at];
+          if (at < c.cap_g) mine[i] = gval[at];
           ++at;
         }
       }
+      __syncwarp();
+#pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        const int v = k * 32 + lane;
+        const uint64_t e0 = __shfl_sync(0xffffffffu, eb, v / VPB);
+        if (e0 == ~0ull) continue;
+        const uint64_t e = e0 + (uint64_t)(v % VPB) * EPV;
+        if (e + EPV <= N) {
+          *reinterpret_cast<uint4*>(out + e) = tv[v];
+        } else {
+#pragma unroll
+          for (int i = 0; i < EPV; ++i)
+            if (e + i < N) out[e + i] = tile[v * EPV + i];
+        }
+      }
+      __syncwarp();                                        // the tile is free for the next chunk
       word = nword; coff = ncoff; o = no; ch = nch;
       continue;
     }
@@ -1091,11 +1107,16 @@ int zen_owner_reduce(const ZenSparseCtx* c, int dtype, int deterministic, void* 
 // K3 (compact + push in one launch).
 int zen_gather_push(const ZenSparseCtx* c, int dtype, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
-  const int g3 = grid_for(c->nchunks, K3_CPS, sm_count() * 3);
+  // chunks per warp and step: as few as still let all steps run in one wave of CTAs (three per SM)
+  const int wave = sm_count() * 3;
+  int cpw = (int)((c->nchunks + (uint32_t)(K3_WARPS * wave) - 1) / (uint32_t)(K3_WARPS * wave));
+  if (cpw < 1) cpw = 1;
+  if (cpw > K3_CPW) cpw = K3_CPW;
+  const int g3 = grid_for(c->nchunks, K3_WARPS * cpw, wave);
   DISPATCH_DTYPE(dtype, {
     const size_t smem = (size_t)K3_WARPS * 1032 * (4 + sizeof(T));
     ZEN_CUDA_CHECK_RET(cudaFuncSetAttribute(zen_gather_push_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    zen_gather_push_kernel<T><<<g3, K3_WARPS * 32, smem, st>>>(*c);
+    zen_gather_push_kernel<T><<<g3, K3_WARPS * 32, smem, st>>>(*c, cpw);
   });
   return (int)cudaGetLastError();
 }
@@ -1105,7 +1126,11 @@ int zen_densify(const ZenSparseCtx* c, void* out, int dtype, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const uint64_t units = (uint64_t)c->nranks * c->nchunks;
   const int g1 = grid_for(units, 8, sm_count() * 8);
-  DISPATCH_DTYPE(dtype, zen_densify_kernel<T><<<g1, 256, 0, st>>>(*c, (T*)out));
+  DISPATCH_DTYPE(dtype, {
+    const size_t smem = 8 * 1024 * sizeof(T);                        // one staging tile per warp
+    ZEN_CUDA_CHECK_RET(cudaFuncSetAttribute(zen_densify_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    zen_densify_kernel<T><<<g1, 256, smem, st>>>(*c, (T*)out);
+  });
   if (c->fmt_mode != ZEN_FMT_BITMAP) {
     DISPATCH_DTYPE(dtype, zen_densify_coo_kernel<T><<<sm_count() * 4, 256, 0, st>>>(*c, (T*)out));
   }

@@ -21,12 +21,14 @@ from .reducer import ZenDDP
 class HybridParallelPlugin:
     def __init__(self, tp_size: int = 1, pp_size: int = 1, precision: str = "bf16", ddp_bucket_cap_mb: float = 25,
                  sparse_embedding: bool = True, overlap: bool = True, enable_sequence_parallelism: bool = False,
-                 sparse_embedding_under_tp: bool = False):
+                 sparse_embedding_under_tp: bool = False, dense_transport: str = "nccl"):
         self.tp_size, self.pp_size, self.precision = tp_size, pp_size, precision
         self.enable_sequence_parallelism = enable_sequence_parallelism    # same switch as ColossalAI's plugin
         # row-sparse synchronisation of the vocabulary-sharded embedding gradient over the DP group when TP > 1
         self.sparse_embedding_under_tp = sparse_embedding_under_tp
         self.ddp_bucket_cap_mb = ddp_bucket_cap_mb
+        # dense buckets: "nccl" (library all-reduce) or "nvls" (this library's multimem kernel through the NVSwitch)
+        self.dense_transport = dense_transport
         self.sparse_embedding = sparse_embedding
         self.overlap = overlap
         self.pg_mesh = ProcessGroupMesh(tp_size, pp_size)
@@ -84,7 +86,8 @@ class Booster:
                 wte.zen_sparse_only = True
             else:
                 wte.zen_early = True         # tied: only the LM-head product is left in the dense gradient
-        ddp = ZenDDP(model, pl.dp_group, pl.ddp_bucket_cap_mb, emb_sync, overlap=pl.overlap)
+        ddp = ZenDDP(model, pl.dp_group, pl.ddp_bucket_cap_mb, emb_sync, overlap=pl.overlap,
+                     dense_transport=pl.dense_transport)
         if emb_sync is not None:
             emb_sync.prepare(pl.device)
         if optimizer is not None:

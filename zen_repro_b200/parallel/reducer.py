@@ -45,10 +45,12 @@ class GradBucket:
 
 
 class _Bucket:
-    def __init__(self, index, params, dtype, device):
+    def __init__(self, index, params, dtype, device, storage=None):
         self.index, self.params = index, params
         sizes = [(p.numel() + 7) // 8 * 8 for p in params]          # 16-byte aligned views for bf16
-        self.buffer = torch.zeros(sum(sizes), dtype=dtype, device=device)
+        self.numel = sum(sizes)
+        self.arena_off = None                                        # byte offset in the multicast arena, when it lives there
+        self.buffer = storage if storage is not None else torch.zeros(self.numel, dtype=dtype, device=device)
         self.views, off = [], 0
         for p, s in zip(params, sizes):
             self.views.append(self.buffer[off:off + p.numel()].view(p.shape))
@@ -60,7 +62,7 @@ class _Bucket:
 
 class ZenDDP(nn.Module):
     def __init__(self, module: nn.Module, process_group=None, bucket_cap_mb: float = 25.0, embedding_sync=None,
-                 overlap: bool = True):
+                 overlap: bool = True, dense_transport: str = "nccl"):
         super().__init__()
         self.module = module
         self.process_group = process_group
@@ -78,21 +80,44 @@ class ZenDDP(nn.Module):
         # leads the bucket order in a bucket of its own, so its all-reduce overlaps the rest of backward instead of
         # waiting at the end with the first layers' parameters.
         early = [p for p in dense if getattr(p, "zen_early", False)]
-        for p in early:
-            self.buckets.append(_Bucket(len(self.buckets), [p], p.dtype, self.device))
+        groups: list[tuple[list, torch.dtype]] = [([p], p.dtype) for p in early]
         cur, cur_bytes, cur_dtype = [], 0, None
         for p in reversed(dense):
             if getattr(p, "zen_early", False):
                 continue
             nbytes = p.numel() * p.element_size()
             if cur and (cur_bytes + nbytes > cap or p.dtype != cur_dtype):
-                self.buckets.append(_Bucket(len(self.buckets), cur, cur_dtype, self.device))
+                groups.append((cur, cur_dtype))
                 cur, cur_bytes = [], 0
             cur.append(p)
             cur_bytes += nbytes
             cur_dtype = p.dtype
         if cur:
-            self.buckets.append(_Bucket(len(self.buckets), cur, cur_dtype, self.device))
+            groups.append((cur, cur_dtype))
+        # "nvls": the buckets live in one multicast-mapped symmetric region and are reduced through the NVSwitch by this
+        # library's own kernel on a few CTAs; otherwise plain device memory and the library all-reduce
+        self.arena = None
+        if (dense_transport == "nvls" and self.world > 1 and self.device.type == "cuda"
+                and all(dt in (torch.bfloat16, torch.float32) for _, dt in groups)):
+            from .nvls_allreduce import MulticastArena
+
+            sizes = [sum((p.numel() + 7) // 8 * 8 for p in ps) * torch.empty(0, dtype=dt).element_size() for ps, dt in groups]
+            offs, off = [], 0
+            for sz in sizes:
+                offs.append(off)
+                off += (sz + 255) // 256 * 256
+            try:
+                self.arena = MulticastArena(off, process_group)
+            except Exception as ex:                               # no multicast on this fabric: keep the library path
+                self.arena, self.arena_error = None, f"{type(ex).__name__}: {ex}"
+        for i, (ps, dt) in enumerate(groups):
+            storage = None
+            if self.arena is not None:
+                storage = self.arena.view(offs[i], sum((p.numel() + 7) // 8 * 8 for p in ps), dt)
+            b = _Bucket(len(self.buckets), ps, dt, self.device, storage)
+            if self.arena is not None:
+                b.arena_off = offs[i]
+            self.buckets.append(b)
         self._bucket_of, self._view_of = {}, {}
         for b in self.buckets:
             for p, v in zip(b.params, b.views):
@@ -108,7 +133,19 @@ class ZenDDP(nn.Module):
         self._cuda = self.device.type == "cuda"
         self.comm_stream = torch.cuda.Stream() if (self._cuda and overlap) else None
         self._launched = 0
+        self._nccl = self.world > 1 and self._cuda and dist.get_backend(process_group) == "nccl"
         self.require_sync = True
+        self.timeline = None             # set to a list to collect per-step CUDA events (see exposed_comm_us)
+
+    def exposed_comm_us(self) -> list[dict]:
+        """Per recorded step (``timeline = []`` switches recording on; eager steps only): microseconds between the end of
+        backward on the compute stream and the end of the bucket communication on the side stream (the part of the
+        dense synchronisation that backward did not hide), and up to the end of the row-sparse embedding exchange."""
+        torch.cuda.synchronize()
+        out = []
+        for a, b, c in self.timeline or []:
+            out.append({"dense_exposed_us": max(0.0, a.elapsed_time(b) * 1e3), "sync_exposed_us": max(0.0, a.elapsed_time(c) * 1e3)})
+        return out
 
     # ---- torch DDP surface --------------------------------------------------------------------
     def forward(self, *a, **kw):
@@ -132,9 +169,15 @@ class ZenDDP(nn.Module):
     # ---- reduction --------------------------------------------------------------------------------
     def _default_hook(self, _state, bucket: GradBucket):
         buf = bucket.buffer()
-        if self.world > 1:
-            buf.div_(self.world)
-            dist.all_reduce(buf, group=self.process_group)
+        b = self.buckets[bucket.index()]
+        if self.world > 1 and self.arena is not None and b.arena_off is not None and buf.data_ptr() == b.buffer.data_ptr():
+            self.arena.allreduce_(b.arena_off, b.numel * buf.element_size(), buf.dtype, 1.0 / self.world)
+        elif self.world > 1:
+            if self._nccl:
+                dist.all_reduce(buf, op=dist.ReduceOp.AVG, group=self.process_group)   # the mean inside the collective
+            else:
+                buf.div_(self.world)
+                dist.all_reduce(buf, group=self.process_group)
         from .hooks import _Ready
 
         return _Ready(buf)
@@ -202,6 +245,13 @@ class ZenDDP(nn.Module):
                             b.buffer.copy_(res.reshape(-1))
                         b.future = None
             if used:                      # join only a stream that was forked from this one during the step
+                if self.timeline is not None:
+                    # backward has been enqueued up to here; what the communication stream still has to do after this
+                    # point is the exposed (not overlapped) part of the gradient synchronisation
+                    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+                    ev[0].record(torch.cuda.current_stream())
+                    ev[1].record(self.comm_stream)
+                    self._timeline_pending = ev
                 torch.cuda.current_stream().wait_stream(self.comm_stream)
                 self._comm_used = False
             if hasattr(self.module, "sync_replicated_grads"):
@@ -210,6 +260,11 @@ class ZenDDP(nn.Module):
                 emb = self.embedding_sync
                 target = emb.target_param
                 emb.sync_into(target.grad, zero_first=getattr(target, "zen_sparse_only", False))
+            if self.timeline is not None and getattr(self, "_timeline_pending", None) is not None:
+                ev = self._timeline_pending
+                ev[2].record(torch.cuda.current_stream())          # after the row synchronisation as well
+                self.timeline.append(ev)
+                self._timeline_pending = None
         for b in self.buckets:
             b.pending = len(b.params)
             b.launched = False

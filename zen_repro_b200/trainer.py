@@ -47,6 +47,7 @@ class TrainConfig:
     heartbeat_s: float = 0.0          # > 0: host heartbeat between ranks, checked before every step (PeerLost is raised)
     cuda_graph: bool = False          # capture forward + backward + sync + optimizer once, then replay it every step
     graph_warmup: int = 2             # real steps launched from the host before the capture
+    dense_transport: str = "nccl"     # dense buckets: "nccl" (library all-reduce) or "nvls" (own multimem kernel through the NVSwitch)
     status_mirror: bool = True        # mirror the kernels' status words to the host every step (read one step late)
     on_sync_error: str = "recover"    # "recover": resync the replicas and switch the failing path to its library form;
                                       # "raise": stop with SyncStatusError
@@ -64,7 +65,8 @@ class Trainer:
         self.plugin = HybridParallelPlugin(tp_size=cfg.tp, pp_size=1, precision=cfg.precision,
                                            ddp_bucket_cap_mb=cfg.bucket_cap_mb,
                                            sparse_embedding=cfg.sparse_embedding and cfg.method == 0, overlap=cfg.overlap,
-                                           sparse_embedding_under_tp=cfg.sparse_embedding_under_tp)
+                                           sparse_embedding_under_tp=cfg.sparse_embedding_under_tp,
+                                           dense_transport="nccl" if cfg.dense_transport == "auto" else cfg.dense_transport)
         self.booster = Booster(self.plugin)
         self.device = self.plugin.device
         mc = get_config(cfg.model, num_layers=cfg.num_layers, num_kv_heads=cfg.kv_heads,
@@ -114,6 +116,8 @@ class Trainer:
             ws = getattr(self.model.unwrap(), "tp_ws", None)
             if ws is not None:
                 self.health.add("tp_fused", ws.status)
+            if getattr(self.model.module, "arena", None) is not None:
+                self.health.add("dense_nvls", self.model.module.arena.status)
         self._graph = None
         self.graph_launches_per_step = 0
         self._static_ids = self._static_loss = None
@@ -198,6 +202,8 @@ class Trainer:
                 self.model.module.embedding_sync.force_library = True
             elif name == "tp_fused":
                 self.model.unwrap().disable_fused_tp()
+            elif name == "dense_nvls":
+                self.model.module.arena = None            # the buckets stay where they are; the library all-reduce takes over
             elif getattr(self, "_hook", None) is not None:
                 self._hook.state["force_dense"] = True
         self.health.clear()
@@ -262,6 +268,9 @@ class Trainer:
         ws = getattr(self.model.unwrap(), "tp_ws", None)
         if ws is not None:
             out["tp_fused"] = int(ws.check())
+        arena = getattr(self.model.module, "arena", None)
+        if arena is not None:
+            out["dense_nvls"] = int(arena.check())
         bad = {k: v for k, v in out.items() if v}
         if bad and raise_on_error:
             raise RuntimeError(f"kernel status words report errors: {bad} (1 = record overflow, 2 = gather overflow, "
