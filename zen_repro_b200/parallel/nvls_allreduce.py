@@ -33,7 +33,7 @@ class MulticastArena:
     def __init__(self, nbytes: int, group=None, wait_ms: float = 30000.0, ctas: int | None = None):
         import os
 
-        ctas = ctas if ctas is not None else int(os.environ.get("ZEN_NVLS_CTAS", "8"))
+        ctas = ctas if ctas is not None else int(os.environ.get("ZEN_NVLS_CTAS", "16"))
         self.group = group if group is not None else dist.group.WORLD
         self.data_bytes = (nbytes + 255) // 256 * 256
         self.region = TorchSymmetric(self.data_bytes + FLAG_BYTES, self.group)

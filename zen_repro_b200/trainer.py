@@ -29,7 +29,7 @@ class TrainConfig:
     tp: int = 1
     method: int = 0                   # 0 dense buckets (+ sparse embedding rows); 1/2/3 ZEN top-k hook on all buckets
     top_k: float = 1.0
-    bucket_cap_mb: float = 32.0
+    bucket_cap_mb: float = 64.0
     sparse_embedding: bool = True
     grad_checkpoint: bool = False
     lr: float = 1e-3
@@ -47,7 +47,8 @@ class TrainConfig:
     heartbeat_s: float = 0.0          # > 0: host heartbeat between ranks, checked before every step (PeerLost is raised)
     cuda_graph: bool = False          # capture forward + backward + sync + optimizer once, then replay it every step
     graph_warmup: int = 2             # real steps launched from the host before the capture
-    dense_transport: str = "nccl"     # dense buckets: "nccl" (library all-reduce) or "nvls" (own multimem kernel through the NVSwitch)
+    dense_transport: str = "auto"     # dense buckets: "nccl" (library all-reduce), "nvls" (own multimem kernel through the
+                                      # NVSwitch), "auto" = nvls for pure data-parallel runs when the fabric has multicast
     status_mirror: bool = True        # mirror the kernels' status words to the host every step (read one step late)
     on_sync_error: str = "recover"    # "recover": resync the replicas and switch the failing path to its library form;
                                       # "raise": stop with SyncStatusError
@@ -66,7 +67,8 @@ class Trainer:
                                            ddp_bucket_cap_mb=cfg.bucket_cap_mb,
                                            sparse_embedding=cfg.sparse_embedding and cfg.method == 0, overlap=cfg.overlap,
                                            sparse_embedding_under_tp=cfg.sparse_embedding_under_tp,
-                                           dense_transport="nccl" if cfg.dense_transport == "auto" else cfg.dense_transport)
+                                           dense_transport=("nvls" if cfg.tp == 1 else "nccl") if cfg.dense_transport == "auto"
+                                           else cfg.dense_transport)
         self.booster = Booster(self.plugin)
         self.device = self.plugin.device
         mc = get_config(cfg.model, num_layers=cfg.num_layers, num_kv_heads=cfg.kv_heads,
