@@ -147,3 +147,28 @@ def test_pair_kernel_with_128_wide_tiles(M, N, K):
         assert G.gemm_error() == 0
     finally:
         _native.lib().zen_gemm2_force_bn(old)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 192, 64), (8192, 768, 768), (8192, 768, 3072), (1000, 1304, 200), (512, 960, 4096)])
+def test_pair_kernel_with_192_wide_tiles(M, N, K):
+    """The CTA-pair kernel with 256 x 192 tiles (K-major B only; picked when 192-wide tiles need fewer tile-widths of
+    time than 256-wide ones, e.g. 8192 x 768 outputs), K-major and MN-major A, bias, fp32 accumulate output."""
+    from zen_repro_b200 import _native
+
+    old = _native.lib().zen_gemm2_force_bn(192)
+    try:
+        torch.manual_seed(8)
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        w = torch.randn(N, K, device="cuda").bfloat16()               # [N, K]: K-major B for gemm_nt
+        at = torch.randn(K, M, device="cuda").bfloat16()
+        bias = torch.randn(N, device="cuda").bfloat16()
+        _check(G.gemm_nt(a, w, bias=bias, bn=512), a.float() @ w.float().t() + bias.float(), K)
+        acc = torch.ones(M, N, device="cuda", dtype=torch.float32)
+        G.gemm_nt(a, w, out=acc, accumulate=True, bn=512)
+        _check(acc, a.float() @ w.float().t() + 1.0, K)
+        # MN-major B falls back to 256-wide tiles under the same setting and must stay correct
+        _check(G.gemm_nn(a, w.t().contiguous(), bn=512), a.float() @ w.float().t(), K)
+        _check(G.gemm_tn(at, w.t().contiguous(), bn=512), at.float().t() @ w.float().t(), K)
+        assert G.gemm_error() == 0
+    finally:
+        _native.lib().zen_gemm2_force_bn(old)

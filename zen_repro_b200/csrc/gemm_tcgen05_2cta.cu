@@ -22,7 +22,8 @@ constexpr int BM2 = 128;          // rows per CTA (256 per pair)
 constexpr int BK2 = 64;
 template <int BN> struct PairCfg {
   static constexpr int BNH = BN / 2;
-  static constexpr int STAGES = (BN == 256) ? 6 : 8;
+  static constexpr int STAGES = (BN >= 192) ? 6 : 8;
+  static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;        // two accumulators; the allocation is a power of two
   static constexpr int STAGE_BYTES = 128 * 64 * 2 + BNH * 64 * 2;      // A rows of this CTA + its half of B
 };
 constexpr int MAX_SPLITS = 3;      // K slices per output tile at most (the last slice to arrive holds the others' partials in registers)
@@ -130,7 +131,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 1) tmem_alloc_pair(tmem_slot, 2 * BN2);
+  if (warp == 1) tmem_alloc_pair(tmem_slot, PairCfg<BN2>::TMEM_COLS);
   fence_before();
   __syncthreads();
   cluster_sync_all();                            // both CTAs' barriers exist before anyone signals them
@@ -466,7 +467,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   cluster_sync_all();                            // the peer may still be reading this CTA's shared memory / barriers
   if (warp == 1) {
     fence_after();
-    tmem_dealloc_pair(tmem_base, 2 * BN2);
+    tmem_dealloc_pair(tmem_base, PairCfg<BN2>::TMEM_COLS);
   }
 }
 
@@ -495,8 +496,14 @@ int g_force_bn = 0;
 // (96 tiles = 1.3 waves), but measured on 8192 x 768 outputs it lost (662 vs 858 TFLOP/s at K = 3072, 410 vs 472 at
 // K = 768): with half the columns per tile the A rows are fetched twice as often and the kernel is bound by that
 // traffic, not by the idle third of the second wave.  It is therefore only taken when forced.
-int pick_pair_bn(int M, int N) {
+// 192-wide tiles (K-major B only: its half of 96 rows is one TMA box; an MN-major half would need one and a half
+// 64-column boxes) exist for the same 1.3-wave outputs: 8192 x 768 is 96 tiles of 256 = two waves of full tiles, but 128
+// tiles of 192 = two waves of three-quarter tiles.  Measured, they gain nothing either (857.9 TFLOP/s both at
+// 8192 x 768 x 3072): a 256 x 256 x 64 step takes 0.47 us here against 0.28 us of tensor-core time, i.e. the main loop
+// is bound by the operand traffic from L2, which per FLOP is higher for the narrower tile.  Taken only when forced.
+int pick_pair_bn(int M, int N, int b_mn, int splits) {
   (void)M; (void)N;
+  if (g_force_bn == 192) return (!b_mn && splits == 1) ? 192 : 256;
   return g_force_bn ? g_force_bn : 256;
 }
 
@@ -534,7 +541,7 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
     const uint64_t units = (uint64_t)((M + 255) / 256) * ((N + 255) / 256) * (uint64_t)splits;
     if (units > (uint64_t)(zen_tmap::sm_count() / 2)) { splits = 1; kb_per = nkb; }
   }
-  const int bn = (splits > 1) ? 256 : pick_pair_bn(M, N);
+  const int bn = (splits > 1) ? 256 : pick_pair_bn(M, N, b_mn, splits);
   if (splits > 1) {
     const uint64_t tiles = (uint64_t)((M + 255) / 256) * ((N + 255) / 256);
     if (!ws || !counters || ws_floats < tiles * splits * 2 * BM2 * 256 || (uint64_t)n_counters < tiles * 16) return -4;
@@ -570,6 +577,10 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
     return launch2<true, true, BN_>(ta, tb, tc, p, st);                         \
   } while (0)
   if (bn == 128) LAUNCH2(128);
+  if (bn == 192) {                                             // K-major B only (see pick_pair_bn)
+    if (!a_mn) return launch2<false, false, 192>(ta, tb, tc, p, st);
+    return launch2<true, false, 192>(ta, tb, tc, p, st);
+  }
   LAUNCH2(256);
 #undef LAUNCH2
 }
@@ -577,7 +588,7 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
 // 0 = choose the N tile per call, 128 / 256 = force it (tests, measurements); returns the previous setting.
 int zen_gemm2_force_bn(int bn) {
   const int old = g_force_bn;
-  if (bn == 0 || bn == 128 || bn == 256) g_force_bn = bn;
+  if (bn == 0 || bn == 128 || bn == 192 || bn == 256) g_force_bn = bn;
   return old;
 }
 
