@@ -96,3 +96,24 @@ def test_split_k_choice_is_limited_to_weight_gradient_shapes():
     assert G.split_k_choice(768, 2304, 1024) == 1          # short K
     assert G.split_k_choice(4096, 4096, 8192) == 1
     assert G.split_k_choice(100, 2304, 8192) == 1          # too narrow for a 256-row pair tile
+
+
+def test_packed_bf16_threshold_pretest_matches_the_exact_compare():
+    """The partition kernel's cheap per-vector test for bf16 (both halves of a 32-bit word against the threshold with one
+    add and one mask, `Raw8<bf16>::hit` in csrc/sparse_kernels.cu), restated on integers: it must never reject a value
+    that the exact compare |x| >= thr keeps, and must reject everything below the threshold rounded up to bf16."""
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    for thr in [0.0, 1e-30, 0.003, 0.5, 0.50001, 1.0, 3.1e38, float("inf")]:
+        tbits = max(int(np.float32(thr).view(np.uint32)), 1)
+        t16 = min((tbits + 0xFFFF) >> 16, 0x8000) or 1
+        addc = ((0x8000 - t16) * 0x00010001) & 0xFFFFFFFF
+        x16 = rng.integers(0, 1 << 16, size=4096, dtype=np.uint32)
+        x16[:8] = [0, 0x8000, 1, 0x3F00, 0x3F01, 0x7F80, 0xFF80, t16]          # +0, -0, tiny, 0.5, next, +inf, -inf, threshold
+        words = x16[0::2] | (x16[1::2] << 16)
+        got = (((words & 0x7FFF7FFF) + addc) & 0x80008000) != 0
+        mag32 = (x16 & 0x7FFF).astype(np.uint64) << 16
+        exact = mag32 >= tbits                                                 # the kernel's keep test on magnitude bits
+        want = exact[0::2] | exact[1::2]
+        assert np.array_equal(got, want), thr

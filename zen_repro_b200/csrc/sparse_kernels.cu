@@ -91,6 +91,14 @@ template <> struct Raw8<float> {
     for (int i = 0; i < 8; ++i) w[i] = 0u;
   }
   __device__ __forceinline__ bool any() const { return ((w[0] | w[1] | w[2] | w[3] | w[4] | w[5] | w[6] | w[7]) & 0x7fffffffu) != 0u; }
+  // cheap test "some element reaches the threshold" (tbits as in keep_mask; hint unused for fp32)
+  __device__ __forceinline__ bool hit(uint32_t tbits, uint32_t) const {
+    if (tbits <= 1u) return any();
+    bool r = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r |= (w[i] & 0x7fffffffu) >= tbits;
+    return r;
+  }
   // select chains instead of dynamic indexing keep the vector in registers
   __device__ __forceinline__ uint32_t bits(int i) const {
     const uint32_t a = (i & 1) ? w[1] : w[0], b = (i & 1) ? w[3] : w[2], c = (i & 1) ? w[5] : w[4], d = (i & 1) ? w[7] : w[6];
@@ -136,6 +144,15 @@ template <typename T16> struct Raw8Half {
 };
 template <> struct Raw8<__nv_bfloat16> : Raw8Half<__nv_bfloat16> {
   __device__ __forceinline__ float value(int i) const { return __uint_as_float(bits(i) << 16); }
+  // cheap test "some element reaches the threshold": both halves of a word at once.  addc = (0x8000 - t16) in each
+  // half, t16 the threshold's magnitude bits rounded up to bf16: a half's bit 15 comes out set exactly when its
+  // 15-bit magnitude is >= t16 (no carry crosses the halves, the sums stay below 0x10000).
+  __device__ __forceinline__ bool hit(uint32_t, uint32_t addc) const {
+    uint32_t acc = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc |= ((w[k] & 0x7fff7fffu) + addc) & 0x80008000u;
+    return acc != 0u;
+  }
   __device__ __forceinline__ uint32_t keep_mask(uint32_t tbits, bool use_thr, float) const {
     uint32_t m = 0;
 #pragma unroll
@@ -149,6 +166,7 @@ template <> struct Raw8<__nv_bfloat16> : Raw8Half<__nv_bfloat16> {
 };
 template <> struct Raw8<__half> : Raw8Half<__half> {
   __device__ __forceinline__ float value(int i) const { return __half2float(__ushort_as_half((unsigned short)bits(i))); }
+  __device__ __forceinline__ bool hit(uint32_t, uint32_t) const { return any(); }     // the threshold is applied in keep_mask
   __device__ __forceinline__ uint32_t keep_mask(uint32_t, bool use_thr, float thr) const {
     uint32_t m = 0;
 #pragma unroll
@@ -202,6 +220,9 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
   const bool use_thr = thr_ptr != nullptr;
   const float thr = use_thr ? fmaxf(*thr_ptr, 0.f) : 0.f;
   const uint32_t tbits = use_thr ? max(__float_as_uint(thr), 1u) : 1u; // magnitude bits an element must reach to be kept
+  // the same threshold for the cheap per-vector test of 16-bit types: rounded up to 16 bits, as an addend per half
+  const uint32_t t16 = min((tbits + 0xffffu) >> 16, 0x8000u) == 0u ? 1u : min((tbits + 0xffffu) >> 16, 0x8000u);
+  const uint32_t addc = (0x8000u - t16) * 0x00010001u;
   const uint64_t N = c.numel;
   const uint32_t nst = (uint32_t)((N + EPS - 1) / EPS);               // stages of the whole bucket
   const uint64_t copy_end = (N * sizeof(T)) & ~15ull;                 // bytes that bulk copies may fetch
@@ -392,7 +413,7 @@ zen_partition_push_kernel(const ZenSparseCtx c, const T* __restrict__ g, const f
       const bool last_it = (it + gridDim.x >= nst);
 #pragma unroll
       for (int u = 0; u < VPL; ++u) {
-        const bool has = v[u].any();
+        const bool has = v[u].hit(tbits, addc);            // with a threshold most vectors of a dense bucket stop here
         const uint32_t bal = __ballot_sync(0xffffffffu, has);
         if (!bal) continue;
         if (has) {
