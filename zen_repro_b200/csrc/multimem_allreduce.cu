@@ -4,7 +4,7 @@
 // reduction itself costs no SM arithmetic and each byte crosses this GPU's links once in each
 // direction, so a handful of CTAs saturates the links and the rest of the GPU keeps running backward.
 // (The library ring all-reduce that this replaces on the data-parallel path occupied 32 SMs at two
-// GPUs.)  Two flag rounds bracket the data movement: "my bucket is complete" before anybody pulls, "my
+// GPUs.)  Two flag exchanges bracket the data movement: "my bucket is complete" before anybody pulls, "my
 // stores have landed and I have finished pulling from you" before anybody's kernel ends.  Every wait
 // is bounded and reports through a status word.
 //
@@ -20,7 +20,7 @@ struct ZenMcArCtx {
   uint32_t pad;
   uint64_t wait_ns;
   char* mc;                    // multicast alias of the region
-  uint32_t* flags[ZEN_MAX_RANKS];   // per rank: uint32 [2 rounds][ZEN_MAX_RANKS sources]
+  uint32_t* flags[ZEN_MAX_RANKS];   // per rank: uint32 [2 exchanges][ZEN_MAX_RANKS sources]
   const uint32_t* epoch_dev;   // optional device-resident call counter (bumped by zen_sparse_epoch_bump before the call)
   uint32_t* status;            // device word, ZEN_TIMEOUT is OR-ed in when a wait runs out
   uint32_t* done;              // device word, CTA arrival counter (left at zero)
@@ -57,7 +57,7 @@ zen_multimem_allreduce_kernel(const ZenMcArCtx c, uint64_t byte_off, uint64_t nv
   __shared__ uint32_t s_ok, s_last;
   const uint32_t epoch = c.epoch_dev ? *c.epoch_dev : c.epoch;
   const int tid = threadIdx.x;
-  // round 0: tell every rank that this rank's bucket is complete (the kernels that wrote it ran earlier on this
+  // first flag exchange: tell every rank that this rank's bucket is complete (the kernels that wrote it ran earlier on this
   // stream), then wait until every rank has said so
   if (blockIdx.x == 0 && tid < c.nranks) zen_st_release_sys(c.flags[tid] + c.rank, epoch);
   if (tid == 0) s_ok = 1u;
@@ -92,7 +92,7 @@ zen_multimem_allreduce_kernel(const ZenMcArCtx c, uint64_t byte_off, uint64_t nv
       }
     }
   }
-  // round 1: when every CTA of this rank has stored its part, tell every rank; the last CTA stays until every rank
+  // second flag exchange: when every CTA of this rank has stored its part, tell every rank; the last CTA stays until every rank
   // has said the same, so that this kernel's end means "the whole bucket is reduced here, and nobody still reads mine"
   __syncthreads();
   if (tid == 0) {

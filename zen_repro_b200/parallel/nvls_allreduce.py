@@ -18,7 +18,7 @@ from .. import _native
 from ..runtime.symmetric import TorchSymmetric
 
 MAX_RANKS = 8
-FLAG_BYTES = 256                      # two rounds x eight sources x four bytes, rounded up
+FLAG_BYTES = 256                      # two exchanges x eight sources x four bytes, rounded up
 
 
 class _McArCtx(ctypes.Structure):
