@@ -733,26 +733,44 @@ __global__ void embed_mark_kernel(const int64_t* __restrict__ ids, int32_t* __re
   }
 }
 
+// One CTA; warp w owns the contiguous range [w * per, (w + 1) * per) of the vocabulary and walks it 32 flags at a
+// time (coalesced), first counting with ballots, then, after a scan over the 32 warp totals, handing out compact ids
+// in ascending row order.
 __global__ void __launch_bounds__(1024)
 embed_compact_kernel(int32_t* __restrict__ flag_cid, int32_t* __restrict__ rows, int32_t* __restrict__ count, int vocab) {
-  __shared__ uint32_t part[1024];
-  const int per = (vocab + 1023) / 1024;
-  const int b = threadIdx.x * per, e = min(vocab, b + per);
+  __shared__ uint32_t wtot[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int per = ((vocab + 31) / 32 + 31) / 32 * 32;                 // per-warp range, a multiple of 32
+  const int b = warp * per, e = min(vocab, b + per);
   uint32_t s = 0;
-  for (int i = b; i < e; ++i) s += flag_cid[i] != 0;
-  part[threadIdx.x] = s;
+  for (int i = b + lane; i < b + per; i += 32) {
+    const bool f = i < e && flag_cid[i] != 0;
+    s += __popc(__ballot_sync(0xffffffffu, f));
+  }
+  if (lane == 0) wtot[warp] = s;
   __syncthreads();
-  for (int d = 1; d < 1024; d <<= 1) {
-    uint32_t t = (threadIdx.x >= (unsigned)d) ? part[threadIdx.x - d] : 0u;
-    __syncthreads();
-    part[threadIdx.x] += t;
-    __syncthreads();
+  uint32_t pre = wtot[lane];                                          // every warp scans the 32 totals
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, pre, d);
+    if (lane >= d) pre += t;
   }
-  uint32_t run = part[threadIdx.x] - s;
-  for (int i = b; i < e; ++i) {
-    if (flag_cid[i] != 0) { flag_cid[i] = (int32_t)run; rows[run] = i; ++run; } else flag_cid[i] = -1;
+  const uint32_t total = __shfl_sync(0xffffffffu, pre, 31);
+  uint32_t run = __shfl_sync(0xffffffffu, pre, warp) - wtot[warp];    // exclusive offset of this warp
+  for (int i = b + lane; i < b + per; i += 32) {
+    const bool in = i < e;
+    const bool f = in && flag_cid[i] != 0;
+    const uint32_t bal = __ballot_sync(0xffffffffu, f);
+    if (f) {
+      const uint32_t u = run + __popc(bal & ((1u << lane) - 1u));
+      flag_cid[i] = (int32_t)u;
+      rows[u] = i;
+    } else if (in) {
+      flag_cid[i] = -1;
+    }
+    run += __popc(bal);
   }
-  if (threadIdx.x == 1023) *count = (int32_t)part[1023];
+  if (threadIdx.x == 0) *count = (int32_t)total;
 }
 
 template <typename T>

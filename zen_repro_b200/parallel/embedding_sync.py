@@ -28,6 +28,7 @@ class EmbeddingRowSync:
         self._pending = None
         self.deterministic = deterministic
         self.last_count = None
+        self.wait_ms = 30000.0         # bound of every wait on a peer (training: generous; tests construct engines with short ones)
         self.early = True              # start the row exchange from ``put`` (on a side stream) instead of from ``sync_into``
         self._stream = None
         self._started = False
@@ -63,7 +64,7 @@ class EmbeddingRowSync:
             from ..sparse.row_engine import RowSparseAllReduce
 
             self._engine = RowSparseAllReduce(self.vocab, self.d, self.max_rows, self.group, dtype=self.dtype,
-                                              deterministic=self.deterministic)
+                                              deterministic=self.deterministic, wait_ms=self.wait_ms)
 
     def sync_into(self, grad: torch.Tensor, zero_first: bool = False):
         if self._pending is None:

@@ -131,12 +131,13 @@ def verified_or_dense(out: torch.Tensor, status: int, masked: torch.Tensor, grou
 
 def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, engines: dict | None = None,
                        skip_first: bool = False, torch_future: bool = True, max_density: float | None = None,
-                       verify: bool = False):
+                       verify: bool = False, wait_ms: float = 30000.0):
     """Build the hook.  ``engines`` caches one CUDA ``SparseAllReduce`` per bucket size (create them with
     ``prepare_engines`` before training so that buffer exchange does not happen inside backward).  ``verify``: read the
     engine's status word after every bucket (one device synchronisation per bucket) and replace the result by the dense
-    all-reduce when a capacity overflow or an expired wait was reported; off by default, where the status is left for
-    ``Trainer.check_health``."""
+    all-reduce when a capacity overflow or an expired wait was reported; off by default, where the status travels through the
+    trainer's status mirror (read one step late) and ``Trainer.check_health``.  ``wait_ms`` bounds every wait on a peer:
+    generous for training (a rank may be late by a data-loading or first-step pause), tests pass short limits."""
     state = {"skip": skip_first, "engines": engines if engines is not None else {}}
     P = dist.get_world_size(dp_group) if dist.is_initialized() else 1
     density = max_density if max_density is not None else min(1.0, top_k / 100.0 * 2.0 + 0.01)
@@ -146,7 +147,7 @@ def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, e
         if eng is None and device.type == "cuda":
             from ..sparse.engine import SparseAllReduce
 
-            eng = SparseAllReduce(numel, dp_group, max_density=density, methods=(1, 2, 3))
+            eng = SparseAllReduce(numel, dp_group, max_density=density, methods=(1, 2, 3), wait_ms=wait_ms)
             state["engines"][numel] = eng
         return eng
 
