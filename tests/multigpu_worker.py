@@ -374,7 +374,32 @@ def check_nvls_dense_allreduce(rank, world, dev):
     print(f"OK nvls_dense rank{rank} {losses['nvls'][0]:.3f}->{losses['nvls'][-1]:.3f}", flush=True)
 
 
-CHECKS = {"nvls_dense": check_nvls_dense_allreduce, "b2b": check_sparse_back_to_back, "nvls": check_sparse_nvls, "verify": check_verify_fallback,
+def check_sample_exchange(rank, world, dev):
+    """Threshold samples exchanged through peer memory equal an NCCL all-gather, five calls in a row without host
+    synchronisation; the TP-aware threshold is then the same number on every rank of the group."""
+    from zen_repro_b200.parallel.hooks import SampleExchange, sampled_threshold
+
+    ns = 3001
+    ex = SampleExchange(None, ns, dev, wait_ms=5000.0)
+    xs = [torch.rand(ns, generator=torch.Generator().manual_seed(10 * i + rank)).to(dev) for i in range(5)]
+    got = [ex(x).clone() for x in xs]
+    torch.cuda.synchronize()
+    assert int(ex.status.item()) == 0
+    for x, g in zip(xs, got):
+        want = torch.empty(world * ns, device=dev)
+        dist.all_gather_into_tensor(want, x)
+        assert torch.equal(g, want)
+    t = torch.randn(200000, generator=torch.Generator().manual_seed(rank)).to(dev).bfloat16()
+    thr = sampled_threshold(t, 1.0, group=dist.group.WORLD).clone()
+    every = [torch.empty_like(thr) for _ in range(world)]
+    dist.all_gather(every, thr)
+    assert all(torch.equal(e, every[0]) for e in every) and float(thr) > 0
+    dist.barrier()
+    ex.region.close()
+    print(f"OK sample_exchange rank{rank} thr={float(thr):.4f}", flush=True)
+
+
+CHECKS = {"samples": check_sample_exchange, "nvls_dense": check_nvls_dense_allreduce, "b2b": check_sparse_back_to_back, "nvls": check_sparse_nvls, "verify": check_verify_fallback,
           "tp2dp2": check_tp2dp2_sparse_embedding, "gemm_ar": check_gemm_allreduce, "sp_trainer": check_sp_trainer, "gemm_rs_ag": check_gemm_rs_ag, "tp_trainer": check_tp_trainer,"sparse": check_sparse_allreduce, "rows": check_row_engine, "trainer": check_trainer_dp,
           "hook": check_zen_hook, "departed": check_departed_rank}
 

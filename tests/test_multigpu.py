@@ -19,7 +19,7 @@ def _run(names, nproc, timeout=600):
     return r.stdout
 
 
-@pytest.mark.parametrize("name", ["sparse", "b2b", "nvls", "nvls_dense", "verify", "rows", "trainer", "hook", "departed", "gemm_ar", "gemm_rs_ag",
+@pytest.mark.parametrize("name", ["sparse", "b2b", "samples", "nvls", "nvls_dense", "verify", "rows", "trainer", "hook", "departed", "gemm_ar", "gemm_rs_ag",
                                   "tp_trainer", "sp_trainer", "tp2dp2"])
 def test_multigpu(name):
     n = torch.cuda.device_count()
@@ -27,6 +27,6 @@ def test_multigpu(name):
         pytest.skip("needs at least two GPUs")
     if name == "tp2dp2" and n < 4:
         pytest.skip("needs four GPUs")
-    nproc = 2 if name in ("departed", "verify", "gemm_ar", "gemm_rs_ag", "tp_trainer", "sp_trainer") else min(n, 4)
+    nproc = 2 if name in ("departed", "verify", "samples", "gemm_ar", "gemm_rs_ag", "tp_trainer", "sp_trainer") else min(n, 4)
     out = _run([name], nproc)
     assert out.count("OK ") >= nproc, out

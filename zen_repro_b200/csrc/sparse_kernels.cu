@@ -1289,3 +1289,73 @@ int zen_select_kth(const float* v, uint32_t n, uint32_t k, uint32_t* hist, uint3
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Exchange of the threshold samples among the ranks of a tensor-parallel group (every shard of a replica must use one
+// threshold: train.py:62-63 all-gathers the samples with NCCL).  Every rank stores its `ns` samples into slot `rank` of
+// every peer's buffer with P2P stores, the last CTA publishes a flag per peer and then waits (bounded) for the flags of
+// all peers: when the kernel ends, this rank's buffer holds the samples of the whole group.  Buffers and flags exist
+// twice and alternate with the call parity, so a rank that is one call ahead writes where nobody reads.
+struct ZenSampleXchg {
+  int32_t rank;
+  int32_t nranks;
+  uint32_t epoch;
+  uint32_t ns;                       // samples per rank
+  uint64_t wait_ns;
+  float* buf[ZEN_MAX_RANKS];         // per rank: float [2][nranks][ns]
+  uint32_t* flags[ZEN_MAX_RANKS];    // per rank: uint32 [2][ZEN_MAX_RANKS]
+  uint32_t* status;
+  uint32_t* done;                    // CTA arrival counter (left at zero)
+  const uint32_t* epoch_dev;         // optional device-resident call counter
+};
+
+__global__ void __launch_bounds__(256)
+zen_sample_exchange_kernel(const ZenSampleXchg c, const float* __restrict__ mine) {
+  __shared__ uint32_t s_last;
+  const uint32_t epoch = c.epoch_dev ? *c.epoch_dev : c.epoch;
+  const uint32_t par = epoch & 1u;
+  const size_t slot = ((size_t)par * c.nranks + c.rank) * c.ns;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < c.ns; i += gridDim.x * blockDim.x) {
+    const float v = mine[i];
+    for (int p = 0; p < c.nranks; ++p) c.buf[p][slot + i] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = (atomicAdd(c.done, 1u) == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if ((int)threadIdx.x < c.nranks) {
+      zen_st_release_sys(c.flags[threadIdx.x] + par * ZEN_MAX_RANKS + c.rank, epoch);
+      if (!zen_wait_epoch(c.flags[c.rank] + par * ZEN_MAX_RANKS + threadIdx.x, epoch, c.wait_ns)) atomicOr(c.status, ZEN_TIMEOUT);
+    }
+    if (threadIdx.x == 0) *c.done = 0u;
+  }
+}
+
+// The gathered samples of this call (the half of the buffer that its parity selects) copied to a fixed place, so that
+// a captured consumer reads the same address at every replay.
+__global__ void __launch_bounds__(256)
+zen_sample_collect_kernel(const ZenSampleXchg c, float* __restrict__ out) {
+  const uint32_t epoch = c.epoch_dev ? *c.epoch_dev : c.epoch;
+  const size_t n = (size_t)c.nranks * c.ns;
+  const float* src = c.buf[c.rank] + (size_t)(epoch & 1u) * n;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = src[i];
+}
+
+extern "C" {
+
+int zen_sample_xchg_size() { return (int)sizeof(ZenSampleXchg); }
+
+// out: nranks * ns floats (slot r = rank r's samples), valid when the two kernels have run.
+int zen_sample_exchange(const ZenSampleXchg* c, const float* mine, float* out, void* stream) {
+  if (!c || c->nranks < 1 || c->nranks > ZEN_MAX_RANKS || c->ns == 0) return -1;
+  const int grid = grid_for(c->ns, 256 * 8, 16);
+  zen_sample_exchange_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*c, mine);
+  zen_sample_collect_kernel<<<grid_for((uint64_t)c->nranks * c->ns, 256 * 4, sm_count()), 256, 0, (cudaStream_t)stream>>>(*c, out);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -27,6 +27,59 @@ _select_state: dict = {}
 _sample_calls = [0]
 
 
+class SampleExchange:
+    """All-gather of ``ns`` fp32 threshold samples per rank over a (tensor-parallel) group through peer memory: one
+    kernel stores this rank's samples into every peer's buffer and returns when all peers' samples have arrived here
+    (bounded wait, status word).  Replaces the NCCL all-gather of the reference's sparsifier (train.py:62-63)."""
+
+    def __init__(self, group, ns: int, device, wait_ms: float = 30000.0):
+        import ctypes
+
+        from ..runtime.symmetric import make_symmetric
+
+        class _X(ctypes.Structure):
+            _fields_ = [("rank", ctypes.c_int32), ("nranks", ctypes.c_int32), ("epoch", ctypes.c_uint32), ("ns", ctypes.c_uint32),
+                        ("wait_ns", ctypes.c_uint64), ("buf", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8),
+                        ("status", ctypes.c_void_p), ("done", ctypes.c_void_p), ("epoch_dev", ctypes.c_void_p)]
+
+        lib = _native.lib()
+        assert lib.zen_sample_xchg_size() == ctypes.sizeof(_X), "sample exchange ctx layout mismatch"
+        P = dist.get_world_size(group)
+        self.P, self.ns = P, ns
+        data = (2 * P * ns * 4 + 255) // 256 * 256
+        self.region = make_symmetric(data + 256, group)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._done = torch.zeros(1, dtype=torch.int32, device=device)
+        self._epoch = torch.zeros(1, dtype=torch.int32, device=device)      # on the device: replays of a captured step advance it
+        c = _X()
+        c.rank, c.nranks, c.ns, c.wait_ns = self.region.rank, P, ns, int(wait_ms * 1e6)
+        for r in range(P):
+            c.buf[r] = self.region.ptrs[r]
+            c.flags[r] = self.region.ptrs[r] + data
+        c.status, c.done, c.epoch_dev = self.status.data_ptr(), self._done.data_ptr(), self._epoch.data_ptr()
+        self.ctx, self._byref = c, ctypes.byref
+        self.out = torch.empty(P * ns, dtype=torch.float32, device=device)  # fixed address: a captured consumer reads it at every replay
+
+    def __call__(self, sample: torch.Tensor) -> torch.Tensor:
+        lib = _native.lib()
+        _native.check(lib.zen_sparse_epoch_bump(_native.ptr(self._epoch), _native.stream_ptr()), "zen_sparse_epoch_bump")
+        _native.check(lib.zen_sample_exchange(self._byref(self.ctx), _native.ptr(sample), _native.ptr(self.out), _native.stream_ptr()),
+                      "zen_sample_exchange")
+        return self.out
+
+
+_exchanges: dict = {}
+
+
+def _exchange_for(group, ns: int, device) -> SampleExchange:
+    key = (id(group), ns, str(device))
+    x = _exchanges.get(key)
+    if x is None:
+        x = SampleExchange(group, ns, device)
+        _exchanges[key] = x
+    return x
+
+
 def _sampled_threshold_cuda(flat: torch.Tensor, ns: int, top_k: float, group) -> torch.Tensor:
     """Kernel path: hash-sampled |g|, optional all-gather over the TP group, radix select of the k-th largest.
     Everything stays on the device; the returned one-element float tensor feeds the partition kernel."""
@@ -45,9 +98,7 @@ def _sampled_threshold_cuda(flat: torch.Tensor, ns: int, top_k: float, group) ->
                                      ctypes.c_uint32(_sample_calls[0] * 2654435761 & 0xFFFFFFFF),
                                      _native.DTYPE_CODE[flat.dtype], _native.stream_ptr()), "zen_sample_abs")
     if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
-        gathered = torch.empty(dist.get_world_size(group) * ns, dtype=torch.float32, device=dev)
-        dist.all_gather_into_tensor(gathered, sample, group=group)
-        sample = gathered
+        sample = _exchange_for(group, ns, dev)(sample)        # peer stores, no library collective
     k = max(1, int(sample.numel() * top_k // 100))
     out = torch.empty(1, dtype=torch.float32, device=dev)
     _native.check(lib.zen_select_kth(_native.ptr(sample), ctypes.c_uint32(sample.numel()), ctypes.c_uint32(k), _native.ptr(hist),
