@@ -86,6 +86,11 @@ def check_zen_hook(rank, world, dev):
                             bucket_cap_mb=0.1), init_dist=False)
     ls = [t.step(next(t.data)) for _ in range(8)]
     assert ls[-1] < ls[0], ls
+    m = t.collect_metrics()                      # counters of the last step's sparse all-reduces, the same on every rank
+    assert m["recoveries"] == 0 and m["buckets"], m
+    for b in m["buckets"].values():
+        assert 0.0 < b["density_sent"] <= 0.35 and b["union_density"] >= b["density_sent"] * 0.5
+        assert 1.0 <= b["partition_max_over_mean"] < 3.0 and b["calls"] >= 7
     print(f"OK zen_hook rank{rank} {ls[0]:.3f}->{ls[-1]:.3f}", flush=True)
 
 
