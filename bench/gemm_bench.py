@@ -43,7 +43,13 @@ def main():
     ap.add_argument("--modes", nargs="+", default=["nt", "nn", "tn"])
     ap.add_argument("--one", type=int, nargs=3, metavar=("M", "N", "K"), default=None)
     ap.add_argument("--bn", type=int, default=0, help="with --one: force the N tile (0 = chosen per call)")
+    ap.add_argument("--tail_min_kb", type=int, default=-1,
+                    help="fewest 64-wide K blocks from which the tiles of a partly filled last round are cut in two "
+                         "(0 = never, -1 = the library's default)")
     args = ap.parse_args()
+    if args.tail_min_kb >= 0:
+        from zen_repro_b200 import _native
+        _native.lib().zen_gemm2_tail_split(args.tail_min_kb)
     if args.one:
         M, N, K = args.one
         torch.manual_seed(0)

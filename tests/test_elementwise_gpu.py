@@ -135,6 +135,47 @@ def test_colsum():
     torch.testing.assert_close(got.cpu().float(), a.float().sum(0), atol=0.3, rtol=2e-2)
 
 
+@pytest.mark.parametrize("kind", ["gelu_tanh", "relu"])
+@pytest.mark.parametrize("rows,inner", [(1000, 3072), (77, 256), (8192, 10240)])
+def test_activation_backward_with_column_sums(kind, rows, inner):
+    """The activation backward that also leaves the bias gradient of the layer before it: same da as the plain kernel,
+    and the column sums of exactly those stored values; the linear layer's backward picks them up from the tensor."""
+    torch.manual_seed(3)
+    x = torch.randn(rows, inner, device=DEV).bfloat16()
+    g = torch.randn(rows, inner, device=DEV).bfloat16()
+    want, _ = E.act_bwd(x, None, g, kind)
+    da, part = E.act_bwd_with_colsum(x, g, kind)
+    assert torch.equal(da, want)
+    out = torch.full((inner,), 1.0, device=DEV, dtype=torch.bfloat16)
+    E.colsum_from_parts(part, out, accumulate=True)
+    torch.testing.assert_close(out.float(), da.float().sum(0) + 1.0, atol=0.3, rtol=2e-2)
+    E.colsum_from_parts(part, out, accumulate=False)
+    torch.testing.assert_close(out.float(), da.float().sum(0), atol=0.3, rtol=2e-2)
+
+
+def test_bias_gradient_rides_with_the_activation_backward():
+    from zen_repro_b200.ops import autograd as AG
+    torch.manual_seed(4)
+    x = torch.randn(4, 64, 256, device=DEV).bfloat16()
+    w = (torch.randn(512, 256, device=DEV) * 0.05).bfloat16().requires_grad_(True)
+    b = torch.zeros(512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    grads = []
+    for fuse in (True, False):
+        AG._FUSE_ACT_COLSUM = fuse
+        try:
+            w.grad = b.grad = None
+            y = AG.activation(AG.linear(x, w, b), "gelu_tanh")
+            (y.float() ** 2).sum().backward()
+            grads.append((w.grad.clone(), b.grad.clone()))
+        finally:
+            AG._FUSE_ACT_COLSUM = True
+    assert torch.equal(grads[0][0], grads[1][0])
+    torch.testing.assert_close(grads[0][1].float(), grads[1][1].float(), atol=0.05, rtol=2e-2)
+    h = (x.float() @ w.detach().float().t() + b.detach().float()).requires_grad_(True)
+    (torch.nn.functional.gelu(h, approximate="tanh") ** 2).sum().backward()
+    torch.testing.assert_close(grads[0][1].float(), h.grad.sum((0, 1)), atol=0.5, rtol=5e-2)
+
+
 def test_cuda_graph_step_matches_eager_steps():
     """The captured training step (replayed) follows the same loss trajectory as launching every kernel from the host."""
     from zen_repro_b200.trainer import TrainConfig, Trainer

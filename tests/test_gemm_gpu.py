@@ -172,3 +172,33 @@ def test_pair_kernel_with_192_wide_tiles(M, N, K):
         assert G.gemm_error() == 0
     finally:
         _native.lib().zen_gemm2_force_bn(old)
+
+
+@pytest.mark.parametrize("M,N,K", [(8192, 768, 3072), (8192, 2048, 1024), (8000, 760, 1100), (8192, 768, 1024)])
+def test_tail_split_of_the_last_round(M, N, K):
+    """Outputs whose 256 x 256 tiles leave the last round of clusters less than half full: those tiles run as two K
+    slices that exchange half an accumulator.  Same result as without the split (fp32 sums of two halves), the same
+    bits on every call, flags left clear for the next launch, all operand layouts, with and without bias."""
+    from zen_repro_b200 import _native
+    torch.manual_seed(11)
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    want = a.float() @ b.float().t()
+    lib = _native.lib()
+    old = lib.zen_gemm2_tail_split(2)
+    try:
+        got = G.gemm_nt(a, b, bn=512)
+        _check(got, want, K)
+        assert torch.equal(got, G.gemm_nt(a, b, bn=512))
+        _check(G.gemm_nt(a, b, bias=bias, bn=512), want + bias.float(), K)
+        _check(G.gemm_nn(a, b.t().contiguous(), bn=512), want, K)
+        _check(G.gemm_tn(a.t().contiguous(), b.t().contiguous(), bn=512), want, K)
+        lib.zen_gemm2_tail_split(0)
+        plain = G.gemm_nt(a, b, bn=512)
+        assert (got.float() - plain.float()).abs().max() <= 0.02 * want.abs().max()
+        lib.zen_gemm2_tail_split(2)
+        _check(G.gemm_nt(a, b, bn=512), want, K)           # split again after an unsplit launch on the same workspace
+    finally:
+        lib.zen_gemm2_tail_split(old)
+    assert G.gemm_error() == 0

@@ -638,6 +638,33 @@ act_bwd_kernel(const T* __restrict__ a, const T* __restrict__ b, const T* __rest
   }
 }
 
+// Backward of an ungated activation (mode 0 / 1) that also leaves the column sums of its result, the bias gradient of
+// the linear layer that produced the activation's input: CTA b handles rows [b * rows_per_cta, ...) of every column and
+// writes part[b][inner], the layout that colreduce_kernel sums.  The separate column-sum kernel would read da again.
+template <typename T>
+__global__ void __launch_bounds__(512)
+act_bwd_colsum_kernel(const T* __restrict__ a, const T* __restrict__ dout, T* __restrict__ da, float* __restrict__ part,
+                      int rows, int inner, int mode, int rows_per_cta) {
+  const int r0 = blockIdx.x * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
+  for (int c8 = threadIdx.x * 8; c8 < inner; c8 += blockDim.x * 8) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 4
+    for (int r = r0; r < r1; ++r) {
+      float x[8], g[8], ga[8];
+      Vec8<T>::load(a + (size_t)r * inner + c8, x);
+      Vec8<T>::load(dout + (size_t)r * inner + c8, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float v = (mode == 0) ? g[i] * gelu_tanh_grad(x[i]) : (x[i] > 0.f ? g[i] : 0.f);
+        ga[i] = ZenVal<T>::to_f(ZenVal<T>::from_f(v));       // the sum is that of the stored values
+        acc[i] += ga[i];
+      }
+      Vec8<T>::store(da + (size_t)r * inner + c8, ga);
+    }
+    Vec8<float>::store(part + (size_t)blockIdx.x * inner + c8, acc);
+  }
+}
+
 // --------------------------------------------------------------------------------------------
 // RoPE (rotate-half convention): x is [tokens, heads, hd] with row stride `ld` elements between
 // tokens; token t sits at position pos0 + t % seq.  sign = -1 applies the inverse rotation
@@ -1194,6 +1221,34 @@ int zen_act_bwd(const void* a, const void* b, const void* dout, void* da, void* 
   if (inner % 8 || lda % 8 || ldb % 8) return -2;
   const int grid = cap_grid(((size_t)rows * (inner / 8) + 255) / 256, 16);
   DISPATCH_T(dtype, act_bwd_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)a, (const T*)b, (const T*)dout, (T*)da, (T*)db, rows, inner, lda, ldb, mode));
+  return (int)cudaGetLastError();
+}
+
+// Rows per CTA of zen_act_bwd_colsum: three CTAs per SM, all resident at once and evenly loaded, at least 8 rows each.
+static int act_colsum_rows_per_cta(int rows) {
+  const int target = sm_count_e() * 3;
+  const int rpc = (rows + target - 1) / target;
+  return rpc < 8 ? 8 : rpc;
+}
+int zen_act_colsum_parts(int rows) { const int rpc = act_colsum_rows_per_cta(rows); return (rows + rpc - 1) / rpc; }
+
+// Ungated activation backward (mode 0 gelu_tanh, 1 relu) on dense [rows, inner] tensors that also writes the partial
+// column sums of da: part[zen_act_colsum_parts(rows)][inner] floats, to be summed by zen_colsum_reduce.
+int zen_act_bwd_colsum(const void* a, const void* dout, void* da, float* part, int rows, int inner, int mode, int dtype,
+                       void* stream) {
+  if (inner % 8 || mode < 0 || mode > 1) return -2;
+  if (rows <= 0) return 0;
+  int threads = ((inner / 8 + 31) / 32) * 32;
+  if (threads > 512) threads = 512;
+  const int rpc = act_colsum_rows_per_cta(rows);
+  DISPATCH_T(dtype, act_bwd_colsum_kernel<T><<<(rows + rpc - 1) / rpc, threads, 0, (cudaStream_t)stream>>>((const T*)a, (const T*)dout, (T*)da, part, rows, inner, mode, rpc));
+  return (int)cudaGetLastError();
+}
+
+// out[c] (+)= sum over p of part[p][c]: the second half of zen_colsum for partial sums that another kernel produced.
+int zen_colsum_reduce(const float* part, void* out, int parts, int cols, int accumulate, int dtype, void* stream) {
+  if (parts <= 0 || cols <= 0) return -2;
+  DISPATCH_T(dtype, colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, (cudaStream_t)stream>>>(part, (T*)out, parts, cols, accumulate));
   return (int)cudaGetLastError();
 }
 

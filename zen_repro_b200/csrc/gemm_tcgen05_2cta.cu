@@ -41,10 +41,49 @@ struct Gemm2Params {
   // split-K: a work unit is (output tile, K slice).  Every unit stores its fp32 partial tile in `ws`; per 32-row
   // group a counter tells the last unit to arrive, which sums the slices in slice order and writes the output.
   int splits, kb_per_split;
-  float* ws;                        // [splits * tiles][2 CTAs][8 column chunks][128 rows][32] floats
+  float* ws;                        // [splits * tiles][2 CTAs][8 column chunks][8 float4 of a row][128 rows] float4:
+                                    // consecutive lanes (rows) are consecutive in memory, so a warp's store covers whole lines
   int* counters;                    // [tiles][2 CTAs][4 row groups][2], zero between launches
   int tma_store;                    // bf16 output written through shared memory and TMA stores (full lines, async)
+  // tail split (splits == 1 only): the last `tail` output tiles, the ones of the launch's final, partly filled round
+  // of clusters, are cut into two K slices [0, tail_kb) and [tail_kb, nkb) that run side by side in that round and
+  // exchange half an accumulator each (the two-slice TMA-store path); 0 = every tile is one unit
+  int tail, tail_kb;
 };
+
+// One unit of work of a cluster: an output tile, or one K slice of it.
+struct Unit {
+  int tile, ks, kb0, kb1;
+  int wtile, wtiles;                // index of the tile among the split ones and their number (workspace / flag addressing)
+  bool split;
+};
+__device__ __forceinline__ Unit decode_unit(const Gemm2Params& p, int unit, int num_tiles, int nkb) {
+  Unit u;
+  if (p.tail == 0) {
+    u.tile = unit % num_tiles;
+    u.ks = unit / num_tiles;
+    u.kb0 = u.ks * p.kb_per_split;
+    u.kb1 = min(nkb, u.kb0 + p.kb_per_split);
+    u.split = p.splits > 1;
+    u.wtile = u.tile;
+    u.wtiles = num_tiles;
+    return u;
+  }
+  const int whole = num_tiles - p.tail;
+  u.wtiles = p.tail;
+  if (unit < whole) {
+    u.tile = unit; u.ks = 0; u.kb0 = 0; u.kb1 = nkb; u.split = false; u.wtile = 0;
+    return u;
+  }
+  const int j = unit - whole;
+  u.ks = j >= p.tail ? 1 : 0;
+  u.wtile = j - u.ks * p.tail;
+  u.tile = whole + u.wtile;
+  u.kb0 = u.ks ? p.tail_kb : 0;
+  u.kb1 = u.ks ? nkb : p.tail_kb;
+  u.split = true;
+  return u;
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -122,7 +161,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const uint32_t cta = cluster_ctarank();
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
   const int num_tiles = p.num_m_pairs * p.num_n_tiles;
-  const int num_units = num_tiles * p.splits;
+  const int num_units = p.tail ? num_tiles + p.tail : num_tiles * p.splits;
   const int nkb = (p.K + BK2 - 1) / BK2;
 
   if (threadIdx.x == 0) {
@@ -144,11 +183,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       uint32_t it = 0;
       bool ok = true;
       for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
-        const int tile = unit % num_tiles, ks = unit / num_tiles;
-        const int m0 = (tile % p.num_m_pairs) * 256 + (int)cta * BM2;
-        const int n0 = (tile / p.num_m_pairs) * BN2 + (int)cta * BNH;
-        const int kb0 = ks * p.kb_per_split, kb1 = min(nkb, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const Unit u = decode_unit(p, unit, num_tiles, nkb);
+        const int m0 = (u.tile % p.num_m_pairs) * 256 + (int)cta * BM2;
+        const int n0 = (u.tile / p.num_m_pairs) * BN2 + (int)cta * BNH;
+        for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
           const int s = it % STAGES2;
           const uint32_t ph = (it / STAGES2) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, 1, &g_gemm2_error)) { ok = false; break; }
@@ -181,7 +219,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         if (!mbar_wait(&tempty[acc], aph ^ 1, abort_flag, 2, &g_gemm2_error)) { ok = false; break; }
         fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN2;
-        const int kb0 = (unit / num_tiles) * p.kb_per_split, kb1 = min(nkb, kb0 + p.kb_per_split);
+        const Unit u = decode_unit(p, unit, num_tiles, nkb);
+        const int kb0 = u.kb0, kb1 = u.kb1;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES2;
           const uint32_t ph = (it / STAGES2) & 1;
@@ -208,30 +247,31 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     uint32_t tcount = 0;
     bool ok = true;
     for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++tcount) {
-      const int tile = unit % num_tiles, ks = unit / num_tiles;
+      const Unit u = decode_unit(p, unit, num_tiles, nkb);
+      const int tile = u.tile, ks = u.ks;
       const int m0 = (tile % p.num_m_pairs) * 256 + (int)cta * BM2, n0 = (tile / p.num_m_pairs) * BN2;
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aph, abort_flag, 4, &g_gemm2_error)) { ok = false; break; }
       fence_after();
       const int row = m0 + grp * 32 + lane;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(grp * 32) << 16) + acc * BN2;
-      const bool split = p.splits > 1;
+      const bool split = u.split;
       if (split && !p.tma_store) {
         // store this K slice's partial tile and count in.  Every slice but the last to arrive for these 32 rows is
         // done then; the last one adds the others' partials to its own accumulator, in slice order, below.
-        float* wp = p.ws + ((size_t)(ks * num_tiles + tile) * 2 + cta) * (BM2 * BN2) + (size_t)(grp * 32 + lane) * 32;
+        float4* wp = reinterpret_cast<float4*>(p.ws + ((size_t)(ks * num_tiles + tile) * 2 + cta) * (BM2 * BN2)) + (grp * 32 + lane);
 #pragma unroll 1
         for (int ch = 0; ch < BN2 / 32; ch += 2) {
           uint32_t r[32], r2[32];
           tmem_ld32_nowait(taddr0 + ch * 32, r);
           tmem_ld32_nowait(taddr0 + ch * 32 + 32, r2);
           tmem_wait_ld();
-          float4* dst = reinterpret_cast<float4*>(wp + (size_t)ch * (BM2 * 32));
-          float4* dst2 = reinterpret_cast<float4*>(wp + (size_t)(ch + 1) * (BM2 * 32));
+          float4* dst = wp + (size_t)ch * (8 * BM2);
+          float4* dst2 = wp + (size_t)(ch + 1) * (8 * BM2);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-            dst2[i] = make_float4(__uint_as_float(r2[4 * i]), __uint_as_float(r2[4 * i + 1]), __uint_as_float(r2[4 * i + 2]), __uint_as_float(r2[4 * i + 3]));
+            dst[i * BM2] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+            dst2[i * BM2] = make_float4(__uint_as_float(r2[4 * i]), __uint_as_float(r2[4 * i + 1]), __uint_as_float(r2[4 * i + 2]), __uint_as_float(r2[4 * i + 3]));
           }
         }
         __threadfence();
@@ -258,28 +298,28 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         // the peer through the workspace, waits (bounded) for the peer's half and adds it to its own.
         unsigned char* stg = epi_stage + grp * 8192;
         int cb_lo = 0, cb_hi = BN2 / 64;
-        const float* peer = nullptr;
+        const float4* peer = nullptr;
         if (split) {
           const int other = 1 - ks;
-          float* wp = p.ws + ((size_t)(ks * num_tiles + tile) * 2 + cta) * (BM2 * BN2) + (size_t)(grp * 32 + lane) * 32;
+          float4* wp = reinterpret_cast<float4*>(p.ws + ((size_t)(ks * u.wtiles + u.wtile) * 2 + cta) * (BM2 * BN2)) + (grp * 32 + lane);
 #pragma unroll 1
           for (int ch = other * (BN2 / 64); ch < (other + 1) * (BN2 / 64); ch += 2) {
             uint32_t r[32], r2[32];
             tmem_ld32_nowait(taddr0 + ch * 32, r);
             tmem_ld32_nowait(taddr0 + ch * 32 + 32, r2);
             tmem_wait_ld();
-            float4* dst = reinterpret_cast<float4*>(wp + (size_t)ch * (BM2 * 32));
-            float4* dst2 = reinterpret_cast<float4*>(wp + (size_t)(ch + 1) * (BM2 * 32));
+            float4* dst = wp + (size_t)ch * (8 * BM2);
+            float4* dst2 = wp + (size_t)(ch + 1) * (8 * BM2);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-              dst2[i] = make_float4(__uint_as_float(r2[4 * i]), __uint_as_float(r2[4 * i + 1]), __uint_as_float(r2[4 * i + 2]), __uint_as_float(r2[4 * i + 3]));
+              dst[i * BM2] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+              dst2[i * BM2] = make_float4(__uint_as_float(r2[4 * i]), __uint_as_float(r2[4 * i + 1]), __uint_as_float(r2[4 * i + 2]), __uint_as_float(r2[4 * i + 3]));
             }
           }
           __threadfence();
           __syncwarp();
           // flags[..][ks] = 1: "slice ks has published its half"; the consumer clears it for the next launch
-          int* flags = p.counters + ((tile * 2 + (int)cta) * 4 + grp) * 2;
+          int* flags = p.counters + ((u.wtile * 2 + (int)cta) * 4 + grp) * 2;
           int got = 1;
           if (lane == 0) {
             atomicExch(flags + ks, 1);
@@ -293,7 +333,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           got = __shfl_sync(0xffffffffu, got, 0);
           if (!got) { ok = false; break; }
           __threadfence();
-          peer = p.ws + ((size_t)(other * num_tiles + tile) * 2 + cta) * (BM2 * BN2) + (size_t)(grp * 32 + lane) * 32;
+          peer = reinterpret_cast<const float4*>(p.ws + ((size_t)(other * u.wtiles + u.wtile) * 2 + cta) * (BM2 * BN2)) + (grp * 32 + lane);
           cb_lo = ks * (BN2 / 128);
           cb_hi = cb_lo + BN2 / 128;
         }
@@ -305,10 +345,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           tmem_ld32_nowait(taddr0 + cb * 64 + 32, rb);
           float4 oa[8], ob[8];
           if (split) {
-            const float4* qa = reinterpret_cast<const float4*>(peer + (size_t)(2 * cb) * (BM2 * 32));
-            const float4* qb = reinterpret_cast<const float4*>(peer + (size_t)(2 * cb + 1) * (BM2 * 32));
+            const float4* qa = peer + (size_t)(2 * cb) * (8 * BM2);
+            const float4* qb = peer + (size_t)(2 * cb + 1) * (8 * BM2);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { oa[i] = __ldcg(qa + i); ob[i] = __ldcg(qb + i); }
+            for (int i = 0; i < 8; ++i) { oa[i] = __ldcg(qa + i * BM2); ob[i] = __ldcg(qb + i * BM2); }
           }
           if (lane == 0) bulk_wait_read<1>();          // the store that read this buffer two boxes ago is done
           __syncwarp();
@@ -367,13 +407,13 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           // the other slices' partials of this chunk first (independent loads, all in flight together), then the
           // own accumulator; the sum runs over slice indices whichever slice arrived last
           float4 buf[MAX_SPLITS][8];
-          const float* src = p.ws + ((size_t)tile * 2 + cta) * (BM2 * BN2) + (size_t)ch * (BM2 * 32) + (size_t)(grp * 32 + lane) * 32;
+          const float4* src = reinterpret_cast<const float4*>(p.ws + ((size_t)tile * 2 + cta) * (BM2 * BN2)) + (size_t)ch * (8 * BM2) + (grp * 32 + lane);
 #pragma unroll
           for (int sidx = 0; sidx < MAX_SPLITS; ++sidx) {
             if (sidx < p.splits && sidx != ks) {
-              const float4* q = reinterpret_cast<const float4*>(src + (size_t)sidx * num_tiles * 2 * (BM2 * BN2));
+              const float4* q = src + (size_t)sidx * num_tiles * 2 * (BM2 * BN2 / 4);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) buf[sidx][i] = __ldcg(q + i);
+              for (int i = 0; i < 8; ++i) buf[sidx][i] = __ldcg(q + i * BM2);
             }
           }
           tmem_ld32(taddr0 + ch * 32, r);
@@ -481,7 +521,7 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
   }
   p.num_m_pairs = (p.M + 255) / 256;
   p.num_n_tiles = (p.N + BN2 - 1) / BN2;
-  const int tiles = p.num_m_pairs * p.num_n_tiles * p.splits;
+  const int tiles = p.tail ? p.num_m_pairs * p.num_n_tiles + p.tail : p.num_m_pairs * p.num_n_tiles * p.splits;
   int clusters = zen_tmap::sm_count() / 2;
   if (tiles < clusters) clusters = tiles;
   gemm_bf16_2cta_kernel<A_MN, B_MN, BN2><<<clusters * 2, 192, pair_smem_bytes<BN2>(), st>>>(ta, tb, tc, p);
@@ -491,6 +531,7 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
 }  // namespace
 
 int g_force_bn = 0;
+int g_tail_min_kb = 16;            // fewest 64-wide K blocks for which the tiles of the last round are cut in two; 0 = never
 
 // 256-wide pair tiles.  The 128-wide variant exists for outputs whose 256-wide tiles fill the 74 CTA pairs unevenly
 // (96 tiles = 1.3 waves), but measured on 8192 x 768 outputs it lost (662 vs 858 TFLOP/s at K = 3072, 410 vs 472 at
@@ -514,6 +555,8 @@ extern "C" {
 // long K, the weight-gradient shape): `ws` must hold splits * tiles * 2 * 128 * 256 floats and `counters`
 // tiles * 16 ints that are zero on entry (the kernel leaves them zero); both are caller-owned and used in stream
 // order.  The slices are summed in slice order, so the result does not depend on timing.
+// With splits == 1 a caller may still pass `ws` and `counters` (same sizes as for two slices of one round of clusters):
+// the launcher then cuts the tiles of the last, partly filled round in two (see zen_gemm2_tail_split).
 // n_store: 0, or a width in [N, ldc] that the kernel may write (columns N.. receive zeros).
 int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
                               int ldb, int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, int splits, float* ws,
@@ -567,7 +610,22 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
     rc = zen_tmap::get(C, (uint64_t)n_store, (uint64_t)M, (uint64_t)ldc, 64, 32, &tc);
     if (rc) return rc;
   }
-  Gemm2Params p{C, bias, M, N, K, ldc, out_fp32, accumulate, 0, 0, splits, kb_per, ws, counters, tma_store};
+  // Tail split: the tiles of the last, partly filled round of clusters run as two K slices each when both slices of
+  // all of them fit in that round (so that the slices that wait for each other are resident together, as above) and K
+  // is long enough for half a tile to outweigh the exchange of half an accumulator.
+  int tail = 0, tail_kb = 0;
+  if (splits == 1 && bn == 256 && tma_store && g_tail_min_kb > 0 && nkb >= g_tail_min_kb && ws && counters &&
+      (reinterpret_cast<uintptr_t>(ws) % 16) == 0) {
+    const int clusters = zen_tmap::sm_count() / 2;
+    const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const int rem = tiles % clusters;
+    if (tiles > clusters && rem > 0 && 2 * rem <= clusters && ws_floats >= (uint64_t)rem * 2 * 2 * BM2 * 256 &&
+        n_counters >= rem * 16) {
+      tail = rem;
+      tail_kb = (nkb + 1) / 2;
+    }
+  }
+  Gemm2Params p{C, bias, M, N, K, ldc, out_fp32, accumulate, 0, 0, splits, kb_per, ws, counters, tma_store, tail, tail_kb};
   cudaStream_t st = (cudaStream_t)stream;
 #define LAUNCH2(BN_)                                                            \
   do {                                                                          \
@@ -589,6 +647,14 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
 int zen_gemm2_force_bn(int bn) {
   const int old = g_force_bn;
   if (bn == 0 || bn == 128 || bn == 192 || bn == 256) g_force_bn = bn;
+  return old;
+}
+
+// Fewest K blocks (of 64) from which the tiles of a launch's last, partly filled round run as two K slices; 0 switches
+// the tail split off.  Returns the previous setting.
+int zen_gemm2_tail_split(int min_kb) {
+  const int old = g_tail_min_kb;
+  if (min_kb >= 0) g_tail_min_kb = (min_kb > 0 && min_kb < 2) ? 2 : min_kb;
   return old;
 }
 

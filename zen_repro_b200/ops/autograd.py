@@ -5,6 +5,7 @@ materialises a transposed operand.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -13,6 +14,9 @@ import torch.nn.functional as F
 from . import elementwise as E
 from . import gemm as G
 from . import attention as A
+
+# the backward of an ungated activation also leaves the column sums of its result (the bias gradient of the layer before)
+_FUSE_ACT_COLSUM = os.environ.get("ZEN_FUSE_ACT_COLSUM", "1") != "0"
 
 
 def _claim(p, needed: bool) -> bool:
@@ -96,9 +100,18 @@ class LinearFn(torch.autograd.Function):
             else:
                 dw = G.gemm_tn(a, b)
         if ctx.has_bias and ctx.needs_input_grad[2]:
+            # partial column sums that the producer of dy left beside it (ActFn.backward): dy is not read again
+            part = getattr(dy, "_zen_colsum_part", None)
+            if part is not None and (part.shape[1] != dy2.shape[1] or part.device != dy2.device):
+                part = None
             if ctx.direct[1]:
-                E.colsum(dy2, out=bp.grad, accumulate=not _take_fresh(bp))
+                if part is not None:
+                    E.colsum_from_parts(part, out=bp.grad, accumulate=not _take_fresh(bp))
+                else:
+                    E.colsum(dy2, out=bp.grad, accumulate=not _take_fresh(bp))
                 bp.zen_ready(bp)
+            elif part is not None:
+                db = E.colsum_from_parts(part, torch.empty(dy2.shape[1], dtype=dy2.dtype, device=dy2.device), accumulate=False)
             else:
                 db = E.colsum(dy2)
         return dx, dw, db, None, None, None
@@ -174,11 +187,17 @@ class ActFn(torch.autograd.Function):
         (x2,) = ctx.saved_tensors
         kind = ctx.kind
         d2 = dout.reshape(-1, dout.shape[-1])
+        part = None
         if kind in ("swiglu", "geglu"):
             dx = E.act_bwd_gated(x2, d2, kind)
+        elif x2.is_cuda and x2.is_contiguous() and x2.shape[1] % 8 == 0 and _FUSE_ACT_COLSUM:
+            dx, part = E.act_bwd_with_colsum(x2, d2, kind)
         else:
             dx, _ = E.act_bwd(x2, None, d2, kind)
-        return dx.view(ctx.xshape), None
+        dx = dx.view(ctx.xshape)
+        if part is not None:
+            dx._zen_colsum_part = part       # read by the backward of the linear layer that receives dx as its dy
+        return dx, None
 
 
 def activation(x, kind):

@@ -202,6 +202,29 @@ def act_bwd(a, b, dout, kind: str):
     return da.view(a.shape), (db.view(a.shape) if db is not None else None)
 
 
+def act_bwd_with_colsum(a: torch.Tensor, dout: torch.Tensor, kind: str):
+    """(da, part) for an ungated activation on a dense CUDA [rows, inner] tensor: ``part`` holds partial column sums of
+    ``da`` (fp32, one row per group of input rows) that :func:`colsum_from_parts` turns into the bias gradient of the
+    layer before the activation, so that ``da`` is not read a second time for it."""
+    mode = _ACT[kind]
+    assert a.is_cuda and mode in (0, 1) and a.dim() == 2 and a.is_contiguous()
+    rows, inner = a.shape
+    d2 = _c(dout).view(rows, inner)
+    lib = _native.lib()
+    da = torch.empty_like(a)
+    part = torch.empty(lib.zen_act_colsum_parts(rows), inner, dtype=torch.float32, device=a.device)
+    _native.check(lib.zen_act_bwd_colsum(_native.ptr(a), _native.ptr(d2), _native.ptr(da), _native.ptr(part), rows, inner,
+                                         mode, _code(a), _native.stream_ptr()), "zen_act_bwd_colsum")
+    return da, part
+
+
+def colsum_from_parts(part: torch.Tensor, out: torch.Tensor, accumulate: bool = True) -> torch.Tensor:
+    """Sum the partial column sums ``part[parts, cols]`` into ``out[cols]`` (added when ``accumulate``, else written)."""
+    _native.check(_native.lib().zen_colsum_reduce(_native.ptr(part), _native.ptr(out), part.shape[0], part.shape[1],
+                                                  int(accumulate), _code(out), _native.stream_ptr()), "zen_colsum_reduce")
+    return out
+
+
 def act_bwd_gated(x: torch.Tensor, dout: torch.Tensor, kind: str) -> torch.Tensor:
     """Gradient of the gated activation with respect to the fused [rows, 2 * inner] input (gate | up), written straight
     into one [rows, 2 * inner] tensor: the kernel reads the two halves through the row stride and stores the two

@@ -48,6 +48,7 @@ def use_pair_kernel(M: int, N: int, K: int) -> bool:
 
 
 _SPLITK = os.environ.get("ZEN_GEMM_SPLITK", "auto")       # auto | 0
+_TAIL_SPLIT = os.environ.get("ZEN_GEMM_TAILSPLIT", "1") != "0"
 _WS_FLOATS = 74 * 2 * 128 * 256                            # one fp32 partial tile per CTA of one full wave
 _N_COUNTERS = 4096
 _ws_cache: dict = {}
@@ -117,10 +118,13 @@ def _launch(a, b, M, N, K, a_mn, b_mn, bias, out, accumulate, out_dtype, bn, pad
     pair = (bn == 512) or (bn == 0 and use_pair_kernel(M, N, K))
     if pair:
         n_store = min((N + 7) // 8 * 8, out.stride(0)) if pad_ok else 0
+        # the workspace lets the launcher cut the tiles of a partly filled last round of clusters into two K slices
+        ws, cnt = _splitk_workspace(a.device) if _TAIL_SPLIT else (None, None)
         rc = _native.lib().zen_gemm_bf16_2cta_splitk(
             _native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K, a2.stride(0), b2.stride(0),
-            out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), 1, None,
-            ctypes.c_uint64(0), None, 0, n_store, _native.stream_ptr())
+            out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), 1,
+            _native.ptr(ws), ctypes.c_uint64(ws.numel() if ws is not None else 0), _native.ptr(cnt),
+            cnt.numel() if cnt is not None else 0, n_store, _native.stream_ptr())
         _native.check(rc, "zen_gemm_bf16_2cta")
         return out
     rc = _native.lib().zen_gemm_bf16(_native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K,
