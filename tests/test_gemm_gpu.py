@@ -202,3 +202,62 @@ def test_tail_split_of_the_last_round(M, N, K):
     finally:
         lib.zen_gemm2_tail_split(old)
     assert G.gemm_error() == 0
+
+
+@pytest.mark.parametrize("shapes", [
+    [(768, 2304, 8192), (768, 768, 8192), (768, 3072, 8192), (3072, 768, 8192)],      # a GPT-2 layer: 108 tiles, tail of 34
+    [(768, 768, 2048), (520, 1000, 1100)],                                            # fewer tiles than clusters: all split
+    [(2048, 2560, 1024), (2048, 2048, 1024), (2048, 4096, 1024), (4096, 2048, 1024), (768, 768, 1024), (256, 256, 1024)],
+])
+def test_grouped_weight_gradients_in_one_launch(shapes):
+    """Several a^T @ b products queued by defer_tn go out as one launch over one list of tiles; each equals its own
+    GEMM, the callbacks run after the launch, accumulation and fp32 outputs keep the plain store path."""
+    torch.manual_seed(13)
+    ops, outs, wants, fired = [], [], [], []
+    for i, (M, N, K) in enumerate(shapes):
+        a = torch.randn(K, M, device="cuda").bfloat16()
+        b = torch.randn(K, N, device="cuda").bfloat16()
+        want = a.float().t() @ b.float()
+        if i == 1:                                       # accumulated into an existing bf16 gradient
+            out = torch.ones(M, N, device="cuda", dtype=torch.bfloat16)
+            want = want + 1.0
+            acc = True
+        elif i == 2 and len(shapes) > 2:                 # fp32 output
+            out = torch.empty(M, N, device="cuda", dtype=torch.float32)
+            acc = False
+        else:
+            out = torch.full((M, N), 7.0, device="cuda", dtype=torch.bfloat16)     # overwritten
+            acc = False
+        ops.append((a, b, out, acc)); outs.append(out); wants.append((want, K))
+    old = G.GROUP_SIZE
+    G.GROUP_SIZE = 6
+    try:
+        for i, (a, b, out, acc) in enumerate(ops):
+            G.defer_tn(a, b, out, acc, done=lambda i=i: fired.append(i))
+        if len(ops) < 6:
+            assert fired == []                           # still queued
+        G.flush_deferred()
+    finally:
+        G.GROUP_SIZE = old
+    assert fired == list(range(len(ops)))
+    for out, (want, K) in zip(outs, wants):
+        _check(out, want, K)
+    assert G.gemm_error() == 0
+    # the same outputs again, everything overwritten this time: bit-identical to separate launches without tail split
+    from zen_repro_b200 import _native
+    G.GROUP_SIZE = 6
+    try:
+        fresh = [torch.empty(M, N, device="cuda", dtype=torch.bfloat16) for (M, N, K) in shapes]
+        for (a, b, _o, _acc), o in zip(ops, fresh):
+            G.defer_tn(a, b, o, False)
+        G.flush_deferred()
+        again = [torch.empty(M, N, device="cuda", dtype=torch.bfloat16) for (M, N, K) in shapes]
+        for (a, b, _o, _acc), o in zip(ops, again):
+            G.defer_tn(a, b, o, False)
+        G.flush_deferred()
+    finally:
+        G.GROUP_SIZE = old
+    for x, y, (want, K) in zip(fresh, again, [( (a.float().t() @ b.float()), a.shape[0]) for (a, b, _o, _c) in ops]):
+        assert torch.equal(x, y)
+        _check(x, want, K)
+    assert G.gemm_error() == 0

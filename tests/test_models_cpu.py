@@ -120,3 +120,15 @@ def test_unshard_inverts_shard(name, tp):
     assert set(back) == set(sd)
     for k in sd:
         assert torch.equal(back[k], sd[k]), k
+
+
+def test_deferred_weight_gradient_runs_at_once_on_cpu():
+    """Without the CUDA kernel there is nothing to group: defer_tn computes immediately and still calls back."""
+    from zen_repro_b200.ops import gemm as G
+    a, b = torch.randn(16, 8), torch.randn(16, 12)
+    out = torch.ones(8, 12)
+    fired = []
+    G.defer_tn(a, b, out, accumulate=True, done=lambda: fired.append(1))
+    assert fired == [1]
+    torch.testing.assert_close(out, a.t() @ b + 1.0, atol=1e-5, rtol=1e-5)
+    G.flush_deferred()

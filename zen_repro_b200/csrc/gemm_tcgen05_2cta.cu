@@ -32,56 +32,81 @@ template <int BN> constexpr int pair_smem_bytes() { return PairCfg<BN>::STAGES *
 
 __device__ int g_gemm2_error = 0;
 
-struct Gemm2Params {
+// One GEMM of a launch.  A launch runs up to MAX_GROUP of them (same operand layouts) as ONE list of output tiles over
+// the persistent clusters: small products that each fill the clusters badly (the four weight gradients of a
+// transformer layer: 27 + 9 + 36 + 36 tiles on 74 clusters) then share rounds, and the fixed cost of a launch
+// (pipeline fill, last epilogue) is paid once.
+constexpr int MAX_GROUP = 6;
+struct GemmProblem {
+  CUtensorMap ta, tb, tc;
   void* C;
   const void* bias;
   int M, N, K, ldc;
   int out_fp32, accumulate;
+  int tma_store;                    // bf16 output written through shared memory and TMA stores (full lines, async)
   int num_m_pairs, num_n_tiles;
-  // split-K: a work unit is (output tile, K slice).  Every unit stores its fp32 partial tile in `ws`; per 32-row
-  // group a counter tells the last unit to arrive, which sums the slices in slice order and writes the output.
+  int tile_start;                   // index of this product's first tile in the launch's list
+};
+struct GemmGroup {
+  GemmProblem pr[MAX_GROUP];
+  int n, num_tiles;                 // products, tiles of all of them
+  // split-K (one product only): a work unit is (output tile, K slice).  Every unit stores its fp32 partial tile in
+  // `ws`; per 32-row group a counter tells the last unit to arrive, which sums the slices in slice order and writes
+  // the output; with two slices and a TMA-stored output the slices exchange half an accumulator each instead.
   int splits, kb_per_split;
-  float* ws;                        // [splits * tiles][2 CTAs][8 column chunks][8 float4 of a row][128 rows] float4:
+  // tail split (splits == 1): the last `tail` tiles of the list, the ones of the launch's final, partly filled round
+  // of clusters, are cut into two K halves that run side by side in that round and exchange half an accumulator
+  // each (the two-slice TMA-store path); 0 = every tile is one unit
+  int tail;
+  float* ws;                        // [slices * tiles][2 CTAs][8 column chunks][8 float4 of a row][128 rows] float4:
                                     // consecutive lanes (rows) are consecutive in memory, so a warp's store covers whole lines
   int* counters;                    // [tiles][2 CTAs][4 row groups][2], zero between launches
-  int tma_store;                    // bf16 output written through shared memory and TMA stores (full lines, async)
-  // tail split (splits == 1 only): the last `tail` output tiles, the ones of the launch's final, partly filled round
-  // of clusters, are cut into two K slices [0, tail_kb) and [tail_kb, nkb) that run side by side in that round and
-  // exchange half an accumulator each (the two-slice TMA-store path); 0 = every tile is one unit
-  int tail, tail_kb;
 };
 
 // One unit of work of a cluster: an output tile, or one K slice of it.
 struct Unit {
-  int tile, ks, kb0, kb1;
+  int pi, tile, lt, ks, kb0, kb1;   // product, tile in the launch's list, tile within the product, K slice and its blocks
   int wtile, wtiles;                // index of the tile among the split ones and their number (workspace / flag addressing)
   bool split;
 };
-__device__ __forceinline__ Unit decode_unit(const Gemm2Params& p, int unit, int num_tiles, int nkb) {
+__device__ __forceinline__ Unit decode_unit(const GemmGroup& g, int unit) {
   Unit u;
-  if (p.tail == 0) {
-    u.tile = unit % num_tiles;
-    u.ks = unit / num_tiles;
-    u.kb0 = u.ks * p.kb_per_split;
-    u.kb1 = min(nkb, u.kb0 + p.kb_per_split);
-    u.split = p.splits > 1;
+  const int T = g.num_tiles;
+  if (g.tail == 0) {
+    u.tile = unit % T;
+    u.ks = unit / T;
+    u.split = g.splits > 1;
     u.wtile = u.tile;
-    u.wtiles = num_tiles;
-    return u;
+    u.wtiles = T;
+  } else {
+    const int whole = T - g.tail;
+    u.wtiles = g.tail;
+    if (unit < whole) {
+      u.tile = unit; u.ks = 0; u.split = false; u.wtile = 0;
+    } else {
+      const int j = unit - whole;
+      u.ks = j >= g.tail ? 1 : 0;
+      u.wtile = j - u.ks * g.tail;
+      u.tile = whole + u.wtile;
+      u.split = true;
+    }
   }
-  const int whole = num_tiles - p.tail;
-  u.wtiles = p.tail;
-  if (unit < whole) {
-    u.tile = unit; u.ks = 0; u.kb0 = 0; u.kb1 = nkb; u.split = false; u.wtile = 0;
-    return u;
+  u.pi = 0;
+#pragma unroll
+  for (int i = 1; i < MAX_GROUP; ++i)
+    if (i < g.n && u.tile >= g.pr[i].tile_start) u.pi = i;
+  u.lt = u.tile - g.pr[u.pi].tile_start;
+  const int nkb = (g.pr[u.pi].K + BK2 - 1) / BK2;
+  if (g.tail == 0) {
+    u.kb0 = u.ks * g.kb_per_split;
+    u.kb1 = min(nkb, u.kb0 + g.kb_per_split);
+  } else if (!u.split) {
+    u.kb0 = 0; u.kb1 = nkb;
+  } else {
+    const int half = (nkb + 1) / 2;
+    u.kb0 = u.ks ? half : 0;
+    u.kb1 = u.ks ? nkb : half;
   }
-  const int j = unit - whole;
-  u.ks = j >= p.tail ? 1 : 0;
-  u.wtile = j - u.ks * p.tail;
-  u.tile = whole + u.wtile;
-  u.kb0 = u.ks ? p.tail_kb : 0;
-  u.kb1 = u.ks ? nkb : p.tail_kb;
-  u.split = true;
   return u;
 }
 
@@ -141,8 +166,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 
 template <bool A_MN, bool B_MN, int BN2>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                      const __grid_constant__ CUtensorMap tma_c, const Gemm2Params p) {
+gemm_bf16_2cta_kernel(const __grid_constant__ GemmGroup gg) {
   constexpr int BNH = PairCfg<BN2>::BNH, STAGES2 = PairCfg<BN2>::STAGES, STAGE_BYTES2 = PairCfg<BN2>::STAGE_BYTES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -160,9 +184,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
-  const int num_tiles = p.num_m_pairs * p.num_n_tiles;
-  const int num_units = p.tail ? num_tiles + p.tail : num_tiles * p.splits;
-  const int nkb = (p.K + BK2 - 1) / BK2;
+  const int num_tiles = gg.num_tiles;
+  const int num_units = gg.tail ? num_tiles + gg.tail : num_tiles * gg.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES2; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -183,9 +206,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       uint32_t it = 0;
       bool ok = true;
       for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters) {
-        const Unit u = decode_unit(p, unit, num_tiles, nkb);
-        const int m0 = (u.tile % p.num_m_pairs) * 256 + (int)cta * BM2;
-        const int n0 = (u.tile / p.num_m_pairs) * BN2 + (int)cta * BNH;
+        const Unit u = decode_unit(gg, unit);
+        const GemmProblem& p = gg.pr[u.pi];
+        const int m0 = (u.lt % p.num_m_pairs) * 256 + (int)cta * BM2;
+        const int n0 = (u.lt / p.num_m_pairs) * BN2 + (int)cta * BNH;
         for (int kb = u.kb0; kb < u.kb1; ++kb, ++it) {
           const int s = it % STAGES2;
           const uint32_t ph = (it / STAGES2) & 1;
@@ -195,16 +219,16 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           if (cta == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES2);
           const int k0 = kb * BK2;
           if (!A_MN) {
-            tma_load_2d_pair(sa, &tma_a, &full[s], k0, m0);
+            tma_load_2d_pair(sa, &p.ta, &full[s], k0, m0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM2 / 64; ++j) tma_load_2d_pair(sa + j * 8192, &tma_a, &full[s], m0 + 64 * j, k0);
+            for (int j = 0; j < BM2 / 64; ++j) tma_load_2d_pair(sa + j * 8192, &p.ta, &full[s], m0 + 64 * j, k0);
           }
           if (!B_MN) {
-            tma_load_2d_pair(sb, &tma_b, &full[s], k0, n0);
+            tma_load_2d_pair(sb, &p.tb, &full[s], k0, n0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * 8192, &tma_b, &full[s], n0 + 64 * j, k0);
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * 8192, &p.tb, &full[s], n0 + 64 * j, k0);
           }
         }
       }
@@ -219,7 +243,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         if (!mbar_wait(&tempty[acc], aph ^ 1, abort_flag, 2, &g_gemm2_error)) { ok = false; break; }
         fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN2;
-        const Unit u = decode_unit(p, unit, num_tiles, nkb);
+        const Unit u = decode_unit(gg, unit);
         const int kb0 = u.kb0, kb1 = u.kb1;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES2;
@@ -247,9 +271,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     uint32_t tcount = 0;
     bool ok = true;
     for (int unit = cluster_id; unit < num_units && ok; unit += num_clusters, ++tcount) {
-      const Unit u = decode_unit(p, unit, num_tiles, nkb);
+      const Unit u = decode_unit(gg, unit);
+      const GemmProblem& p = gg.pr[u.pi];
       const int tile = u.tile, ks = u.ks;
-      const int m0 = (tile % p.num_m_pairs) * 256 + (int)cta * BM2, n0 = (tile / p.num_m_pairs) * BN2;
+      const int m0 = (u.lt % p.num_m_pairs) * 256 + (int)cta * BM2, n0 = (u.lt / p.num_m_pairs) * BN2;
       const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
       if (!mbar_wait(&tfull[acc], aph, abort_flag, 4, &g_gemm2_error)) { ok = false; break; }
       fence_after();
@@ -259,7 +284,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       if (split && !p.tma_store) {
         // store this K slice's partial tile and count in.  Every slice but the last to arrive for these 32 rows is
         // done then; the last one adds the others' partials to its own accumulator, in slice order, below.
-        float4* wp = reinterpret_cast<float4*>(p.ws + ((size_t)(ks * num_tiles + tile) * 2 + cta) * (BM2 * BN2)) + (grp * 32 + lane);
+        float4* wp = reinterpret_cast<float4*>(gg.ws + ((size_t)(ks * num_tiles + tile) * 2 + cta) * (BM2 * BN2)) + (grp * 32 + lane);
 #pragma unroll 1
         for (int ch = 0; ch < BN2 / 32; ch += 2) {
           uint32_t r[32], r2[32];
@@ -276,14 +301,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         }
         __threadfence();
         __syncwarp();
-        int* cnt = p.counters + (tile * 2 + (int)cta) * 4 + grp;
+        int* cnt = gg.counters + (tile * 2 + (int)cta) * 4 + grp;
         int old = 0;
         if (lane == 0) {
           old = atomicAdd(cnt, 1);
-          if (old == p.splits - 1) *cnt = 0;           // every slice has arrived: ready for the next launch
+          if (old == gg.splits - 1) *cnt = 0;           // every slice has arrived: ready for the next launch
         }
         old = __shfl_sync(0xffffffffu, old, 0);
-        if (old != p.splits - 1) {
+        if (old != gg.splits - 1) {
           fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_leader(&tempty[acc]);
@@ -301,7 +326,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         const float4* peer = nullptr;
         if (split) {
           const int other = 1 - ks;
-          float4* wp = reinterpret_cast<float4*>(p.ws + ((size_t)(ks * u.wtiles + u.wtile) * 2 + cta) * (BM2 * BN2)) + (grp * 32 + lane);
+          float4* wp = reinterpret_cast<float4*>(gg.ws + ((size_t)(ks * u.wtiles + u.wtile) * 2 + cta) * (BM2 * BN2)) + (grp * 32 + lane);
 #pragma unroll 1
           for (int ch = other * (BN2 / 64); ch < (other + 1) * (BN2 / 64); ch += 2) {
             uint32_t r[32], r2[32];
@@ -319,7 +344,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           __threadfence();
           __syncwarp();
           // flags[..][ks] = 1: "slice ks has published its half"; the consumer clears it for the next launch
-          int* flags = p.counters + ((u.wtile * 2 + (int)cta) * 4 + grp) * 2;
+          int* flags = gg.counters + ((u.wtile * 2 + (int)cta) * 4 + grp) * 2;
           int got = 1;
           if (lane == 0) {
             atomicExch(flags + ks, 1);
@@ -333,7 +358,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           got = __shfl_sync(0xffffffffu, got, 0);
           if (!got) { ok = false; break; }
           __threadfence();
-          peer = reinterpret_cast<const float4*>(p.ws + ((size_t)(other * u.wtiles + u.wtile) * 2 + cta) * (BM2 * BN2)) + (grp * 32 + lane);
+          peer = reinterpret_cast<const float4*>(gg.ws + ((size_t)(other * u.wtiles + u.wtile) * 2 + cta) * (BM2 * BN2)) + (grp * 32 + lane);
           cb_lo = ks * (BN2 / 128);
           cb_hi = cb_lo + BN2 / 128;
         }
@@ -391,7 +416,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (col0 < p.N && m0 + grp * 32 < p.M) tma_store_2d(&tma_c, st, col0, m0 + grp * 32);
+            if (col0 < p.N && m0 + grp * 32 < p.M) tma_store_2d(&p.tc, st, col0, m0 + grp * 32);
             bulk_commit();
           }
         }
@@ -407,10 +432,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           // the other slices' partials of this chunk first (independent loads, all in flight together), then the
           // own accumulator; the sum runs over slice indices whichever slice arrived last
           float4 buf[MAX_SPLITS][8];
-          const float4* src = reinterpret_cast<const float4*>(p.ws + ((size_t)tile * 2 + cta) * (BM2 * BN2)) + (size_t)ch * (8 * BM2) + (grp * 32 + lane);
+          const float4* src = reinterpret_cast<const float4*>(gg.ws + ((size_t)tile * 2 + cta) * (BM2 * BN2)) + (size_t)ch * (8 * BM2) + (grp * 32 + lane);
 #pragma unroll
           for (int sidx = 0; sidx < MAX_SPLITS; ++sidx) {
-            if (sidx < p.splits && sidx != ks) {
+            if (sidx < gg.splits && sidx != ks) {
               const float4* q = src + (size_t)sidx * num_tiles * 2 * (BM2 * BN2 / 4);
 #pragma unroll
               for (int i = 0; i < 8; ++i) buf[sidx][i] = __ldcg(q + i * BM2);
@@ -422,7 +447,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
           for (int i = 0; i < 32; ++i) a[i] = 0.f;
 #pragma unroll
           for (int sidx = 0; sidx < MAX_SPLITS; ++sidx) {
-            if (sidx < p.splits) {
+            if (sidx < gg.splits) {
               const bool own = (sidx == ks);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
@@ -493,7 +518,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(&tempty[acc]);
     }
-    if (p.tma_store && lane == 0) bulk_wait_all();     // shared memory stays valid until the last store has read it
+    if (lane == 0) bulk_wait_all();                    // shared memory stays valid until the last store has read it
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -512,20 +537,66 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 }
 
 template <bool A_MN, bool B_MN, int BN2>
-int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, Gemm2Params p, cudaStream_t st) {
+int launch2(const GemmGroup& g, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN, BN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem_bytes<BN2>());
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  p.num_m_pairs = (p.M + 255) / 256;
-  p.num_n_tiles = (p.N + BN2 - 1) / BN2;
-  const int tiles = p.tail ? p.num_m_pairs * p.num_n_tiles + p.tail : p.num_m_pairs * p.num_n_tiles * p.splits;
+  const int units = g.tail ? g.num_tiles + g.tail : g.num_tiles * g.splits;
   int clusters = zen_tmap::sm_count() / 2;
-  if (tiles < clusters) clusters = tiles;
-  gemm_bf16_2cta_kernel<A_MN, B_MN, BN2><<<clusters * 2, 192, pair_smem_bytes<BN2>(), st>>>(ta, tb, tc, p);
+  if (units < clusters) clusters = units;
+  gemm_bf16_2cta_kernel<A_MN, B_MN, BN2><<<clusters * 2, 192, pair_smem_bytes<BN2>(), st>>>(g);
   return (int)cudaGetLastError();
+}
+
+int launch2_layout(const GemmGroup& g, int a_mn, int b_mn, int bn, cudaStream_t st) {
+#define LAUNCH2(BN_)                                                   \
+  do {                                                                 \
+    if (!a_mn && !b_mn) return launch2<false, false, BN_>(g, st);      \
+    if (!a_mn && b_mn) return launch2<false, true, BN_>(g, st);        \
+    if (a_mn && !b_mn) return launch2<true, false, BN_>(g, st);        \
+    return launch2<true, true, BN_>(g, st);                            \
+  } while (0)
+  if (bn == 128) LAUNCH2(128);
+  if (bn == 192) {                                             // K-major B only (see pick_pair_bn)
+    if (!a_mn) return launch2<false, false, 192>(g, st);
+    return launch2<true, false, 192>(g, st);
+  }
+  LAUNCH2(256);
+#undef LAUNCH2
+}
+
+// Tensor maps, tile counts and the output path of one product.  n_store: 0, or a width in [N, ldc] that the kernel may
+// write (columns N.. receive zeros); max_slices: K slices that will write this output (the TMA-store path sums at most two).
+int fill_problem(GemmProblem& q, const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                 int ldb, int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, int n_store, int bn, int max_slices) {
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -2;
+  int rc;
+  if (!a_mn) rc = zen_tmap::get(A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 128, &q.ta);
+  else rc = zen_tmap::get(A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, 64, &q.ta);
+  if (rc) return rc;
+  if (!b_mn) rc = zen_tmap::get(B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, (uint32_t)(bn / 2), &q.tb);
+  else rc = zen_tmap::get(B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64, &q.tb);
+  if (rc) return rc;
+  // Plain bf16 output with a TMA-compatible layout: store through shared memory.  The stored width must be a
+  // multiple of 8 columns (16 bytes); a caller whose buffer has spare columns after N may allow them to be written
+  // (with zeros) by passing n_store = N rounded up.
+  if (n_store < N || n_store > ldc) n_store = N;
+  q.tma_store = (!out_fp32 && !accumulate && max_slices <= 2 && (ldc % 8) == 0 && (n_store % 8) == 0 &&
+                 (reinterpret_cast<uintptr_t>(C) % 16) == 0) ? 1 : 0;
+  q.tc = q.ta;
+  if (q.tma_store) {
+    rc = zen_tmap::get(C, (uint64_t)n_store, (uint64_t)M, (uint64_t)ldc, 64, 32, &q.tc);
+    if (rc) return rc;
+  }
+  q.C = C; q.bias = bias; q.M = M; q.N = N; q.K = K; q.ldc = ldc; q.out_fp32 = out_fp32; q.accumulate = accumulate;
+  q.num_m_pairs = (M + 255) / 256;
+  q.num_n_tiles = (N + bn - 1) / bn;
+  q.tile_start = 0;
+  return 0;
 }
 
 }  // namespace
@@ -590,57 +661,78 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
     if (!ws || !counters || ws_floats < tiles * splits * 2 * BM2 * 256 || (uint64_t)n_counters < tiles * 16) return -4;
     if (reinterpret_cast<uintptr_t>(ws) % 16) return -2;
   }
-  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -2;
-  CUtensorMap ta, tb;
-  int rc;
-  if (!a_mn) rc = zen_tmap::get(A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, 64, 128, &ta);
-  else rc = zen_tmap::get(A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, 64, &ta);
+  GemmGroup g;
+  int rc = fill_problem(g.pr[0], A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_fp32, accumulate, n_store, bn, splits);
   if (rc) return rc;
-  if (!b_mn) rc = zen_tmap::get(B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, 64, (uint32_t)(bn / 2), &tb);
-  else rc = zen_tmap::get(B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, 64, &tb);
-  if (rc) return rc;
-  // Plain bf16 output with a TMA-compatible layout: store through shared memory.  The stored width must be a
-  // multiple of 8 columns (16 bytes); a caller whose buffer has spare columns after N may allow them to be written
-  // (with zeros) by passing n_store = N rounded up.
-  if (n_store < N || n_store > ldc) n_store = N;
-  const int tma_store = (!out_fp32 && !accumulate && splits <= 2 && (ldc % 8) == 0 && (n_store % 8) == 0 &&
-                         (reinterpret_cast<uintptr_t>(C) % 16) == 0) ? 1 : 0;
-  CUtensorMap tc = ta;
-  if (tma_store) {
-    rc = zen_tmap::get(C, (uint64_t)n_store, (uint64_t)M, (uint64_t)ldc, 64, 32, &tc);
-    if (rc) return rc;
-  }
+  g.n = 1;
+  g.num_tiles = g.pr[0].num_m_pairs * g.pr[0].num_n_tiles;
+  g.splits = splits;
+  g.kb_per_split = kb_per;
+  g.ws = ws;
+  g.counters = counters;
   // Tail split: the tiles of the last, partly filled round of clusters run as two K slices each when both slices of
   // all of them fit in that round (so that the slices that wait for each other are resident together, as above) and K
   // is long enough for half a tile to outweigh the exchange of half an accumulator.
-  int tail = 0, tail_kb = 0;
-  if (splits == 1 && bn == 256 && tma_store && g_tail_min_kb > 0 && nkb >= g_tail_min_kb && ws && counters &&
+  g.tail = 0;
+  if (splits == 1 && bn == 256 && g.pr[0].tma_store && g_tail_min_kb > 0 && nkb >= g_tail_min_kb && ws && counters &&
       (reinterpret_cast<uintptr_t>(ws) % 16) == 0) {
     const int clusters = zen_tmap::sm_count() / 2;
-    const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
-    const int rem = tiles % clusters;
-    if (tiles > clusters && rem > 0 && 2 * rem <= clusters && ws_floats >= (uint64_t)rem * 2 * 2 * BM2 * 256 &&
-        n_counters >= rem * 16) {
-      tail = rem;
-      tail_kb = (nkb + 1) / 2;
+    const int rem = g.num_tiles % clusters;
+    if (g.num_tiles > clusters && rem > 0 && 2 * rem <= clusters && ws_floats >= (uint64_t)rem * 2 * 2 * BM2 * 256 &&
+        n_counters >= rem * 16)
+      g.tail = rem;
+  }
+  return launch2_layout(g, a_mn, b_mn, bn, (cudaStream_t)stream);
+}
+
+// Several products with the same operand layouts in ONE launch (see GemmProblem): the tiles of all of them form one
+// list that the persistent clusters walk, and the tiles of the last, partly filled round are cut into two K halves when
+// their outputs take the TMA-store path.  `descs`: n records of ZenGemmDesc; every product follows the contract of
+// zen_gemm_bf16_2cta (no bias).  ws / counters as for zen_gemm_bf16_2cta_splitk (may be null: no tail split).
+struct ZenGemmDesc {
+  const void* A;
+  const void* B;
+  void* C;
+  int32_t M, N, K, lda, ldb, ldc;
+  int32_t out_fp32, accumulate;
+};
+int zen_gemm_desc_size() { return (int)sizeof(ZenGemmDesc); }
+int zen_gemm_group_max() { return MAX_GROUP; }
+
+int zen_gemm_bf16_2cta_group(const ZenGemmDesc* descs, int n, int a_mn, int b_mn, float* ws, uint64_t ws_floats,
+                             int* counters, int n_counters, void* stream) {
+  if (!descs || n < 1 || n > MAX_GROUP) return -1;
+  GemmGroup g;
+  int tiles = 0, min_kb = 1 << 30;
+  for (int i = 0; i < n; ++i) {
+    const ZenGemmDesc& d = descs[i];
+    int rc = fill_problem(g.pr[i], d.A, d.B, d.C, nullptr, d.M, d.N, d.K, d.lda, d.ldb, d.ldc, a_mn, b_mn, d.out_fp32,
+                          d.accumulate, 0, 256, 2);
+    if (rc) return rc;
+    g.pr[i].tile_start = tiles;
+    tiles += g.pr[i].num_m_pairs * g.pr[i].num_n_tiles;
+    const int nkb = (d.K + BK2 - 1) / BK2;
+    if (nkb < min_kb) min_kb = nkb;
+  }
+  g.n = n;
+  g.num_tiles = tiles;
+  g.splits = 1;
+  g.kb_per_split = 1 << 30;
+  g.ws = ws;
+  g.counters = counters;
+  g.tail = 0;
+  const int clusters = zen_tmap::sm_count() / 2;
+  const int rem = tiles % clusters;
+  if (g_tail_min_kb > 0 && min_kb >= g_tail_min_kb && ws && counters && (reinterpret_cast<uintptr_t>(ws) % 16) == 0 &&
+      rem > 0 && 2 * rem <= clusters && ws_floats >= (uint64_t)rem * 2 * 2 * BM2 * 256 && n_counters >= rem * 16) {
+    bool ok = true;                                           // every tile of the tail must take the two-slice store path
+    for (int i = 0; i < n; ++i) {
+      const int end = g.pr[i].tile_start + g.pr[i].num_m_pairs * g.pr[i].num_n_tiles;
+      if (end > tiles - rem && !g.pr[i].tma_store) ok = false;
     }
+    if (ok) g.tail = rem;
   }
-  Gemm2Params p{C, bias, M, N, K, ldc, out_fp32, accumulate, 0, 0, splits, kb_per, ws, counters, tma_store, tail, tail_kb};
-  cudaStream_t st = (cudaStream_t)stream;
-#define LAUNCH2(BN_)                                                            \
-  do {                                                                          \
-    if (!a_mn && !b_mn) return launch2<false, false, BN_>(ta, tb, tc, p, st);   \
-    if (!a_mn && b_mn) return launch2<false, true, BN_>(ta, tb, tc, p, st);     \
-    if (a_mn && !b_mn) return launch2<true, false, BN_>(ta, tb, tc, p, st);     \
-    return launch2<true, true, BN_>(ta, tb, tc, p, st);                         \
-  } while (0)
-  if (bn == 128) LAUNCH2(128);
-  if (bn == 192) {                                             // K-major B only (see pick_pair_bn)
-    if (!a_mn) return launch2<false, false, 192>(ta, tb, tc, p, st);
-    return launch2<true, false, 192>(ta, tb, tc, p, st);
-  }
-  LAUNCH2(256);
-#undef LAUNCH2
+  return launch2_layout(g, a_mn, b_mn, 256, (cudaStream_t)stream);
 }
 
 // 0 = choose the N tile per call, 128 / 256 = force it (tests, measurements); returns the previous setting.

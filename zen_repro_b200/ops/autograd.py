@@ -95,8 +95,8 @@ class LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             a, b = (dy2, x2) if ctx.layout == "out_in" else (x2, dy2)
             if ctx.direct[0]:
-                G.gemm_tn(a, b, out=wp.grad, accumulate=not _take_fresh(wp))
-                wp.zen_ready(wp)
+                # written straight into the reducer's bucket view; may share one launch with the next few weight gradients
+                G.defer_tn(a, b, wp.grad, accumulate=not _take_fresh(wp), done=lambda: wp.zen_ready(wp))
             else:
                 dw = G.gemm_tn(a, b)
         if ctx.has_bias and ctx.needs_input_grad[2]:

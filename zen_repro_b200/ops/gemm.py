@@ -166,6 +166,72 @@ def gemm_tn(a, b, out=None, accumulate=False, out_dtype=None, bn=0):
     return _launch(a, b, M, N, K, True, True, None, out, accumulate, out_dtype, bn)
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# Deferred weight gradients.  The weight-gradient products of a transformer layer are small (27 / 9 / 36 / 36 output
+# tiles for GPT-2 small against 74 CTA pairs) and nothing downstream in backward waits for them, so a linear layer's
+# backward may queue its product here instead of launching it; GROUP_SIZE queued products (or the end of the backward
+# pass, or an explicit flush) go out as ONE launch whose clusters walk the tiles of all of them.
+class _GemmDesc(ctypes.Structure):
+    _fields_ = [("A", ctypes.c_void_p), ("B", ctypes.c_void_p), ("C", ctypes.c_void_p),
+                ("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32),
+                ("lda", ctypes.c_int32), ("ldb", ctypes.c_int32), ("ldc", ctypes.c_int32),
+                ("out_fp32", ctypes.c_int32), ("accumulate", ctypes.c_int32)]
+
+
+GROUP_SIZE = int(os.environ.get("ZEN_GEMM_GROUP", "4"))      # 0 / 1 = launch every weight gradient by itself
+_pending: list = []
+_callback_armed = [False]
+
+
+def defer_tn(a, b, out, accumulate: bool, done=None) -> None:
+    """Queue ``out (+)= a[K,M]^T @ b[K,N]`` (bf16 CUDA operands, ``out`` a 2-D bf16 / fp32 tensor with unit inner stride);
+    ``done()`` runs right after the launch that contains it has been enqueued.  Falls back to an immediate
+    :func:`gemm_tn` when grouping is off or the operands do not qualify."""
+    M, N = a.shape[-1], b.shape[-1]
+    K = a.numel() // M
+    ok = (GROUP_SIZE > 1 and _use_kernel(a, b) and _PAIR_MODE != "0" and M >= 256 and N >= 256 and out.is_cuda
+          and out.dim() == 2 and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32))
+    if not ok:
+        gemm_tn(a, b, out=out, accumulate=accumulate)
+        if done is not None:
+            done()
+        return
+    if any(item[2].data_ptr() == out.data_ptr() for item in _pending):
+        flush_deferred()                           # two products into one output never share a launch
+    a2, b2 = _rowmajor(a), _rowmajor(b)
+    _pending.append((a2, b2, out, M, N, K, bool(accumulate), done, torch.cuda.current_stream(a.device).cuda_stream))
+    if not _callback_armed[0]:
+        try:                                       # inside a backward pass: flush when it ends, whatever is still queued
+            torch.autograd.Variable._execution_engine.queue_callback(flush_deferred)
+            _callback_armed[0] = True
+        except RuntimeError:
+            pass                                   # not called from a backward pass: the caller flushes
+    if len(_pending) >= GROUP_SIZE:
+        flush_deferred()
+
+
+def flush_deferred() -> None:
+    """Launch whatever :func:`defer_tn` has queued (one launch per GROUP_SIZE products) and run the callbacks."""
+    _callback_armed[0] = False
+    while _pending:
+        batch = _pending[:min(max(GROUP_SIZE, 1), _native.lib().zen_gemm_group_max())]
+        del _pending[:len(batch)]
+        lib = _native.lib()
+        n = len(batch)
+        descs = (_GemmDesc * n)()
+        for i, (a2, b2, out, M, N, K, acc, _done, _st) in enumerate(batch):
+            descs[i] = _GemmDesc(a2.data_ptr(), b2.data_ptr(), out.data_ptr(), M, N, K, a2.stride(0), b2.stride(0),
+                                 out.stride(0), int(out.dtype == torch.float32), int(acc))
+        dev = batch[0][0].device
+        ws, cnt = _splitk_workspace(dev) if _TAIL_SPLIT else (None, None)
+        rc = lib.zen_gemm_bf16_2cta_group(descs, n, 1, 1, _native.ptr(ws), ctypes.c_uint64(ws.numel() if ws is not None else 0),
+                                          _native.ptr(cnt), cnt.numel() if cnt is not None else 0, _native.stream_ptr())
+        _native.check(rc, "zen_gemm_bf16_2cta_group")
+        for item in batch:
+            if item[7] is not None:
+                item[7]()
+
+
 def _finish(r, bias, out, accumulate, dtype):
     if bias is not None:
         r = r + bias.float()

@@ -225,6 +225,9 @@ class ZenDDP(nn.Module):
 
     def finalize_grads(self) -> None:
         """Join all bucket communication, write hook results back, then apply the sparse embedding rows."""
+        from ..ops import gemm as _gemm
+
+        _gemm.flush_deferred()               # weight gradients still queued for a grouped launch (normally none here)
         if self.require_sync:
             for b in self.buckets:
                 if not b.launched:           # parameters without a gradient this step, or undeclared uses
