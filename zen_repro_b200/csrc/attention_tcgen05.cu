@@ -49,6 +49,9 @@ struct FwdCfg {
   static constexpr int ATOMS = HD / 64;
   static constexpr int TILE_BYTES = 128 * HD * 2;
   static constexpr int KV_STAGES = (HD <= 128) ? 2 : 1;
+  // With two K / V stages S = Q K^T of tile j + 1 is issued as soon as the softmax warps have read the scores of tile j
+  // out of tensor memory, ahead of P V of tile j, so that it leaves the per-tile chain softmax -> P V -> next softmax.
+  static constexpr bool EARLY_SCORES = KV_STAGES >= 2;
   static constexpr int P_BYTES = 128 * 128 * 2;
   // No slack for re-aligning the base: the kernel has no static shared memory, so its dynamic window starts at the
   // CTA's shared-memory base, which is 1024-byte aligned; the kernel checks this and gives up cleanly otherwise.
@@ -79,7 +82,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
   uint64_t* s_full = bars + 5;
   uint64_t* p_ready = bars + 6;
   uint64_t* o_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* s_free = bars + 8;                                     // the softmax warps hold the scores in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -95,6 +99,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     mbar_init(s_full, 1);
     mbar_init(p_ready, 4);
     mbar_init(o_full, 1);
+    mbar_init(s_free, 4);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -131,18 +136,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
       // ---------------------------------------------------------------- MMA issuer
       bool ok = mbar_wait(q_full, 0, abort_flag, 2, &g_attn_error);
       const uint32_t qa = smem_u32(q_s), pa = smem_u32(p_s);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int st = j % C::KV_STAGES;
-        const uint32_t ph = (j / C::KV_STAGES) & 1;
-        if (!mbar_wait(&kv_full[st], ph, abort_flag, 3, &g_attn_error)) { ok = false; break; }
+      auto issue_scores = [&](int t) -> bool {
+        const int st = t % C::KV_STAGES;
+        const uint32_t ph = (t / C::KV_STAGES) & 1;
+        if (!mbar_wait(&kv_full[st], ph, abort_flag, 3, &g_attn_error)) return false;
         fence_after();
-        const uint32_t ka = smem_u32(kv_s + st * 2 * C::TILE_BYTES), va = ka + C::TILE_BYTES;
+        const uint32_t ka = smem_u32(kv_s + st * 2 * C::TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
           umma_bf16(tS, make_desc(qa + off, 16, 1024), make_desc(ka + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
         }
         umma_commit(s_full);
+        return true;
+      };
+      if (C::EARLY_SCORES && ok && ntiles > 0) ok = issue_scores(0);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int st = j % C::KV_STAGES;
+        if (!C::EARLY_SCORES) {
+          if (!issue_scores(j)) { ok = false; break; }
+        } else if (j + 1 < ntiles) {
+          if (!mbar_wait(s_free, j & 1, abort_flag, 8, &g_attn_error)) { ok = false; break; }
+          fence_after();
+          if (!issue_scores(j + 1)) { ok = false; break; }
+        }
+        const uint32_t va = smem_u32(kv_s + st * 2 * C::TILE_BYTES) + C::TILE_BYTES;
         if (!mbar_wait(p_ready, j & 1, abort_flag, 4, &g_attn_error)) { ok = false; break; }
         fence_after();
 #pragma unroll
@@ -163,7 +181,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
       if (!mbar_wait(s_full, j & 1, abort_flag, 5, &g_attn_error)) { ok = false; break; }
-      if (j > 0 && !mbar_wait(o_full, (j - 1) & 1, abort_flag, 6, &g_attn_error)) { ok = false; break; }
       fence_after();
       const bool diag = (j == qi);
       // the whole score row of this thread (128 values) in registers: one tensor-memory round trip
@@ -172,7 +189,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const AttnParams p) {
       tmem_ld32_nowait(tS + lane_addr + 32, r1);
       tmem_ld32_nowait(tS + lane_addr + 64, r2);
       tmem_ld32_nowait(tS + lane_addr + 96, r3);
+      // P of the previous tile is still being read by its P V product (and O is not final): wait while the loads fly
+      if (j > 0 && !mbar_wait(o_full, (j - 1) & 1, abort_flag, 6, &g_attn_error)) { tmem_wait_ld(); ok = false; break; }
       tmem_wait_ld();
+      if (C::EARLY_SCORES) {
+        fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+      }
       if (p.cap_a != 0.f) {
         const float a = p.cap_a, ia = 1.f / p.cap_a;
 #pragma unroll
@@ -328,6 +352,8 @@ struct DqCfg {
   static constexpr int ATOMS = HD / 64;
   static constexpr int TILE_BYTES = 128 * HD * 2;
   static constexpr int KV_STAGES = (HD <= 128) ? 2 : 1;     // hd 128: 64 + 128 + 32 KB = 224 KB, still one CTA's worth
+  // with two K / V stages the scores of tile j + 1 are issued ahead of dQ += dS K of tile j (see FwdCfg)
+  static constexpr bool EARLY_SCORES = KV_STAGES >= 2;
   static constexpr int DS_BYTES = 128 * 128 * 2;
   static constexpr int SMEM_BYTES = 2 * TILE_BYTES + KV_STAGES * 2 * TILE_BYTES + DS_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
@@ -353,7 +379,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
   uint64_t* sdp_full = bars + 5;
   uint64_t* ds_ready = bars + 6;
   uint64_t* dq_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* s_free = bars + 8;                                     // the softmax warps hold S and dP in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -369,6 +396,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
     mbar_init(sdp_full, 1);
     mbar_init(ds_ready, 8);
     mbar_init(dq_done, 1);
+    mbar_init(s_free, 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -406,10 +434,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
     if (lane == 0) {
       bool ok = mbar_wait(q_full, 0, abort_flag, 12, &g_attn_error);
       const uint32_t qa = smem_u32(q_s), doa = smem_u32(do_s), dsa = smem_u32(ds_s);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int st = j % C::KV_STAGES;
-        const uint32_t ph = (j / C::KV_STAGES) & 1;
-        if (!mbar_wait(&kv_full[st], ph, abort_flag, 13, &g_attn_error)) { ok = false; break; }
+      auto issue_scores = [&](int t) -> bool {
+        const int st = t % C::KV_STAGES;
+        const uint32_t ph = (t / C::KV_STAGES) & 1;
+        if (!mbar_wait(&kv_full[st], ph, abort_flag, 13, &g_attn_error)) return false;
         fence_after();
         const uint32_t ka = smem_u32(kv_s + st * 2 * C::TILE_BYTES), va = ka + C::TILE_BYTES;
 #pragma unroll
@@ -423,6 +451,19 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
           umma_bf16(tDP, make_desc(doa + off, 16, 1024), make_desc(va + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
         }
         umma_commit(sdp_full);
+        return true;
+      };
+      if (C::EARLY_SCORES && ok && ntiles > 0) ok = issue_scores(0);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int st = j % C::KV_STAGES;
+        if (!C::EARLY_SCORES) {
+          if (!issue_scores(j)) { ok = false; break; }
+        } else if (j + 1 < ntiles) {
+          if (!mbar_wait(s_free, j & 1, abort_flag, 17, &g_attn_error)) { ok = false; break; }
+          fence_after();
+          if (!issue_scores(j + 1)) { ok = false; break; }
+        }
+        const uint32_t ka = smem_u32(kv_s + st * 2 * C::TILE_BYTES);
         if (!mbar_wait(ds_ready, j & 1, abort_flag, 14, &g_attn_error)) { ok = false; break; }
         fence_after();
 #pragma unroll
@@ -445,7 +486,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
     bool ok = true;
     for (int j = 0; j < ntiles && ok; ++j) {
       if (!mbar_wait(sdp_full, j & 1, abort_flag, 15, &g_attn_error)) { ok = false; break; }
-      if (j > 0 && !mbar_wait(dq_done, (j - 1) & 1, abort_flag, 16, &g_attn_error)) { ok = false; break; }
       fence_after();
       const bool diag = (j == qi);
       const float cs = p.scale_log2, nl = -lse;
@@ -456,6 +496,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
         tmem_ld32_nowait(tDP + lane_addr + hf * 64, da);
         tmem_ld32_nowait(tDP + lane_addr + hf * 64 + 32, db);
         tmem_wait_ld();
+        if (C::EARLY_SCORES) {                                     // S and dP are in registers: the next tile's may be issued
+          fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_free);
+        }
         if (diag) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -463,21 +508,26 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_co
             if (hf * 64 + 32 + i > row) sb[i] = 0xff800000u;
           }
         }
-#define ZEN_DS_CHUNK(SS, DD, COL0)                                                                      \
-        {                                                                                               \
-          uint32_t pk[16];                                                                              \
-          _Pragma("unroll") for (int i = 0; i < 32; i += 2) {                                           \
-            const float p0 = ex2f(fmaf(__uint_as_float(SS[i]), cs, nl));                                \
-            const float p1 = ex2f(fmaf(__uint_as_float(SS[i + 1]), cs, nl));                            \
-            pk[i >> 1] = pack_bf16(p0 * (__uint_as_float(DD[i]) - Dr), p1 * (__uint_as_float(DD[i + 1]) - Dr)); \
-          }                                                                                             \
-          _Pragma("unroll") for (int q = 0; q < 4; ++q)                                                 \
-            *reinterpret_cast<uint4*>(ds_s + hf * 16384 + swz128(row, (COL0) + q * 8)) =                \
-                make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);                     \
+        // dS of this tile in registers first: the previous tile's copy in shared memory is still being read by its
+        // dQ product, which finishes meanwhile
+        uint32_t pk0[16], pk1[16];
+#define ZEN_DS_CHUNK(SS, DD, PK)                                                                        \
+        _Pragma("unroll") for (int i = 0; i < 32; i += 2) {                                             \
+          const float p0 = ex2f(fmaf(__uint_as_float(SS[i]), cs, nl));                                  \
+          const float p1 = ex2f(fmaf(__uint_as_float(SS[i + 1]), cs, nl));                              \
+          PK[i >> 1] = pack_bf16(p0 * (__uint_as_float(DD[i]) - Dr), p1 * (__uint_as_float(DD[i + 1]) - Dr)); \
         }
-        ZEN_DS_CHUNK(sa, da, 0)
-        ZEN_DS_CHUNK(sb, db, 32)
+        ZEN_DS_CHUNK(sa, da, pk0)
+        ZEN_DS_CHUNK(sb, db, pk1)
 #undef ZEN_DS_CHUNK
+        if (j > 0 && !mbar_wait(dq_done, (j - 1) & 1, abort_flag, 16, &g_attn_error)) { ok = false; break; }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          *reinterpret_cast<uint4*>(ds_s + hf * 16384 + swz128(row, q * 8)) =
+              make_uint4(pk0[4 * q], pk0[4 * q + 1], pk0[4 * q + 2], pk0[4 * q + 3]);
+          *reinterpret_cast<uint4*>(ds_s + hf * 16384 + swz128(row, 32 + q * 8)) =
+              make_uint4(pk1[4 * q], pk1[4 * q + 1], pk1[4 * q + 2], pk1[4 * q + 3]);
+        }
       }
       fence_before();
       fence_async_smem();
@@ -526,7 +576,10 @@ template <int HD>
 struct DkvCfg {
   static constexpr int ATOMS = HD / 64;
   static constexpr int TILE_BYTES = 128 * HD * 2;
-  static constexpr int Q_STAGES = (HD <= 64) ? 2 : 1;
+  static constexpr int Q_STAGES = (HD <= 64) ? 3 : 1;
+  // With more than one Q / dO stage the scores of tile i + 1 are issued as soon as the softmax warps have read those of
+  // tile i out of tensor memory, so the two score products leave the per-tile dependency chain.
+  static constexpr bool EARLY_SCORES = Q_STAGES >= 2;
   static constexpr int PT_BYTES = 128 * 128 * 2;
   static constexpr int SMEM_BYTES = 2 * TILE_BYTES + Q_STAGES * 2 * TILE_BYTES + 2 * PT_BYTES + 2 * 2 * 128 * 4 + 1024 + 256;
   static constexpr int TMEM_COLS = 512;
@@ -549,12 +602,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
   float* vec_s = reinterpret_cast<float*>(dst_s + C::PT_BYTES);     // [2 parities][lse | D][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(vec_s) + 2 * 2 * 128 * 4);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 3;
-  uint64_t* st_full = bars + 5;
-  uint64_t* pt_ready = bars + 6;
-  uint64_t* dkv_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* qdo_full = bars + 1;                                    // [3]
+  uint64_t* qdo_empty = bars + 4;                                   // [3]
+  uint64_t* st_full = bars + 7;
+  uint64_t* pt_ready = bars + 8;
+  uint64_t* dkv_done = bars + 9;
+  uint64_t* st_free = bars + 10;                                    // the softmax warps hold S and dP in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -568,10 +622,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
+    for (int i = 0; i < 3; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
     mbar_init(st_full, 1);
     mbar_init(pt_ready, 8);
     mbar_init(dkv_done, 1);
+    mbar_init(st_free, 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -610,10 +665,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
     if (lane == 0) {
       bool ok = mbar_wait(kv_full, 0, abort_flag, 22, &g_attn_error);
       const uint32_t ka = smem_u32(k_s), va = smem_u32(v_s), pta = smem_u32(pt_s), dsta = smem_u32(dst_s);
-      for (int it = 0; it < niter && ok; ++it) {
-        const int st = it % C::Q_STAGES;
-        const uint32_t ph = (it / C::Q_STAGES) & 1;
-        if (!mbar_wait(&qdo_full[st], ph, abort_flag, 23, &g_attn_error)) { ok = false; break; }
+      // S = Q K^T and dP = dO V^T of tile `t` into tensor memory
+      auto issue_scores = [&](int t) -> bool {
+        const int st = t % C::Q_STAGES;
+        const uint32_t ph = (t / C::Q_STAGES) & 1;
+        if (!mbar_wait(&qdo_full[st], ph, abort_flag, 23, &g_attn_error)) return false;
         fence_after();
         const uint32_t qa = smem_u32(qdo_s + st * 2 * C::TILE_BYTES), doa = qa + C::TILE_BYTES;
 #pragma unroll
@@ -627,6 +683,20 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
           umma_bf16(tDPT, make_desc(doa + off, 16, 1024), make_desc(va + off, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
         }
         umma_commit(st_full);
+        return true;
+      };
+      if (C::EARLY_SCORES && ok && niter > 0) ok = issue_scores(0);
+      for (int it = 0; it < niter && ok; ++it) {
+        const int st = it % C::Q_STAGES;
+        if (!C::EARLY_SCORES) {
+          if (!issue_scores(it)) { ok = false; break; }
+        } else if (it + 1 < niter) {
+          // the scores of the next tile, as soon as the softmax warps have taken this tile's out of tensor memory
+          if (!mbar_wait(st_free, it & 1, abort_flag, 28, &g_attn_error)) { ok = false; break; }
+          fence_after();
+          if (!issue_scores(it + 1)) { ok = false; break; }
+        }
+        const uint32_t qa = smem_u32(qdo_s + st * 2 * C::TILE_BYTES), doa = qa + C::TILE_BYTES;
         if (!mbar_wait(pt_ready, it & 1, abort_flag, 24, &g_attn_error)) { ok = false; break; }
         fence_after();
 #pragma unroll
@@ -657,7 +727,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
       const size_t vec = ((size_t)b * p.Hq + h) * p.S + qi * 128 + row;
       const float nl = -p.lse2[vec], Dr = p.D[vec];
       if (!mbar_wait(st_full, it & 1, abort_flag, 25, &g_attn_error)) { ok = false; break; }
-      if (it > 0 && !mbar_wait(dkv_done, (it - 1) & 1, abort_flag, 26, &g_attn_error)) { ok = false; break; }
       fence_after();
       const bool diag = (qi == kj);
       const float cs = p.scale_log2;
@@ -668,6 +737,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
         tmem_ld32_nowait(tDPT + lane_addr + hf * 64, da);
         tmem_ld32_nowait(tDPT + lane_addr + hf * 64 + 32, db);
         tmem_wait_ld();
+        if (C::EARLY_SCORES) {                                     // S and dP are in registers: the next tile's may be issued
+          fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(st_free);
+        }
         if (diag) {                                                // causal: key column beyond the query row
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -675,24 +749,28 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_c
             if (hf * 64 + 32 + i > row) sb[i] = 0xff800000u;
           }
         }
-#define ZEN_DKV_CHUNK(SS, DD, COL0)                                                                     \
-        {                                                                                               \
-          uint32_t pk[16], dk[16];                                                                      \
-          _Pragma("unroll") for (int i = 0; i < 32; i += 2) {                                           \
-            const float p0 = ex2f(fmaf(__uint_as_float(SS[i]), cs, nl));                                \
-            const float p1 = ex2f(fmaf(__uint_as_float(SS[i + 1]), cs, nl));                            \
-            pk[i >> 1] = pack_bf16(p0, p1);                                                             \
-            dk[i >> 1] = pack_bf16(p0 * (__uint_as_float(DD[i]) - Dr), p1 * (__uint_as_float(DD[i + 1]) - Dr)); \
-          }                                                                                             \
-          _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                               \
-            const uint32_t off = hf * 16384 + swz128(row, (COL0) + q * 8);                              \
-            *reinterpret_cast<uint4*>(pt_s + off) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]); \
-            *reinterpret_cast<uint4*>(dst_s + off) = make_uint4(dk[4 * q], dk[4 * q + 1], dk[4 * q + 2], dk[4 * q + 3]); \
-          }                                                                                             \
+        // P and dS of this tile in registers first: the shared-memory copies of the previous tile are still being read
+        // by its dV / dK products, which finish meanwhile
+        uint32_t pk0[16], dk0[16], pk1[16], dk1[16];
+#define ZEN_DKV_CHUNK(SS, DD, PK, DK)                                                                   \
+        _Pragma("unroll") for (int i = 0; i < 32; i += 2) {                                             \
+          const float p0 = ex2f(fmaf(__uint_as_float(SS[i]), cs, nl));                                  \
+          const float p1 = ex2f(fmaf(__uint_as_float(SS[i + 1]), cs, nl));                              \
+          PK[i >> 1] = pack_bf16(p0, p1);                                                               \
+          DK[i >> 1] = pack_bf16(p0 * (__uint_as_float(DD[i]) - Dr), p1 * (__uint_as_float(DD[i + 1]) - Dr)); \
         }
-        ZEN_DKV_CHUNK(sa, da, 0)
-        ZEN_DKV_CHUNK(sb, db, 32)
+        ZEN_DKV_CHUNK(sa, da, pk0, dk0)
+        ZEN_DKV_CHUNK(sb, db, pk1, dk1)
 #undef ZEN_DKV_CHUNK
+        if (it > 0 && !mbar_wait(dkv_done, (it - 1) & 1, abort_flag, 26, &g_attn_error)) { ok = false; break; }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off0 = hf * 16384 + swz128(row, q * 8), off1 = hf * 16384 + swz128(row, 32 + q * 8);
+          *reinterpret_cast<uint4*>(pt_s + off0) = make_uint4(pk0[4 * q], pk0[4 * q + 1], pk0[4 * q + 2], pk0[4 * q + 3]);
+          *reinterpret_cast<uint4*>(dst_s + off0) = make_uint4(dk0[4 * q], dk0[4 * q + 1], dk0[4 * q + 2], dk0[4 * q + 3]);
+          *reinterpret_cast<uint4*>(pt_s + off1) = make_uint4(pk1[4 * q], pk1[4 * q + 1], pk1[4 * q + 2], pk1[4 * q + 3]);
+          *reinterpret_cast<uint4*>(dst_s + off1) = make_uint4(dk1[4 * q], dk1[4 * q + 1], dk1[4 * q + 2], dk1[4 * q + 3]);
+        }
       }
       fence_before();
       fence_async_smem();
@@ -1036,6 +1114,9 @@ struct Rs64Cfg {
   static constexpr int W_BYTES = 128 * 64 * 2;
   static constexpr int SMEM_BYTES = 2 * RES_BYTES + STAGES * 2 * STR_BYTES + 2 * W_BYTES + STAGES * 512 + 1024 + 256;
   static constexpr int TMEM_COLS = 256;
+  // Issuing the next tile's scores ahead of this tile's accumulating products (as the 128 x 128 kernels do) measured
+  // 3 % slower here: the second CTA of the SM already fills the gaps, and the two-stage ring leaves no tile to run ahead on.
+  static constexpr bool EARLY_SCORES = false;
   static constexpr uint32_t IDESC_S = make_idesc(128, 64, false, false);
   static constexpr uint32_t IDESC_ACC = make_idesc(128, 64, false, true);
 };
@@ -1062,7 +1143,8 @@ attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_
   uint64_t* sdp_full = bars + 5;
   uint64_t* w_ready = bars + 6;
   uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* s_free = bars + 8;                                    // the softmax warps hold S' and dP' in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1082,6 +1164,7 @@ attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_
     mbar_init(sdp_full, 1);
     mbar_init(w_ready, 8);
     mbar_init(acc_done, 1);
+    mbar_init(s_free, 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -1130,10 +1213,11 @@ attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_
     if (lane == 0) {
       bool ok = mbar_wait(r_full, 0, abort_flag, 42, &g_attn_error);
       const uint32_t r1a = smem_u32(r1_s), r2a = smem_u32(r2_s), w1a = smem_u32(w1_s), w2a = smem_u32(w2_s);
-      for (int it = 0; it < niter && ok; ++it) {
-        const int st = it % C::STAGES;
-        const uint32_t ph = (it / C::STAGES) & 1;
-        if (!mbar_wait(&t_full[st], ph, abort_flag, 43, &g_attn_error)) { ok = false; break; }
+      // S' and dP' of streamed tile `t`
+      auto issue_scores = [&](int t) -> bool {
+        const int st = t % C::STAGES;
+        const uint32_t ph = (t / C::STAGES) & 1;
+        if (!mbar_wait(&t_full[st], ph, abort_flag, 43, &g_attn_error)) return false;
         fence_after();
         const uint32_t t1a = smem_u32(t_s + st * 2 * C::STR_BYTES), t2a = t1a + C::STR_BYTES;
 #pragma unroll
@@ -1143,6 +1227,19 @@ attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_
         for (int kk = 0; kk < HD / 16; ++kk)
           umma_bf16(tDP, make_desc(r2a + kk * 32, 16, 1024), make_desc(t2a + kk * 32, 16, 1024), C::IDESC_S, kk > 0 ? 1u : 0u);
         umma_commit(sdp_full);
+        return true;
+      };
+      if (C::EARLY_SCORES && ok && niter > 0) ok = issue_scores(0);
+      for (int it = 0; it < niter && ok; ++it) {
+        const int st = it % C::STAGES;
+        if (!C::EARLY_SCORES) {
+          if (!issue_scores(it)) { ok = false; break; }
+        } else if (it + 1 < niter) {
+          if (!mbar_wait(s_free, it & 1, abort_flag, 50, &g_attn_error)) { ok = false; break; }
+          fence_after();
+          if (!issue_scores(it + 1)) { ok = false; break; }
+        }
+        const uint32_t t1a = smem_u32(t_s + st * 2 * C::STR_BYTES), t2a = t1a + C::STR_BYTES;
         if (!mbar_wait(w_ready, it & 1, abort_flag, 44, &g_attn_error)) { ok = false; break; }
         fence_after();
 #pragma unroll
@@ -1191,12 +1288,18 @@ attn_bwd64_kernel(const __grid_constant__ CUtensorMap tmap_qkv128, const __grid_
       const int h = (MODE == RS_DQ) ? hres : g * rep + it / per_head;
       const int t = (MODE == RS_DQ) ? it : 2 * ri + it % per_head;
       if (!mbar_wait(sdp_full, it & 1, abort_flag, 45, &g_attn_error)) { ok = false; break; }
-      if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, abort_flag, 46, &g_attn_error)) { ok = false; break; }
       fence_after();
       uint32_t sa[32], da[32];
       tmem_ld32_nowait(tS + lane_addr + hf * 32, sa);
       tmem_ld32_nowait(tDP + lane_addr + hf * 32, da);
+      // the weights of the previous tile are still being read by its accumulating products: wait while the loads fly
+      if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, abort_flag, 46, &g_attn_error)) { tmem_wait_ld(); ok = false; break; }
       tmem_wait_ld();
+      if (C::EARLY_SCORES) {                                      // S' and dP' are in registers: the next tile's may be issued
+        fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+      }
       const int res_idx = ri * 128 + row, str0 = t * 64 + hf * 32;
       const bool need_mask = (MODE == RS_DQ) ? (str0 + 31 > ri * 128) : (str0 < ri * 128 + 128);
       if (need_mask) {

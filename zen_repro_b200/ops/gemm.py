@@ -189,7 +189,9 @@ def defer_tn(a, b, out, accumulate: bool, done=None) -> None:
     :func:`gemm_tn` when grouping is off or the operands do not qualify."""
     M, N = a.shape[-1], b.shape[-1]
     K = a.numel() // M
-    ok = (GROUP_SIZE > 1 and _use_kernel(a, b) and _PAIR_MODE != "0" and M >= 256 and N >= 256 and out.is_cuda
+    # products with many tiles fill the clusters by themselves; grouping them only delays their gradient
+    small = ((M + 255) // 256) * ((N + 255) // 256) <= 2 * _clusters()
+    ok = (GROUP_SIZE > 1 and small and _use_kernel(a, b) and _PAIR_MODE != "0" and M >= 256 and N >= 256 and out.is_cuda
           and out.dim() == 2 and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32))
     if not ok:
         gemm_tn(a, b, out=out, accumulate=accumulate)
