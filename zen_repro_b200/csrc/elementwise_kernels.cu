@@ -269,7 +269,7 @@ norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __re
 #define NORMW_WARPS 8
 
 template <typename T, bool kLayer, int NV>
-__global__ void __launch_bounds__(NORMW_WARPS * 32)
+__global__ void __launch_bounds__(NORMW_WARPS * 32, 4)      // 64 registers: four CTAs (32 warps, a row each) per SM
 norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ wgt,
                      const T* __restrict__ bias, T* __restrict__ y, T* __restrict__ hout, float* __restrict__ rstd_out,
                      float* __restrict__ mean_out, int rows, int cols, float eps, int unit_offset) {
@@ -341,7 +341,7 @@ norm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res, const T
 }
 
 template <typename T, bool kLayer, int NV, bool kParams>
-__global__ void __launch_bounds__(NORMW_WARPS * 32)
+__global__ void __launch_bounds__(NORMW_WARPS * 32, (NV <= 3 && !kParams) ? 4 : 2)   // up to 768 columns: four CTAs per SM
 norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T* __restrict__ wgt,
                      const float* __restrict__ rstd_in, const float* __restrict__ mean_in, const T* __restrict__ dres,
                      T* __restrict__ dh, float* __restrict__ part_dw, float* __restrict__ part_db, int rows, int cols,
@@ -351,18 +351,15 @@ norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T*
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = (gridDim.x * blockDim.x) >> 5;
   const int nv = cols / 8;
   float aw[kParams ? NV : 1][8], ab[(kLayer && kParams) ? NV : 1][8];
-  float wv[NV][8];
+  // the weights stay packed (a warp usually handles one or two rows: half the registers of an unpacked copy, and with
+  // them a fourth CTA per SM)
+  typename Pack<T>::raw_t rw[NV];
+  const float woff = (!kLayer && unit_offset) ? 1.f : 0.f;
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) { if (kParams) { aw[j][i] = 0.f; if (kLayer) ab[j][i] = 0.f; } wv[j][i] = 0.f; }
-    if (lane + 32 * j < nv) {
-      Vec8<T>::load(wgt + (size_t)(lane + 32 * j) * 8, wv[j]);
-      if (!kLayer && unit_offset) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) wv[j][i] += 1.f;
-      }
-    }
+    for (int i = 0; i < 8; ++i) { if (kParams) { aw[j][i] = 0.f; if (kLayer) ab[j][i] = 0.f; } }
+    if (lane + 32 * j < nv) rw[j] = Pack<T>::load(wgt + (size_t)(lane + 32 * j) * 8);
   }
   for (int row = gw; row < rows; row += nw) {
     const size_t base = (size_t)row * cols;
@@ -380,14 +377,15 @@ norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T*
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       if (lane + 32 * j < nv) {
-        float d[8], xh[8];
+        float d[8], xh[8], wv[8];
         Pack<T>::unpack(rd[j], d);
         Pack<T>::unpack(rh[j], xh);
+        Pack<T>::unpack(rw[j], wv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           xh[i] = (xh[i] - mean) * rstd;
           if (kParams) { aw[j][i] += d[i] * xh[i]; if (kLayer) ab[j][i] += d[i]; }
-          const float g = d[i] * wv[j][i];
+          const float g = d[i] * (wv[i] + woff);
           s1 += g;
           s2 += g * xh[i];
         }
@@ -399,14 +397,15 @@ norm_bwd_warp_kernel(const T* __restrict__ dy, const T* __restrict__ h, const T*
     for (int j = 0; j < NV; ++j) {
       const int v = lane + 32 * j;
       if (v < nv) {
-        float d[8], xh[8], o[8];
+        float d[8], xh[8], o[8], wv[8];
         Pack<T>::unpack(rd[j], d);
         Pack<T>::unpack(rh[j], xh);
+        Pack<T>::unpack(rw[j], wv);
         if (dres) Vec8<T>::load(dres + base + (size_t)v * 8, o);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float xhat = (xh[i] - mean) * rstd;
-          const float t = rstd * (d[i] * wv[j][i] - s1 - xhat * s2);
+          const float t = rstd * (d[i] * (wv[i] + woff) - s1 - xhat * s2);
           o[i] = dres ? o[i] + t : t;
         }
         Vec8<T>::store(dh + base + (size_t)v * 8, o);
@@ -1122,6 +1121,7 @@ int zen_norm_bwd_parts(int rows) { const int a = cap_grid((size_t)rows, 2), b = 
 #define NORMW_NV_DISPATCH(cols, ...)                        \
   if (cols <= 256) { constexpr int NV = 1; __VA_ARGS__; }   \
   else if (cols <= 512) { constexpr int NV = 2; __VA_ARGS__; } \
+  else if (cols <= 768) { constexpr int NV = 3; __VA_ARGS__; } \
   else { constexpr int NV = 4; __VA_ARGS__; }
 
 int zen_norm_fwd(const void* x, const void* res, const void* w, const void* b, void* y, void* hout, float* rstd,
