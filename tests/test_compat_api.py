@@ -1,3 +1,4 @@
+import pytest
 import torch
 
 from _dist_util import run_gloo
@@ -64,3 +65,25 @@ def test_compress_keeps_about_top_k_percent():
     assert 0.03 < frac < 0.08
     small = torch.randn(4096)
     assert compress_with_allgather(1, small, None) is small
+
+
+def test_every_native_entry_point_named_in_the_package_is_exported():
+    """A C entry point whose signature mentions a type from an unnamed namespace silently gets internal linkage; catch
+    that (and plain typos) without a GPU: every ``zen_*`` name the Python package calls must be a symbol of the library."""
+    import ctypes
+    import pathlib
+    import re
+
+    from zen_repro_b200 import build as zbuild
+
+    path = zbuild.lib_path()
+    if not path.exists():
+        pytest.skip("native library not built")
+    cdll = ctypes.CDLL(str(path))
+    root = pathlib.Path(zbuild.__file__).parent
+    names = set()
+    for f in root.rglob("*.py"):
+        names |= set(re.findall(r"\b(?:lib\(\)|lib|_lib)\.(zen_[a-z0-9_]+)\b", f.read_text()))
+    assert len(names) > 40
+    missing = sorted(n for n in names if not hasattr(cdll, n))
+    assert not missing, missing

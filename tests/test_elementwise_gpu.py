@@ -176,6 +176,30 @@ def test_bias_gradient_rides_with_the_activation_backward():
     torch.testing.assert_close(grads[0][1].float(), h.grad.sum((0, 1)), atol=0.5, rtol=5e-2)
 
 
+def test_queued_column_reductions_go_out_as_one_launch():
+    """Reductions of different widths and part counts, one with a second (part, out) pair, one accumulating: the grouped
+    kernel gives what the single reductions give, callbacks fire in order after the launch."""
+    torch.manual_seed(6)
+    specs = [(256, 768, False, False), (256, 3072, True, False), (37, 2304, False, True), (256, 768, True, True), (8, 64, False, False)]
+    jobs, fired = [], []
+    for i, (parts, cols, acc, pair) in enumerate(specs):
+        part = torch.randn(parts, cols, device=DEV)
+        out = torch.full((cols,), 0.5, device=DEV, dtype=torch.bfloat16)
+        part2 = torch.randn(parts, cols, device=DEV) if pair else None
+        out2 = torch.full((cols,), -1.0, device=DEV, dtype=torch.bfloat16) if pair else None
+        jobs.append((part, out, acc, part2, out2))
+        E._queue_reduce(part, parts, out, acc, (lambda i=i: fired.append(i)), part2, out2)
+    assert fired == []
+    E.flush_colreduce()
+    assert fired == list(range(len(specs)))
+    for part, out, acc, part2, out2 in jobs:
+        want = part.sum(0) + (0.5 if acc else 0.0)
+        torch.testing.assert_close(out.float(), want, atol=0.15, rtol=2e-2)
+        if part2 is not None:
+            want2 = part2.sum(0) + (-1.0 if acc else 0.0)
+            torch.testing.assert_close(out2.float(), want2, atol=0.15, rtol=2e-2)
+
+
 def test_cuda_graph_step_matches_eager_steps():
     """The captured training step (replayed) follows the same loss trajectory as launching every kernel from the host."""
     from zen_repro_b200.trainer import TrainConfig, Trainer

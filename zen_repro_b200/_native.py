@@ -24,7 +24,7 @@ class NativeUnavailable(RuntimeError):
 # kernels launched by one call of each entry point (entries not listed launch one, helpers launch none)
 KERNELS_PER_CALL = {
     "zen_gather_push": 1, "zen_densify": 2, "zen_sparse_allreduce": 5, "zen_sample_exchange": 2, "zen_sample_xchg_size": 0, "zen_mc_ar_ctx_size": 0, "zen_norm_bwd": 2, "zen_colsum": 2, "zen_embedding_bwd_rows": 5,
-    "zen_row_gather_push": 2, "zen_attn_bwd": 3, "zen_attn_error": 0, "zen_attn_bwd64_variant": 0, "zen_gemm2_force_bn": 0, "zen_gemm2_tail_split": 0, "zen_gemm_desc_size": 0, "zen_gemm_group_max": 0, "zen_act_bwd_colsum": 1, "zen_act_colsum_parts": 0, "zen_colsum_reduce": 1, "zen_select_kth": 7, "zen_gemm2_error": 0, "zen_gemm_ar_ctx_size": 0, "zen_sparse_ctx_size": 0, "zen_row_ctx_size": 0, "zen_adam_tensor_size": 0,
+    "zen_row_gather_push": 2, "zen_attn_bwd": 3, "zen_attn_error": 0, "zen_attn_bwd64_variant": 0, "zen_gemm2_force_bn": 0, "zen_gemm2_tail_split": 0, "zen_gemm_desc_size": 0, "zen_gemm_group_max": 0, "zen_act_bwd_colsum": 1, "zen_act_colsum_parts": 0, "zen_colsum_reduce": 1, "zen_colsum_partial": 1, "zen_colreduce_multi": 1, "zen_colreduce_job_size": 0, "zen_colreduce_max_jobs": 0, "zen_norm_bwd_parts_used": 0, "zen_norm_bwd_ex": 2, "zen_select_kth": 7, "zen_gemm2_error": 0, "zen_gemm_ar_ctx_size": 0, "zen_sparse_ctx_size": 0, "zen_row_ctx_size": 0, "zen_adam_tensor_size": 0,
     "zen_norm_bwd_parts": 0, "zen_colsum_parts": 0, "zen_gemm_error": 0, "zen_sym_alloc": 0, "zen_sym_free": 0,
     "zen_ipc_get_handle": 0, "zen_ipc_open": 0, "zen_ipc_close": 0, "zen_enable_peer": 0, "zen_ipc_handle_size": 0,
 }

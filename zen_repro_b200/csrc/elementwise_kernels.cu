@@ -513,6 +513,44 @@ colreduce_kernel(const float* __restrict__ part, T* __restrict__ out, int nparts
   }
 }
 
+// Several reductions of that kind in one launch (the bias and norm-parameter gradients of a layer): blockIdx.y = 2 * job
+// (+ 1 for the job's second pair, if it has one), blockIdx.x = 32-column block of that job.
+#define COLREDUCE_MAX_JOBS 8
+struct ColReduceJob {
+  const float* part;
+  void* out;
+  const float* part2;             // optional second (part, out) pair of the same shape (dw and db of a LayerNorm)
+  void* out2;
+  int nparts, cols, accumulate, pad;
+};
+struct ColReduceJobs {
+  ColReduceJob j[COLREDUCE_MAX_JOBS];
+  int n;
+};
+template <typename T>
+__global__ void __launch_bounds__(1024)
+colreduce_multi_kernel(const ColReduceJobs jobs) {
+  const ColReduceJob& jb = jobs.j[blockIdx.y >> 1];
+  const float* part = (blockIdx.y & 1) ? jb.part2 : jb.part;
+  T* out = reinterpret_cast<T*>((blockIdx.y & 1) ? jb.out2 : jb.out);
+  if (!part || !out || (int)blockIdx.x * 32 >= jb.cols) return;                // uniform over the CTA
+  __shared__ float sh[32][33];
+  const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + x;
+  float s = 0.f;
+  if (c < jb.cols)
+    for (int p = y; p < jb.nparts; p += 32) s += part[(size_t)p * jb.cols + c];
+  sh[y][x] = s;
+  __syncthreads();
+  if (y == 0 && c < jb.cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t += sh[i][x];
+    if (jb.accumulate) t += ZenVal<T>::to_f(out[c]);
+    out[c] = ZenVal<T>::from_f(t);
+  }
+}
+
 // Column sums of a [rows, cols] matrix: CTA b sums rows [b * COLSUM_ROWS, ...) for every column (thread = one
 // 8-column vector, coalesced along the row) into part[b][cols] (bias gradients).
 #define COLSUM_ROWS 32
@@ -1150,9 +1188,35 @@ int zen_norm_fwd(const void* x, const void* res, const void* w, const void* b, v
 
 // part_dw / part_db: fp32 scratch of zen_norm_bwd_parts(rows) * cols each.  dw / db are written (or
 // accumulated into when accumulate != 0) in dtype.
+int zen_norm_bwd_ex(const void* dy, const void* h, const void* w, const float* rstd, const float* mean, const void* dres,
+                    void* dh, float* part_dw, float* part_db, void* dw, void* db, int rows, int cols, int layer,
+                    int unit_offset, int accumulate, int dtype, int skip_reduce, void* stream);
+
 int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const float* mean, const void* dres,
                  void* dh, float* part_dw, float* part_db, void* dw, void* db, int rows, int cols, int layer,
                  int unit_offset, int accumulate, int dtype, void* stream) {
+  return zen_norm_bwd_ex(dy, h, w, rstd, mean, dres, dh, part_dw, part_db, dw, db, rows, cols, layer, unit_offset, accumulate,
+                         dtype, 0, stream);
+}
+
+// Rows per CTA of the column-sum pass of the wide-row norm backward: 32, fewer when that would leave SMs idle.
+static int norm_wide_rpc(int rows) {
+  int rpc = 32;
+  while (rpc > 8 && (rows + rpc - 1) / rpc < 4 * sm_count_e() && (rows + rpc / 2 - 1) / (rpc / 2) <= zen_norm_bwd_parts(rows)) rpc /= 2;
+  return rpc;
+}
+// Partial rows that zen_norm_bwd_ex leaves in part_dw / part_db for a matrix of this shape.
+int zen_norm_bwd_parts_used(int rows, int cols) {
+  if (norm_warp_path(cols, 0)) return (rows + 31) / 32;
+  const int rpc = norm_wide_rpc(rows);
+  return (rows + rpc - 1) / rpc;
+}
+
+// skip_reduce != 0: leave the partial sums in part_dw / part_db (zen_norm_bwd_parts_used(rows, cols) rows of cols floats)
+// for a later zen_colreduce_multi; dw / db are not touched.
+int zen_norm_bwd_ex(const void* dy, const void* h, const void* w, const float* rstd, const float* mean, const void* dres,
+                    void* dh, float* part_dw, float* part_db, void* dw, void* db, int rows, int cols, int layer,
+                    int unit_offset, int accumulate, int dtype, int skip_reduce, void* stream) {
   if (cols % 8 || cols > NORM_THREADS * NORM_MAXV * 8) return -2;
   cudaStream_t st = (cudaStream_t)stream;
   const int grid = cap_grid((size_t)rows, 2);
@@ -1167,7 +1231,8 @@ int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd
       });
       if (layer) norm_dwdb_partial_kernel<T, true><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, 32);
       else norm_dwdb_partial_kernel<T, false><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, 32);
-      if (layer && db) colreduce_kernel<T><<<dim3((cols + 31) / 32, 2), 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate, part_db, (T*)db);
+      if (skip_reduce) {}
+      else if (layer && db) colreduce_kernel<T><<<dim3((cols + 31) / 32, 2), 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate, part_db, (T*)db);
       else colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate);
     });
     return (int)cudaGetLastError();
@@ -1178,8 +1243,7 @@ int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd
   const int g2 = cap_grid((size_t)rows, 6);
   // rows per CTA of the column-sum pass: 32, fewer when that would leave SMs idle (the partial buffer holds
   // zen_norm_bwd_parts(rows) rows)
-  int rpc = 32;
-  while (rpc > 8 && (rows + rpc - 1) / rpc < 4 * sm_count_e() && (rows + rpc / 2 - 1) / (rpc / 2) <= zen_norm_bwd_parts(rows)) rpc /= 2;
+  const int rpc = norm_wide_rpc(rows);
   const int parts = (rows + rpc - 1) / rpc;
   DISPATCH_T(dtype, {
     NORM_NV_DISPATCH(cols, {
@@ -1188,7 +1252,8 @@ int zen_norm_bwd(const void* dy, const void* h, const void* w, const float* rstd
     });
     if (layer) norm_dwdb_partial_kernel<T, true><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, rpc);
     else norm_dwdb_partial_kernel<T, false><<<dim3(parts, (cols + 2047) / 2048), 256, 0, st>>>((const T*)dy, (const T*)h, rstd, mean, part_dw, part_db, rows, cols, rpc);
-    if (layer && db) colreduce_kernel<T><<<dim3((cols + 31) / 32, 2), 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate, part_db, (T*)db);
+    if (skip_reduce) {}
+    else if (layer && db) colreduce_kernel<T><<<dim3((cols + 31) / 32, 2), 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate, part_db, (T*)db);
     else colreduce_kernel<T><<<(cols + 31) / 32, 1024, 0, st>>>(part_dw, (T*)dw, parts, cols, accumulate);
   });
   return (int)cudaGetLastError();
@@ -1242,6 +1307,33 @@ int zen_act_bwd_colsum(const void* a, const void* dout, void* da, float* part, i
   if (threads > 512) threads = 512;
   const int rpc = act_colsum_rows_per_cta(rows);
   DISPATCH_T(dtype, act_bwd_colsum_kernel<T><<<(rows + rpc - 1) / rpc, threads, 0, (cudaStream_t)stream>>>((const T*)a, (const T*)dout, (T*)da, part, rows, inner, mode, rpc));
+  return (int)cudaGetLastError();
+}
+
+// First half of zen_colsum only: part[zen_colsum_parts(rows)][cols] partial column sums of a.
+int zen_colsum_partial(const void* a, float* part, int rows, int cols, int dtype, void* stream) {
+  if (cols % 8) return -2;
+  DISPATCH_T(dtype, colsum_partial_kernel<T><<<zen_colsum_parts(rows), 256, 0, (cudaStream_t)stream>>>((const T*)a, part, rows, cols));
+  return (int)cudaGetLastError();
+}
+
+// Up to COLREDUCE_MAX_JOBS reductions out[c] (+)= sum_p part[p][c] in ONE launch; a job may carry a second (part2, out2)
+// pair of the same shape.  All outputs have type `dtype`.
+int zen_colreduce_job_size() { return (int)sizeof(ColReduceJob); }
+int zen_colreduce_max_jobs() { return COLREDUCE_MAX_JOBS; }
+int zen_colreduce_multi(const void* jobs_, int n, int dtype, void* stream) {
+  const ColReduceJob* jobs = static_cast<const ColReduceJob*>(jobs_);      // records of zen_colreduce_job_size() bytes
+  if (!jobs || n < 1 || n > COLREDUCE_MAX_JOBS) return -2;
+  ColReduceJobs t;
+  int max_cols = 0;
+  for (int i = 0; i < n; ++i) {
+    t.j[i] = jobs[i];
+    if (jobs[i].nparts <= 0 || jobs[i].cols <= 0 || !jobs[i].part || !jobs[i].out) return -2;
+    if (jobs[i].cols > max_cols) max_cols = jobs[i].cols;
+  }
+  for (int i = n; i < COLREDUCE_MAX_JOBS; ++i) t.j[i] = ColReduceJob{nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0};
+  t.n = n;
+  DISPATCH_T(dtype, colreduce_multi_kernel<T><<<dim3((max_cols + 31) / 32, 2 * n), 1024, 0, (cudaStream_t)stream>>>(t));
   return (int)cudaGetLastError();
 }
 

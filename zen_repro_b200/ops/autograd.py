@@ -105,11 +105,11 @@ class LinearFn(torch.autograd.Function):
             if part is not None and (part.shape[1] != dy2.shape[1] or part.device != dy2.device):
                 part = None
             if ctx.direct[1]:
+                ready = lambda: bp.zen_ready(bp)     # after the (possibly queued) fold of the partial sums
                 if part is not None:
-                    E.colsum_from_parts(part, out=bp.grad, accumulate=not _take_fresh(bp))
+                    E.colsum_from_parts(part, out=bp.grad, accumulate=not _take_fresh(bp), done=ready)
                 else:
-                    E.colsum(dy2, out=bp.grad, accumulate=not _take_fresh(bp))
-                bp.zen_ready(bp)
+                    E.colsum(dy2, out=bp.grad, accumulate=not _take_fresh(bp), done=ready)
             elif part is not None:
                 db = E.colsum_from_parts(part, torch.empty(dy2.shape[1], dtype=dy2.dtype, device=dy2.device), accumulate=False)
             else:
@@ -148,14 +148,16 @@ class NormFn(torch.autograd.Function):
             if fb is not None and fb != fw:          # one of the pair was written before: zero the fresh one, then add
                 (wp if fw else bp).grad.zero_()
                 acc = True
-        dh, dw, db = E.norm_bwd(dy.contiguous(), h, weight, rstd, mean if layer else None, dh_in,
-                                layer=layer, unit_offset=unit_offset, has_bias=has_bias,
-                                dw_out=wp.grad if direct else None, db_out=bp.grad if (direct and bp is not None) else None,
-                                accumulate=acc)
-        if direct:
+        def ready():
             wp.zen_ready(wp)
             if bp is not None:
                 bp.zen_ready(bp)
+
+        dh, dw, db = E.norm_bwd(dy.contiguous(), h, weight, rstd, mean if layer else None, dh_in,
+                                layer=layer, unit_offset=unit_offset, has_bias=has_bias,
+                                dw_out=wp.grad if direct else None, db_out=bp.grad if (direct and bp is not None) else None,
+                                accumulate=acc, done=ready if direct else None)
+        if direct:
             dw = db = None
         return dh, (dh if has_res else None), dw, db, None, None, None
 

@@ -73,7 +73,7 @@ def norm_fwd(x, weight, bias=None, residual=None, *, eps=1e-5, layer=False, unit
 
 
 def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_offset=False, has_bias=False,
-             dw_out=None, db_out=None, accumulate=True):
+             dw_out=None, db_out=None, accumulate=True, done=None):
     """Returns (dh, dweight, dbias): dh includes ``dres`` (gradient on the residual stream) when given.
     With ``dw_out`` / ``db_out`` the parameter gradients are added into those tensors instead (``accumulate``) or
     overwrite them."""
@@ -101,40 +101,116 @@ def norm_bwd(dy, h, weight, rstd, mean=None, dres=None, *, layer=False, unit_off
         if db_out is not None and db is not None:
             db_out.add_(db) if accumulate else db_out.copy_(db)
             db = db_out
+        if done is not None:
+            done()
         return dh.to(h.dtype).view(h.shape), dw, db
     lib = _native.lib()
-    parts = lib.zen_norm_bwd_parts(rows)
-    part_dw = _scratch_buf("norm_dw", parts * cols, torch.float32, h.device)
-    part_db = _scratch_buf("norm_db", parts * cols, torch.float32, h.device) if layer else None
     dh = torch.empty_like(h2)
     acc = dw_out is not None and accumulate
     dw = dw_out if dw_out is not None else torch.empty_like(weight)
     db = (db_out if db_out is not None else torch.empty_like(weight)) if (layer and has_bias) else None
     dres2 = _c(dres).view(-1, cols) if dres is not None else None
+    if dw_out is not None and (db is None or db_out is not None) and _may_defer(done):
+        # partial sums now, the fold into dw / db with the layer's other reductions
+        used = lib.zen_norm_bwd_parts_used(rows, cols)
+        part_dw = torch.empty(used, cols, dtype=torch.float32, device=h.device)
+        part_db = torch.empty(used, cols, dtype=torch.float32, device=h.device) if layer else None
+        rc = lib.zen_norm_bwd_ex(_native.ptr(dy2), _native.ptr(h2), _native.ptr(weight), _native.ptr(rstd), _native.ptr(mean),
+                                 _native.ptr(dres2), _native.ptr(dh), _native.ptr(part_dw), _native.ptr(part_db),
+                                 _native.ptr(dw), _native.ptr(db), rows, cols, int(layer), int(unit_offset), int(acc),
+                                 _code(h2), 1, _native.stream_ptr())
+        _native.check(rc, "zen_norm_bwd_ex")
+        _queue_reduce(part_dw, used, dw, acc, done, part_db if db is not None else None, db)
+        return dh.view(h.shape), dw, db
+    parts = lib.zen_norm_bwd_parts(rows)
+    part_dw = _scratch_buf("norm_dw", parts * cols, torch.float32, h.device)
+    part_db = _scratch_buf("norm_db", parts * cols, torch.float32, h.device) if layer else None
     rc = lib.zen_norm_bwd(_native.ptr(dy2), _native.ptr(h2), _native.ptr(weight), _native.ptr(rstd), _native.ptr(mean),
                           _native.ptr(dres2), _native.ptr(dh), _native.ptr(part_dw), _native.ptr(part_db),
                           _native.ptr(dw), _native.ptr(db), rows, cols, int(layer), int(unit_offset), int(acc), _code(h2),
                           _native.stream_ptr())
     _native.check(rc, "zen_norm_bwd")
+    if done is not None:
+        done()
     return dh.view(h.shape), dw, db
 
 
-def colsum(a: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = True) -> torch.Tensor:
+# ---------------------------------------------------------------------------------------------------------------
+# Deferred column reductions.  A bias or norm-parameter gradient is a two-step sum: per-row-group partials [parts, cols]
+# (written by the kernel that has the data), then a tiny kernel that folds the parts into the gradient.  Inside a
+# backward pass the second step may be queued (``done`` given): the queue goes out as ONE launch of up to eight
+# reductions together with the grouped weight gradients (ops/gemm.py:flush_deferred), instead of six launches of a
+# few microseconds per layer.
+class _ReduceJob(ctypes.Structure):
+    _fields_ = [("part", ctypes.c_void_p), ("out", ctypes.c_void_p), ("part2", ctypes.c_void_p), ("out2", ctypes.c_void_p),
+                ("nparts", ctypes.c_int32), ("cols", ctypes.c_int32), ("accumulate", ctypes.c_int32), ("pad", ctypes.c_int32)]
+
+
+_reduce_jobs: list = []
+
+
+def _may_defer(done) -> bool:
+    from . import gemm as _G
+
+    return done is not None and _G.GROUP_SIZE > 1 and _G.arm_flush_at_end_of_backward()
+
+
+def _queue_reduce(part, nparts, out, accumulate, done, part2=None, out2=None) -> None:
+    ptrs = {out.data_ptr()} | ({out2.data_ptr()} if out2 is not None else set())
+    clash = any(j[2].data_ptr() in ptrs or (j[6] is not None and j[6].data_ptr() in ptrs) for j in _reduce_jobs)
+    if _reduce_jobs and (clash or _reduce_jobs[0][2].dtype != out.dtype or _reduce_jobs[0][2].device != out.device):
+        flush_colreduce()                          # one launch never holds two reductions into one gradient
+    _reduce_jobs.append((part, nparts, out, bool(accumulate), done, part2, out2))
+    if len(_reduce_jobs) >= _native.lib().zen_colreduce_max_jobs():
+        flush_colreduce()
+
+
+def flush_colreduce() -> None:
+    """Launch the queued column reductions (one launch) and run their callbacks."""
+    if not _reduce_jobs:
+        return
+    jobs = list(_reduce_jobs)
+    _reduce_jobs.clear()
+    arr = (_ReduceJob * len(jobs))()
+    for i, (part, nparts, out, acc, _done, part2, out2) in enumerate(jobs):
+        arr[i] = _ReduceJob(part.data_ptr(), out.data_ptr(), part2.data_ptr() if part2 is not None else None,
+                            out2.data_ptr() if out2 is not None else None, nparts, out.numel(), int(acc), 0)
+    _native.check(_native.lib().zen_colreduce_multi(arr, len(jobs), _code(jobs[0][2]), _native.stream_ptr()),
+                  "zen_colreduce_multi")
+    for job in jobs:
+        if job[4] is not None:
+            job[4]()
+
+
+def colsum(a: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = True, done=None) -> torch.Tensor:
     """Column sums of a [rows, cols] matrix (bias gradients); added into ``out`` when given (``accumulate``) or written
-    over it."""
+    over it.  ``done``: called once ``out`` has been (or, inside a backward pass, has been queued to be and then was)
+    written; see the deferred reductions above."""
     cols = a.shape[-1]
     a2 = _c(a).view(-1, cols)
     if not a.is_cuda:
         r = a2.float().sum(0).to(a.dtype)
-        return r if out is None else (out.add_(r) if accumulate else out.copy_(r))
+        r = r if out is None else (out.add_(r) if accumulate else out.copy_(r))
+        if done is not None:
+            done()
+        return r
     lib = _native.lib()
     rows = a2.shape[0]
+    if out is not None and _may_defer(done):
+        parts = lib.zen_colsum_parts(rows)
+        part = torch.empty(parts, cols, dtype=torch.float32, device=a.device)
+        _native.check(lib.zen_colsum_partial(_native.ptr(a2), _native.ptr(part), rows, cols, _code(a2), _native.stream_ptr()),
+                      "zen_colsum_partial")
+        _queue_reduce(part, parts, out, accumulate, done)
+        return out
     part = _scratch_buf("colsum", lib.zen_colsum_parts(rows) * cols, torch.float32, a.device)
     acc = out is not None and accumulate
     if out is None:
         out = torch.empty(cols, dtype=a.dtype, device=a.device)
     _native.check(lib.zen_colsum(_native.ptr(a2), _native.ptr(part), _native.ptr(out), rows, cols, int(acc), _code(a2),
                                  _native.stream_ptr()), "zen_colsum")
+    if done is not None:
+        done()
     return out
 
 
@@ -218,8 +294,18 @@ def act_bwd_with_colsum(a: torch.Tensor, dout: torch.Tensor, kind: str):
     return da, part
 
 
-def colsum_from_parts(part: torch.Tensor, out: torch.Tensor, accumulate: bool = True) -> torch.Tensor:
+def colsum_from_parts(part: torch.Tensor, out: torch.Tensor, accumulate: bool = True, done=None) -> torch.Tensor:
     """Sum the partial column sums ``part[parts, cols]`` into ``out[cols]`` (added when ``accumulate``, else written)."""
+    if _may_defer(done):
+        _queue_reduce(part, part.shape[0], out, accumulate, done)
+        return out
+    _colsum_from_parts_now(part, out, accumulate)
+    if done is not None:
+        done()
+    return out
+
+
+def _colsum_from_parts_now(part, out, accumulate):
     _native.check(_native.lib().zen_colsum_reduce(_native.ptr(part), _native.ptr(out), part.shape[0], part.shape[1],
                                                   int(accumulate), _code(out), _native.stream_ptr()), "zen_colsum_reduce")
     return out

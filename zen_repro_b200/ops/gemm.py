@@ -202,14 +202,21 @@ def defer_tn(a, b, out, accumulate: bool, done=None) -> None:
         flush_deferred()                           # two products into one output never share a launch
     a2, b2 = _rowmajor(a), _rowmajor(b)
     _pending.append((a2, b2, out, M, N, K, bool(accumulate), done, torch.cuda.current_stream(a.device).cuda_stream))
+    arm_flush_at_end_of_backward()
+    if len(_pending) >= GROUP_SIZE:
+        flush_deferred()
+
+
+def arm_flush_at_end_of_backward() -> bool:
+    """Ask the autograd engine to call :func:`flush_deferred` when the running backward pass ends.  False when no
+    backward pass is running (the caller then flushes, or does not defer)."""
     if not _callback_armed[0]:
-        try:                                       # inside a backward pass: flush when it ends, whatever is still queued
+        try:
             torch.autograd.Variable._execution_engine.queue_callback(flush_deferred)
             _callback_armed[0] = True
         except RuntimeError:
-            pass                                   # not called from a backward pass: the caller flushes
-    if len(_pending) >= GROUP_SIZE:
-        flush_deferred()
+            return False
+    return True
 
 
 def flush_deferred() -> None:
@@ -232,6 +239,9 @@ def flush_deferred() -> None:
         for item in batch:
             if item[7] is not None:
                 item[7]()
+    from . import elementwise as _E
+
+    _E.flush_colreduce()                           # the bias / norm-parameter reductions queued beside them
 
 
 def _finish(r, bias, out, accumulate, dtype):
