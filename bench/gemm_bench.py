@@ -54,7 +54,7 @@ def main():
     ap.add_argument("--group", action="store_true",
                     help="the weight gradients of one layer of --shapes: separate launches against one grouped launch")
     ap.add_argument("--tail_min_kb", type=int, default=-1,
-                    help="fewest 64-wide K blocks from which the tiles of a partly filled last round are cut in two "
+                    help="fewest 64-wide K blocks from which the tiles of a partly filled last wave are cut in two "
                          "(0 = never, -1 = the library's default)")
     args = ap.parse_args()
     if args.tail_min_kb >= 0:

@@ -176,7 +176,7 @@ def test_pair_kernel_with_192_wide_tiles(M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(8192, 768, 3072), (8192, 2048, 1024), (8000, 760, 1100), (8192, 768, 1024)])
 def test_tail_split_of_the_last_round(M, N, K):
-    """Outputs whose 256 x 256 tiles leave the last round of clusters less than half full: those tiles run as two K
+    """Outputs whose 256 x 256 tiles leave the last wave of clusters less than half full: those tiles run as two K
     slices that exchange half an accumulator.  Same result as without the split (fp32 sums of two halves), the same
     bits on every call, flags left clear for the next launch, all operand layouts, with and without bias."""
     from zen_repro_b200 import _native

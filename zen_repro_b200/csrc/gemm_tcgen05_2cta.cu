@@ -54,8 +54,8 @@ struct GemmGroup {
   // `ws`; per 32-row group a counter tells the last unit to arrive, which sums the slices in slice order and writes
   // the output; with two slices and a TMA-stored output the slices exchange half an accumulator each instead.
   int splits, kb_per_split;
-  // tail split (splits == 1): the last `tail` tiles of the list, the ones of the launch's final, partly filled round
-  // of clusters, are cut into two K halves that run side by side in that round and exchange half an accumulator
+  // tail split (splits == 1): the last `tail` tiles of the list, the ones of the launch's final, partly filled wave
+  // of clusters, are cut into two K halves that run side by side in that wave and exchange half an accumulator
   // each (the two-slice TMA-store path); 0 = every tile is one unit
   int tail;
   float* ws;                        // [slices * tiles][2 CTAs][8 column chunks][8 float4 of a row][128 rows] float4:
@@ -602,7 +602,7 @@ int fill_problem(GemmProblem& q, const void* A, const void* B, void* C, const vo
 }  // namespace
 
 int g_force_bn = 0;
-int g_tail_min_kb = 16;            // fewest 64-wide K blocks for which the tiles of the last round are cut in two; 0 = never
+int g_tail_min_kb = 16;            // fewest 64-wide K blocks for which the tiles of the last wave are cut in two; 0 = never
 
 // 256-wide pair tiles.  The 128-wide variant exists for outputs whose 256-wide tiles fill the 74 CTA pairs unevenly
 // (96 tiles = 1.3 waves), but measured on 8192 x 768 outputs it lost (662 vs 858 TFLOP/s at K = 3072, 410 vs 472 at
@@ -626,8 +626,8 @@ extern "C" {
 // long K, the weight-gradient shape): `ws` must hold splits * tiles * 2 * 128 * 256 floats and `counters`
 // tiles * 16 ints that are zero on entry (the kernel leaves them zero); both are caller-owned and used in stream
 // order.  The slices are summed in slice order, so the result does not depend on timing.
-// With splits == 1 a caller may still pass `ws` and `counters` (same sizes as for two slices of one round of clusters):
-// the launcher then cuts the tiles of the last, partly filled round in two (see zen_gemm2_tail_split).
+// With splits == 1 a caller may still pass `ws` and `counters` (same sizes as for two slices of one wave of clusters):
+// the launcher then cuts the tiles of the last, partly filled wave in two (see zen_gemm2_tail_split).
 // n_store: 0, or a width in [N, ldc] that the kernel may write (columns N.. receive zeros).
 int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
                               int ldb, int ldc, int a_mn, int b_mn, int out_fp32, int accumulate, int splits, float* ws,
@@ -670,8 +670,8 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
   g.kb_per_split = kb_per;
   g.ws = ws;
   g.counters = counters;
-  // Tail split: the tiles of the last, partly filled round of clusters run as two K slices each when both slices of
-  // all of them fit in that round (so that the slices that wait for each other are resident together, as above) and K
+  // Tail split: the tiles of the last, partly filled wave of clusters run as two K slices each when both slices of
+  // all of them fit in that wave (so that the slices that wait for each other are resident together, as above) and K
   // is long enough for half a tile to outweigh the exchange of half an accumulator.
   g.tail = 0;
   if (splits == 1 && bn == 256 && g.pr[0].tma_store && g_tail_min_kb > 0 && nkb >= g_tail_min_kb && ws && counters &&
@@ -686,7 +686,7 @@ int zen_gemm_bf16_2cta_splitk(const void* A, const void* B, void* C, const void*
 }
 
 // Several products with the same operand layouts in ONE launch (see GemmProblem): the tiles of all of them form one
-// list that the persistent clusters walk, and the tiles of the last, partly filled round are cut into two K halves when
+// list that the persistent clusters walk, and the tiles of the last, partly filled wave are cut into two K halves when
 // their outputs take the TMA-store path.  `descs`: n records of ZenGemmDesc; every product follows the contract of
 // zen_gemm_bf16_2cta (no bias).  ws / counters as for zen_gemm_bf16_2cta_splitk (may be null: no tail split).
 struct ZenGemmDesc {
@@ -742,7 +742,7 @@ int zen_gemm2_force_bn(int bn) {
   return old;
 }
 
-// Fewest K blocks (of 64) from which the tiles of a launch's last, partly filled round run as two K slices; 0 switches
+// Fewest K blocks (of 64) from which the tiles of a launch's last, partly filled wave run as two K slices; 0 switches
 // the tail split off.  Returns the previous setting.
 int zen_gemm2_tail_split(int min_kb) {
   const int old = g_tail_min_kb;

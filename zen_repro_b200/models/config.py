@@ -94,14 +94,14 @@ class ModelConfig:
 
 
 PRESETS = {
-    # BASELINE config 2: GPT-2 small
+    # headline benchmark config 2: GPT-2 small
     "gpt2": ModelConfig(family="gpt2", name="gpt2", vocab_size=50257, hidden_size=768, num_layers=12, num_heads=12,
                         num_kv_heads=12, head_dim=64, intermediate_size=3072, max_position=1024, norm_eps=1e-5),
-    # BASELINE config 3: Gemma-2B (18 layers, MQA, head_dim 256, GeGLU 16384, vocab 256000)
+    # benchmark config 3: Gemma-2B (18 layers, MQA, head_dim 256, GeGLU 16384, vocab 256000)
     "gemma-2b": ModelConfig(family="gemma", name="gemma-2b", vocab_size=256000, hidden_size=2048, num_layers=18,
                             num_heads=8, num_kv_heads=1, head_dim=256, intermediate_size=16384, max_position=8192,
                             norm_eps=1e-6, tie_embeddings=True),
-    # BASELINE config 4: Llama-3-8B
+    # benchmark config 4: Llama-3-8B
     "llama-3-8b": ModelConfig(family="llama", name="llama-3-8b", vocab_size=128256, hidden_size=4096, num_layers=32,
                               num_heads=32, num_kv_heads=8, head_dim=128, intermediate_size=14336, max_position=8192,
                               norm_eps=1e-5, rope_theta=500000.0, tie_embeddings=False),

@@ -118,7 +118,7 @@ def _launch(a, b, M, N, K, a_mn, b_mn, bias, out, accumulate, out_dtype, bn, pad
     pair = (bn == 512) or (bn == 0 and use_pair_kernel(M, N, K))
     if pair:
         n_store = min((N + 7) // 8 * 8, out.stride(0)) if pad_ok else 0
-        # the workspace lets the launcher cut the tiles of a partly filled last round of clusters into two K slices
+        # the workspace lets the launcher cut the tiles of a partly filled last wave of clusters into two K slices
         ws, cnt = _splitk_workspace(a.device) if _TAIL_SPLIT else (None, None)
         rc = _native.lib().zen_gemm_bf16_2cta_splitk(
             _native.ptr(a2), _native.ptr(b2), _native.ptr(out), _native.ptr(bias), M, N, K, a2.stride(0), b2.stride(0),
