@@ -201,7 +201,7 @@ def defer_tn(a, b, out, accumulate: bool, done=None) -> None:
     if any(item[2].data_ptr() == out.data_ptr() for item in _pending):
         flush_deferred()                           # two products into one output never share a launch
     a2, b2 = _rowmajor(a), _rowmajor(b)
-    _pending.append((a2, b2, out, M, N, K, bool(accumulate), done, torch.cuda.current_stream(a.device).cuda_stream))
+    _pending.append((a2, b2, out, M, N, K, bool(accumulate), done))
     arm_flush_at_end_of_backward()
     if len(_pending) >= GROUP_SIZE:
         flush_deferred()
@@ -228,7 +228,7 @@ def flush_deferred() -> None:
         lib = _native.lib()
         n = len(batch)
         descs = (_GemmDesc * n)()
-        for i, (a2, b2, out, M, N, K, acc, _done, _st) in enumerate(batch):
+        for i, (a2, b2, out, M, N, K, acc, _done) in enumerate(batch):
             descs[i] = _GemmDesc(a2.data_ptr(), b2.data_ptr(), out.data_ptr(), M, N, K, a2.stride(0), b2.stride(0),
                                  out.stride(0), int(out.dtype == torch.float32), int(acc))
         dev = batch[0][0].device
