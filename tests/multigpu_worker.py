@@ -294,7 +294,8 @@ def check_verify_fallback(rank, world, dev):
 
     n = 200000
     eng = SparseAllReduce(n, None, max_density=0.3, methods=(1, 2, 3), wait_ms=300.0)
-    hook = make_zen_comm_hook(None, None, top_k=100, method=3, engines={n: eng}, torch_future=False, verify=True)
+    hook = make_zen_comm_hook(None, None, top_k=100, method=3, engines={n: eng}, torch_future=False, verify=True,
+                              dense_above=2.0)                  # keep the bucket on the sparse engine whatever top_k says
     x = make_sparse(n, 0.05, rank, torch.float32, dev)
     want = x.clone()
     dist.all_reduce(want)

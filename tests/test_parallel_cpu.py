@@ -196,6 +196,37 @@ def test_hook_recovery_agrees_on_the_status_and_falls_back_to_dense():
         assert stats["last_status"] == 4 and stats["fallbacks"] == 1
 
 
+def _dense_by_density_worker(rank, world):
+    from zen_repro_b200.parallel.hooks import make_zen_comm_hook
+    from zen_repro_b200.parallel.reducer import GradBucket
+
+    torch.manual_seed(rank)
+    out = {}
+    for top_k in (1, 30):
+        hook = make_zen_comm_hook(None, None, top_k=top_k, method=3, torch_future=False)
+        x = torch.randn(70000)
+        thr = x.abs().kthvalue(int(x.numel() * (1 - top_k / 100.0))).values
+        res = hook(None, GradBucket(0, x.clone(), [], True)).wait()
+        out[top_k] = (bool(hook.state["dense_by_density"]), round(hook.state["expected_union"], 4), res.clone())
+    return out
+
+
+def test_hook_hands_dense_unions_to_the_dense_allreduce():
+    """Three ranks: at top_k 1 % the union of the selections is about 3 % and the bucket takes the sparse exchange; at
+    30 % it is 66 %, past the break-even measured against the dense all-reduce, and the thresholded bucket is summed
+    densely.  Either way every rank gets the same sum of (approximately) its top fraction of entries."""
+    res = run_gloo(_dense_by_density_worker, 3)
+    for r in res:
+        assert r[1][0] is False and r[1][1] == pytest.approx(0.0297, abs=1e-4)
+        assert r[30][0] is True and r[30][1] == pytest.approx(0.657, abs=1e-3)
+    for k in (1, 30):
+        a = torch.as_tensor(res[0][k][2])
+        for r in res[1:]:
+            torch.testing.assert_close(torch.as_tensor(r[k][2]), a, atol=1e-6, rtol=1e-6)
+        frac = float((a != 0).float().mean())
+        assert 0.5 * res[0][k][1] < frac < 1.6 * res[0][k][1]       # sampled thresholds: about the expected union
+
+
 def _tp_dp_worker(rank, world, sparse_tp):
     from zen_repro_b200.trainer import TrainConfig, Trainer
 

@@ -182,15 +182,20 @@ def verified_or_dense(out: torch.Tensor, status: int, masked: torch.Tensor, grou
 
 def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, engines: dict | None = None,
                        skip_first: bool = False, torch_future: bool = True, max_density: float | None = None,
-                       verify: bool = False, wait_ms: float = 30000.0):
+                       verify: bool = False, wait_ms: float = 30000.0, dense_above: float = 0.45):
     """Build the hook.  ``engines`` caches one CUDA ``SparseAllReduce`` per bucket size (create them with
     ``prepare_engines`` before training so that buffer exchange does not happen inside backward).  ``verify``: read the
     engine's status word after every bucket (one device synchronisation per bucket) and replace the result by the dense
     all-reduce when a capacity overflow or an expired wait was reported; off by default, where the status travels through the
     trainer's status mirror (read one step late) and ``Trainer.check_health``.  ``wait_ms`` bounds every wait on a peer:
-    generous for training (a rank may be late by a data-loading or first-step pause), tests pass short limits."""
+    generous for training (a rank may be late by a data-loading or first-step pause), tests pass short limits.
+    ``dense_above``: when the union of the ranks' selections is expected to cover more than this fraction of the bucket
+    (1 - (1 - top_k / 100) ** P for independent selections), the thresholded bucket goes through the dense all-reduce:
+    measured on 8 GPUs the sparse exchange is 1.2-1.4x ahead of the dense one at a union of 33 % and 0.8-1.1x at 55 %."""
     state = {"skip": skip_first, "engines": engines if engines is not None else {}}
     P = dist.get_world_size(dp_group) if dist.is_initialized() else 1
+    state["expected_union"] = 1.0 - (1.0 - min(1.0, max(0.0, top_k / 100.0))) ** max(P, 1)
+    state["dense_by_density"] = P > 1 and state["expected_union"] > dense_above
     density = max_density if max_density is not None else min(1.0, top_k / 100.0 * 2.0 + 0.01)
 
     def engine_for(numel: int, device):
@@ -213,7 +218,8 @@ def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, e
             if thr is not None:
                 buf.copy_(torch.where(buf.abs() >= thr.to(buf.dtype), buf, torch.zeros((), device=buf.device, dtype=buf.dtype)))
             return _future(buf, torch_future)
-        if buf.device.type == "cuda" and buf.numel() > SMALL_BUCKET and not state.get("force_dense"):
+        dense = state.get("force_dense") or state.get("dense_by_density")
+        if buf.device.type == "cuda" and buf.numel() > SMALL_BUCKET and not dense:
             eng = engine_for(buf.numel(), buf.device)
             # in place unless the bucket is still needed for a dense fallback: no second buffer, no copy back
             out = eng(buf, method=method, threshold=thr, out=None if verify else buf)
@@ -222,7 +228,7 @@ def make_zen_comm_hook(dp_group, tp_group=None, *, top_k: float = 1, method=3, e
                 out = verified_or_dense(out, eng.check(), masked, dp_group, state)
         else:
             masked = buf if thr is None else torch.where(buf.abs() >= thr.to(buf.dtype), buf, torch.zeros_like(buf))
-            if buf.numel() <= SMALL_BUCKET or state.get("force_dense"):
+            if buf.numel() <= SMALL_BUCKET or dense:
                 out = masked.clone()
                 dist.all_reduce(out, group=dp_group)
             else:
