@@ -176,6 +176,7 @@ def _measure(args, config_name: str, method: int, top_k: float, e2e_pass: bool) 
                    "embedding_row_sync": ddp.embedding_sync is not None, "bucket_cap_mb": cfg.bucket_cap_mb,
                    "n_buckets": len(ddp.buckets), "dense_allreduce": "nvls multimem kernel" if getattr(ddp, "arena", None) is not None else "nccl", "grad_checkpoint": bool(trainer.model_cfg.grad_checkpoint),
                    "num_layers": trainer.model_cfg.num_layers, "cuda_graph": bool(graph_on),
+                   "weight_grad_group": int(gemm.GROUP_SIZE),
                    "l2": "per-step working set (weights + activations, > 1 GB) exceeds the 126 MB L2"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "gemm_error": gemm.gemm_error(),
         "kernel_status": {k: v for k, v in health.items() if v},
