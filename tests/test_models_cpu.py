@@ -132,3 +132,28 @@ def test_deferred_weight_gradient_runs_at_once_on_cpu():
     assert fired == [1]
     torch.testing.assert_close(out, a.t() @ b + 1.0, atol=1e-5, rtol=1e-5)
     G.flush_deferred()
+
+
+def test_gemm_launch_heuristics():
+    """Host-side choices of the GEMM wrappers for a 148-SM device: the CTA-pair kernel when 256 x 256 tiles fill the 74
+    clusters reasonably, two K slices for weight-gradient shapes whose tiles fit the clusters twice, no split otherwise."""
+    from zen_repro_b200.ops import gemm as G
+
+    assert G._clusters() == 74
+    assert G.use_pair_kernel(8192, 768, 3072) and G.use_pair_kernel(8192, 50304, 768)
+    assert not G.use_pair_kernel(256, 256, 4096) and not G.use_pair_kernel(8192, 128, 768)
+    assert G.split_k_choice(768, 3072, 8192) == 2          # 36 tiles x 2 slices = 72 clusters
+    assert G.split_k_choice(768, 768, 8192) == 2           # the store path sums two slices at most
+    assert G.split_k_choice(2048, 2560, 8192) == 1         # 80 tiles: both slices of every tile would not be resident together
+    assert G.split_k_choice(768, 3072, 1024) == 1          # K too short for the exchange to pay
+
+
+def test_reductions_are_not_deferred_outside_a_backward_pass():
+    from zen_repro_b200.ops import elementwise as E
+
+    assert E._may_defer(None) is False
+    assert E._may_defer(lambda: None) is False             # no autograd engine running: the caller reduces at once
+    out = torch.zeros(12)
+    fired = []
+    E.colsum(torch.ones(5, 12), out=out, accumulate=False, done=lambda: fired.append(1))
+    assert fired == [1] and torch.equal(out, torch.full((12,), 5.0))
